@@ -1,0 +1,111 @@
+"""ctypes binding of the C-ABI library ``libaila_nf4.so`` (include/aila_nf4.h).
+
+The library is the product; there is no Python or CPU fallback. Importing this module with the
+library missing raises ImportError with the build command.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libaila_nf4.so")
+
+OK = 0
+ERR_INVALID_ARGUMENT = 1
+ERR_UNSUPPORTED = 2
+ERR_CUDA = 3
+ERR_OUT_OF_MEMORY = 4
+NOT_APPLICABLE = 5
+ERR_KERNEL_TIMEOUT = 6
+
+SHARD_ROWS = 0
+SHARD_COLS = 1
+
+
+class WeightDesc(ctypes.Structure):
+    """AilaNf4WeightDesc."""
+    _fields_ = [
+        ("out_features", ctypes.c_int64),
+        ("in_features", ctypes.c_int64),
+        ("blocksize", ctypes.c_int32),
+        ("nested", ctypes.c_int32),
+        ("nested_blocksize", ctypes.c_int32),
+        ("nested_offset", ctypes.c_float),
+        ("packed_weight", ctypes.c_void_p),
+        ("absmax", ctypes.c_void_p),
+        ("quant_map", ctypes.c_void_p),
+        ("nested_absmax", ctypes.c_void_p),
+        ("nested_quant_map", ctypes.c_void_p),
+        ("nested_absmax_count", ctypes.c_int64),
+        ("pointers_on_device", ctypes.c_int32),
+        ("device", ctypes.c_int32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/aila_nf4.h declares
+_VP = ctypes.c_void_p
+_SIGNATURES = {
+    "aila_nf4_last_error": (ctypes.c_char_p, []),
+    "aila_nf4_version": (ctypes.c_int, []),
+    "aila_nf4_linear_create": (ctypes.c_int, [ctypes.POINTER(WeightDesc), ctypes.POINTER(_VP)]),
+    "aila_nf4_linear_create_shard": (ctypes.c_int, [ctypes.POINTER(WeightDesc), ctypes.c_int,
+                                                    ctypes.c_int, ctypes.c_int,
+                                                    ctypes.POINTER(_VP)]),
+    "aila_nf4_linear_create_fused_rows": (ctypes.c_int, [ctypes.POINTER(_VP), ctypes.c_int,
+                                                         ctypes.POINTER(_VP)]),
+    "aila_nf4_linear_destroy": (None, [_VP]),
+    "aila_nf4_linear_in_features": (ctypes.c_int64, [_VP]),
+    "aila_nf4_linear_out_features": (ctypes.c_int64, [_VP]),
+    "aila_nf4_linear_device_bytes": (ctypes.c_int64, [_VP]),
+    "aila_nf4_linear_device": (ctypes.c_int, [_VP]),
+    "aila_nf4_scratch_create": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(_VP)]),
+    "aila_nf4_scratch_destroy": (None, [_VP]),
+    "aila_nf4_scratch_reserve": (ctypes.c_int, [_VP, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                                                ctypes.c_int]),
+    "aila_nf4_scratch_check": (ctypes.c_int, [_VP, _VP]),
+    "aila_nf4_forward": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int, _VP, _VP]),
+    "aila_nf4_forward_gate_up_swiglu": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int,
+                                                       ctypes.c_int64, _VP]),
+    "aila_nf4_forward_host": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int, _VP]),
+    "aila_nf4_forward_gate_up_swiglu_host": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int,
+                                                            ctypes.c_int64, _VP]),
+    "aila_nf4_dequantize": (ctypes.c_int, [_VP, _VP, _VP]),
+    "aila_nf4_dequantize_rowmajor": (ctypes.c_int, [_VP, _VP, _VP]),
+    "aila_nf4_expand_absmax": (ctypes.c_int, [_VP, _VP, _VP]),
+    "aila_nf4_set_gemv_kernel": (ctypes.c_int, [ctypes.c_int]),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library (once) and declares every prototype."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `make -C aila_b200/csrc` "
+            "(or `python -c 'import __graft_entry__ as g; g.build()'`). "
+            "There is no fallback implementation.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class Nf4Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"aila_nf4 status {status}: {message}")
+        self.status = status
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise Nf4Error(status, load().aila_nf4_last_error().decode("utf-8", "replace"))

@@ -1,0 +1,154 @@
+// Whole-weight dequantisation kernels (bit-exact) and the row-wise SwiGLU.
+//   dequant_kn : Wt[K][N] bf16, the layout and arithmetic of Bnb4BitLinear::dequantize_weight
+//                (reference src/ops/Bnb4BitLinear.cpp:723-757)
+//   dequant_nk : W[N][K] bf16, same values in the orientation the tcgen05 GEMM reads
+//   expand     : fp32 absmax per block, the values Bnb4BitLinear::init computes on the host
+//                (:472-488)
+//   swiglu     : ops::fused_gate_up_swiglu (reference src/ops/ElementwiseOps.cpp:247-294)
+// HBM-bound: dequant_nk reads 0.516 B and writes 2 B per weight.
+#include "nf4_internal.h"
+
+namespace nf4 {
+
+namespace {
+
+__device__ __forceinline__ float unit_absmax(const uint8_t* unit, int absmax_kind,
+                                             const ScaleParams& sp, int n, int kb, int r) {
+    if (absmax_kind == kAbsmaxCodes) return decode_absmax(sp, n, kb, unit[kUnitNibbleBytes + r]);
+    return reinterpret_cast<const float*>(unit + kUnitNibbleBytes)[r];
+}
+
+// One block per unit, 256 threads: thread (r = tid % 16, c = tid / 16) converts the two
+// stored bytes p = 2c, 2c+1 of row r, i.e. k = 16*j + 4*t + {0..3} with t = c / 4, j = c % 4.
+// Consecutive threads hold consecutive output columns n, so each k-row of Wt gets one 32-byte
+// store per warp half.
+__global__ void __launch_bounds__(256)
+dequant_kn_kernel(const uint8_t* __restrict__ units, const float* __restrict__ qmap,
+                  ScaleParams sp, uint16_t* __restrict__ out, int N, int KU, int unit_stride,
+                  int absmax_kind) {
+    const long long u = blockIdx.x;
+    const int kb = (int)(u % KU);
+    const int rt = (int)(u / KU);
+    const int r = threadIdx.x & 15;
+    const int c = threadIdx.x >> 4;
+    const int n = rt * kTileRows + r;
+    if (n >= N) return;
+    const uint8_t* unit = units + (size_t)u * unit_stride;
+    const float am = unit_absmax(unit, absmax_kind, sp, n, kb, r);
+    const uint16_t two = *reinterpret_cast<const uint16_t*>(unit + r * 32 + 2 * c);
+    const int t = c >> 2, j = c & 3;
+    const int k0 = kb * kUnitK + 16 * j + 4 * t;
+    const uint32_t b0 = two & 0xff, b1 = two >> 8;
+    const float w0 = __fmul_rn(__ldg(qmap + (b0 >> 4)), am);
+    const float w1 = __fmul_rn(__ldg(qmap + (b0 & 15)), am);
+    const float w2 = __fmul_rn(__ldg(qmap + (b1 >> 4)), am);
+    const float w3 = __fmul_rn(__ldg(qmap + (b1 & 15)), am);
+    out[(size_t)(k0 + 0) * N + n] = f32_to_bf16_bits(w0);
+    out[(size_t)(k0 + 1) * N + n] = f32_to_bf16_bits(w1);
+    out[(size_t)(k0 + 2) * N + n] = f32_to_bf16_bits(w2);
+    out[(size_t)(k0 + 3) * N + n] = f32_to_bf16_bits(w3);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+}
+
+// One thread per (unit, row, 8-byte chunk t): 16 weights -> four 8-byte stores at
+// k = 16*j + 4*t. The four lanes of a row write one full 32-byte sector per j.
+__global__ void __launch_bounds__(256)
+dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ qmap,
+                  ScaleParams sp, uint16_t* __restrict__ out, int N, long long K, int KU,
+                  long long total_units, int unit_stride, int absmax_kind) {
+    __shared__ float q[16];
+    if (threadIdx.x < 16) q[threadIdx.x] = qmap[threadIdx.x];
+    __syncthreads();
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long u = tid >> 6;
+    if (u >= total_units) return;
+    const int r = (int)((tid >> 2) & 15);
+    const int t = (int)(tid & 3);
+    const int kb = (int)(u % KU);
+    const int rt = (int)(u / KU);
+    const int n = rt * kTileRows + r;
+    if (n >= N) return;
+    const uint8_t* unit = units + (size_t)u * unit_stride;
+    const float am = unit_absmax(unit, absmax_kind, sp, n, kb, r);
+    const uint2 v = *reinterpret_cast<const uint2*>(unit + r * 32 + 8 * t);
+    uint16_t* orow = out + (size_t)n * K + (size_t)kb * kUnitK + 4 * t;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t two = ((j < 2 ? v.x : v.y) >> (16 * (j & 1))) & 0xffff;
+        const uint32_t b0 = two & 0xff, b1 = two >> 8;
+        uint2 o;
+        o.x = pack_bf16x2(__fmul_rn(q[b0 >> 4], am), __fmul_rn(q[b0 & 15], am));
+        o.y = pack_bf16x2(__fmul_rn(q[b1 >> 4], am), __fmul_rn(q[b1 & 15], am));
+        *reinterpret_cast<uint2*>(orow + 16 * j) = o;
+    }
+}
+
+__global__ void expand_absmax_kernel(const uint8_t* __restrict__ units, ScaleParams sp,
+                                     float* __restrict__ out, int N, int KU, int blocks_per_row,
+                                     int unit_stride, int absmax_kind) {
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= (long long)N * blocks_per_row) return;
+    const int b = (int)(tid % blocks_per_row);
+    const int n = (int)(tid / blocks_per_row);
+    const int kb = b << sp.blk_shift;
+    const uint8_t* unit = units + ((size_t)(n / kTileRows) * KU + kb) * unit_stride;
+    out[tid] = unit_absmax(unit, absmax_kind, sp, n, kb, n % kTileRows);
+}
+
+// out[m][i] = bf16( silu(g) * u ), g = gate_up[m][i], u = gate_up[m][ff + i], both read as
+// bf16; silu(g) = g / (1 + exp(-g)) in fp32.
+__global__ void swiglu_rows_kernel(const uint16_t* __restrict__ gate_up,
+                                   uint16_t* __restrict__ out, int M, long long ff) {
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= (long long)M * ff) return;
+    const long long m = tid / ff, i = tid % ff;
+    const float g = bf16_bits_to_f32(gate_up[m * 2 * ff + i]);
+    const float u = bf16_bits_to_f32(gate_up[m * 2 * ff + ff + i]);
+    const float silu = g / (1.0f + __expf(-g));
+    out[tid] = f32_to_bf16_bits(silu * u);
+}
+
+}  // namespace
+
+cudaError_t launch_dequant_kn(const AilaNf4Linear& w, void* out_kn, cudaStream_t s) {
+    const long long units = (long long)w.RT * w.KU;
+    if (units == 0) return cudaSuccess;
+    dequant_kn_kernel<<<(unsigned)units, 256, 0, s>>>(w.d_units, w.d_qmap, w.scale_params(),
+                                                     static_cast<uint16_t*>(out_kn), (int)w.N,
+                                                     w.KU, w.unit_stride, w.absmax_kind);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequant_nk(const AilaNf4Linear& w, void* out_nk, cudaStream_t s) {
+    const long long units = (long long)w.RT * w.KU;
+    if (units == 0) return cudaSuccess;
+    const long long threads = units * 64;
+    const long long blocks = (threads + 255) / 256;
+    dequant_nk_kernel<<<(unsigned)blocks, 256, 0, s>>>(w.d_units, w.d_qmap, w.scale_params(),
+                                                      static_cast<uint16_t*>(out_nk), (int)w.N,
+                                                      (long long)w.K, w.KU, units, w.unit_stride,
+                                                      w.absmax_kind);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_expand_absmax(const AilaNf4Linear& w, float* out, cudaStream_t s) {
+    const int bpr = (int)(w.K / w.blocksize);
+    const long long total = (long long)w.N * bpr;
+    if (total == 0) return cudaSuccess;
+    expand_absmax_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(
+        w.d_units, w.scale_params(), out, (int)w.N, w.KU, bpr, w.unit_stride, w.absmax_kind);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_rows(const void* gate_up, void* out, int M, int64_t ff, cudaStream_t s) {
+    const long long total = (long long)M * ff;
+    if (total == 0) return cudaSuccess;
+    swiglu_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(
+        static_cast<const uint16_t*>(gate_up), static_cast<uint16_t*>(out), M, (long long)ff);
+    return cudaGetLastError();
+}
+
+}  // namespace nf4

@@ -1,0 +1,458 @@
+// Prefill (seq_len > 1) contraction: y[M][N] = x[M][K] * w[N][K]^T, bf16 operands, fp32
+// accumulation in tensor memory, bf16 output. `w` is the NF4 weight already rounded to bf16
+// exactly as the reference's dequantize_weight does (src/ops/Bnb4BitLinear.cpp:746,:754), so
+// this kernel stands where the reference calls oneDNN's bf16 matmul (:689-721, :944).
+//
+// Blackwell-native structure (sm_100a):
+//   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) stages 128 x 64 tiles of x
+//     and BN x 64 tiles of w in a 4-deep shared-memory ring;
+//   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN,
+//     K = 16) with both operands K-major in shared memory and the accumulator in TMEM;
+//   * two TMEM accumulator buffers (2 x 256 columns) let the epilogue warps drain tile i with
+//     tcgen05.ld while the tensor core already works on tile i+1;
+//   * persistent CTAs, one per SM; BN is chosen per problem (multiple of 16, <= 256) so the
+//     tile count fills whole waves of 148 SMs.
+// Optional epilogues: + residual, or SwiGLU over a gate|up weight (tile = 128 gate columns'
+// worth + the matching up columns), rounding gate and up to bf16 first as the reference's
+// forward + ops::fused_gate_up_swiglu pair does (src/ops/ElementwiseOps.cpp:247-294).
+//
+// Roofline: tensor pipe. Algorithmic flops 2*M*N*K.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "nf4_internal.h"
+
+namespace nf4 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kMaxBN = 256;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;         // 16 KB
+constexpr int kBBytes = kMaxBN * BK * 2;     // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kGemmThreads = 192;            // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kAccStages = 2;
+constexpr int kTmemCols = 512;
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+
+struct GemmParams {
+    uint16_t* y;
+    const uint16_t* residual;
+    int* status;
+    int M;
+    int N;        // rows of w (gate|up: 2*ff)
+    int K;
+    int n_out;    // row pitch of y in elements (N, or ff with SwiGLU)
+    int BN;       // UMMA N (SwiGLU: BN/2 gate + BN/2 up columns)
+    int m_tiles;
+    int n_tiles;
+    int swiglu_ff;  // 0 = plain
+    uint32_t idesc;
+};
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle; rows are 128 B apart,
+// 8-row groups 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);       // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+    d |= (uint64_t)1 << 46;                        // version
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+}
+
+extern __shared__ __align__(1024) uint8_t gemm_smem[];
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
+                         const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    // 1024-byte aligned ring (the swizzle pattern is a function of the absolute address)
+    uint8_t* base = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + kStages * kStageBytes);
+    uint64_t* full = bars;                      // [kStages]
+    uint64_t* empty = bars + kStages;           // [kStages]
+    uint64_t* acc_full = bars + 2 * kStages;    // [kAccStages]
+    uint64_t* acc_empty = acc_full + kAccStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccStages);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int k_blocks = p.K / BK;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < kAccStages; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const uint32_t b_bytes = (uint32_t)p.BN * BK * 2;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+                const int m0 = mt * BM;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (it >= kStages) {
+                        if (*abort_flag || !mbar_wait_bounded(&empty[s], ((it / kStages) - 1) & 1)) {
+                            if (!*abort_flag) atomicExch(p.status, kStatusTimeoutEmpty);
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                    }
+                    uint8_t* sa = base + s * kStageBytes;
+                    uint8_t* sb = sa + kABytes;
+                    mbar_expect_tx(&full[s], kABytes + b_bytes);
+                    tma_load_2d(sa, &map_x, kb * BK, m0, &full[s]);
+                    if (p.swiglu_ff == 0) {
+                        tma_load_2d(sb, &map_w, kb * BK, nt * p.BN, &full[s]);
+                    } else {
+                        const int half = p.BN / 2;
+                        tma_load_2d(sb, &map_w, kb * BK, nt * half, &full[s]);
+                        tma_load_2d(sb + half * BK * 2, &map_w, kb * BK, p.swiglu_ff + nt * half,
+                                    &full[s]);
+                    }
+                }
+            }
+            // drain: copies issued by this thread must have landed before the CTA exits
+            for (int g = max(0, it - kStages); g < it; ++g)
+                mbar_wait_bounded(&full[g % kStages], (g / kStages) & 1);
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            int it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+                const int as = tcount % kAccStages;
+                if (tcount >= kAccStages) {
+                    if (*abort_flag ||
+                        !mbar_wait_bounded(&acc_empty[as], ((tcount / kAccStages) - 1) & 1)) {
+                        if (!*abort_flag) atomicExch(p.status, kStatusTimeoutTmem);
+                        *abort_flag = 1;
+                        break;
+                    }
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tacc = tmem_base + (uint32_t)(as * kMaxBN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (*abort_flag || !mbar_wait_bounded(&full[s], (it / kStages) & 1)) {
+                        if (!*abort_flag) atomicExch(p.status, kStatusTimeoutFull);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_u32(base + s * kStageBytes);
+                    const uint64_t adesc = make_smem_desc(sa);
+                    const uint64_t bdesc = make_smem_desc(sa + kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // advance 16 elements (32 bytes) along K inside the swizzled row
+                        umma_bf16(tacc, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
+                                  p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);  // frees the stage when these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[as]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (warps 2..5) ------------------------------
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32)
+        int tcount = 0;
+        const bool vec_ok = (p.n_out % 8) == 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+            const int as = tcount % kAccStages;
+            const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+            bool ok = true;
+            if (lane == 0) {
+                if (*abort_flag || !mbar_wait_bounded(&acc_full[as], (tcount / kAccStages) & 1)) {
+                    if (!*abort_flag) atomicExch(p.status, kStatusTimeoutTmem);
+                    *abort_flag = 1;
+                    ok = false;
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m = mt * BM + quarter * 32 + lane;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * kMaxBN);
+            if (p.swiglu_ff == 0) {
+                const int n0 = nt * p.BN;
+                for (int c = 0; c < p.BN; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(trow + c, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int n = n0 + c;
+                    if (m < p.M && n < p.N) {
+                        uint16_t* yp = p.y + (size_t)m * p.n_out + n;
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+                        if (vec_ok && n + 16 <= p.N) {
+                            if (p.residual) {
+                                const uint4* rp = reinterpret_cast<const uint4*>(
+                                    p.residual + (size_t)m * p.n_out + n);
+                                const uint4 r0 = rp[0], r1 = rp[1];
+                                const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    v[2 * i] += bf16_bits_to_f32(rw[i] & 0xffff);
+                                    v[2 * i + 1] += bf16_bits_to_f32(rw[i] >> 16);
+                                }
+                            }
+                            uint4 o0, o1;
+                            o0.x = pack2(v[0], v[1]);   o0.y = pack2(v[2], v[3]);
+                            o0.z = pack2(v[4], v[5]);   o0.w = pack2(v[6], v[7]);
+                            o1.x = pack2(v[8], v[9]);   o1.y = pack2(v[10], v[11]);
+                            o1.z = pack2(v[12], v[13]); o1.w = pack2(v[14], v[15]);
+                            reinterpret_cast<uint4*>(yp)[0] = o0;
+                            reinterpret_cast<uint4*>(yp)[1] = o1;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                if (n + i < p.N) {
+                                    float o = v[i];
+                                    if (p.residual)
+                                        o += bf16_bits_to_f32(p.residual[(size_t)m * p.n_out + n + i]);
+                                    yp[i] = f32_to_bf16_bits(o);
+                                }
+                            }
+                        }
+                    }
+                }
+            } else {
+                const int half = p.BN / 2;
+                const int n0 = nt * half;
+                for (int c = 0; c < half; c += 16) {
+                    uint32_t rg[16], ru[16];
+                    tmem_ld16(trow + c, rg);
+                    tmem_ld16(trow + half + c, ru);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int n = n0 + c;
+                    if (m < p.M && n < p.swiglu_ff) {
+                        uint16_t* yp = p.y + (size_t)m * p.n_out + n;
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            // gate and up pass through bf16 first, like a bf16 gate_up buffer
+                            const float g = bf16_bits_to_f32(f32_to_bf16_bits(__uint_as_float(rg[i])));
+                            const float u = bf16_bits_to_f32(f32_to_bf16_bits(__uint_as_float(ru[i])));
+                            v[i] = (g / (1.0f + __expf(-g))) * u;
+                        }
+                        if (vec_ok && n + 16 <= p.swiglu_ff) {
+                            uint4 o0, o1;
+                            o0.x = pack2(v[0], v[1]);   o0.y = pack2(v[2], v[3]);
+                            o0.z = pack2(v[4], v[5]);   o0.w = pack2(v[6], v[7]);
+                            o1.x = pack2(v[8], v[9]);   o1.y = pack2(v[10], v[11]);
+                            o1.z = pack2(v[12], v[13]); o1.w = pack2(v[14], v[15]);
+                            reinterpret_cast<uint4*>(yp)[0] = o0;
+                            reinterpret_cast<uint4*>(yp)[1] = o1;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (n + i < p.swiglu_ff) yp[i] = f32_to_bf16_bits(v[i]);
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+        }
+    }
+
+    // teardown: everyone done with TMEM before it is released
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// cuTensorMapEncodeTiled, fetched through the runtime so the library has no link-time
+// dependency on the driver library.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D bf16 row-major [rows][K] tensor, box = 64 columns x box_rows rows, 128-byte swizzle,
+// out-of-bounds elements read as zero.
+bool encode_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tile width for this problem: the multiple of `step` (<= max_bn) that minimises
+// waves * (UMMA N + overhead), i.e. fills whole waves of SMs with the widest tiles that do.
+// width_scale = 2 when each output column costs two accumulator columns (SwiGLU).
+int choose_bn(int M, int64_t n_cols, int step, int max_bn, int width_scale, int sm_count) {
+    const int m_tiles = (M + BM - 1) / BM;
+    int best = step;
+    double best_cost = 1e30;
+    for (int bn = step; bn <= max_bn; bn += step) {
+        const int64_t n_tiles = (n_cols + bn - 1) / bn;
+        const int64_t tiles = n_tiles * m_tiles;
+        const int64_t waves = (tiles + sm_count - 1) / sm_count;
+        const double cost = (double)waves * (bn * width_scale + 24);
+        if (cost <= best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+}  // namespace
+
+AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const void* residual,
+                               int M, int64_t N, int64_t K, int64_t swiglu_ff, int device,
+                               int sm_count, int* d_status, cudaStream_t s) {
+    (void)device;
+    if (K % BK != 0) return fail(AILA_NF4_ERR_UNSUPPORTED, "prefill GEMM needs in_features % 64 == 0");
+    if ((reinterpret_cast<uintptr_t>(w_nk) | reinterpret_cast<uintptr_t>(x)) & 15)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "prefill GEMM operands must be 16-byte aligned");
+    GemmParams p;
+    p.y = static_cast<uint16_t*>(y);
+    p.residual = static_cast<const uint16_t*>(residual);
+    p.status = d_status;
+    p.M = M;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.swiglu_ff = (int)swiglu_ff;
+    p.m_tiles = (M + BM - 1) / BM;
+    if (swiglu_ff > 0) {
+        // a tile holds `half` gate columns and the matching `half` up columns
+        const int half = choose_bn(M, swiglu_ff, 16, kMaxBN / 2, 2, sm_count);
+        p.BN = 2 * half;
+        p.n_tiles = (int)((swiglu_ff + half - 1) / half);
+        p.n_out = (int)swiglu_ff;
+    } else {
+        p.BN = choose_bn(M, N, 16, kMaxBN, 1, sm_count);
+        p.n_tiles = (int)((N + p.BN - 1) / p.BN);
+        p.n_out = (int)N;
+    }
+    // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4
+    p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) |
+              ((uint32_t)(BM >> 4) << 24);
+    CUtensorMap map_x, map_w;
+    if (!encode_map(&map_x, x, (uint64_t)M, (uint64_t)K, BM))
+        return fail(AILA_NF4_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation tensor");
+    const uint32_t w_box = (uint32_t)(swiglu_ff > 0 ? p.BN / 2 : p.BN);
+    if (!encode_map(&map_w, w_nk, (uint64_t)N, (uint64_t)K, w_box))
+        return fail(AILA_NF4_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
+
+    static std::once_flag attr_once[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once[dev & 63], [&] {
+        attr_err = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(gemm)");
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int grid = total_tiles < sm_count ? total_tiles : sm_count;
+    if (grid <= 0) return AILA_NF4_OK;
+    gemm_bf16_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmem, s>>>(map_x, map_w, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05_kernel launch");
+    return AILA_NF4_OK;
+}
+
+}  // namespace nf4

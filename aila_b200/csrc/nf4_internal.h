@@ -1,0 +1,117 @@
+// Host-side objects behind the opaque C handles, and the launchers each .cu file exports.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/aila_nf4.h"
+#include "nf4_common.cuh"
+
+struct AilaNf4Linear {
+    int device = 0;
+    int64_t N = 0, K = 0;
+    int blocksize = 64;
+    int absmax_kind = nf4::kAbsmaxCodes;
+    int RT = 0, KU = 0;      // row tiles (16 rows), units per row tile (64 k)
+    int unit_stride = nf4::kUnitStrideCodes;
+    uint8_t* d_units = nullptr;  // RT*KU*unit_stride bytes
+    float* d_qmap = nullptr;     // [16]
+    float* d_nmap = nullptr;     // [256]
+    float* d_nabs = nullptr;     // concatenated nested_absmax
+    int64_t nabs_count = 0;
+    float h_qmap[16] = {0};
+    int nbs = 256;
+    // segments (sources of a fused linear); a plain linear has one
+    int nseg = 1;
+    int seg_row0[nf4::kMaxSegments] = {0, 0, 0, 0};
+    int seg_rows[nf4::kMaxSegments] = {0, 0, 0, 0};
+    int64_t seg_flat0[nf4::kMaxSegments] = {0, 0, 0, 0};   // flat index of (row0, k = 0) block, source numbering
+    int64_t seg_row_stride[nf4::kMaxSegments] = {0, 0, 0, 0};
+    int64_t seg_nabs_base[nf4::kMaxSegments] = {0, 0, 0, 0};
+    float seg_offset[nf4::kMaxSegments] = {0, 0, 0, 0};
+    int64_t device_bytes = 0;
+
+    nf4::ScaleParams scale_params() const;
+    size_t units_bytes() const { return (size_t)RT * (size_t)KU * (size_t)unit_stride; }
+};
+
+struct AilaNf4Scratch {
+    int device = 0;
+    // split-K fix-up space of the streaming GEMV: per-CTA partial sums and per-row-tile
+    // arrival counters (counters are zero between launches; the last arriver resets them).
+    float* d_partials = nullptr;
+    size_t partials_floats = 0;
+    int* d_counters = nullptr;
+    size_t counters_ints = 0;
+    int* d_status = nullptr;  // device status word written by bounded waits
+    // bf16 [N][K] weight of the seq_len > 1 route
+    void* d_weight = nullptr;
+    size_t weight_bytes = 0;
+    // staging for the host-buffer entry points
+    void* d_io_in = nullptr;
+    size_t io_in_bytes = 0;
+    void* d_io_out = nullptr;
+    size_t io_out_bytes = 0;
+    int sm_count = 0;
+};
+
+namespace nf4 {
+
+// error plumbing (nf4_api.cu)
+AilaNf4Status fail(AilaNf4Status code, const std::string& message);
+AilaNf4Status cuda_fail(cudaError_t e, const char* what);
+#define NF4_CUDA(call)                                         \
+    do {                                                       \
+        cudaError_t e__ = (call);                              \
+        if (e__ != cudaSuccess) return nf4::cuda_fail(e__, #call); \
+    } while (0)
+
+// nf4_repack.cu -------------------------------------------------------------------------
+struct RepackSource {
+    const uint8_t* packed;     // device, row-major nibbles of the source tensor
+    int64_t row_stride_bytes;  // bytes between source rows (K_src / 2)
+    int64_t col_byte0;         // first byte of the kept column range inside a row
+    const void* absmax;        // device u8 codes or f32, [rows][abs_row_stride]
+    int64_t abs_row_stride;    // elements between source rows (K_src / blocksize)
+    int64_t abs_col0;          // first kept absmax column
+    int64_t row0;              // first kept source row
+};
+cudaError_t launch_repack(const RepackSource& src, const AilaNf4Linear& dst, cudaStream_t s);
+
+struct GatherSource {
+    const uint8_t* units;
+    int KU;          // units per row tile in the source
+    int unit_stride;
+    int src_row0;    // source row that lands on dst_row0
+    int src_kb0;     // source unit column that lands on unit column 0
+    int dst_row0;
+    int rows;
+};
+cudaError_t launch_gather(const GatherSource* srcs, int n_src, const AilaNf4Linear& dst,
+                          cudaStream_t s);
+
+// nf4_dequant.cu ------------------------------------------------------------------------
+cudaError_t launch_dequant_kn(const AilaNf4Linear& w, void* out_kn, cudaStream_t s);
+cudaError_t launch_dequant_nk(const AilaNf4Linear& w, void* out_nk, cudaStream_t s);
+cudaError_t launch_expand_absmax(const AilaNf4Linear& w, float* out, cudaStream_t s);
+cudaError_t launch_swiglu_rows(const void* gate_up, void* out, int M, int64_t ff,
+                               cudaStream_t s);
+
+// nf4_gemv.cu ---------------------------------------------------------------------------
+cudaError_t launch_gemv_simple(const AilaNf4Linear& w, const void* x, void* y,
+                               const void* residual, int64_t ff_pair, cudaStream_t s);
+size_t gemv_stream_partials_floats(int sm_count);
+cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
+                               void* y, const void* residual, int64_t ff_pair, cudaStream_t s);
+bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);
+
+// nf4_gemm.cu ---------------------------------------------------------------------------
+// y[M][N_out] = x[M][K] * w_nk[N][K]^T on tcgen05. swiglu_ff > 0: N == 2*ff and the output
+// is [M][ff] = silu(bf16(gate)) * bf16(up).
+AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const void* residual,
+                               int M, int64_t N, int64_t K, int64_t swiglu_ff, int device,
+                               int sm_count, int* d_status, cudaStream_t s);
+
+}  // namespace nf4

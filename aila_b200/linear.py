@@ -1,0 +1,228 @@
+"""Host-side mirror of the reference operator ``Bnb4BitLinear`` over the C-ABI library.
+
+Names, argument meaning and error behaviour follow reference src/ops/Bnb4BitLinear.hpp:12-59:
+``init`` / ``init_fused_rows`` return ``False`` and set ``last_error`` on invalid input,
+``forward`` raises ``RuntimeError`` for a non-bf16 tensor or ``seq_len <= 0``
+(Bnb4BitLinear.cpp:805-811), ``try_forward_decode_gate_up_swiglu`` returns ``False`` when the
+fused path does not apply (:764-776). torch supplies device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+from .synth import Nf4Tensors
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+class Bnb4BitLinearScratch:
+    """Per-engine work space (reference Bnb4BitLinearScratch, Bnb4BitLinear.hpp:12-24)."""
+
+    def __init__(self, device: int | torch.device = 0):
+        self.device = torch.device("cuda", device) if isinstance(device, int) else device
+        lib = _lib.load()
+        h = ctypes.c_void_p()
+        _lib.check(lib.aila_nf4_scratch_create(self.device.index or 0, ctypes.byref(h)))
+        self._h = h
+
+    def ensure(self, seq_len: int, in_features: int, out_features: int, need_weight: bool) -> None:
+        """Bnb4BitLinearScratch::ensure (Bnb4BitLinear.cpp:414-451): grow-only pre-sizing."""
+        _lib.check(_lib.load().aila_nf4_scratch_reserve(self._h, seq_len, in_features, out_features,
+                                                        1 if need_weight else 0))
+
+    def check(self) -> None:
+        """Raises if a bounded wait inside a kernel expired since the last check."""
+        _lib.check(_lib.load().aila_nf4_scratch_check(self._h, _stream_ptr(self.device)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.load().aila_nf4_scratch_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _np_ptr(a: np.ndarray | None) -> int | None:
+    return None if a is None else a.ctypes.data
+
+
+class Bnb4BitLinear:
+    """One NF4 linear on one GPU (reference class Bnb4BitLinear, Bnb4BitLinear.hpp:26-59)."""
+
+    def __init__(self):
+        self._h = None
+        self.last_error = ""
+        self.device = None
+
+    # -- construction -----------------------------------------------------------------
+    @staticmethod
+    def _desc(w: Nf4Tensors, device: int, keep: list) -> _lib.WeightDesc:
+        d = _lib.WeightDesc()
+        d.out_features, d.in_features, d.blocksize = w.out_features, w.in_features, w.blocksize
+        d.nested = 1 if w.nested else 0
+        d.nested_blocksize = w.nested_blocksize if w.nested else 0
+        d.nested_offset = float(w.nested_offset) if w.nested else 0.0
+        packed = np.ascontiguousarray(w.packed, np.uint8)
+        absmax = np.ascontiguousarray(w.absmax_codes, np.uint8) if w.nested else \
+            np.ascontiguousarray(w.absmax_f32, np.float32)
+        qmap = np.ascontiguousarray(w.quant_map, np.float32)
+        keep += [packed, absmax, qmap]
+        d.packed_weight, d.absmax, d.quant_map = packed.ctypes.data, absmax.ctypes.data, qmap.ctypes.data
+        if w.nested:
+            nabs = np.ascontiguousarray(w.nested_absmax, np.float32)
+            nmap = np.ascontiguousarray(w.nested_quant_map, np.float32)
+            keep += [nabs, nmap]
+            d.nested_absmax, d.nested_quant_map = nabs.ctypes.data, nmap.ctypes.data
+            d.nested_absmax_count = nabs.size
+        d.pointers_on_device = 0
+        d.device = device
+        return d
+
+    def init(self, weight: Nf4Tensors, device: int = 0) -> bool:
+        """Bnb4BitLinear::init (Bnb4BitLinear.cpp:453-497) from host checkpoint tensors."""
+        return self._create(weight, device, None)
+
+    def init_shard(self, weight: Nf4Tensors, mode: int, rank: int, world: int,
+                   device: int = 0) -> bool:
+        """Rank ``rank`` of ``world`` of the weight: rows (mode 0) or input columns (mode 1)."""
+        return self._create(weight, device, (mode, rank, world))
+
+    def _create(self, weight, device, shard) -> bool:
+        lib = _lib.load()
+        keep: list = []
+        d = self._desc(weight, device, keep)
+        h = ctypes.c_void_p()
+        if shard is None:
+            st = lib.aila_nf4_linear_create(ctypes.byref(d), ctypes.byref(h))
+        else:
+            st = lib.aila_nf4_linear_create_shard(ctypes.byref(d), shard[0], shard[1], shard[2],
+                                                  ctypes.byref(h))
+        if st != _lib.OK:
+            self.last_error = lib.aila_nf4_last_error().decode()
+            self.last_status = st
+            return False
+        self.close()
+        self._h = h
+        self.device = torch.device("cuda", device)
+        return True
+
+    def init_fused_rows(self, *sources: "Bnb4BitLinear") -> bool:
+        """Bnb4BitLinear::init_fused_rows (Bnb4BitLinear.cpp:499-629): 2..4 sources."""
+        lib = _lib.load()
+        arr = (ctypes.c_void_p * max(len(sources), 1))(*[s._h for s in sources])
+        h = ctypes.c_void_p()
+        st = lib.aila_nf4_linear_create_fused_rows(arr, len(sources), ctypes.byref(h))
+        if st != _lib.OK:
+            self.last_error = lib.aila_nf4_last_error().decode()
+            self.last_status = st
+            return False
+        self.close()
+        self._h = h
+        self.device = sources[0].device
+        return True
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.load().aila_nf4_linear_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- queries ----------------------------------------------------------------------
+    def in_features(self) -> int:
+        return int(_lib.load().aila_nf4_linear_in_features(self._h))
+
+    def out_features(self) -> int:
+        return int(_lib.load().aila_nf4_linear_out_features(self._h))
+
+    def device_bytes(self) -> int:
+        return int(_lib.load().aila_nf4_linear_device_bytes(self._h))
+
+    # -- compute ----------------------------------------------------------------------
+    def forward(self, scratch: Bnb4BitLinearScratch, input: torch.Tensor, output: torch.Tensor,
+                seq_len: int, add_residual: torch.Tensor | None = None) -> None:
+        """Bnb4BitLinear::forward (Bnb4BitLinear.cpp:799-949)."""
+        if input.dtype != torch.bfloat16 or output.dtype != torch.bfloat16:
+            raise RuntimeError("Bnb4BitLinear expects bf16 input/output tensors")
+        if seq_len <= 0:
+            raise RuntimeError("Bnb4BitLinear::forward: seq_len must be positive")
+        assert input.is_cuda and output.is_cuda and input.is_contiguous() and output.is_contiguous()
+        assert input.numel() >= seq_len * self.in_features()
+        assert output.numel() >= seq_len * self.out_features()
+        res = add_residual.data_ptr() if add_residual is not None else None
+        _lib.check(_lib.load().aila_nf4_forward(self._h, scratch._h, input.data_ptr(),
+                                                output.data_ptr(), seq_len, res,
+                                                _stream_ptr(self.device)))
+
+    @staticmethod
+    def try_forward_decode_gate_up_swiglu(fused_gate_up: "Bnb4BitLinear",
+                                          scratch: Bnb4BitLinearScratch, input: torch.Tensor,
+                                          output: torch.Tensor, ff_dim: int,
+                                          seq_len: int = 1) -> bool:
+        """Bnb4BitLinear::try_forward_decode_gate_up_swiglu (Bnb4BitLinear.cpp:759-797); also
+        takes seq_len > 1, where it stands for forward + ops::fused_gate_up_swiglu."""
+        if input.dtype != torch.bfloat16 or output.dtype != torch.bfloat16:
+            return False
+        if input.dim() != 2:
+            return False
+        st = _lib.load().aila_nf4_forward_gate_up_swiglu(
+            fused_gate_up._h, scratch._h, input.data_ptr(), output.data_ptr(), seq_len, ff_dim,
+            _stream_ptr(fused_gate_up.device))
+        if st == _lib.NOT_APPLICABLE:
+            return False
+        _lib.check(st)
+        return True
+
+    def forward_host(self, scratch: Bnb4BitLinearScratch, x_host: torch.Tensor,
+                     y_host: torch.Tensor, seq_len: int) -> None:
+        """forward with (pinned) host tensors; copies in, runs, copies out, waits."""
+        _lib.check(_lib.load().aila_nf4_forward_host(self._h, scratch._h, x_host.data_ptr(),
+                                                     y_host.data_ptr(), seq_len,
+                                                     _stream_ptr(self.device)))
+
+    def gate_up_swiglu_host(self, scratch: Bnb4BitLinearScratch, x_host: torch.Tensor,
+                            y_host: torch.Tensor, seq_len: int, ff_dim: int) -> None:
+        _lib.check(_lib.load().aila_nf4_forward_gate_up_swiglu_host(
+            self._h, scratch._h, x_host.data_ptr(), y_host.data_ptr(), seq_len, ff_dim,
+            _stream_ptr(self.device)))
+
+    def dequantize_weight(self) -> torch.Tensor:
+        """bf16 [in_features, out_features], the transposed layout of
+        Bnb4BitLinear::dequantize_weight (Bnb4BitLinear.cpp:723-757)."""
+        out = torch.empty(self.in_features(), self.out_features(), dtype=torch.bfloat16,
+                          device=self.device)
+        _lib.check(_lib.load().aila_nf4_dequantize(self._h, out.data_ptr(), _stream_ptr(self.device)))
+        return out
+
+    def dequantize_rowmajor(self) -> torch.Tensor:
+        out = torch.empty(self.out_features(), self.in_features(), dtype=torch.bfloat16,
+                          device=self.device)
+        _lib.check(_lib.load().aila_nf4_dequantize_rowmajor(self._h, out.data_ptr(),
+                                                            _stream_ptr(self.device)))
+        return out
+
+    def expand_absmax(self, blocksize: int) -> torch.Tensor:
+        out = torch.empty(self.out_features(), self.in_features() // blocksize,
+                          dtype=torch.float32, device=self.device)
+        _lib.check(_lib.load().aila_nf4_expand_absmax(self._h, out.data_ptr(),
+                                                      _stream_ptr(self.device)))
+        return out
+
+
+def set_gemv_kernel(which: int) -> None:
+    """0 automatic, 1 plain CUDA-core kernel, 2 streaming tensor-core kernel."""
+    _lib.check(_lib.load().aila_nf4_set_gemv_kernel(which))

@@ -1,0 +1,218 @@
+/*
+ * aila_nf4.h - C ABI of the B200 (sm_100a) bitsandbytes-NF4 linear operator.
+ *
+ * This is the drop-in boundary for the NF4 linear path of the Aila inference engine: the
+ * C++ operator class `Bnb4BitLinear` (reference src/ops/Bnb4BitLinear.hpp:26-59) keeps its
+ * signatures in include/aila_nf4_linear.hpp and forwards to the functions below. Each entry
+ * point names the reference interface it replaces.
+ *
+ * Conventions
+ *  - plain C, `extern "C"`, default visibility (same export convention as the reference's
+ *    include/aila_api.h:19-35); no C++ or framework types cross the boundary;
+ *  - every function returns an AilaNf4Status; nothing throws. A message for the last failure
+ *    on the calling thread is available from aila_nf4_last_error();
+ *  - all device work is enqueued on the caller's stream (`stream` is a cudaStream_t passed as
+ *    void*; NULL = the default stream) and nothing on the forward path synchronises the host;
+ *  - a linear is immutable after creation and may be shared by several threads; a scratch
+ *    object belongs to one stream at a time (like the reference's one
+ *    Bnb4BitLinearScratch per backend, src/models/Qwen3Bnb4Backend.hpp:54);
+ *  - activations are bfloat16, row-major [seq_len][features], exactly as the reference's
+ *    Tensor buffers; outputs are bfloat16 with fp32 accumulation;
+ *  - there is no CPU fallback: without a usable CUDA device every compute call fails with
+ *    AILA_NF4_ERR_CUDA.
+ */
+#ifndef AILA_NF4_H
+#define AILA_NF4_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+#define AILA_NF4_EXTERN extern "C"
+#else
+#define AILA_NF4_EXTERN extern
+#endif
+#define AILA_NF4_API AILA_NF4_EXTERN __attribute__((visibility("default")))
+
+typedef struct AilaNf4Linear AilaNf4Linear;   /* opaque: one quantised weight on one GPU  */
+typedef struct AilaNf4Scratch AilaNf4Scratch; /* opaque: per-stream work space            */
+
+typedef enum AilaNf4Status {
+    AILA_NF4_OK = 0,
+    AILA_NF4_ERR_INVALID_ARGUMENT = 1, /* bad descriptor, shape, pointer or dtype contract    */
+    AILA_NF4_ERR_UNSUPPORTED = 2,      /* valid NF4 data this build does not handle            */
+    AILA_NF4_ERR_CUDA = 3,             /* a CUDA runtime/driver call failed (message has it)   */
+    AILA_NF4_ERR_OUT_OF_MEMORY = 4,
+    AILA_NF4_NOT_APPLICABLE = 5,       /* fused fast path does not apply: caller falls back    */
+    AILA_NF4_ERR_KERNEL_TIMEOUT = 6    /* a bounded device-side wait expired (status query)    */
+} AilaNf4Status;
+
+typedef enum AilaNf4ShardMode {
+    AILA_NF4_SHARD_ROWS = 0, /* split out_features (column-parallel linear): q/k/v, gate, up */
+    AILA_NF4_SHARD_COLS = 1  /* split in_features (row-parallel linear): o_proj, down        */
+} AilaNf4ShardMode;
+
+/*
+ * One bitsandbytes 4-bit weight in checkpoint form. Mirrors Bnb4BitWeightRef +
+ * Bnb4BitQuantState (reference src/utils/SafeTensors.hpp:40-81): the same tensors, as raw
+ * pointers. The library copies what it needs during creation; the caller may free
+ * everything as soon as the create call returns (the reference's callers erase the
+ * per-projection tensors right after fusion, src/models/Qwen3Bnb4Backend.cpp:237-243).
+ */
+typedef struct AilaNf4WeightDesc {
+    int64_t out_features;        /* quant_state.shape[0]                                    */
+    int64_t in_features;         /* quant_state.shape[1]; multiple of blocksize             */
+    int32_t blocksize;           /* weights per absmax; a multiple of 64                    */
+    int32_t nested;              /* 1: absmax is uint8 codes (double quant); 0: float32     */
+    int32_t nested_blocksize;    /* absmax values per nested_absmax (power of two), if nested */
+    float nested_offset;         /* quant_state.nested_offset                               */
+    const uint8_t* packed_weight;   /* [out*in/2]; high nibble = even k                     */
+    const void* absmax;             /* uint8[out*in/blocksize] if nested else float[...]    */
+    const float* quant_map;         /* [16]  NF4 code book                                  */
+    const float* nested_absmax;     /* [ceil(blocks/nested_blocksize)] or NULL              */
+    const float* nested_quant_map;  /* [256] or NULL                                        */
+    int64_t nested_absmax_count;    /* elements in nested_absmax                            */
+    int32_t pointers_on_device;  /* 1: the five pointers are device memory of `device`; 0: host */
+    int32_t device;              /* CUDA device ordinal that will own the linear            */
+} AilaNf4WeightDesc;
+
+/* Thread-local text of the most recent failure (never NULL). Reference analogue: the
+ * std::string* error_message out-parameters of Bnb4BitLinear::init*
+ * (src/ops/Bnb4BitLinear.cpp:248-252) and aila_get_last_error (include/aila_api.h). */
+AILA_NF4_API const char* aila_nf4_last_error(void);
+
+/* Library/ABI version, major*10000 + minor*100 + patch. */
+AILA_NF4_API int aila_nf4_version(void);
+
+/*
+ * Create a linear from checkpoint tensors: validates the descriptor with the reference
+ * loader's rules (LoadBnb4BitWeightRef, src/utils/SafeTensors.cpp:443-487), regroups
+ * nibbles and absmax codes into the 16-byte-aligned unit stream and keeps the second-level
+ * scales for in-kernel expansion. Replaces Bnb4BitLinear::init
+ * (src/ops/Bnb4BitLinear.cpp:453-497), which expands absmax to fp32 on the host.
+ * Synchronous (load time).
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_linear_create(const AilaNf4WeightDesc* desc,
+                                                  AilaNf4Linear** out);
+
+/*
+ * Create only rank `rank` of `world` of the weight described by `desc` (which describes the
+ * WHOLE weight). ROWS keeps rows [rank*N/world, (rank+1)*N/world); COLS keeps input columns
+ * [rank*K/world, (rank+1)*K/world) and requires K/world to be a multiple of blocksize. The
+ * shard keeps the original second-level numbering, so its dequantised values are bit-equal
+ * to the same slice of the whole weight. No reference counterpart (the reference is
+ * single-device); net-new for the multi-GPU layer.
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_linear_create_shard(const AilaNf4WeightDesc* desc,
+                                                        AilaNf4ShardMode mode, int rank,
+                                                        int world, AilaNf4Linear** out);
+
+/*
+ * Concatenate 2..4 linears along out_features into a new linear (q|k|v, gate|up). Sources
+ * must share device, in_features, blocksize and quant_map (max abs difference 1e-6), the
+ * checks of Bnb4BitLinear::init_fused_rows (src/ops/Bnb4BitLinear.cpp:499-629). The result
+ * owns its memory; sources may be destroyed afterwards. Synchronous (load time).
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_linear_create_fused_rows(AilaNf4Linear* const* sources,
+                                                             int n_sources,
+                                                             AilaNf4Linear** out);
+
+AILA_NF4_API void aila_nf4_linear_destroy(AilaNf4Linear* linear);
+
+/* Bnb4BitLinear::in_features() / out_features() (src/ops/Bnb4BitLinear.hpp:58-59). */
+AILA_NF4_API int64_t aila_nf4_linear_in_features(const AilaNf4Linear* linear);
+AILA_NF4_API int64_t aila_nf4_linear_out_features(const AilaNf4Linear* linear);
+/* Bytes of device memory the linear owns (weights + scales). */
+AILA_NF4_API int64_t aila_nf4_linear_device_bytes(const AilaNf4Linear* linear);
+AILA_NF4_API int aila_nf4_linear_device(const AilaNf4Linear* linear);
+
+/*
+ * Work space used by forward calls: split-K partial sums and tile counters of the decode
+ * kernels, and the bf16 weight buffer of the prefill route. Mirrors Bnb4BitLinearScratch
+ * (src/ops/Bnb4BitLinear.hpp:12-24): grow-only, shared by all linears of one engine.
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_scratch_create(int device, AilaNf4Scratch** out);
+AILA_NF4_API void aila_nf4_scratch_destroy(AilaNf4Scratch* scratch);
+/*
+ * Pre-size the work space so later forward calls never allocate (call before capturing a
+ * CUDA graph). Mirrors Bnb4BitLinearScratch::ensure (src/ops/Bnb4BitLinear.cpp:414-451);
+ * need_weight != 0 reserves the [out,in] bf16 weight buffer the seq_len > 1 route uses.
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_scratch_reserve(AilaNf4Scratch* scratch, int seq_len,
+                                                    int64_t in_features, int64_t out_features,
+                                                    int need_weight);
+/* Reads (and clears) the device-side status word: AILA_NF4_OK, or
+ * AILA_NF4_ERR_KERNEL_TIMEOUT if a bounded wait inside a kernel expired since the last
+ * query. Synchronises `stream`. */
+AILA_NF4_API AilaNf4Status aila_nf4_scratch_check(AilaNf4Scratch* scratch, void* stream);
+
+/*
+ * y[seq_len][out] = x[seq_len][in] * W^T (+ residual), all bfloat16 device pointers.
+ * Replaces Bnb4BitLinear::forward (src/ops/Bnb4BitLinear.cpp:799-949):
+ *   seq_len == 1  -> streaming decode GEMV (reference packed_nf4_gemv_bf16, :271-410),
+ *                    fp32 accumulation, one rounding to bf16;
+ *   seq_len  > 1  -> weights rounded to bf16 exactly as dequantize_weight (:723-757) does,
+ *                    then a tcgen05 tensor-core GEMM with fp32 accumulation (the reference
+ *                    runs an oneDNN bf16 matmul, :689-721, :944).
+ * `residual` (or NULL) is bf16 [seq_len][out] added before the final rounding - the
+ * documented meaning of add_residual (:323); the reference's SG16 branch ignores it.
+ * Errors: seq_len <= 0 and NULL pointers give AILA_NF4_ERR_INVALID_ARGUMENT where the
+ * reference throws std::runtime_error (:805-811).
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_forward(const AilaNf4Linear* linear, AilaNf4Scratch* scratch,
+                                            const void* x_bf16, void* y_bf16, int seq_len,
+                                            const void* residual_bf16, void* stream);
+
+/*
+ * out[seq_len][ff_dim] = silu(x*Wg^T) .* (x*Wu^T) for a fused gate|up linear whose first
+ * ff_dim rows are gate and last ff_dim rows are up. Replaces
+ * Bnb4BitLinear::try_forward_decode_gate_up_swiglu (src/ops/Bnb4BitLinear.cpp:759-797) for
+ * seq_len == 1 (gate and up stay fp32 until the product is rounded once, :241-242) and the
+ * forward + ops::fused_gate_up_swiglu pair (src/ops/ElementwiseOps.cpp:247-294) for
+ * seq_len > 1 (gate and up are rounded to bf16 first, as that pair does).
+ * Returns AILA_NF4_NOT_APPLICABLE where the reference returns false (out_features !=
+ * 2*ff_dim, :772) or when ff_dim is not a multiple of 16; the caller then uses
+ * aila_nf4_forward followed by its own SwiGLU.
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* fused_gate_up,
+                                                           AilaNf4Scratch* scratch,
+                                                           const void* x_bf16, void* out_bf16,
+                                                           int seq_len, int64_t ff_dim,
+                                                           void* stream);
+
+/*
+ * Same two operations with HOST buffers: copies x to the device, runs the operator, copies
+ * the result back and waits for it. For callers that keep activations on the host, and the
+ * end-to-end timing path of the benchmark. Host buffers should be pinned.
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_forward_host(const AilaNf4Linear* linear,
+                                                 AilaNf4Scratch* scratch, const void* x_host_bf16,
+                                                 void* y_host_bf16, int seq_len, void* stream);
+AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_host(
+    const AilaNf4Linear* fused_gate_up, AilaNf4Scratch* scratch, const void* x_host_bf16,
+    void* out_host_bf16, int seq_len, int64_t ff_dim, void* stream);
+
+/*
+ * Whole-weight dequantisation into the TRANSPOSED bf16 matrix Wt[in][out], bit-equal to
+ * Bnb4BitLinear::dequantize_weight (src/ops/Bnb4BitLinear.cpp:723-757):
+ * Wt[k*out + n] = bf16(quant_map[nibble(n,k)] * absmax(n, k/blocksize)).
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_dequantize(const AilaNf4Linear* linear, void* out_bf16_kn,
+                                               void* stream);
+/* Same values in the natural orientation W[out][in] (what the prefill GEMM consumes). */
+AILA_NF4_API AilaNf4Status aila_nf4_dequantize_rowmajor(const AilaNf4Linear* linear,
+                                                        void* out_bf16_nk, void* stream);
+/* fp32 absmax of every (row, block), [out][in/blocksize]: what Bnb4BitLinear::init
+ * (src/ops/Bnb4BitLinear.cpp:472-488) computes on the host. */
+AILA_NF4_API AilaNf4Status aila_nf4_expand_absmax(const AilaNf4Linear* linear, void* out_f32,
+                                                  void* stream);
+
+/*
+ * Kernel selection for the seq_len == 1 route, for A/B measurement: 0 = automatic,
+ * 1 = plain CUDA-core kernel (fp32 weights, exactly the reference's arithmetic up to
+ * summation order), 2 = streaming tensor-core kernel. Process-wide; also settable with the
+ * environment variable AILA_NF4_GEMV_KERNEL read at first use.
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_set_gemv_kernel(int which);
+
+#endif /* AILA_NF4_H */

@@ -1,0 +1,357 @@
+"""Parity of the CUDA library with the CPU oracle, through the C ABI (ctypes), on a B200.
+
+Bars: dequantised weights and absmax bit-exact; GEMV / fused gate+up+SiLU / prefill GEMM
+outputs within max|err| <= 2e-2 * ||y||_inf at bf16 output (the bound BASELINE.json states).
+"""
+import numpy as np
+import pytest
+import torch
+
+from aila_b200 import synth
+from tests.helpers import (assert_close_norm, bf16_bits, bits_to_f32, make_weight, oracle_absmax)
+
+pytestmark = pytest.mark.gpu
+
+REL = 2e-2  # max |err| <= REL * ||y||_inf
+
+
+@pytest.fixture(scope="module")
+def nf4():
+    from aila_b200 import linear
+    assert torch.cuda.is_available()
+    return linear
+
+
+@pytest.fixture(scope="module")
+def scratch(nf4):
+    s = nf4.Bnb4BitLinearScratch(0)
+    yield s
+    torch.cuda.synchronize()
+    s.check()
+    s.close()
+
+
+def _lin(nf4, w):
+    l = nf4.Bnb4BitLinear()
+    assert l.init(w, 0), l.last_error
+    return l
+
+
+def _act(seed, *shape):
+    return synth.gaussian_activation(seed, *shape)
+
+
+# ---------------------------------------------------------------- dequantisation (bit-exact)
+@pytest.mark.parametrize("N,K,nested", [(16, 64, True), (64, 64, False), (48, 448, True),
+                                        (100, 512, True), (33, 128, False), (512, 2560, True),
+                                        (1024, 9728, True)])
+def test_dequant_bit_exact(nf4, oracle, N, K, nested):
+    w = make_weight(100 + N + K, N, K, 64, nested)
+    am = oracle_absmax(oracle, w)
+    l = _lin(nf4, w)
+    assert (l.in_features(), l.out_features()) == (K, N)
+    got_am = l.expand_absmax(64).cpu().numpy().reshape(-1)
+    assert np.array_equal(got_am.view(np.uint32), am.view(np.uint32)), "absmax not bit-exact"
+    want = oracle.dequantize_kn(w.packed, w.quant_map, am, N, K, 64)
+    assert np.array_equal(bf16_bits(l.dequantize_weight()), want), "Wt[K,N] not bit-exact"
+    assert np.array_equal(bf16_bits(l.dequantize_rowmajor()), want.T), "W[N,K] not bit-exact"
+
+
+def test_dequant_every_byte_value(nf4, oracle):
+    """All 256 packed byte values against sampled fp32 absmax, bitwise."""
+    N, K = 64, 512
+    rng = np.random.default_rng(5)
+    packed = np.tile(np.arange(256, dtype=np.uint8), N * K // 2 // 256)
+    rng.shuffle(packed)
+    absmax = np.exp(rng.uniform(-12, 4, N * K // 64)).astype(np.float32)
+    w = synth.Nf4Tensors(N, K, 64, packed, None, absmax, synth.nf4_codebook(), None, None)
+    l = _lin(nf4, w)
+    want = oracle.dequantize_kn(packed, w.quant_map, absmax, N, K, 64)
+    assert np.array_equal(bf16_bits(l.dequantize_weight()), want)
+
+
+@pytest.mark.parametrize("bs", [128, 256])
+def test_dequant_larger_blocksize(nf4, oracle, bs):
+    N, K = 32, 1024
+    w = make_weight(77, N, K, bs, True)
+    am = oracle_absmax(oracle, w)
+    l = _lin(nf4, w)
+    want = oracle.dequantize_kn(w.packed, w.quant_map, am, N, K, bs)
+    assert np.array_equal(bf16_bits(l.dequantize_weight()), want)
+    assert np.array_equal(l.expand_absmax(bs).cpu().numpy().reshape(-1).view(np.uint32),
+                          am.view(np.uint32))
+
+
+# ---------------------------------------------------------------- decode GEMV
+GEMV_SHAPES = [(16, 64), (40, 128), (48, 448), (100, 512), (256, 2560), (2560, 9728),
+               (9728, 2560), (6144, 2560), (2560, 4096)]
+
+
+@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("N,K", GEMV_SHAPES)
+def test_gemv(nf4, oracle, scratch, kernel, N, K):
+    w = make_weight(1000 + N + K, N, K)
+    am = oracle_absmax(oracle, w)
+    l = _lin(nf4, w)
+    x = _act(1009 + N, 1, K)
+    y = torch.full((1, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    nf4.set_gemv_kernel(kernel)
+    try:
+        l.forward(scratch, x.cuda(), y, 1)
+        torch.cuda.synchronize()
+    finally:
+        nf4.set_gemv_kernel(0)
+    scratch.check()
+    want = oracle.gemv(w.packed, w.quant_map, am, bf16_bits(x).reshape(-1), N, K, 64)
+    assert_close_norm(bf16_bits(y).reshape(-1), want, REL, f"gemv k{kernel} {N}x{K}")
+
+
+def test_gemv_repeatable_and_residual(nf4, oracle, scratch):
+    N, K = 2560, 9728
+    w = make_weight(31, N, K)
+    am = oracle_absmax(oracle, w)
+    l = _lin(nf4, w)
+    x = _act(32, 1, K).cuda()
+    res = _act(33, 1, N)
+    ys = []
+    for _ in range(3):  # the split-K counters must return to zero after every launch
+        y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+        l.forward(scratch, x, y, 1, add_residual=res.cuda())
+        ys.append(bf16_bits(y))
+    assert np.array_equal(ys[0], ys[1]) and np.array_equal(ys[1], ys[2]), "not deterministic"
+    want = oracle.gemv(w.packed, w.quant_map, am, bf16_bits(x).reshape(-1), N, K, 64,
+                       residual=bf16_bits(res).reshape(-1))
+    assert_close_norm(ys[0].reshape(-1), want, REL, "gemv+residual")
+
+
+def test_gemv_non_nested(nf4, oracle, scratch):
+    N, K = 512, 2560
+    w = make_weight(41, N, K, 64, nested=False)
+    l = _lin(nf4, w)
+    x = _act(42, 1, K)
+    for kernel in (1, 2):
+        y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+        nf4.set_gemv_kernel(kernel)
+        try:
+            l.forward(scratch, x.cuda(), y, 1)
+        finally:
+            nf4.set_gemv_kernel(0)
+        want = oracle.gemv(w.packed, w.quant_map, w.absmax_f32, bf16_bits(x).reshape(-1), N, K, 64)
+        assert_close_norm(bf16_bits(y).reshape(-1), want, REL, f"gemv f32-absmax k{kernel}")
+
+
+# ---------------------------------------------------------------- fused rows, gate+up+SiLU
+def _fused(nf4, ws):
+    ls = [_lin(nf4, w) for w in ws]
+    f = nf4.Bnb4BitLinear()
+    assert f.init_fused_rows(*ls), f.last_error
+    return f, ls
+
+
+def test_fused_rows_qkv(nf4, oracle, scratch):
+    K = 2560
+    ws = [make_weight(51, 4096, K), make_weight(52, 1024, K), make_weight(53, 1024, K)]
+    f, _ = _fused(nf4, ws)
+    assert f.out_features() == 6144
+    packed = np.concatenate([w.packed for w in ws])
+    am = np.concatenate([oracle_absmax(oracle, w) for w in ws])
+    assert np.array_equal(f.expand_absmax(64).cpu().numpy().reshape(-1).view(np.uint32),
+                          am.view(np.uint32))
+    want = oracle.dequantize_kn(packed, ws[0].quant_map, am, 6144, K, 64)
+    assert np.array_equal(bf16_bits(f.dequantize_weight()), want)
+    x = _act(54, 1, K)
+    y = torch.empty(1, 6144, dtype=torch.bfloat16, device="cuda")
+    f.forward(scratch, x.cuda(), y, 1)
+    wanty = oracle.gemv(packed, ws[0].quant_map, am, bf16_bits(x).reshape(-1), 6144, K, 64)
+    assert_close_norm(bf16_bits(y).reshape(-1), wanty, REL, "qkv gemv")
+
+
+def test_fused_rows_ragged_sources(nf4, oracle):
+    """Sources whose row counts are not multiples of the 16-row tile."""
+    K = 256
+    ws = [make_weight(61, 40, K), make_weight(62, 7, K), make_weight(63, 33, K),
+          make_weight(64, 16, K)]
+    f, _ = _fused(nf4, ws)
+    packed = np.concatenate([w.packed for w in ws])
+    am = np.concatenate([oracle_absmax(oracle, w) for w in ws])
+    want = oracle.dequantize_kn(packed, ws[0].quant_map, am, 96, K, 64)
+    assert np.array_equal(bf16_bits(f.dequantize_weight()), want)
+
+
+def test_fused_rows_rejects_mismatch(nf4):
+    a, b = _lin(nf4, make_weight(1, 32, 128)), _lin(nf4, make_weight(2, 32, 256))
+    f = nf4.Bnb4BitLinear()
+    assert not f.init_fused_rows(a, b)
+    assert "incompatible" in f.last_error
+    assert not f.init_fused_rows(a)
+    assert "2 to 4" in f.last_error
+
+
+@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("ff,K", [(64, 512), (1216, 2560), (9728, 2560)])
+def test_gate_up_swiglu_decode(nf4, oracle, scratch, kernel, ff, K):
+    ws = [make_weight(2000 + ff, ff, K), make_weight(2001 + ff, ff, K)]
+    f, _ = _fused(nf4, ws)
+    packed = np.concatenate([w.packed for w in ws])
+    am = np.concatenate([oracle_absmax(oracle, w) for w in ws])
+    x = _act(2009, 1, K)
+    out = torch.full((1, ff), float("nan"), dtype=torch.bfloat16, device="cuda")
+    nf4.set_gemv_kernel(kernel)
+    try:
+        assert nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x.cuda(), out, ff)
+        torch.cuda.synchronize()
+    finally:
+        nf4.set_gemv_kernel(0)
+    scratch.check()
+    want = oracle.gemv_gate_up_swiglu(packed, ws[0].quant_map, am, bf16_bits(x).reshape(-1), ff, K, 64)
+    assert_close_norm(bf16_bits(out).reshape(-1), want, REL, f"gate_up k{kernel}")
+
+
+def test_gate_up_not_applicable(nf4, scratch):
+    f, _ = _fused(nf4, [make_weight(1, 64, 128), make_weight(2, 64, 128)])
+    x = _act(3, 1, 128).cuda()
+    out = torch.empty(1, 64, dtype=torch.bfloat16, device="cuda")
+    assert not nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x, out, 48)
+    assert not nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x.float(), out, 64)
+
+
+# ---------------------------------------------------------------- prefill GEMM (tcgen05)
+@pytest.mark.parametrize("M,N,K", [(2, 32, 64), (7, 48, 128), (128, 256, 512), (200, 272, 448),
+                                   (333, 1000, 1024), (512, 2560, 2560), (2048, 1024, 2560)])
+def test_prefill_gemm(nf4, oracle, scratch, M, N, K):
+    w = make_weight(3000 + M + N, N, K)
+    am = oracle_absmax(oracle, w)
+    l = _lin(nf4, w)
+    x = _act(3009 + M, M, K)
+    y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    l.forward(scratch, x.cuda(), y, M)
+    torch.cuda.synchronize()
+    scratch.check()
+    want = oracle.forward(w.packed, w.quant_map, am, bf16_bits(x), M, N, K, 64)
+    assert_close_norm(bf16_bits(y), want, REL, f"prefill {M}x{N}x{K}")
+
+
+def test_prefill_residual(nf4, oracle, scratch):
+    M, N, K = 130, 264, 256
+    w = make_weight(3100, N, K)
+    am = oracle_absmax(oracle, w)
+    l = _lin(nf4, w)
+    x, res = _act(3101, M, K), _act(3102, M, N)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    l.forward(scratch, x.cuda(), y, M, add_residual=res.cuda())
+    wb = bits_to_f32(oracle.dequantize_nk(w.packed, w.quant_map, am, N, K, 64)).astype(np.float64)
+    want = bits_to_f32(bf16_bits(x)).astype(np.float64) @ wb.T + bits_to_f32(bf16_bits(res))
+    got = bits_to_f32(bf16_bits(y)).astype(np.float64)
+    assert np.abs(got - want).max() <= REL * np.abs(want).max()
+
+
+@pytest.mark.parametrize("M,ff,K", [(5, 64, 128), (130, 1216, 512), (2048, 1216, 2560)])
+def test_prefill_gate_up_swiglu(nf4, oracle, scratch, M, ff, K):
+    ws = [make_weight(3200 + ff, ff, K), make_weight(3201 + ff, ff, K)]
+    f, _ = _fused(nf4, ws)
+    packed = np.concatenate([w.packed for w in ws])
+    am = np.concatenate([oracle_absmax(oracle, w) for w in ws])
+    x = _act(3209, M, K)
+    out = torch.full((M, ff), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x.cuda(), out, ff,
+                                                              seq_len=M)
+    torch.cuda.synchronize()
+    scratch.check()
+    gu = oracle.forward(packed, ws[0].quant_map, am, bf16_bits(x), M, 2 * ff, K, 64)
+    want = oracle.swiglu_rows(gu, M, ff)
+    assert_close_norm(bf16_bits(out), want, REL, f"prefill swiglu {M}x{ff}x{K}")
+
+
+def test_prefill_pair_full_size_properties(nf4, oracle, scratch):
+    """cfg3 at full size (M = 2048, gate_up 2560 -> 2*9728, down 9728 -> 2560): linearity in
+    x and a row-sample check against the oracle (the full CPU product would take minutes)."""
+    M, H, FF = 2048, 2560, 9728
+    gate, up = make_weight(3004, FF, H), make_weight(3005, FF, H)
+    f, _ = _fused(nf4, [gate, up])
+    down = _lin(nf4, make_weight(3006, H, FF))
+    x = _act(3009, M, H).cuda()
+    mid = torch.empty(M, FF, dtype=torch.bfloat16, device="cuda")
+    assert nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x, mid, FF, seq_len=M)
+    y = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    down.forward(scratch, mid, y, M)
+    torch.cuda.synchronize()
+    scratch.check()
+    assert torch.isfinite(y.float()).all()
+    # sampled rows against the oracle, gate_up + SwiGLU then down
+    rows = [0, 1, 127, 128, 1029, 2047]
+    packed = np.concatenate([gate.packed, up.packed])
+    am = np.concatenate([oracle_absmax(oracle, gate), oracle_absmax(oracle, up)])
+    xs = bf16_bits(x)[rows]
+    gu = oracle.forward(packed, gate.quant_map, am, xs, len(rows), 2 * FF, H, 64)
+    mid_want = oracle.swiglu_rows(gu, len(rows), FF)
+    assert_close_norm(bf16_bits(mid)[rows], mid_want, REL, "cfg3 gate_up+swiglu rows")
+    dw = make_weight(3006, H, FF)
+    y_want = oracle.forward(dw.packed, dw.quant_map, oracle_absmax(oracle, dw),
+                            bf16_bits(mid)[rows], len(rows), H, FF, 64)
+    assert_close_norm(bf16_bits(y)[rows], y_want, REL, "cfg3 down rows")
+    # linearity: W(2x) == 2 W(x) exactly in bf16 (power-of-two scaling)
+    y2 = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    down.forward(scratch, mid * 2, y2, M)
+    assert torch.equal(y2.float(), y.float() * 2)
+
+
+# ---------------------------------------------------------------- shards
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_row_shards_bit_equal_slices(nf4, oracle, world):
+    N, K = 1024, 2560
+    w = make_weight(4000, N, K)
+    am = oracle_absmax(oracle, w)
+    full = oracle.dequantize_kn(w.packed, w.quant_map, am, N, K, 64)  # [K, N]
+    for r in range(world):
+        l = nf4.Bnb4BitLinear()
+        assert l.init_shard(w, 0, r, world, 0), l.last_error
+        rows = N // world
+        assert np.array_equal(bf16_bits(l.dequantize_weight()), full[:, r * rows:(r + 1) * rows])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_col_shards_sum_to_full(nf4, oracle, scratch, world):
+    N, K = 512, 4096
+    w = make_weight(4100, N, K)
+    am = oracle_absmax(oracle, w)
+    full = oracle.dequantize_kn(w.packed, w.quant_map, am, N, K, 64)
+    x = _act(4101, 1, K)
+    acc = np.zeros(N, np.float64)
+    cols = K // world
+    for r in range(world):
+        l = nf4.Bnb4BitLinear()
+        assert l.init_shard(w, 1, r, world, 0), l.last_error
+        assert np.array_equal(bf16_bits(l.dequantize_weight()), full[r * cols:(r + 1) * cols, :])
+        y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+        l.forward(scratch, x[:, r * cols:(r + 1) * cols].contiguous().cuda(), y, 1)
+        acc += bits_to_f32(bf16_bits(y).reshape(-1))
+    want = bits_to_f32(oracle.gemv(w.packed, w.quant_map, am, bf16_bits(x).reshape(-1), N, K, 64))
+    assert np.abs(acc - want).max() <= REL * np.abs(want).max()
+
+
+# ---------------------------------------------------------------- host-buffer entry points
+def test_host_entry_points(nf4, oracle, scratch):
+    ff, K = 256, 512
+    ws = [make_weight(5000, ff, K), make_weight(5001, ff, K)]
+    f, _ = _fused(nf4, ws)
+    packed = np.concatenate([w.packed for w in ws])
+    am = np.concatenate([oracle_absmax(oracle, w) for w in ws])
+    x = _act(5002, 1, K).pin_memory()
+    y = torch.empty(1, 2 * ff, dtype=torch.bfloat16).pin_memory()
+    f.forward_host(scratch, x, y, 1)
+    want = oracle.gemv(packed, ws[0].quant_map, am, bf16_bits(x).reshape(-1), 2 * ff, K, 64)
+    assert_close_norm(bf16_bits(y).reshape(-1), want, REL, "forward_host")
+    out = torch.empty(1, ff, dtype=torch.bfloat16).pin_memory()
+    f.gate_up_swiglu_host(scratch, x, out, 1, ff)
+    want = oracle.gemv_gate_up_swiglu(packed, ws[0].quant_map, am, bf16_bits(x).reshape(-1), ff, K, 64)
+    assert_close_norm(bf16_bits(out).reshape(-1), want, REL, "gate_up_swiglu_host")
+
+
+def test_forward_error_behaviour(nf4, scratch):
+    l = _lin(nf4, make_weight(1, 32, 128))
+    x = torch.zeros(1, 128, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(1, 32, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="bf16"):
+        l.forward(scratch, x.float(), y, 1)
+    with pytest.raises(RuntimeError, match="seq_len"):
+        l.forward(scratch, x, y, 0)
