@@ -1,0 +1,148 @@
+// aila_nf4_linear.hpp - header-only C++ adapter that keeps the reference operator's interface
+// (class Bnb4BitLinear, struct Bnb4BitLinearScratch; reference src/ops/Bnb4BitLinear.hpp:12-59)
+// on top of the C ABI in aila_nf4.h, so the two model backends that call it
+// (src/models/Qwen3Bnb4Backend.cpp:339-418, src/models/Qwen35HybridBnb4Backend.cpp:2167-2197)
+// compile against it with their call sites unchanged.
+//
+// What changes for the caller
+//   Context      -> aila::nf4::Context {device ordinal, cudaStream_t}: the reference's Context
+//                   (src/core/Context.hpp:14-90) owns one in-order SYCL queue; here the caller's
+//                   CUDA stream plays that role.
+//   Tensor       -> aila::nf4::TensorView {void* data, dims, is_bf16}: the subset of
+//                   src/core/Tensor.hpp:15-202 the operator touches (data(), dtype(), ndim()).
+//   Bnb4BitWeightRef -> AilaNf4WeightDesc (same tensors as raw pointers, aila_nf4.h).
+// Error behaviour is the reference's: init* return bool and fill *error_message, forward throws
+// std::runtime_error, try_forward_decode_gate_up_swiglu returns false to mean "fall back".
+#pragma once
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include "aila_nf4.h"
+
+namespace aila {
+namespace nf4 {
+
+struct Context {
+    int device = 0;
+    void* stream = nullptr;  // cudaStream_t
+};
+
+struct TensorView {
+    void* ptr = nullptr;
+    int64_t rows = 0, cols = 0;
+    int dims = 2;
+    bool bf16 = true;
+    void* data() const { return ptr; }
+    int ndim() const { return dims; }
+    bool is_bf16() const { return bf16; }
+};
+
+// Bnb4BitLinearScratch (reference src/ops/Bnb4BitLinear.hpp:12-24): grow-only work space
+// shared by all linears of one backend.
+struct Bnb4BitLinearScratch {
+    AilaNf4Scratch* handle = nullptr;
+
+    Bnb4BitLinearScratch() = default;
+    Bnb4BitLinearScratch(const Bnb4BitLinearScratch&) = delete;
+    Bnb4BitLinearScratch& operator=(const Bnb4BitLinearScratch&) = delete;
+    ~Bnb4BitLinearScratch() { aila_nf4_scratch_destroy(handle); }
+
+    // Bnb4BitLinearScratch::ensure (reference src/ops/Bnb4BitLinear.cpp:414-451).
+    void ensure(Context& ctx, int seq_len, int in_features, int out_features, bool need_weight) {
+        open(ctx);
+        if (aila_nf4_scratch_reserve(handle, seq_len, in_features, out_features,
+                                     need_weight ? 1 : 0) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+    }
+
+    void open(Context& ctx) {
+        if (!handle && aila_nf4_scratch_create(ctx.device, &handle) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+    }
+};
+
+class Bnb4BitLinear {
+public:
+    Bnb4BitLinear() = default;
+    Bnb4BitLinear(const Bnb4BitLinear&) = delete;
+    Bnb4BitLinear& operator=(const Bnb4BitLinear&) = delete;
+    ~Bnb4BitLinear() { aila_nf4_linear_destroy(handle_); }
+
+    // Bnb4BitLinear::init (reference src/ops/Bnb4BitLinear.cpp:453-497).
+    bool init(Context& ctx, const AilaNf4WeightDesc& weight, std::string* error_message = nullptr) {
+        AilaNf4WeightDesc d = weight;
+        d.device = ctx.device;
+        return adopt(aila_nf4_linear_create(&d, &fresh_), error_message);
+    }
+
+    // Bnb4BitLinear::init_fused_rows, 2..4 sources (reference :499-521).
+    bool init_fused_rows(Context&, const Bnb4BitLinear& a, const Bnb4BitLinear& b,
+                         std::string* error_message = nullptr) {
+        AilaNf4Linear* s[2] = {a.handle_, b.handle_};
+        return adopt(aila_nf4_linear_create_fused_rows(s, 2, &fresh_), error_message);
+    }
+    bool init_fused_rows(Context&, const Bnb4BitLinear& a, const Bnb4BitLinear& b,
+                         const Bnb4BitLinear& c, std::string* error_message = nullptr) {
+        AilaNf4Linear* s[3] = {a.handle_, b.handle_, c.handle_};
+        return adopt(aila_nf4_linear_create_fused_rows(s, 3, &fresh_), error_message);
+    }
+    bool init_fused_rows(Context&, const Bnb4BitLinear& a, const Bnb4BitLinear& b,
+                         const Bnb4BitLinear& c, const Bnb4BitLinear& d,
+                         std::string* error_message = nullptr) {
+        AilaNf4Linear* s[4] = {a.handle_, b.handle_, c.handle_, d.handle_};
+        return adopt(aila_nf4_linear_create_fused_rows(s, 4, &fresh_), error_message);
+    }
+
+    // Bnb4BitLinear::forward (reference :799-949). add_residual: bf16 [seq_len][out] or null.
+    void forward(Context& ctx, Bnb4BitLinearScratch& scratch, TensorView& input, TensorView& output,
+                 int seq_len, const void* add_residual = nullptr) {
+        if (!input.is_bf16() || !output.is_bf16())
+            throw std::runtime_error("Bnb4BitLinear expects bf16 input/output tensors");
+        if (seq_len <= 0)
+            throw std::runtime_error("Bnb4BitLinear::forward: seq_len must be positive");
+        scratch.open(ctx);
+        if (aila_nf4_forward(handle_, scratch.handle, input.data(), output.data(), seq_len,
+                             add_residual, ctx.stream) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+    }
+
+    // Bnb4BitLinear::try_forward_decode_gate_up_swiglu (reference :759-797). The reference
+    // takes no scratch here; this one needs the split-K work space, hence the extra argument.
+    static bool try_forward_decode_gate_up_swiglu(Context& ctx, Bnb4BitLinearScratch& scratch,
+                                                  Bnb4BitLinear& fused_gate_up, TensorView& input,
+                                                  TensorView& output, int ff_dim, int seq_len = 1) {
+        if (!input.is_bf16() || !output.is_bf16()) return false;
+        if (input.ndim() != 2) return false;
+        scratch.open(ctx);
+        const AilaNf4Status st = aila_nf4_forward_gate_up_swiglu(
+            fused_gate_up.handle_, scratch.handle, input.data(), output.data(), seq_len, ff_dim,
+            ctx.stream);
+        if (st == AILA_NF4_NOT_APPLICABLE) return false;
+        if (st != AILA_NF4_OK) throw std::runtime_error(aila_nf4_last_error());
+        return true;
+    }
+
+    int in_features() const { return static_cast<int>(aila_nf4_linear_in_features(handle_)); }
+    int out_features() const { return static_cast<int>(aila_nf4_linear_out_features(handle_)); }
+    AilaNf4Linear* handle() const { return handle_; }
+
+private:
+    bool adopt(AilaNf4Status st, std::string* error_message) {
+        if (st != AILA_NF4_OK) {
+            if (error_message) *error_message = aila_nf4_last_error();
+            fresh_ = nullptr;
+            return false;
+        }
+        aila_nf4_linear_destroy(handle_);
+        handle_ = fresh_;
+        fresh_ = nullptr;
+        return true;
+    }
+    AilaNf4Linear* handle_ = nullptr;
+    AilaNf4Linear* fresh_ = nullptr;
+};
+
+}  // namespace nf4
+}  // namespace aila
