@@ -70,6 +70,7 @@ _SIGNATURES = {
     "aila_nf4_forward_host": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int, _VP]),
     "aila_nf4_forward_gate_up_swiglu_host": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int,
                                                             ctypes.c_int64, _VP]),
+    "aila_nf4_forward_decode_static": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP]),
     "aila_nf4_dequantize": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_dequantize_rowmajor": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_expand_absmax": (ctypes.c_int, [_VP, _VP, _VP]),

@@ -638,6 +638,17 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_host(
     return AILA_NF4_OK;
 }
 
+AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_static(const AilaNf4Linear* l, const void* x,
+                                                          void* y, const void* residual,
+                                                          void* stream) {
+    if (!l) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "linear handle is NULL");
+    if (!x || !y)
+        return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Bnb4BitLinear expects bf16 input/output tensors");
+    DeviceGuard guard(l->device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    return nf4::launch_gemv_stream_static(*l, x, y, residual, static_cast<cudaStream_t>(stream));
+}
+
 AILA_NF4_API AilaNf4Status aila_nf4_dequantize(const AilaNf4Linear* l, void* out_kn, void* stream) {
     if (!l || !out_kn) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
     DeviceGuard guard(l->device);

@@ -15,6 +15,8 @@
 //    scratch, summed in CTA order by whichever CTA arrives last (no spinning, deterministic).
 //
 // Roofline: HBM. Algorithmic bytes per weight: 0.5 (nibbles) + 1/64 (code) + 4/16384 (scale).
+#include <mutex>
+
 #include "nf4_internal.h"
 
 namespace nf4 {
@@ -457,6 +459,29 @@ cudaError_t launch_stream_t(const StreamParams& p, int grid, int smem, cudaStrea
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------
+// Fixed work space for the entry point that never allocates (aila_nf4_forward_decode_static).
+// The streaming kernel's split-K partial sums, row-tile counters and status word live in this
+// file-scope device array instead of an AilaNf4Scratch. Every GPU that loads the library holds
+// the array until the process exits. Limits that follow from its size: at most
+// kStaticMaxCtas CTAs per launch and kStaticMaxRowTiles row tiles (262,144 output rows).
+// ------------------------------------------------------------------------------------------
+constexpr int kStaticMaxCtas = 8 * 160;
+constexpr int kStaticMaxRowTiles = 16384;
+struct StaticScratchLayout {
+    float partials[kStaticMaxCtas * 2 * 2 * 16];  // 327,680 B
+    int counters[kStaticMaxRowTiles];             //  65,536 B
+    int status[64];
+};
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[sizeof(StaticScratchLayout)];
+
+struct StaticScratchHost {
+    StaticScratchLayout* ptr = nullptr;  // device address of the array on this device
+    int sm_count = 0;
+};
+StaticScratchHost g_static_host[64];
+std::mutex g_static_mutex;
+
 }  // namespace
 
 cudaError_t launch_gemv_simple(const AilaNf4Linear& w, const void* x, void* y,
@@ -517,6 +542,51 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
                       : launch_stream_t<kAbsmaxCodes, false>(p, pl.grid, pl.smem, s);
     return paired ? launch_stream_t<kAbsmaxF32, true>(p, pl.grid, pl.smem, s)
                   : launch_stream_t<kAbsmaxF32, false>(p, pl.grid, pl.smem, s);
+}
+
+// Decode GEMV on the static work space: no allocation of any kind. The first call on a device
+// resolves the device address of the array (the array's name is only a host-side stand-in for
+// it, so the address comes from cudaGetSymbolAddress with that device current).
+AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
+                                        const void* residual, cudaStream_t s) {
+    int dev = 0;
+    NF4_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(AILA_NF4_ERR_UNSUPPORTED, "device ordinal above 63");
+    StaticScratchHost host;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!g_static_host[dev].ptr) {
+            void* p = nullptr;
+            NF4_CUDA(cudaGetSymbolAddress(&p, g_gemv_static_scratch));
+            int sms = 0;
+            NF4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            g_static_host[dev].sm_count = sms;
+            g_static_host[dev].ptr = static_cast<StaticScratchLayout*>(p);
+        }
+        host = g_static_host[dev];
+    }
+    if (w.RT > kStaticMaxRowTiles)
+        return fail(AILA_NF4_ERR_UNSUPPORTED,
+                    "aila_nf4_forward_decode_static: out_features " + std::to_string(w.N) +
+                        " exceeds the fixed work space (max " +
+                        std::to_string(kStaticMaxRowTiles * kTileRows) + " rows)");
+    const StreamPlan pl = stream_plan(w, false, 0, host.sm_count);
+    if (!pl.ok || pl.grid > kStaticMaxCtas || w.K > 65535 * 4)
+        return fail(AILA_NF4_ERR_UNSUPPORTED,
+                    "aila_nf4_forward_decode_static: shape not taken by the streaming kernel "
+                    "within the fixed work space");
+    if (reinterpret_cast<uintptr_t>(x) & 15)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "x must be 16-byte aligned");
+    // The array keeps whatever the previous call left: counters must start at zero.
+    NF4_CUDA(cudaMemsetAsync(host.ptr->counters, 0, sizeof(int) * (size_t)w.RT, s));
+    AilaNf4Scratch view;
+    view.device = dev;
+    view.d_partials = host.ptr->partials;
+    view.d_counters = host.ptr->counters;
+    view.d_status = host.ptr->status;
+    view.sm_count = host.sm_count;
+    NF4_CUDA(launch_gemv_stream(w, view, x, y, residual, 0, s));
+    return AILA_NF4_OK;
 }
 
 }  // namespace nf4

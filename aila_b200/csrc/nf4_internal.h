@@ -106,6 +106,8 @@ size_t gemv_stream_partials_floats(int sm_count);
 cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
                                void* y, const void* residual, int64_t ff_pair, cudaStream_t s);
 bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);
+AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
+                                        const void* residual, cudaStream_t s);
 
 // nf4_gemm.cu ---------------------------------------------------------------------------
 // y[M][N_out] = x[M][K] * w_nk[N][K]^T on tcgen05. swiglu_ff > 0: N == 2*ff and the output

@@ -200,6 +200,17 @@ class Bnb4BitLinear:
             self._h, scratch._h, x_host.data_ptr(), y_host.data_ptr(), seq_len, ff_dim,
             _stream_ptr(self.device)))
 
+    def forward_decode_static(self, input: torch.Tensor, output: torch.Tensor,
+                              add_residual: torch.Tensor | None = None) -> None:
+        """seq_len == 1 forward on the library's built-in fixed work space: no scratch object
+        and no allocation. For hosts that keep the CUDA allocator off their decode loop; calls
+        on one GPU must stay on one stream (they share the work space)."""
+        if input.dtype != torch.bfloat16 or output.dtype != torch.bfloat16:
+            raise RuntimeError("Bnb4BitLinear expects bf16 input/output tensors")
+        res = add_residual.data_ptr() if add_residual is not None else None
+        _lib.check(_lib.load().aila_nf4_forward_decode_static(
+            self._h, input.data_ptr(), output.data_ptr(), res, _stream_ptr(self.device)))
+
     def dequantize_weight(self) -> torch.Tensor:
         """bf16 [in_features, out_features], the transposed layout of
         Bnb4BitLinear::dequantize_weight (Bnb4BitLinear.cpp:723-757)."""

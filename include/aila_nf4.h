@@ -193,6 +193,28 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_host(
     void* out_host_bf16, int seq_len, int64_t ff_dim, void* stream);
 
 /*
+ * Decode step (seq_len == 1) y = W x (+ residual) that allocates nothing, ever: no cudaMalloc,
+ * no cudaFree, no scratch object. No counterpart in the reference (its Context::alloc_device,
+ * src/core/Context.hpp:28-40, is always available to it); added for hosts that must keep the
+ * CUDA allocator off their token loop - for instance an engine that hands all device memory to
+ * its own pool at start-up, so a late cudaMalloc could fail or fragment it, or a serving loop
+ * that cannot afford the device-wide synchronisation an allocation or free implies.
+ * The split-K work space of the streaming kernel is a fixed array inside the library
+ * (about 385 KB per GPU, held from library load to process exit). Consequences:
+ *  - out_features is limited to 262,144 rows; larger or otherwise untaken shapes return
+ *    AILA_NF4_ERR_UNSUPPORTED with a message, never a silent fallback;
+ *  - all calls on one GPU share the array: two calls whose kernels overlap on the GPU (different
+ *    streams) race on it - keep calls to this entry point on one stream per GPU;
+ *  - the first call on each GPU looks up the array's device address; make that call before any
+ *    stream capture begins.
+ * Results are identical to aila_nf4_forward with seq_len == 1.
+ */
+AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_static(const AilaNf4Linear* linear,
+                                                          const void* x_bf16, void* y_bf16,
+                                                          const void* residual_bf16,
+                                                          void* stream);
+
+/*
  * Whole-weight dequantisation into the TRANSPOSED bf16 matrix Wt[in][out], bit-equal to
  * Bnb4BitLinear::dequantize_weight (src/ops/Bnb4BitLinear.cpp:723-757):
  * Wt[k*out + n] = bf16(quant_map[nibble(n,k)] * absmax(n, k/blocksize)).
