@@ -6,15 +6,23 @@
 //  * gemv_simple: one warp per output row, fp32 weights q*absmax and fp32 FMA, i.e. the
 //    reference's arithmetic with a different summation order. Baseline and fallback for
 //    shapes the streaming kernel does not take.
-//  * gemv_stream: the HBM-roofline kernel. One persistent CTA per SM owns an equal, contiguous
-//    slice of the unit stream (split along rows AND k, so any shape balances over 148 SMs),
-//    a producer thread keeps a ring of bulk-async copies in flight, 16 consumer warps turn
-//    nibbles into bf16 tensor-core operands through a bank-private shared-memory table and
-//    accumulate in fp32 with mma.sync m16n8k16; absmax is applied in fp32 per 64-block.
-//    Row tiles cut by a slice boundary are completed through per-CTA partial sums in global
-//    scratch, summed in CTA order by whichever CTA arrives last (no spinning, deterministic).
+//  * gemv_stream: the streaming kernel. One persistent CTA per SM owns an equal, contiguous
+//    slice of the unit stream (split along rows AND k, so any shape balances over 148 SMs).
+//    A producer thread keeps a ring of bulk-async (TMA) copies in flight; 16 consumer warps turn
+//    nibbles into bf16 tensor-core operands through a bank-private shared-memory table (one PRMT
+//    plus one LDS per two weights) and accumulate in fp32 with mma.sync m16n8k16; absmax is
+//    decoded from its 8-bit code in fp32 (two rounded operations) and applied per 64-block.
+//    A CTA walks its slice starting with its LAST row tile, so the two tiles it may share with
+//    neighbouring CTAs complete first: their per-CTA partial sums go to global scratch and
+//    whichever CTA arrives last at the tile's counter sums them in CTA order (no spinning,
+//    deterministic) while everybody streams on. Row tiles are completed as soon as every warp
+//    has signed them off, so there is no end-of-kernel reduction phase.
+//    The kernel is launched with programmatic stream serialisation: it issues
+//    griddepcontrol.launch_dependents at once and waits (griddepcontrol.wait) only before it
+//    fetches x, so its table build and first weight copies overlap the previous kernel's tail.
 //
 // Roofline: HBM. Algorithmic bytes per weight: 0.5 (nibbles) + 1/64 (code) + 4/16384 (scale).
+#include <cstdlib>
 #include <mutex>
 
 #include "nf4_internal.h"
@@ -88,16 +96,24 @@ gemv_simple_kernel(const uint8_t* __restrict__ units, const float* __restrict__ 
 // ------------------------------------------------------------------------------------------
 // gemv_stream
 // ------------------------------------------------------------------------------------------
-constexpr int kConsumerWarps = 16;
+#ifndef NF4_W
+#define NF4_W 16
+#endif
+#ifndef NF4_IPW
+#define NF4_IPW 2
+#endif
+constexpr int kConsumerWarps = NF4_W;
 constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
-constexpr int kLutBytes = 256 * 256;                       // 256 byte values x 256 B (lane-private word)
+constexpr int kItemsPerWarp = NF4_IPW;   // work items a consumer warp takes from one stage
+constexpr int kStageItems = kConsumerWarps * kItemsPerWarp;
 constexpr int kMaxStages = 24;
-constexpr int kMaxLocalTiles = 16;  // row tiles one CTA slice may touch
+constexpr int kMaxLocalTiles = 8;  // row tiles one CTA slice may touch
 constexpr int kMaxGridMult = 8;     // grid <= 8 x SM count
+constexpr int kNabsWindow = 256;    // second-level scales kept in shared memory per half
 
 struct StreamParams {
     const uint8_t* units;
-    const float* qmap;
+    float qmap_v[16];       // NF4 code book by value
     ScaleParams sp;
     const uint16_t* x;
     uint16_t* y;
@@ -113,12 +129,15 @@ struct StreamParams {
     int pair_rt_offset;     // paired: row-tile distance from a gate tile to its up tile
     int stages;
     int x_bytes;            // K*2 rounded up to 16
+    int x_in_b;             // 1: x lives above the table (large K), 0: below it
+    int smem_bytes;         // dynamic shared memory of the launch
+    int n_rows;             // rows of the linear (for clamping the padded rows of the last tile)
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1,
                                                uint32_t a2, uint32_t a3, uint32_t b0,
                                                uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -127,12 +146,50 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 
 extern __shared__ __align__(1024) uint8_t smem_raw[];
 
-// Bank-private table lookup: entry for byte value b of lane l sits at b*256 + l*4, so the 32
-// lanes of a warp always hit 32 different banks. One PRMT builds the address.
+// ---- shared-memory access by 32-bit shared-window address (keeps address arithmetic 32-bit) ----
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+// 8-byte load executed only by lanes whose `pred_zero` is 0; the others get zeros
+__device__ __forceinline__ uint2 lds_v2_if_zero(uint32_t a, int pred_zero) {
+    uint2 v;
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.eq.u32 q, %3, 0;\n\t"
+        "mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\t"
+        "@q ld.shared.v2.u32 {%0, %1}, [%2];\n\t}"
+        : "=&r"(v.x), "=&r"(v.y)
+        : "r"(a), "r"(pred_zero));
+    return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
+}
+
+// Bank-private table lookup. The 64 KB table sits on a 64 KB boundary of the shared window and
+// holds, for byte value b and lane l, the bf16 pair of b's two nibbles at b*256 + l*4: the 32
+// lanes of a warp always hit 32 different banks. `lane_base` = table address + l*4; ONE PRMT
+// splices the byte into bits [8,16) of it and the result is the load address.
 template <int BYTE>
-__device__ __forceinline__ uint32_t lut_pair(uint32_t word, uint32_t lane4) {
-    const uint32_t off = __byte_perm(word, lane4, 0x5504 | (BYTE << 4));
-    return *reinterpret_cast<const uint32_t*>(smem_raw + off);
+__device__ __forceinline__ uint32_t lut_pair(uint32_t word, uint32_t lane_base) {
+    return lds_u32(__byte_perm(word, lane_base, 0x7604 | (BYTE << 4)));
 }
 
 __device__ __forceinline__ long long slice_begin(long long total, int c, int G) {
@@ -142,18 +199,33 @@ __device__ __forceinline__ long long slice_begin(long long total, int c, int G) 
 template <int KIND, bool PAIRED>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
     constexpr int NP = PAIRED ? 2 : 1;
-    const int unit_stride = (KIND == kAbsmaxCodes) ? kUnitStrideCodes : kUnitStrideF32;
-    const int stage_bytes = kConsumerWarps * unit_stride * NP;
+    constexpr int W = kConsumerWarps;
+    constexpr int IPW = kItemsPerWarp;
+    constexpr int unit_stride = (KIND == kAbsmaxCodes) ? kUnitStrideCodes : kUnitStrideF32;
+    constexpr int half_bytes = kStageItems * unit_stride;  // one stage of gate (or plain) units
+    constexpr int stage_bytes = half_bytes * NP;
 
-    // shared-memory carve-up
-    uint8_t* lut = smem_raw;                               // [0, 64 KB)
-    uint8_t* xs = smem_raw + kLutBytes;                    // x in fragment order
-    uint8_t* ring = xs + p.x_bytes;                        // stages * stage_bytes
-    float* slots = reinterpret_cast<float*>(ring + (size_t)p.stages * stage_bytes);
-    // slots[local tile][pair][warp][16]
-    uint64_t* full = reinterpret_cast<uint64_t*>(slots + kMaxLocalTiles * NP * kConsumerWarps * 16);
+    // ---- shared-memory map (absolute shared-window addresses) ----
+    // region A = [base, 64 KB): barriers, tile counters, code book, per-warp slots, x (if small)
+    // table    = [64 KB, 128 KB)
+    // region B = [128 KB, ...): x (if large), ring of stages
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t a_bar = (base + 15u) & ~15u;                 // full[kMaxStages], empty[], aux
+    const uint32_t a_tile = a_bar + 400;                         // tile_done[kMaxLocalTiles], abort
+    static_assert((2 * kMaxStages + 1) * 8 <= 400, "barrier block");
+    const uint32_t a_nmap = a_tile + 64;
+    const uint32_t a_nabsw = a_nmap + 1024;                      // [2][kNabsWindow] second-level scales
+    const uint32_t a_slots = a_nabsw + 2 * kNabsWindow * 4;      // [tile][pair][warp][16] floats
+    const uint32_t a_xs_small = a_slots + kMaxLocalTiles * NP * W * 64;
+    const uint32_t a_lut = 65536u;
+    const uint32_t a_xs = p.x_in_b ? 131072u : a_xs_small;
+    const uint32_t a_ring = 131072u + (p.x_in_b ? (uint32_t)p.x_bytes : 0u);
+    uint8_t* gen = smem_raw - base;  // generic pointer to shared-window address 0
+    uint64_t* full = reinterpret_cast<uint64_t*>(gen + a_bar);
     uint64_t* empty = full + kMaxStages;
-    int* abort_flag = reinterpret_cast<int*>(empty + kMaxStages);
+    uint64_t* aux = empty + kMaxStages;
+    int* tile_done = reinterpret_cast<int*>(gen + a_tile);
+    int* abort_flag = tile_done + kMaxLocalTiles;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -162,26 +234,52 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const int c = blockIdx.x;
     const long long i0 = slice_begin(p.total_items, c, G);
     const long long i1 = slice_begin(p.total_items, c + 1, G);
-    const int n_groups = (int)((i1 - i0 + kConsumerWarps - 1) / kConsumerWarps);
+    const int len = (int)(i1 - i0);
+    const int n_groups = (len + kStageItems - 1) / kStageItems;
     const int rt_first = (int)(i0 / p.KU);
     const int rt_last = (int)((i1 - 1) / p.KU);
     const int n_local = rt_last - rt_first + 1;
+    // Traversal order: the slice's LAST row tile first, then the rest from the front. Both row
+    // tiles that may be shared with a neighbouring CTA are then finished early, and their
+    // cross-CTA completion overlaps the streaming of the tiles this CTA owns alone.
+    const long long tail0 = max(i0, (long long)rt_last * p.KU);
+    const int tail_len = (int)(i1 - tail0);
+    // virtual index v in [0, len): item = v < tail_len ? tail0 + v : i0 + (v - tail_len)
 
+    if (base > 2048u || base + (uint32_t)p.smem_bytes < a_ring + (uint32_t)p.stages * stage_bytes ||
+        a_xs_small + (p.x_in_b ? 0u : (uint32_t)p.x_bytes) > 65536u) {
+        if (tid == 0) atomicExch(p.status, kStatusBadArgument);
+        return;
+    }
     if (tid == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kConsumerWarps);
+            mbar_init(&empty[s], W);
         }
+        mbar_init(aux, 1);
+        for (int i = 0; i < kMaxLocalTiles; ++i) tile_done[i] = 0;
         *abort_flag = 0;
         mbar_fence_init();
     }
     __syncthreads();
+    // let a dependent launch begin its own set-up; it waits for our completion before reading
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (warp == kConsumerWarps) {
+    if (warp == W) {
         // ---------------- producer: one thread keeps the ring full ----------------
         if (lane == 0) {
             int issued = 0;
-            for (int g = 0; g < n_groups; ++g) {
+            bool aux_sent = false;
+            for (int g = 0; g <= n_groups; ++g) {
+                if (!aux_sent && (g == p.stages || g == n_groups)) {
+                    // the weights above do not depend on the previous kernel; x does
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                    mbar_expect_tx(aux, (uint32_t)p.x_bytes + (KIND == kAbsmaxCodes ? 1024u : 0u));
+                    bulk_g2s(gen + a_xs, p.x, (uint32_t)p.x_bytes, aux);
+                    if (KIND == kAbsmaxCodes) bulk_g2s(gen + a_nmap, p.sp.nmap, 1024u, aux);
+                    aux_sent = true;
+                }
+                if (g == n_groups) break;
                 const int s = g % p.stages;
                 if (g >= p.stages) {
                     if (*(volatile int*)abort_flag) break;
@@ -191,203 +289,146 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                         break;
                     }
                 }
-                const long long item = i0 + (long long)g * kConsumerWarps;
-                const int cnt = (int)min((long long)kConsumerWarps, i1 - item);
-                const uint32_t bytes = (uint32_t)cnt * unit_stride;
-                uint8_t* dst = ring + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full[s], bytes * NP);
-                bulk_g2s(dst, p.units + (size_t)item * unit_stride, bytes, &full[s]);
-                if (PAIRED)
-                    bulk_g2s(dst + kConsumerWarps * unit_stride,
-                             p.units + ((size_t)item + (size_t)p.pair_rt_offset * p.KU) * unit_stride,
-                             bytes, &full[s]);
+                const int v0 = g * kStageItems;
+                const int cnt = min(kStageItems, len - v0);
+                uint8_t* dst = gen + a_ring + (size_t)s * stage_bytes;
+                mbar_expect_tx(&full[s], (uint32_t)cnt * unit_stride * NP);
+                // up to two contiguous pieces (the traversal wraps from the tail tile to the front)
+                const int n1 = v0 < tail_len ? min(cnt, tail_len - v0) : 0;
+                if (n1 > 0) {
+                    const size_t it = (size_t)(tail0 + v0);
+                    bulk_g2s(dst, p.units + it * unit_stride, (uint32_t)n1 * unit_stride, &full[s]);
+                    if (PAIRED)
+                        bulk_g2s(dst + half_bytes,
+                                 p.units + (it + (size_t)p.pair_rt_offset * p.KU) * unit_stride,
+                                 (uint32_t)n1 * unit_stride, &full[s]);
+                }
+                if (cnt > n1) {
+                    const size_t it = (size_t)(i0 + (v0 + n1 - tail_len));
+                    bulk_g2s(dst + n1 * unit_stride, p.units + it * unit_stride,
+                             (uint32_t)(cnt - n1) * unit_stride, &full[s]);
+                    if (PAIRED)
+                        bulk_g2s(dst + half_bytes + n1 * unit_stride,
+                                 p.units + (it + (size_t)p.pair_rt_offset * p.KU) * unit_stride,
+                                 (uint32_t)(cnt - n1) * unit_stride, &full[s]);
+                }
                 issued = g + 1;
             }
             // never leave the CTA with copies still landing in its shared memory
             for (int g = max(0, issued - p.stages); g < issued; ++g)
                 mbar_wait_bounded(&full[g % p.stages], (g / p.stages) & 1);
+            if (aux_sent) mbar_wait_bounded(aux, 0);
         }
-    } else {
-        // ---------------- consumers ----------------
-        // build the byte -> bf16x2 table (lane-private columns) and stage x
-        {
-            const float qv = __ldg(p.qmap + (lane & 15));
-            const uint32_t qb = f32_to_bf16_bits(qv);
-            // every lane owns the table column of its own lane index: word (b*64 + lane)
-            for (int b = warp; b < 256; b += kConsumerWarps) {
-                const uint32_t hi = __shfl_sync(0xffffffffu, qb, b >> 4);
-                const uint32_t lo = __shfl_sync(0xffffffffu, qb, b & 15);
-                // low half = first weight of the byte (even k, HIGH nibble)
-                reinterpret_cast<uint32_t*>(lut)[b * 64 + lane] = hi | (lo << 16);
-            }
-            // x: element k = 64*kb + 16*j + 4*t + e  ->  fragment order
-            const int ctid = tid;  // 0..511
-            const int n4 = p.K >> 2;  // groups of 4 elements (8 bytes)
-            const uint2* xg = reinterpret_cast<const uint2*>(p.x);
-            uint2* xd = reinterpret_cast<uint2*>(xs);
-            for (int q4 = ctid; q4 < n4; q4 += kConsumerWarps * 32) {
-                const int kb = q4 >> 4, j = (q4 >> 2) & 3, t = q4 & 3;
-                xd[((kb * 2 + (j >> 1)) * 4 + t) * 2 + (j & 1)] = __ldg(xg + q4);
-            }
-            for (int i = ctid; i < kMaxLocalTiles * NP * kConsumerWarps * 16; i += kConsumerWarps * 32)
-                slots[i] = 0.0f;
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    {
+        const uint32_t qb = f32_to_bf16_bits(p.qmap_v[lane & 15]);
+        // every lane owns the table column of its own lane index
+        for (int b = warp; b < 256; b += W) {
+            const uint32_t hi = __shfl_sync(0xffffffffu, qb, b >> 4);
+            const uint32_t lo = __shfl_sync(0xffffffffu, qb, b & 15);
+            // low half = first weight of the byte (even k, HIGH nibble)
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(a_lut + (uint32_t)b * 256u + (uint32_t)lane * 4u),
+                         "r"(hi | (lo << 16))
+                         : "memory");
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-
-        const int gq = lane >> 2;  // row inside the tile (and row + 8)
-        const int t = lane & 3;
-        const uint32_t lane4 = (uint32_t)lane << 2;
-        float acc[NP][2];
+        for (int i = tid; i < kMaxLocalTiles * NP * W * 16; i += W * 32) sts_f32(a_slots + 4u * i, 0.0f);
+    }
+    // Second-level scales this CTA can need: one window of consecutive nested_absmax entries per
+    // half (gate/plain rows, up rows), copied to shared memory so the absmax chain has no global
+    // load in it. A window that does not fit is read from global memory instead.
+    unsigned win_lo[NP];
+    bool win_ok[NP];
 #pragma unroll
-        for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
-        int cur_li = -1;
-
-        long long item = i0 + warp;
-        int kb = (int)(item % p.KU);
-        int rt = (int)(item / p.KU);
-        const int kb_step = kConsumerWarps % p.KU;
-        const int rt_step = kConsumerWarps / p.KU;
-
-        for (int g = 0; g < n_groups; ++g) {
-            const int s = g % p.stages;
-            if (*(volatile int*)abort_flag) break;
-            if (!mbar_wait_bounded(&full[s], (g / p.stages) & 1)) {
-                atomicExch(p.status, kStatusTimeoutFull);
-                *(volatile int*)abort_flag = 1;
-                break;
-            }
-            if (item < i1) {
-                const int li = rt - rt_first;
-                if (li != cur_li) {
-                    if (cur_li >= 0 && t == 0) {
-#pragma unroll
-                        for (int h = 0; h < NP; ++h) {
-                            float* sl = slots + ((cur_li * NP + h) * kConsumerWarps + warp) * 16;
-                            sl[gq] = acc[h][0];
-                            sl[gq + 8] = acc[h][1];
-                        }
-                    }
-#pragma unroll
-                    for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
-                    cur_li = li;
-                }
-                const uint8_t* stage = ring + (size_t)s * stage_bytes;
-                // x fragments for batch column 0 (held by the lanes with gq == 0)
-                uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
-                if (gq == 0) {
-                    const uint4* xf = reinterpret_cast<const uint4*>(xs) + (size_t)kb * 8;
-                    xa = xf[t];
-                    xb = xf[4 + t];
-                }
-#pragma unroll
-                for (int h = 0; h < NP; ++h) {
-                    const uint8_t* ub = stage + h * (kConsumerWarps * unit_stride) + warp * unit_stride;
-                    const uint2 wl = *reinterpret_cast<const uint2*>(ub + gq * 32 + 8 * t);
-                    const uint2 wh = *reinterpret_cast<const uint2*>(ub + (gq + 8) * 32 + 8 * t);
-                    float am0, am1;
-                    const int rth = rt + h * p.pair_rt_offset;
-                    if (KIND == kAbsmaxCodes) {
-                        am0 = decode_absmax(p.sp, rth * kTileRows + gq, kb, ub[kUnitNibbleBytes + gq]);
-                        am1 = decode_absmax(p.sp, rth * kTileRows + gq + 8, kb,
-                                            ub[kUnitNibbleBytes + gq + 8]);
-                    } else {
-                        const float* af = reinterpret_cast<const float*>(ub + kUnitNibbleBytes);
-                        am0 = af[gq];
-                        am1 = af[gq + 8];
-                    }
-                    float cfrag[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    // j = 0: bytes 0,1 of wl.x / wh.x ; j = 1: bytes 2,3 ; j = 2,3: .y
-                    mma_bf16_16816(cfrag, lut_pair<0>(wl.x, lane4), lut_pair<0>(wh.x, lane4),
-                                   lut_pair<1>(wl.x, lane4), lut_pair<1>(wh.x, lane4), xa.x, xa.y);
-                    mma_bf16_16816(cfrag, lut_pair<2>(wl.x, lane4), lut_pair<2>(wh.x, lane4),
-                                   lut_pair<3>(wl.x, lane4), lut_pair<3>(wh.x, lane4), xa.z, xa.w);
-                    mma_bf16_16816(cfrag, lut_pair<0>(wl.y, lane4), lut_pair<0>(wh.y, lane4),
-                                   lut_pair<1>(wl.y, lane4), lut_pair<1>(wh.y, lane4), xb.x, xb.y);
-                    mma_bf16_16816(cfrag, lut_pair<2>(wl.y, lane4), lut_pair<2>(wh.y, lane4),
-                                   lut_pair<3>(wl.y, lane4), lut_pair<3>(wh.y, lane4), xb.z, xb.w);
-                    acc[h][0] = fmaf(am0, cfrag[0], acc[h][0]);
-                    acc[h][1] = fmaf(am1, cfrag[2], acc[h][1]);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            item += kConsumerWarps;
-            kb += kb_step;
-            rt += rt_step;
-            if (kb >= p.KU) {
-                kb -= p.KU;
-                rt += 1;
-            }
-        }
-        if (cur_li >= 0 && t == 0) {
-#pragma unroll
-            for (int h = 0; h < NP; ++h) {
-                float* sl = slots + ((cur_li * NP + h) * kConsumerWarps + warp) * 16;
-                sl[gq] = acc[h][0];
-                sl[gq + 8] = acc[h][1];
-            }
+    for (int h = 0; h < NP; ++h) {
+        win_lo[h] = 0;
+        win_ok[h] = false;
+        if (KIND == kAbsmaxCodes) {
+            const int n_a = min((rt_first + h * p.pair_rt_offset) * kTileRows, p.n_rows - 1);
+            const int n_b = min((rt_last + h * p.pair_rt_offset) * kTileRows + kTileRows - 1, p.n_rows - 1);
+            const int sa = segment_of(p.sp, n_a), sb = segment_of(p.sp, n_b);
+            const unsigned f_lo = p.sp.flat0[sa] + (unsigned)(n_a - p.sp.row0[sa]) * p.sp.row_stride[sa];
+            const unsigned f_hi = p.sp.flat0[sb] + (unsigned)(n_b - p.sp.row0[sb]) * p.sp.row_stride[sb] +
+                                  ((unsigned)(p.KU - 1) >> p.sp.blk_shift);
+            win_lo[h] = f_lo >> p.sp.nbs_shift;
+            const unsigned cnt = (f_hi >> p.sp.nbs_shift) - win_lo[h] + 1;
+            win_ok[h] = cnt <= (unsigned)kNabsWindow;
+            if (win_ok[h])
+                for (unsigned i = tid; i < cnt; i += W * 32)
+                    sts_f32(a_nabsw + (uint32_t)(h * kNabsWindow + i) * 4u, __ldg(p.sp.nabs + win_lo[h] + i));
         }
     }
-    __syncthreads();
-    if (*(volatile int*)abort_flag) return;
+    asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
 
-    // ---------------- finish: one 16-lane half-warp per local row tile ----------------
-    if (warp < kMaxLocalTiles / 2) {
-        const int li = warp * 2 + (lane >> 4);
+    const int gq = lane >> 2;  // row inside the tile (and row + 8)
+    const int t = lane & 3;
+    const uint32_t lane_base = a_lut + ((uint32_t)lane << 2);
+    const uint32_t w_off = (uint32_t)(gq * 32 + 8 * t);  // this lane's 8 bytes inside a unit
+    // absmax decode: lane (half, r) owns row r of the gate/plain unit (half 0) or of the up
+    // unit (half 1); its flat block index base follows the row tile
+    const int dhalf = PAIRED ? (lane >> 4) : 0;
+    const int drow = lane & 15;
+    const uint32_t code_off = (uint32_t)(dhalf * half_bytes + kUnitNibbleBytes + drow);
+    const bool my_win_ok = win_ok[PAIRED ? dhalf : 0];
+    const unsigned my_win_lo = win_lo[PAIRED ? dhalf : 0];
+    const uint32_t my_win = a_nabsw + (uint32_t)((PAIRED ? dhalf : 0) * kNabsWindow) * 4u;
+
+    float acc[NP][2];
+#pragma unroll
+    for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
+    int cur_li = -1;
+    unsigned done_mask = 0;  // local tiles this warp has signed off
+
+    // ---- completing a row tile: the warp that signs off last sums the per-warp slots ----
+    auto finalize_tile = [&](int li) {
         const int r = lane & 15;
-        const bool active = li < n_local;
         const int rtile = rt_first + li;
         float v[NP];
 #pragma unroll
-        for (int h = 0; h < NP; ++h) v[h] = 0.0f;
-        bool is_full = false;
-        if (active) {
+        for (int h = 0; h < NP; ++h) {
+            const uint32_t sl = a_slots + (uint32_t)(((li * NP + h) * W) * 16 + r) * 4u;
+            float sacc = 0.0f;
 #pragma unroll
-            for (int h = 0; h < NP; ++h) {
-                const float* sl = slots + ((li * NP + h) * kConsumerWarps) * 16 + r;
-                float sacc = 0.0f;
-#pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w) sacc += sl[w * 16];
-                v[h] = sacc;
-            }
-            const long long t0 = (long long)rtile * p.KU, t1 = t0 + p.KU;
-            is_full = (i0 <= t0) && (i1 >= t1);
+            for (int w = 0; w < W; ++w) sacc += lds_f32(sl + w * 64);
+            v[h] = sacc;
         }
-        const bool is_partial = active && !is_full;
-        bool finalize = active && is_full;
-        int c_lo = 0, c_hi = 0;
-        if (is_partial) {
+        const long long t0 = (long long)rtile * p.KU, t1 = t0 + p.KU;
+        const bool is_full = (i0 <= t0) && (i1 >= t1);
+        bool write = is_full;
+        if (!is_full) {
+            // shared with neighbouring CTAs: publish, count, and let the last arriver sum all
+            // contributions in CTA order (deterministic, nobody waits)
             const int hslot = (li == 0) ? 0 : 1;
-#pragma unroll
-            for (int h = 0; h < NP; ++h)
-                p.partials[(((size_t)c * 2 + hslot) * NP + h) * 16 + r] = v[h];
-            __threadfence();
-        }
-        __syncwarp();
-        int old = 0;
-        if (is_partial) {
-            const long long t0 = (long long)rtile * p.KU, t1 = t0 + p.KU;
-            c_lo = (int)(((t0 + 1) * G - 1) / p.total_items);
-            c_hi = (int)((t1 * G - 1) / p.total_items);
-            if (r == 0) old = atomicAdd(p.counters + rtile, 1);
-        }
-        old = __shfl_sync(0xffffffffu, old, lane & 16);
-        if (is_partial && old == (c_hi - c_lo)) {
-            // last arriver: sum every contributor's partial in CTA order
-            __threadfence();
-#pragma unroll
-            for (int h = 0; h < NP; ++h) v[h] = 0.0f;
-            for (int cc = c_lo; cc <= c_hi; ++cc) {
-                const int cc_first = (int)(slice_begin(p.total_items, cc, G) / p.KU);
-                const int hslot = (rtile == cc_first) ? 0 : 1;
+            if (lane < 16) {
 #pragma unroll
                 for (int h = 0; h < NP; ++h)
-                    v[h] += __ldcg(p.partials + (((size_t)cc * 2 + hslot) * NP + h) * 16 + r);
+                    p.partials[(((size_t)c * 2 + hslot) * NP + h) * 16 + r] = v[h];
             }
-            if (r == 0) p.counters[rtile] = 0;
-            finalize = true;
+            __threadfence();
+            __syncwarp();
+            const int c_lo = (int)(((t0 + 1) * G - 1) / p.total_items);
+            const int c_hi = (int)((t1 * G - 1) / p.total_items);
+            int old = 0;
+            if (lane == 0) old = atomicAdd(p.counters + rtile, 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == c_hi - c_lo) {
+                __threadfence();
+#pragma unroll
+                for (int h = 0; h < NP; ++h) v[h] = 0.0f;
+                for (int cc = c_lo; cc <= c_hi; ++cc) {
+                    const int cc_first = (int)(slice_begin(p.total_items, cc, G) / p.KU);
+                    const int hs = (rtile == cc_first) ? 0 : 1;
+#pragma unroll
+                    for (int h = 0; h < NP; ++h)
+                        v[h] += __ldcg(p.partials + (((size_t)cc * 2 + hs) * NP + h) * 16 + r);
+                }
+                if (lane == 0) p.counters[rtile] = 0;
+                write = true;
+            }
         }
-        if (finalize) {
+        if (write && lane < 16) {
             const int n = rtile * kTileRows + r;
             if (n < p.n_out) {
                 float o;
@@ -401,13 +442,203 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 p.y[n] = f32_to_bf16_bits(o);
             }
         }
+    };
+    // every warp signs off every local tile exactly once, after its last contribution to it
+    auto sign_off = [&](int li) {
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) {
+            __threadfence_block();
+            old = atomicAdd(&tile_done[li], 1);
+        }
+        old = __shfl_sync(0xffffffffu, old, 0);
+        done_mask |= 1u << li;
+        if (old == W - 1) {
+            __threadfence_block();
+            finalize_tile(li);
+        }
+    };
+    auto flush_current = [&]() {
+        if (cur_li >= 0) {
+            if (t == 0) {
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    const uint32_t sl = a_slots + (uint32_t)(((cur_li * NP + h) * W + warp) * 16) * 4u;
+                    sts_f32(sl + 4u * gq, acc[h][0]);
+                    sts_f32(sl + 4u * (gq + 8), acc[h][1]);
+                }
+            }
+            sign_off(cur_li);
+        }
+#pragma unroll
+        for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
+    };
+
+    // position of this warp's first item of the current group; its IPW items are consecutive
+    int v = warp * IPW;
+    int kb = 0, rt = rt_first;
+    unsigned d_flat = 0;
+    float d_off = 0.0f;
+    auto locate = [&](int vv) {  // (kb, rt) of virtual position vv
+        const long long it = vv < tail_len ? tail0 + vv : i0 + (vv - tail_len);
+        kb = (int)(it % p.KU);
+        rt = (int)(it / p.KU);
+    };
+    auto refresh = [&]() {  // absmax row base of this lane for row tile rt
+        if (KIND == kAbsmaxCodes) {
+            // rows past the end of the linear (padding of the last tile) borrow the last row's scale
+            const int n = min((rt + dhalf * p.pair_rt_offset) * kTileRows + drow, p.n_rows - 1);
+            const int sg = segment_of(p.sp, n);
+            d_flat = p.sp.flat0[sg] + (unsigned)(n - p.sp.row0[sg]) * p.sp.row_stride[sg];
+            d_off = p.sp.offset[sg];
+        }
+    };
+    if (v < len) {
+        locate(v);
+        refresh();
     }
+    const int kb_step = (kStageItems - IPW) % p.KU;  // from a run's last item + 1 to the next run
+    const int rt_step = (kStageItems - IPW) / p.KU;
+
+    // x (and the second-level code book) must have landed before the first product
+    if (!mbar_wait_bounded(aux, 0)) {
+        atomicExch(p.status, kStatusTimeoutFull);
+        *(volatile int*)abort_flag = 1;
+        return;
+    }
+
+    bool failed = false;
+    for (int g = 0; g < n_groups; ++g) {
+        const int s = g % p.stages;
+        if (!mbar_wait_bounded(&full[s], (g / p.stages) & 1)) {
+            atomicExch(p.status, kStatusTimeoutFull);
+            *(volatile int*)abort_flag = 1;
+            failed = true;
+            break;
+        }
+        uint32_t ua = a_ring + (uint32_t)s * stage_bytes + (uint32_t)(warp * IPW) * unit_stride;
+        const int nvalid = min(IPW, len - v);
+#pragma unroll
+        for (int i = 0; i < IPW; ++i) {
+            if (i < nvalid) {
+                // ---- one work item: unit (rt, kb) [and its up partner] ----
+                const uint32_t xa = a_xs + (uint32_t)kb * 128u + 8u * t;
+                uint2 xf[4];
+                // x fragments (batch column 0) live in the four lanes with gq == 0; the other
+                // columns of the 8-wide tile stay zero. 8 bytes per tile: x[64kb + 16j + 4t ..]
+#pragma unroll
+                for (int j = 0; j < 4; ++j) xf[j] = lds_v2_if_zero(xa + 32u * j, gq);
+                float am0[NP], am1[NP];
+                if (KIND == kAbsmaxCodes) {
+                    const unsigned code = lds_u8(ua + code_off);
+                    const unsigned flat = d_flat + ((unsigned)kb >> p.sp.blk_shift);
+                    const unsigned sidx = flat >> p.sp.nbs_shift;
+                    const float scale = my_win_ok ? lds_f32(my_win + (sidx - my_win_lo) * 4u)
+                                                  : __ldg(p.sp.nabs + sidx);
+                    const float am = __fadd_rn(__fmul_rn(lds_f32(a_nmap + 4u * code), scale), d_off);
+#pragma unroll
+                    for (int h = 0; h < NP; ++h) {
+                        am0[h] = __shfl_sync(0xffffffffu, am, h * 16 + gq);
+                        am1[h] = __shfl_sync(0xffffffffu, am, h * 16 + gq + 8);
+                    }
+                } else {
+#pragma unroll
+                    for (int h = 0; h < NP; ++h) {
+                        am0[h] = lds_f32(ua + h * half_bytes + kUnitNibbleBytes + 4u * gq);
+                        am1[h] = lds_f32(ua + h * half_bytes + kUnitNibbleBytes + 4u * (gq + 8));
+                    }
+                }
+                float c0[NP][4], c1[NP][4];
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    const uint2 l = lds_v2(ua + h * half_bytes + w_off);
+                    const uint2 u = lds_v2(ua + h * half_bytes + w_off + 256u);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) c0[h][e] = c1[h][e] = 0.0f;
+                    // all 16 table lookups first (independent loads), then the four tiles:
+                    // j = 0: bytes 0,1 of .x ; j = 1: bytes 2,3 of .x ; j = 2,3: .y
+                    uint32_t a[16];
+                    a[0] = lut_pair<0>(l.x, lane_base);  a[1] = lut_pair<0>(u.x, lane_base);
+                    a[2] = lut_pair<1>(l.x, lane_base);  a[3] = lut_pair<1>(u.x, lane_base);
+                    a[4] = lut_pair<2>(l.x, lane_base);  a[5] = lut_pair<2>(u.x, lane_base);
+                    a[6] = lut_pair<3>(l.x, lane_base);  a[7] = lut_pair<3>(u.x, lane_base);
+                    a[8] = lut_pair<0>(l.y, lane_base);  a[9] = lut_pair<0>(u.y, lane_base);
+                    a[10] = lut_pair<1>(l.y, lane_base); a[11] = lut_pair<1>(u.y, lane_base);
+                    a[12] = lut_pair<2>(l.y, lane_base); a[13] = lut_pair<2>(u.y, lane_base);
+                    a[14] = lut_pair<3>(l.y, lane_base); a[15] = lut_pair<3>(u.y, lane_base);
+                    mma_bf16_16816(c0[h], a[0], a[1], a[2], a[3], xf[0].x, xf[0].y);
+                    mma_bf16_16816(c1[h], a[4], a[5], a[6], a[7], xf[1].x, xf[1].y);
+                    mma_bf16_16816(c0[h], a[8], a[9], a[10], a[11], xf[2].x, xf[2].y);
+                    mma_bf16_16816(c1[h], a[12], a[13], a[14], a[15], xf[3].x, xf[3].y);
+                }
+                // ---- accumulate into the current row tile (switching tiles is rare) ----
+                const int li = rt - rt_first;
+                if (li != cur_li) {
+                    flush_current();
+                    if (v + i >= tail_len) {
+                        // the front part runs through the tiles in order and never returns to
+                        // the slice's last tile: sign off what this warp will not touch again
+                        for (int q = 0; q < li; ++q)
+                            if (!((done_mask >> q) & 1u)) sign_off(q);
+                        if (!((done_mask >> (n_local - 1)) & 1u)) sign_off(n_local - 1);
+                    }
+                    cur_li = li;
+                }
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    acc[h][0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][0]);
+                    acc[h][1] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][1]);
+                }
+                // ---- next item of the run ----
+                ua += unit_stride;
+                if (v + i + 1 == tail_len) {
+                    if (v + i + 1 < len) {
+                        locate(v + i + 1);  // wrapped from the tail tile to the front of the slice
+                        refresh();
+                    }
+                } else if (++kb == p.KU) {
+                    kb = 0;
+                    ++rt;
+                    refresh();
+                }
+            }
+        }
+        // the stage's shared memory is no longer needed by this warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+        // ---- first item of this warp's run in the next group ----
+        // (kb, rt) now describe position v + nvalid of the traversal
+        const int vend = v + nvalid;
+        v += kStageItems;
+        if (v < len) {
+            if (nvalid == IPW && !(vend < tail_len && v >= tail_len)) {
+                const int rt_old = rt;
+                kb += kb_step;
+                rt += rt_step;
+                if (kb >= p.KU) {
+                    kb -= p.KU;
+                    ++rt;
+                }
+                if (rt != rt_old) refresh();
+            } else {
+                locate(v);
+                refresh();
+            }
+        }
+    }
+    if (failed) return;
+    // last contribution of this warp, then sign off whatever it never touched
+    flush_current();
+    cur_li = -1;
+    for (int q = 0; q < n_local; ++q)
+        if (!((done_mask >> q) & 1u)) sign_off(q);
 }
 
 struct StreamPlan {
     int grid = 0;
     int stages = 0;
     int smem = 0;
+    int x_in_b = 0;
     bool ok = false;
 };
 
@@ -417,15 +648,19 @@ struct StreamPlan {
 StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int sm_count) {
     StreamPlan pl;
     const int np = paired ? 2 : 1;
-    const int stage_bytes = kConsumerWarps * w.unit_stride * np;
+    const int stage_bytes = kStageItems * w.unit_stride * np;
     const int x_bytes = (int)((w.K * 2 + 15) / 16 * 16);
-    const int fixed = kLutBytes + x_bytes + kMaxLocalTiles * np * kConsumerWarps * 16 * 4 +
-                      2 * kMaxStages * 8 + 16;
-    const int budget = 227 * 1024 - fixed;
-    if (budget < 3 * stage_bytes) return pl;
-    pl.stages = budget / stage_bytes;
+    // region A (below the table, which sits at shared address 64 KB): barriers, counters, code
+    // book, slots and x if it fits; region B (from 128 KB): x otherwise, then the ring
+    const int a_used = 2048 + 16 + 400 + 64 + 1024 + 2 * kNabsWindow * 4 +
+                       kMaxLocalTiles * np * kConsumerWarps * 64;
+    pl.x_in_b = (a_used + x_bytes > 65536) ? 1 : 0;
+    const int b_capacity = 227 * 1024 - 131072;
+    const int ring_budget = b_capacity - (pl.x_in_b ? x_bytes : 0);
+    if (ring_budget < 2 * stage_bytes) return pl;
+    pl.stages = ring_budget / stage_bytes;
     if (pl.stages > kMaxStages) pl.stages = kMaxStages;
-    pl.smem = fixed + pl.stages * stage_bytes;
+    pl.smem = 131072 + (pl.x_in_b ? x_bytes : 0) + pl.stages * stage_bytes;
     const long long rt_work = paired ? ff_pair / kTileRows : w.RT;
     const long long total = rt_work * w.KU;
     if (total <= 0 || sm_count <= 0) return pl;
@@ -455,8 +690,24 @@ cudaError_t launch_stream_t(const StreamParams& p, int grid, int smem, cudaStrea
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    gemv_stream_kernel<KIND, PAIRED><<<grid, kStreamThreads, smem, s>>>(p);
-    return cudaGetLastError();
+    // Programmatic dependent launch: the next kernel on the stream may start its set-up (table
+    // build, first weight copies) while this one drains; it waits for our completion before it
+    // reads x. Disabled with AILA_NF4_PDL=0.
+    static const bool use_pdl = [] {
+        const char* e = std::getenv("AILA_NF4_PDL");
+        return !(e && e[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kStreamThreads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<KIND, PAIRED>, p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -520,7 +771,7 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     if (!pl.ok) return cudaErrorInvalidConfiguration;
     StreamParams p;
     p.units = w.d_units;
-    p.qmap = w.d_qmap;
+    for (int i = 0; i < 16; ++i) p.qmap_v[i] = w.h_qmap[i];
     p.sp = w.scale_params();
     p.x = static_cast<const uint16_t*>(x);
     p.y = static_cast<uint16_t*>(y);
@@ -537,6 +788,9 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.pair_rt_offset = paired ? (int)(ff_pair / kTileRows) : 0;
     p.x_bytes = (int)((w.K * 2 + 15) / 16 * 16);
     p.stages = pl.stages;
+    p.x_in_b = pl.x_in_b;
+    p.smem_bytes = pl.smem;
+    p.n_rows = (int)w.N;
     if (w.absmax_kind == kAbsmaxCodes)
         return paired ? launch_stream_t<kAbsmaxCodes, true>(p, pl.grid, pl.smem, s)
                       : launch_stream_t<kAbsmaxCodes, false>(p, pl.grid, pl.smem, s);

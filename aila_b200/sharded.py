@@ -1,0 +1,172 @@
+"""Multi-GPU layer for the NF4 linears: one process per GPU, torch.distributed for the exchange.
+
+Net-new relative to the reference (single device, no collectives). A weight shards naturally:
+  * rows (out_features)  -> column-parallel linear, no exchange inside the op: q/k/v, gate, up;
+  * columns (in_features) -> row-parallel linear, exactly one sum exchange: o_proj, down.
+The MLP is chained Megatron-style: gate|up row-sharded with the SwiGLU kept local (each rank
+holds gate_r and up_r), down column-sharded on the same ranks, so the only collective per MLP is
+one all-reduce of the [M, hidden] partial sums.
+
+Shards are cut from the whole-weight descriptor by ``aila_nf4_linear_create_shard`` and keep the
+original second-level absmax numbering, so their dequantised values are bit-equal to the same
+slice of the unsharded weight.
+
+The compute object is injectable so that the host logic (slicing rules, collectives, result
+assembly) can be exercised on CPU ranks with the gloo backend; the default is the CUDA library
+and it has no fallback.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .synth import Nf4Tensors
+
+ROWS, COLS = _lib.SHARD_ROWS, _lib.SHARD_COLS
+
+
+def check_shardable(w: Nf4Tensors, mode: int, world: int) -> None:
+    """The divisibility rules of aila_nf4_linear_create_shard, raised early on the host."""
+    if world <= 0:
+        raise ValueError("world must be positive")
+    if mode == ROWS:
+        if w.out_features % world:
+            raise ValueError(f"out_features {w.out_features} is not divisible by {world} shards")
+    elif mode == COLS:
+        if w.in_features % world or (w.in_features // world) % w.blocksize:
+            raise ValueError(f"in_features {w.in_features} / {world} shards must be a multiple of "
+                             f"blocksize {w.blocksize}")
+    else:
+        raise ValueError("unknown shard mode")
+
+
+def shard_bounds(w: Nf4Tensors, mode: int, rank: int, world: int) -> tuple[int, int, int, int]:
+    """(row0, rows, col0, cols) kept by ``rank``."""
+    check_shardable(w, mode, world)
+    if not 0 <= rank < world:
+        raise ValueError("rank out of range")
+    if mode == ROWS:
+        rows = w.out_features // world
+        return rank * rows, rows, 0, w.in_features
+    cols = w.in_features // world
+    return 0, w.out_features, rank * cols, cols
+
+
+class CudaBackend:
+    """Compute through libaila_nf4.so on this rank's GPU."""
+
+    def __init__(self, device: int):
+        from .linear import Bnb4BitLinear, Bnb4BitLinearScratch
+        self._L = Bnb4BitLinear
+        self.device = device
+        self.scratch = Bnb4BitLinearScratch(device)
+
+    def make_shard(self, w: Nf4Tensors, mode: int, rank: int, world: int):
+        lin = self._L()
+        if not lin.init_shard(w, mode, rank, world, self.device):
+            raise RuntimeError(lin.last_error)
+        return lin
+
+    def fuse(self, *handles):
+        f = self._L()
+        if not f.init_fused_rows(*handles):
+            raise RuntimeError(f.last_error)
+        return f
+
+    def empty(self, *shape, dtype=torch.bfloat16):
+        return torch.empty(*shape, dtype=dtype, device=torch.device("cuda", self.device))
+
+    def forward(self, handle, x: torch.Tensor, out: torch.Tensor, seq_len: int) -> None:
+        handle.forward(self.scratch, x, out, seq_len)
+
+    def gate_up_swiglu(self, handle, x: torch.Tensor, out: torch.Tensor, seq_len: int,
+                       ff: int) -> bool:
+        return self._L.try_forward_decode_gate_up_swiglu(handle, self.scratch, x, out, ff,
+                                                         seq_len=seq_len)
+
+
+def _group_info(group):
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+class ColumnParallelNf4Linear:
+    """y[:, rank's rows] = x W_r^T; optional all-gather of the row slices."""
+
+    def __init__(self, w: Nf4Tensors, backend, group=None):
+        self.rank, self.world = _group_info(group)
+        self.group, self.backend = group, backend
+        self.out_features, self.in_features = w.out_features, w.in_features
+        self.local_out = w.out_features // self.world
+        self.handle = backend.make_shard(w, ROWS, self.rank, self.world)
+
+    def forward(self, x: torch.Tensor, gather: bool = False) -> torch.Tensor:
+        m = x.shape[0]
+        y = self.backend.empty(m, self.local_out)
+        self.backend.forward(self.handle, x, y, m)
+        if not gather:
+            return y
+        parts = [torch.empty_like(y) for _ in range(self.world)]
+        dist.all_gather(parts, y, group=self.group)
+        return torch.cat(parts, dim=1)
+
+
+class RowParallelNf4Linear:
+    """y = sum_r x[:, rank's columns] W_r^T with one all-reduce (fp32 for small M)."""
+
+    def __init__(self, w: Nf4Tensors, backend, group=None):
+        self.rank, self.world = _group_info(group)
+        self.group, self.backend = group, backend
+        self.out_features, self.in_features = w.out_features, w.in_features
+        self.local_in = w.in_features // self.world
+        self.handle = backend.make_shard(w, COLS, self.rank, self.world)
+
+    def forward(self, x_local: torch.Tensor, fp32_reduce: bool | None = None) -> torch.Tensor:
+        """x_local: this rank's column slice [M, in/world]."""
+        m = x_local.shape[0]
+        part = self.backend.empty(m, self.out_features)
+        self.backend.forward(self.handle, x_local, part, m)
+        return reduce_partials(part, self.group, m <= 64 if fp32_reduce is None else fp32_reduce)
+
+
+def reduce_partials(part: torch.Tensor, group, fp32: bool) -> torch.Tensor:
+    """Sum of the ranks' partial outputs. fp32 exchange for decode-sized messages (tens of KB,
+    latency-bound either way), bf16 for prefill-sized ones (halves the NVLink bytes)."""
+    if dist.get_world_size(group) == 1:
+        return part
+    if fp32:
+        acc = part.float()
+        dist.all_reduce(acc, group=group)
+        return acc.to(torch.bfloat16)
+    dist.all_reduce(part, group=group)
+    return part
+
+
+class ShardedNf4Mlp:
+    """SwiGLU MLP: gate|up row-sharded (SwiGLU local) -> down column-sharded -> one all-reduce."""
+
+    def __init__(self, gate: Nf4Tensors, up: Nf4Tensors, down: Nf4Tensors, backend, group=None):
+        self.rank, self.world = _group_info(group)
+        self.group, self.backend = group, backend
+        if gate.out_features != up.out_features or gate.in_features != up.in_features:
+            raise ValueError("gate and up must have the same shape")
+        if down.in_features != gate.out_features or down.out_features != gate.in_features:
+            raise ValueError("down must map ff back to hidden")
+        check_shardable(gate, ROWS, self.world)
+        check_shardable(down, COLS, self.world)
+        self.hidden, self.ff = gate.in_features, gate.out_features
+        self.local_ff = self.ff // self.world
+        g = backend.make_shard(gate, ROWS, self.rank, self.world)
+        u = backend.make_shard(up, ROWS, self.rank, self.world)
+        self.gate_up = backend.fuse(g, u)  # gate_r rows then up_r rows: SwiGLU stays local
+        self.down = backend.make_shard(down, COLS, self.rank, self.world)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        m = x.shape[0]
+        mid = self.backend.empty(m, self.local_ff)
+        if not self.backend.gate_up_swiglu(self.gate_up, x, mid, m, self.local_ff):
+            raise RuntimeError("fused gate+up+SiLU path not applicable to this shard "
+                               "(ff / world must be a multiple of 16)")
+        part = self.backend.empty(m, self.hidden)
+        self.backend.forward(self.down, mid, part, m)
+        return reduce_partials(part, self.group, m <= 64)
