@@ -660,8 +660,8 @@ AILA_NF4_API AilaNf4Status aila_nf4_dequantize(const AilaNf4Linear* l, void* out
 AILA_NF4_API AilaNf4Status aila_nf4_dequantize_rowmajor(const AilaNf4Linear* l, void* out_nk,
                                                         void* stream) {
     if (!l || !out_nk) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
-    if (reinterpret_cast<uintptr_t>(out_nk) & 7)
-        return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "output must be 8-byte aligned");
+    if (reinterpret_cast<uintptr_t>(out_nk) & 15)
+        return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "output must be 16-byte aligned");
     DeviceGuard guard(l->device);
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     NF4_CUDA(nf4::launch_dequant_nk(*l, out_nk, static_cast<cudaStream_t>(stream)));

@@ -57,22 +57,39 @@ struct ScaleParams {
     float offset[kMaxSegments];
 };
 
-__device__ __forceinline__ int segment_of(const ScaleParams& sp, int n) {
-    int s = 0;
+// Constants of the segment that owns row n, selected with static indices only (no dynamically
+// indexed copy of the parameter block in local memory).
+struct SegmentRow {
+    unsigned flat;  // flat index of the row's first block (second-level numbering base included)
+    float offset;
+};
+
+__device__ __forceinline__ SegmentRow segment_row(const ScaleParams& sp, int n) {
+    int row0 = sp.row0[0];
+    unsigned flat0 = sp.flat0[0], stride = sp.row_stride[0];
+    float off = sp.offset[0];
 #pragma unroll
-    for (int i = 1; i < kMaxSegments; ++i)
-        if (i < sp.nseg && n >= sp.row0[i]) s = i;
-    return s;
+    for (int i = 1; i < kMaxSegments; ++i) {
+        if (i < sp.nseg && n >= sp.row0[i]) {
+            row0 = sp.row0[i];
+            flat0 = sp.flat0[i];
+            stride = sp.row_stride[i];
+            off = sp.offset[i];
+        }
+    }
+    SegmentRow r;
+    r.flat = flat0 + (unsigned)(n - row0) * stride;
+    r.offset = off;
+    return r;
 }
 
 // fp32 absmax of (row n, unit column kb) from its 8-bit code: two separately rounded fp32
 // operations, never a fused multiply-add (Bnb4BitLinear.cpp:485-487 writes mul then add).
 __device__ __forceinline__ float decode_absmax(const ScaleParams& sp, int n, int kb, unsigned code) {
-    const int s = segment_of(sp, n);
-    const unsigned flat = sp.flat0[s] + (unsigned)(n - sp.row0[s]) * sp.row_stride[s] +
-                          ((unsigned)kb >> sp.blk_shift);
+    const SegmentRow sr = segment_row(sp, n);
+    const unsigned flat = sr.flat + ((unsigned)kb >> sp.blk_shift);
     const float scale = __ldg(sp.nabs + (flat >> sp.nbs_shift));
-    return __fadd_rn(__fmul_rn(__ldg(sp.nmap + code), scale), sp.offset[s]);
+    return __fadd_rn(__fmul_rn(__ldg(sp.nmap + code), scale), sr.offset);
 }
 
 // Source byte offset (0..31) inside a row's 32-byte segment for stored byte p.

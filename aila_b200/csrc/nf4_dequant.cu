@@ -53,8 +53,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
 }
 
-// One thread per (unit, row, 8-byte chunk t): 16 weights -> four 8-byte stores at
-// k = 16*j + 4*t. The four lanes of a row write one full 32-byte sector per j.
+// One thread per (unit, row): reads the row's 32 stored bytes (two 16-byte loads; a warp reads
+// two whole units, 1 KB contiguous), undoes the intra-row permutation in registers and writes the
+// 64 bf16 weights of the block as one contiguous 128-byte run W[n][64kb .. 64kb+64).
 __global__ void __launch_bounds__(256)
 dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ qmap,
                   ScaleParams sp, uint16_t* __restrict__ out, int N, long long K, int KU,
@@ -63,27 +64,34 @@ dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ q
     if (threadIdx.x < 16) q[threadIdx.x] = qmap[threadIdx.x];
     __syncthreads();
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long u = tid >> 6;
+    const long long u = tid >> 4;
     if (u >= total_units) return;
-    const int r = (int)((tid >> 2) & 15);
-    const int t = (int)(tid & 3);
+    const int r = (int)(tid & 15);
     const int kb = (int)(u % KU);
     const int rt = (int)(u / KU);
     const int n = rt * kTileRows + r;
     if (n >= N) return;
     const uint8_t* unit = units + (size_t)u * unit_stride;
+    const uint4 lo = *reinterpret_cast<const uint4*>(unit + r * 32);
+    const uint4 hi = *reinterpret_cast<const uint4*>(unit + r * 32 + 16);
     const float am = unit_absmax(unit, absmax_kind, sp, n, kb, r);
-    const uint2 v = *reinterpret_cast<const uint2*>(unit + r * 32 + 8 * t);
-    uint16_t* orow = out + (size_t)n * K + (size_t)kb * kUnitK + 4 * t;
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    uint32_t o[32];  // 64 bf16, natural k order
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t two = ((j < 2 ? v.x : v.y) >> (16 * (j & 1))) & 0xffff;
-        const uint32_t b0 = two & 0xff, b1 = two >> 8;
-        uint2 o;
-        o.x = pack_bf16x2(__fmul_rn(q[b0 >> 4], am), __fmul_rn(q[b0 & 15], am));
-        o.y = pack_bf16x2(__fmul_rn(q[b1 >> 4], am), __fmul_rn(q[b1 & 15], am));
-        *reinterpret_cast<uint2*>(orow + 16 * j) = o;
-    }
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int p = 8 * t + 2 * j + e;               // stored byte
+                const uint32_t b = (w[p >> 2] >> (8 * (p & 3))) & 0xffu;
+                // byte covers k = 16j + 4t + 2e (high nibble) and + 1 (low nibble)
+                o[(16 * j + 4 * t + 2 * e) >> 1] =
+                    pack_bf16x2(__fmul_rn(q[b >> 4], am), __fmul_rn(q[b & 15], am));
+            }
+    uint4* orow = reinterpret_cast<uint4*>(out + (size_t)n * K + (size_t)kb * kUnitK);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) orow[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
 }
 
 __global__ void expand_absmax_kernel(const uint8_t* __restrict__ units, ScaleParams sp,
@@ -125,7 +133,7 @@ cudaError_t launch_dequant_kn(const AilaNf4Linear& w, void* out_kn, cudaStream_t
 cudaError_t launch_dequant_nk(const AilaNf4Linear& w, void* out_nk, cudaStream_t s) {
     const long long units = (long long)w.RT * w.KU;
     if (units == 0) return cudaSuccess;
-    const long long threads = units * 64;
+    const long long threads = units * 16;
     const long long blocks = (threads + 255) / 256;
     dequant_nk_kernel<<<(unsigned)blocks, 256, 0, s>>>(w.d_units, w.d_qmap, w.scale_params(),
                                                       static_cast<uint16_t*>(out_nk), (int)w.N,

@@ -348,10 +348,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         if (KIND == kAbsmaxCodes) {
             const int n_a = min((rt_first + h * p.pair_rt_offset) * kTileRows, p.n_rows - 1);
             const int n_b = min((rt_last + h * p.pair_rt_offset) * kTileRows + kTileRows - 1, p.n_rows - 1);
-            const int sa = segment_of(p.sp, n_a), sb = segment_of(p.sp, n_b);
-            const unsigned f_lo = p.sp.flat0[sa] + (unsigned)(n_a - p.sp.row0[sa]) * p.sp.row_stride[sa];
-            const unsigned f_hi = p.sp.flat0[sb] + (unsigned)(n_b - p.sp.row0[sb]) * p.sp.row_stride[sb] +
-                                  ((unsigned)(p.KU - 1) >> p.sp.blk_shift);
+            const unsigned f_lo = segment_row(p.sp, n_a).flat;
+            const unsigned f_hi = segment_row(p.sp, n_b).flat + ((unsigned)(p.KU - 1) >> p.sp.blk_shift);
             win_lo[h] = f_lo >> p.sp.nbs_shift;
             const unsigned cnt = (f_hi >> p.sp.nbs_shift) - win_lo[h] + 1;
             win_ok[h] = cnt <= (unsigned)kNabsWindow;
@@ -488,9 +486,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         if (KIND == kAbsmaxCodes) {
             // rows past the end of the linear (padding of the last tile) borrow the last row's scale
             const int n = min((rt + dhalf * p.pair_rt_offset) * kTileRows + drow, p.n_rows - 1);
-            const int sg = segment_of(p.sp, n);
-            d_flat = p.sp.flat0[sg] + (unsigned)(n - p.sp.row0[sg]) * p.sp.row_stride[sg];
-            d_off = p.sp.offset[sg];
+            const SegmentRow sr = segment_row(p.sp, n);
+            d_flat = sr.flat;
+            d_off = sr.offset;
         }
     };
     if (v < len) {
