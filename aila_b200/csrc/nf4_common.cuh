@@ -155,19 +155,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Returns false after the cycle limit; the caller records a status and stops using the pipe.
+// A waiting thread backs off with nanosleep so that it does not take issue slots from the warps
+// of its scheduler that have work.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 64; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(100);
+        }
         if (clock64() - t0 > kSpinLimitCycles) return false;
     }
 }
 
 // Untiled bulk-async copy global -> shared of `bytes` (multiple of 16, both sides 16-byte
-// aligned), completion counted on `bar`. No cluster multicast anywhere in this library.
+// aligned), completion counted on `bar`. Every CTA fetches its own copy.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
                                          uint64_t* bar) {
     asm volatile(

@@ -54,44 +54,69 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // One thread per (unit, row): reads the row's 32 stored bytes (two 16-byte loads; a warp reads
-// two whole units, 1 KB contiguous), undoes the intra-row permutation in registers and writes the
-// 64 bf16 weights of the block as one contiguous 128-byte run W[n][64kb .. 64kb+64).
+// two whole units, 1 KB contiguous), undoes the intra-row permutation in registers and puts the
+// 64 bf16 weights of the block (128 bytes) into shared memory; the warp then writes its 32 rows
+// out four at a time, 8 lanes x 16 bytes per row, so every store instruction fills whole
+// 128-byte lines of W[n][64kb .. 64kb+64).
+constexpr int kDqRowPitch = 144;  // 128 B of bf16 + 16 B pad: conflict-free 16-byte accesses
+
 __global__ void __launch_bounds__(256)
 dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ qmap,
                   ScaleParams sp, uint16_t* __restrict__ out, int N, long long K, int KU,
                   long long total_units, int unit_stride, int absmax_kind) {
     __shared__ float q[16];
+    __shared__ __align__(16) uint8_t tile[8][32 * kDqRowPitch];
     if (threadIdx.x < 16) q[threadIdx.x] = qmap[threadIdx.x];
     __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long u = tid >> 4;
-    if (u >= total_units) return;
+    const long long u = tid >> 4;  // this lane's unit (two units per warp)
     const int r = (int)(tid & 15);
-    const int kb = (int)(u % KU);
-    const int rt = (int)(u / KU);
+    const bool live = u < total_units;
+    const int kb = live ? (int)(u % KU) : 0;
+    const int rt = live ? (int)(u / KU) : 0;
     const int n = rt * kTileRows + r;
-    if (n >= N) return;
-    const uint8_t* unit = units + (size_t)u * unit_stride;
-    const uint4 lo = *reinterpret_cast<const uint4*>(unit + r * 32);
-    const uint4 hi = *reinterpret_cast<const uint4*>(unit + r * 32 + 16);
-    const float am = unit_absmax(unit, absmax_kind, sp, n, kb, r);
-    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-    uint32_t o[32];  // 64 bf16, natural k order
+    uint8_t* mine = tile[warp] + lane * kDqRowPitch;
+    if (live && n < N) {
+        const uint8_t* unit = units + (size_t)u * unit_stride;
+        const uint4 lo = *reinterpret_cast<const uint4*>(unit + r * 32);
+        const uint4 hi = *reinterpret_cast<const uint4*>(unit + r * 32 + 16);
+        const float am = unit_absmax(unit, absmax_kind, sp, n, kb, r);
+        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        uint32_t o[32];  // 64 bf16, natural k order
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
+            for (int t = 0; t < 4; ++t)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int p = 8 * t + 2 * j + e;               // stored byte
-                const uint32_t b = (w[p >> 2] >> (8 * (p & 3))) & 0xffu;
-                // byte covers k = 16j + 4t + 2e (high nibble) and + 1 (low nibble)
-                o[(16 * j + 4 * t + 2 * e) >> 1] =
-                    pack_bf16x2(__fmul_rn(q[b >> 4], am), __fmul_rn(q[b & 15], am));
+                for (int e = 0; e < 2; ++e) {
+                    const int p = 8 * t + 2 * j + e;  // stored byte
+                    const uint32_t b = (w[p >> 2] >> (8 * (p & 3))) & 0xffu;
+                    // byte covers k = 16j + 4t + 2e (high nibble) and + 1 (low nibble)
+                    o[(16 * j + 4 * t + 2 * e) >> 1] =
+                        pack_bf16x2(__fmul_rn(q[b >> 4], am), __fmul_rn(q[b & 15], am));
+                }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            reinterpret_cast<uint4*>(mine)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    }
+    __syncwarp();
+    // lane -> (row within the group of four, 16-byte piece of the row)
+    const int piece = lane & 7, sub = lane >> 3;
+    const long long u0 = (tid - lane) >> 4;  // first unit of this warp
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const int row = g * 4 + sub;          // 0..31: rows 0-15 unit u0, 16-31 unit u0 + 1
+        const long long uu = u0 + (row >> 4);
+        if (uu < total_units) {
+            const int kbb = (int)(uu % KU);
+            const int nn = (int)(uu / KU) * kTileRows + (row & 15);
+            if (nn < N) {
+                const uint4 v = *reinterpret_cast<const uint4*>(tile[warp] + row * kDqRowPitch + piece * 16);
+                *reinterpret_cast<uint4*>(out + (size_t)nn * K + (size_t)kbb * kUnitK + piece * 8) = v;
             }
-    uint4* orow = reinterpret_cast<uint4*>(out + (size_t)n * K + (size_t)kb * kUnitK);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) orow[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
+    }
 }
 
 __global__ void expand_absmax_kernel(const uint8_t* __restrict__ units, ScaleParams sp,

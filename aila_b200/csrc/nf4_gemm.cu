@@ -4,7 +4,7 @@
 // this kernel stands where the reference calls oneDNN's bf16 matmul (:689-721, :944).
 //
 // Blackwell-native structure (sm_100a):
-//   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) stages 128 x 64 tiles of x
+//   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, one copy per CTA) stages 128 x 64 tiles of x
 //     and BN x 64 tiles of w in a 4-deep shared-memory ring;
 //   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN,
 //     K = 16) with both operands K-major in shared memory and the accumulator in TMEM;

@@ -121,7 +121,8 @@ struct StreamParams {
     float* partials;
     int* counters;
     int* status;
-    long long total_items;  // work items (units, or gate/up unit pairs)
+    int total_items;        // work items (units, or gate/up unit pairs), < 2^31
+    int slice_q, slice_r;   // total_items = slice_q * grid + slice_r
     int n_out;              // rows written (ff when paired)
     int K;
     int KU;
@@ -192,8 +193,9 @@ __device__ __forceinline__ uint32_t lut_pair(uint32_t word, uint32_t lane_base) 
     return lds_u32(__byte_perm(word, lane_base, 0x7604 | (BYTE << 4)));
 }
 
-__device__ __forceinline__ long long slice_begin(long long total, int c, int G) {
-    return (total * c) / G;
+// First work item of CTA c: floor(total * c / G) in 32-bit arithmetic, with total = q*G + r.
+__device__ __forceinline__ int slice_begin(int q, int r, int c, int G) {
+    return q * c + (int)(((unsigned)r * (unsigned)c) / (unsigned)G);
 }
 
 template <int KIND, bool PAIRED>
@@ -232,18 +234,18 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const int lane = tid & 31;
     const int G = gridDim.x;
     const int c = blockIdx.x;
-    const long long i0 = slice_begin(p.total_items, c, G);
-    const long long i1 = slice_begin(p.total_items, c + 1, G);
-    const int len = (int)(i1 - i0);
+    const int i0 = slice_begin(p.slice_q, p.slice_r, c, G);
+    const int i1 = slice_begin(p.slice_q, p.slice_r, c + 1, G);
+    const int len = i1 - i0;
     const int n_groups = (len + kStageItems - 1) / kStageItems;
-    const int rt_first = (int)(i0 / p.KU);
-    const int rt_last = (int)((i1 - 1) / p.KU);
+    const int rt_first = i0 / p.KU;
+    const int rt_last = (i1 - 1) / p.KU;
     const int n_local = rt_last - rt_first + 1;
     // Traversal order: the slice's LAST row tile first, then the rest from the front. Both row
     // tiles that may be shared with a neighbouring CTA are then finished early, and their
     // cross-CTA completion overlaps the streaming of the tiles this CTA owns alone.
-    const long long tail0 = max(i0, (long long)rt_last * p.KU);
-    const int tail_len = (int)(i1 - tail0);
+    const int tail0 = max(i0, rt_last * p.KU);
+    const int tail_len = i1 - tail0;
     // virtual index v in [0, len): item = v < tail_len ? tail0 + v : i0 + (v - tail_len)
 
     if (base > 2048u || base + (uint32_t)p.smem_bytes < a_ring + (uint32_t)p.stages * stage_bytes ||
@@ -324,12 +326,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 
     // ---------------- consumers ----------------
     {
-        const uint32_t qb = f32_to_bf16_bits(p.qmap_v[lane & 15]);
-        // every lane owns the table column of its own lane index
+        // every lane owns the table column of its own lane index; warp w fills the rows of the
+        // byte values w, w + W, ...: low half = first weight of the byte (even k, HIGH nibble)
+#pragma unroll 4
         for (int b = warp; b < 256; b += W) {
-            const uint32_t hi = __shfl_sync(0xffffffffu, qb, b >> 4);
-            const uint32_t lo = __shfl_sync(0xffffffffu, qb, b & 15);
-            // low half = first weight of the byte (even k, HIGH nibble)
+            const uint32_t hi = f32_to_bf16_bits(p.qmap_v[b >> 4]);
+            const uint32_t lo = f32_to_bf16_bits(p.qmap_v[b & 15]);
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(a_lut + (uint32_t)b * 256u + (uint32_t)lane * 4u),
                          "r"(hi | (lo << 16))
                          : "memory");
@@ -392,7 +394,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             for (int w = 0; w < W; ++w) sacc += lds_f32(sl + w * 64);
             v[h] = sacc;
         }
-        const long long t0 = (long long)rtile * p.KU, t1 = t0 + p.KU;
+        const int t0 = rtile * p.KU, t1 = t0 + p.KU;
         const bool is_full = (i0 <= t0) && (i1 >= t1);
         bool write = is_full;
         if (!is_full) {
@@ -406,8 +408,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             }
             __threadfence();
             __syncwarp();
-            const int c_lo = (int)(((t0 + 1) * G - 1) / p.total_items);
-            const int c_hi = (int)((t1 * G - 1) / p.total_items);
+            const int c_lo = (int)((((long long)t0 + 1) * G - 1) / p.total_items);
+            const int c_hi = (int)(((long long)t1 * G - 1) / p.total_items);
             int old = 0;
             if (lane == 0) old = atomicAdd(p.counters + rtile, 1);
             old = __shfl_sync(0xffffffffu, old, 0);
@@ -416,7 +418,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #pragma unroll
                 for (int h = 0; h < NP; ++h) v[h] = 0.0f;
                 for (int cc = c_lo; cc <= c_hi; ++cc) {
-                    const int cc_first = (int)(slice_begin(p.total_items, cc, G) / p.KU);
+                    const int cc_first = slice_begin(p.slice_q, p.slice_r, cc, G) / p.KU;
                     const int hs = (rtile == cc_first) ? 0 : 1;
 #pragma unroll
                     for (int h = 0; h < NP; ++h)
@@ -478,9 +480,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     unsigned d_flat = 0;
     float d_off = 0.0f;
     auto locate = [&](int vv) {  // (kb, rt) of virtual position vv
-        const long long it = vv < tail_len ? tail0 + vv : i0 + (vv - tail_len);
-        kb = (int)(it % p.KU);
-        rt = (int)(it / p.KU);
+        const int it = vv < tail_len ? tail0 + vv : i0 + (vv - tail_len);
+        rt = it / p.KU;
+        kb = it - rt * p.KU;
     };
     auto refresh = [&]() {  // absmax row base of this lane for row tile rt
         if (KIND == kAbsmaxCodes) {
@@ -661,7 +663,7 @@ StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int
     pl.smem = 131072 + (pl.x_in_b ? x_bytes : 0) + pl.stages * stage_bytes;
     const long long rt_work = paired ? ff_pair / kTileRows : w.RT;
     const long long total = rt_work * w.KU;
-    if (total <= 0 || sm_count <= 0) return pl;
+    if (total <= 0 || total >= (1ll << 31) || sm_count <= 0) return pl;
     for (int mult = 1; mult <= kMaxGridMult; ++mult) {
         long long grid = (long long)sm_count * mult;
         if (grid > total) grid = total;
@@ -778,7 +780,9 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.counters = scratch.d_counters;
     p.status = scratch.d_status;
     const int rt_work = paired ? (int)(ff_pair / kTileRows) : w.RT;
-    p.total_items = (long long)rt_work * w.KU;
+    p.total_items = rt_work * w.KU;
+    p.slice_q = p.total_items / pl.grid;
+    p.slice_r = p.total_items % pl.grid;
     p.n_out = paired ? (int)ff_pair : (int)w.N;
     p.K = (int)w.K;
     p.KU = w.KU;

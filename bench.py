@@ -177,6 +177,145 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+
+# ------------------------------------------------------------------------------------------
+def _time_stream(fn, stream, reps, warm=3):
+    import torch
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            fn()
+        stream.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+        stream.synchronize()
+    return a.elapsed_time(b) * 1e3 / reps  # us
+
+
+def tp_mlp_latency(rank, world, local, stream):
+    """cfg5 MLP (hidden 5120, intermediate 25600) sharded over `world` GPUs: gate|up by rows with
+    local SwiGLU, down by columns, one all-reduce. Per-layer latency at M = 1 and M = 2048, with
+    and without the collective. Strong scaling: total work fixed, ideal = t(1)/world."""
+    import torch
+    import torch.distributed as dist
+
+    from aila_b200 import sharded, synth
+    H5, FF5 = 5120, 25600
+    gate = synth.synth_linear(synth.seed_for(5, 0, "gate"), FF5, H5)
+    up = synth.synth_linear(synth.seed_for(5, 0, "up"), FF5, H5)
+    down = synth.synth_linear(synth.seed_for(5, 0, "down"), H5, FF5)
+    be = sharded.CudaBackend(local)
+    be.scratch.ensure(2048, FF5, 2 * FF5 // world, True)
+    if world > 1:
+        mlp = sharded.ShardedNf4Mlp(gate, up, down, be)
+        gate_up, dn, local_ff = mlp.gate_up, mlp.down, mlp.local_ff
+    else:
+        g, u = be.make_shard(gate, 0, 0, 1), be.make_shard(up, 0, 0, 1)
+        gate_up, dn, local_ff = be.fuse(g, u), be.make_shard(down, 1, 0, 1), FF5
+    out = {"workload": "cfg5 MLP 5120 -> 2x25600 -> 5120, NF4; gate|up row-sharded + local SwiGLU, "
+                       "down column-sharded, one all-reduce", "world": world, "scaling": "strong"}
+    for M, reps in ((1, 200), (2048, 10)):
+        x = synth.gaussian_activation(5009 + M, M, H5).to(torch.device("cuda", local))
+        mid = be.empty(M, local_ff)
+        part = be.empty(M, H5)
+
+        def compute():
+            assert be.gate_up_swiglu(gate_up, x, mid, M, local_ff)
+            be.forward(dn, mid, part, M)
+
+        def full():
+            compute()
+            sharded.reduce_partials(part, None, M <= 64)
+
+        if world > 1:
+            dist.barrier()
+        t_c = _time_stream(compute, stream, reps)
+        t_f = _time_stream(full, stream, reps) if world > 1 else t_c
+        if world > 1:
+            t = torch.tensor([t_c, t_f], device=torch.device("cuda", local))
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_c, t_f = float(t[0]), float(t[1])
+        out[f"M{M}_compute_us"] = t_c
+        out[f"M{M}_with_allreduce_us"] = t_f
+    be.scratch.check()
+    return out
+
+
+def decode_stack(local, stream):
+    """cfg4: the NF4 linears of one decode step of a 36-layer GQA transformer (hidden 2560, q 4096,
+    k/v 1024, ff 9728): per layer fused qkv 2560->6144, o 4096->2560, fused gate|up+SiLU
+    2560->2x9728, down 9728->2560; each linear gets its own N(0,1) input. One CUDA graph of 144
+    launches, 1.87 GB of weights per step. (The bf16 lm_head of cfg4 is not part of this library.)"""
+    import dataclasses
+
+    import numpy as np
+    import torch
+
+    from aila_b200 import synth
+    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch
+    dev = torch.device("cuda", local)
+    HID, Q, KV, F = 2560, 4096, 1024, 9728
+    shapes = {"q": (Q, HID), "k": (KV, HID), "v": (KV, HID), "o": (HID, Q), "gate": (F, HID),
+              "up": (F, HID), "down": (HID, F)}
+    base = {k: synth.synth_linear(synth.seed_for(4, 0, k), *v) for k, v in shapes.items()}
+
+    def rolled(w, shift):
+        n, k = w.out_features, w.in_features
+        return dataclasses.replace(
+            w, packed=np.roll(np.asarray(w.packed).reshape(n, k // 2), shift, 0).reshape(-1),
+            absmax_codes=np.roll(np.asarray(w.absmax_codes).reshape(n, k // 64), shift, 0).reshape(-1))
+
+    def lin(w):
+        l = Bnb4BitLinear()
+        assert l.init(w, local), l.last_error
+        return l
+
+    def fuse(*ls):
+        f = Bnb4BitLinear()
+        assert f.init_fused_rows(*ls), f.last_error
+        for l in ls:
+            l.close()
+        return f
+
+    layers = []
+    for i in range(36):
+        w = {k: rolled(v, 16 * i) for k, v in base.items()}
+        layers.append((fuse(lin(w["q"]), lin(w["k"]), lin(w["v"])), lin(w["o"]),
+                       fuse(lin(w["gate"]), lin(w["up"])), lin(w["down"])))
+    scratch = Bnb4BitLinearScratch(local)
+    scratch.ensure(1, F, 2 * F, False)
+    x_h = synth.gaussian_activation(4009, 1, HID).to(dev)
+    x_q = synth.gaussian_activation(4019, 1, Q).to(dev)
+    x_f = synth.gaussian_activation(4029, 1, F).to(dev)
+    y_qkv = torch.empty(1, Q + 2 * KV, dtype=torch.bfloat16, device=dev)
+    y_h = torch.empty(1, HID, dtype=torch.bfloat16, device=dev)
+    y_f = torch.empty(1, F, dtype=torch.bfloat16, device=dev)
+
+    def step():
+        for qkv, o, gu, dn in layers:
+            qkv.forward(scratch, x_h, y_qkv, 1)
+            o.forward(scratch, x_q, y_h, 1)
+            assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(gu, scratch, x_h, y_f, F)
+            dn.forward(scratch, x_f, y_h, 1)
+
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+    us = _time_stream(graph.replay, stream, 20)
+    scratch.check()
+    wbytes = 36 * (weight_bytes(Q + 2 * KV, HID) + weight_bytes(HID, Q) + 2 * weight_bytes(F, HID) +
+                   weight_bytes(HID, F))
+    pk = peaks()
+    return {"workload": "cfg4 NF4 linear stack, M=1: 36 x {qkv 2560->6144, o 4096->2560, "
+                        "gate|up+SiLU 2560->2x9728, down 9728->2560}", "launches_per_step": 144,
+            "weight_bytes_per_step": wbytes, "us_per_step": us, "weight_GBps": wbytes / us / 1e3,
+            "frac_of_measured_hbm": wbytes / us / 1e3 / pk["hbm"]}
+
 # ------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -187,6 +326,9 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--no-tp", action="store_true", help="skip the sharded cfg5 MLP latency (N > 1)")
+    ap.add_argument("--tp", action="store_true", help="also time the cfg5 MLP at N = 1")
+    ap.add_argument("--stack", action="store_true", help="also time the cfg4 decode linear stack")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -345,6 +487,25 @@ def main():
                                 "frac": tf / pk["tf"], "peak_source": pk["source"] + " burst"},
                    "l2": "256 MB flush between iterations"}
 
+    tp = None
+    if (world > 1 and not args.no_tp) or args.tp:
+        for f in linears:
+            f.close()
+        linears = []
+        try:
+            tp = tp_mlp_latency(rank, world, local, stream)
+        except Exception as e:  # keep the headline line even if the extra fails
+            tp = {"error": repr(e)}
+    stack = None
+    if args.stack and rank == 0:
+        for f in linears:
+            f.close()
+        linears = []
+        try:
+            stack = decode_stack(local, stream)
+        except Exception as e:
+            stack = {"error": repr(e)}
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -382,6 +543,10 @@ def main():
         line["cpu_baseline"] = cpu
     if prefill:
         line["prefill"] = prefill
+    if tp:
+        line["tp"] = tp
+    if stack:
+        line["stack"] = stack
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

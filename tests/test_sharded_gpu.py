@@ -1,0 +1,85 @@
+"""Multi-GPU layer on real GPUs: one process per GPU, NCCL. Skipped with fewer than 2 GPUs.
+
+Checks the Megatron-style MLP (gate|up row-sharded with local SwiGLU -> down column-sharded ->
+one all-reduce) against the unsharded CPU oracle at decode (M = 1) and prefill (M = 256) sizes.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from aila_b200 import synth
+from tests.helpers import bits_to_f32, make_weight, oracle_absmax
+
+pytestmark = pytest.mark.gpu
+
+H, FF = 1024, 2048
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from aila_b200 import sharded
+        be = sharded.CudaBackend(rank)
+        gate, up, down = make_weight(1, FF, H), make_weight(2, FF, H), make_weight(3, H, FF)
+        mlp = sharded.ShardedNf4Mlp(gate, up, down, be)
+        outs = {}
+        for M in (1, 256):
+            x = synth.gaussian_activation(10 + M, M, H).cuda()
+            y = mlp.forward(x)
+            torch.cuda.synchronize()
+            outs[M] = y.cpu().view(torch.uint16).numpy()
+        be.scratch.check()
+        if rank == 0:
+            q.put(("ok", outs))
+        dist.barrier()
+    except Exception as e:  # pragma: no cover
+        if rank == 0:
+            q.put(("err", repr(e)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_mlp_nccl(oracle, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+    assert res[0] == "ok", res
+    gate, up, down = make_weight(1, FF, H), make_weight(2, FF, H), make_weight(3, H, FF)
+    packed = np.concatenate([gate.packed, up.packed])
+    am = np.concatenate([oracle_absmax(oracle, gate), oracle_absmax(oracle, up)])
+    for M, got in res[1].items():
+        x = synth.gaussian_activation(10 + M, M, H).view(torch.uint16).numpy()
+        if M == 1:
+            mid = oracle.gemv_gate_up_swiglu(packed, gate.quant_map, am, x.reshape(-1), FF, H, 64).reshape(1, FF)
+        else:
+            mid = oracle.swiglu_rows(oracle.forward(packed, gate.quant_map, am, x, M, 2 * FF, H, 64), M, FF)
+        want = bits_to_f32(oracle.forward(down.packed, down.quant_map, oracle_absmax(oracle, down),
+                                          mid, M, H, FF, 64))
+        err = np.abs(bits_to_f32(got) - want).max()
+        assert err <= 2e-2 * np.abs(want).max(), (M, err)
