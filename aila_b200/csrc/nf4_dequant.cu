@@ -66,6 +66,9 @@ dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ q
                   long long total_units, int unit_stride, int absmax_kind) {
     __shared__ float q[16];
     __shared__ __align__(16) uint8_t tile[8][32 * kDqRowPitch];
+    // the GEMM that consumes this pass may start its set-up now; it waits for our completion
+    // before it reads the weights
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x < 16) q[threadIdx.x] = qmap[threadIdx.x];
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

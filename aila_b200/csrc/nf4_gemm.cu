@@ -8,10 +8,13 @@
 //     and BN x 64 tiles of w in a 4-deep shared-memory ring;
 //   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN,
 //     K = 16) with both operands K-major in shared memory and the accumulator in TMEM;
-//   * two TMEM accumulator buffers (2 x 256 columns) let the epilogue warps drain tile i with
-//     tcgen05.ld while the tensor core already works on tile i+1;
-//   * persistent CTAs, one per SM; BN is chosen per problem (multiple of 16, <= 256) so the
-//     tile count fills whole waves of 148 SMs.
+//   * two shapes of CTA tile, chosen per problem by a cost model (bytes per flop vs. waves):
+//     128 x BN with two TMEM accumulator buffers (2 x 256 columns), so the epilogue warps drain
+//     tile i with tcgen05.ld while the tensor core already works on tile i+1; or 256 x BN, two
+//     M = 128 MMAs per K step sharing one w tile (a third fewer operand bytes per flop, three
+//     64 KB stages in flight), with both accumulators live and eight epilogue warps;
+//   * persistent CTAs, one per SM; BN is a multiple of 16 (<= 256) picked so the tile count
+//     fills whole waves of 148 SMs.
 // Optional epilogues: + residual, or SwiGLU over a gate|up weight (tile = 128 gate columns'
 // worth + the matching up columns), rounding gate and up to bf16 first as the reference's
 // forward + ops::fused_gate_up_swiglu pair does (src/ops/ElementwiseOps.cpp:247-294).
@@ -19,6 +22,7 @@
 // Roofline: tensor pipe. Algorithmic flops 2*M*N*K.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "nf4_internal.h"
@@ -30,14 +34,14 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kMaxBN = 256;
-constexpr int kStages = 4;
-constexpr int kABytes = BM * BK * 2;         // 16 KB
+constexpr int kMaxStages = 4;
+constexpr int kABytes = BM * BK * 2;         // 16 KB per 128 rows of x
 constexpr int kBBytes = kMaxBN * BK * 2;     // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kGemmThreads = 192;            // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kRingBytes = 4 * (kABytes + kBBytes);  // = 3 * (2 * kABytes + kBBytes) = 192 KB
+constexpr int kGemmThreads = 320;            // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
-constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kGemmSmem = kRingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 
 struct GemmParams {
     uint16_t* y;
@@ -51,6 +55,8 @@ struct GemmParams {
     int m_tiles;
     int n_tiles;
     int swiglu_ff;  // 0 = plain
+    int mtile;      // 1: CTA tile 128 x BN (double-buffered accumulator); 2: 256 x BN
+    int stages;     // 4 (mtile 1) or 3 (mtile 2)
     uint32_t idesc;
 };
 
@@ -113,10 +119,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     // 1024-byte aligned ring (the swizzle pattern is a function of the absolute address)
     uint8_t* base = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + kStages * kStageBytes);
-    uint64_t* full = bars;                      // [kStages]
-    uint64_t* empty = bars + kStages;           // [kStages]
-    uint64_t* acc_full = bars + 2 * kStages;    // [kAccStages]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + kRingBytes);
+    uint64_t* full = bars;                      // [kMaxStages]
+    uint64_t* empty = bars + kMaxStages;        // [kMaxStages]
+    uint64_t* acc_full = bars + 2 * kMaxStages; // [kAccStages]
     uint64_t* acc_empty = acc_full + kAccStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccStages);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -125,6 +131,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     const int lane = threadIdx.x & 31;
     const int k_blocks = p.K / BK;
     const int total_tiles = p.m_tiles * p.n_tiles;
+    const int kStages = p.stages;
+    const int a_bytes = kABytes * p.mtile;
+    const int kStageBytes = a_bytes + kBBytes;
+    const int acc_stages = p.mtile == 1 ? kAccStages : 1;  // 256-row tiles keep both halves live
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -133,7 +143,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         for (int a = 0; a < kAccStages; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);
+            mbar_init(&acc_empty[a], 4 * p.mtile);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -148,6 +158,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Launched with programmatic stream serialisation: everything above overlapped the tail of
+    // the kernel that produces w (the dequantisation pass); from here on its output is needed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -157,7 +170,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
-                const int m0 = mt * BM;
+                const int m0 = mt * BM * p.mtile;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kStages;
                     if (it >= kStages) {
@@ -169,8 +182,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                         }
                     }
                     uint8_t* sa = base + s * kStageBytes;
-                    uint8_t* sb = sa + kABytes;
-                    mbar_expect_tx(&full[s], kABytes + b_bytes);
+                    uint8_t* sb = sa + a_bytes;
+                    mbar_expect_tx(&full[s], a_bytes + b_bytes);
                     tma_load_2d(sa, &map_x, kb * BK, m0, &full[s]);
                     if (p.swiglu_ff == 0) {
                         tma_load_2d(sb, &map_w, kb * BK, nt * p.BN, &full[s]);
@@ -192,10 +205,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             int it = 0, tcount = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-                const int as = tcount % kAccStages;
-                if (tcount >= kAccStages) {
+                const int as = tcount % acc_stages;
+                if (tcount >= acc_stages) {
                     if (*abort_flag ||
-                        !mbar_wait_bounded(&acc_empty[as], ((tcount / kAccStages) - 1) & 1)) {
+                        !mbar_wait_bounded(&acc_empty[as], ((tcount / acc_stages) - 1) & 1)) {
                         if (!*abort_flag) atomicExch(p.status, kStatusTimeoutTmem);
                         *abort_flag = 1;
                         break;
@@ -214,12 +227,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = smem_u32(base + s * kStageBytes);
                     const uint64_t adesc = make_smem_desc(sa);
-                    const uint64_t bdesc = make_smem_desc(sa + kABytes);
+                    const uint64_t adesc2 = make_smem_desc(sa + kABytes);  // rows 128..255 of x
+                    const uint64_t bdesc = make_smem_desc(sa + a_bytes);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         // advance 16 elements (32 bytes) along K inside the swizzled row
                         umma_bf16(tacc, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
                                   p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        if (p.mtile == 2)
+                            umma_bf16(tacc + kMaxBN, adesc2 + (uint64_t)(2 * k),
+                                      bdesc + (uint64_t)(2 * k), p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[s]);  // frees the stage when these MMAs have read it
                 }
@@ -227,16 +244,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             }
         }
     } else {
-        // ------------------------------ epilogue (warps 2..5) ------------------------------
-        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32)
+        // ------------------------------ epilogue (warps 2..9) ------------------------------
+        const int quarter = warp & 3;      // TMEM lanes [32*quarter, +32)
+        const int mhalf = (warp - 2) >> 2;  // which 128-row half of a 256-row tile
         int tcount = 0;
         const bool vec_ok = (p.n_out % 8) == 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
-            const int as = tcount % kAccStages;
+        // 128-row tiles use four epilogue warps; the other four have nothing to drain
+        for (int tile = (mhalf < p.mtile ? (int)blockIdx.x : total_tiles); tile < total_tiles;
+             tile += gridDim.x, ++tcount) {
+            const int as = tcount % acc_stages;
             const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
             bool ok = true;
             if (lane == 0) {
-                if (*abort_flag || !mbar_wait_bounded(&acc_full[as], (tcount / kAccStages) & 1)) {
+                if (*abort_flag || !mbar_wait_bounded(&acc_full[as], (tcount / acc_stages) & 1)) {
                     if (!*abort_flag) atomicExch(p.status, kStatusTimeoutTmem);
                     *abort_flag = 1;
                     ok = false;
@@ -245,8 +265,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int m = mt * BM + quarter * 32 + lane;
-            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * kMaxBN);
+            const int m = (mt * p.mtile + mhalf) * BM + quarter * 32 + lane;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                                  (uint32_t)((as + mhalf) * kMaxBN);
             if (p.swiglu_ff == 0) {
                 const int n0 = nt * p.BN;
                 for (int c = 0; c < p.BN; c += 16) {
@@ -308,7 +329,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                             // gate and up pass through bf16 first, like a bf16 gate_up buffer
                             const float g = bf16_bits_to_f32(f32_to_bf16_bits(__uint_as_float(rg[i])));
                             const float u = bf16_bits_to_f32(f32_to_bf16_bits(__uint_as_float(ru[i])));
-                            v[i] = (g / (1.0f + __expf(-g))) * u;
+                            v[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
                         }
                         if (vec_ok && n + 16 <= p.swiglu_ff) {
                             uint4 o0, o1;
@@ -378,21 +399,35 @@ bool encode_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t K, ui
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Tile width for this problem: the multiple of `step` (<= max_bn) that minimises
-// waves * (UMMA N + overhead), i.e. fills whole waves of SMs with the widest tiles that do.
-// width_scale = 2 when each output column costs two accumulator columns (SwiGLU).
-int choose_bn(int M, int64_t n_cols, int step, int max_bn, int width_scale, int sm_count) {
-    const int m_tiles = (M + BM - 1) / BM;
-    int best = step;
-    double best_cost = 1e30;
-    for (int bn = step; bn <= max_bn; bn += step) {
-        const int64_t n_tiles = (n_cols + bn - 1) / bn;
-        const int64_t tiles = n_tiles * m_tiles;
-        const int64_t waves = (tiles + sm_count - 1) / sm_count;
-        const double cost = (double)waves * (bn * width_scale + 24);
-        if (cost <= best_cost) {
-            best_cost = cost;
-            best = bn;
+// Tile shape for this problem. For each candidate (rows 128 or 256, width a multiple of `step`)
+// the cost is waves x (K steps x max(tensor-pipe cycles, operand bytes / L2-to-SM rate) +
+// exposed epilogue). The 128-row shape hides its epilogue behind the next tile; the 256-row
+// shape moves a third fewer bytes per flop and keeps more K steps in flight.
+struct TileChoice {
+    int mtile;
+    int bn;  // accumulator columns per 128-row half
+};
+
+TileChoice choose_tile(int M, int64_t n_cols, int step, int max_bn, int width_scale, int k_blocks,
+                       int sm_count) {
+    constexpr double kL2BytesPerClk = 70.0;  // sustained L2 -> SM operand rate per SM (measured)
+    TileChoice best = {1, step};
+    double best_cost = 1e300;
+    for (int mtile = 1; mtile <= 2; ++mtile) {
+        if (mtile == 2 && M <= BM) continue;
+        const int m_tiles = (M + BM * mtile - 1) / (BM * mtile);
+        for (int bn = step; bn <= max_bn; bn += step) {
+            const int umma_n = bn * width_scale;
+            const int64_t n_tiles = (n_cols + bn - 1) / bn;
+            const int64_t waves = (n_tiles * m_tiles + sm_count - 1) / sm_count;
+            const double mma = 2.0 * umma_n * mtile;                       // cycles per K step
+            const double mem = (kABytes * mtile + umma_n * BK * 2) / kL2BytesPerClk;
+            const double epi = mtile == 2 ? 6.0 * umma_n : 0.0;            // exposed drain
+            const double cost = (double)waves * (k_blocks * (mma > mem ? mma : mem) + epi + 400.0);
+            if (cost < best_cost * 0.999 || (cost <= best_cost * 1.001 && bn > best.bn)) {
+                best_cost = cost;
+                best = {mtile, bn};
+            }
         }
     }
     return best;
@@ -415,23 +450,44 @@ AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const v
     p.N = (int)N;
     p.K = (int)K;
     p.swiglu_ff = (int)swiglu_ff;
-    p.m_tiles = (M + BM - 1) / BM;
+    const int k_blocks = (int)(K / BK);
     if (swiglu_ff > 0) {
         // a tile holds `half` gate columns and the matching `half` up columns
-        const int half = choose_bn(M, swiglu_ff, 16, kMaxBN / 2, 2, sm_count);
-        p.BN = 2 * half;
-        p.n_tiles = (int)((swiglu_ff + half - 1) / half);
+        const TileChoice tc = choose_tile(M, swiglu_ff, 16, kMaxBN / 2, 2, k_blocks, sm_count);
+        p.mtile = tc.mtile;
+        p.BN = 2 * tc.bn;
+        p.n_tiles = (int)((swiglu_ff + tc.bn - 1) / tc.bn);
         p.n_out = (int)swiglu_ff;
     } else {
-        p.BN = choose_bn(M, N, 16, kMaxBN, 1, sm_count);
+        const TileChoice tc = choose_tile(M, N, 16, kMaxBN, 1, k_blocks, sm_count);
+        p.mtile = tc.mtile;
+        p.BN = tc.bn;
         p.n_tiles = (int)((N + p.BN - 1) / p.BN);
         p.n_out = (int)N;
     }
+    if (const char* e = std::getenv("AILA_NF4_GEMM_MTILE")) {  // measurement override: 1 or 2
+        const int f = std::atoi(e);
+        if ((f == 1 || f == 2) && !(f == 2 && M <= BM)) p.mtile = f;
+    }
+    if (const char* e = std::getenv("AILA_NF4_GEMM_BN")) {  // measurement override: columns per tile
+        const int bn = std::atoi(e);
+        if (bn >= 16 && bn % 16 == 0) {
+            if (swiglu_ff > 0 && bn <= kMaxBN / 2) {
+                p.BN = 2 * bn;
+                p.n_tiles = (int)((swiglu_ff + bn - 1) / bn);
+            } else if (swiglu_ff == 0 && bn <= kMaxBN) {
+                p.BN = bn;
+                p.n_tiles = (int)((N + bn - 1) / bn);
+            }
+        }
+    }
+    p.m_tiles = (M + BM * p.mtile - 1) / (BM * p.mtile);
+    p.stages = p.mtile == 2 ? 3 : 4;
     // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) |
               ((uint32_t)(BM >> 4) << 24);
     CUtensorMap map_x, map_w;
-    if (!encode_map(&map_x, x, (uint64_t)M, (uint64_t)K, BM))
+    if (!encode_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)(BM * p.mtile)))
         return fail(AILA_NF4_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation tensor");
     const uint32_t w_box = (uint32_t)(swiglu_ff > 0 ? p.BN / 2 : p.BN);
     if (!encode_map(&map_w, w_nk, (uint64_t)N, (uint64_t)K, w_box))
@@ -449,8 +505,17 @@ AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const v
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int grid = total_tiles < sm_count ? total_tiles : sm_count;
     if (grid <= 0) return AILA_NF4_OK;
-    gemm_bf16_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmem, s>>>(map_x, map_w, p);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kGemmSmem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel, map_x, map_w, p);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05_kernel launch");
     return AILA_NF4_OK;
 }
