@@ -225,7 +225,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     uint8_t* gen = smem_raw - base;  // generic pointer to shared-window address 0
     uint64_t* full = reinterpret_cast<uint64_t*>(gen + a_bar);
     uint64_t* empty = full + kMaxStages;
-    uint64_t* aux = empty + kMaxStages;
     int* tile_done = reinterpret_cast<int*>(gen + a_tile);
     int* abort_flag = tile_done + kMaxLocalTiles;
 
@@ -258,7 +257,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], W);
         }
-        mbar_init(aux, 1);
         for (int i = 0; i < kMaxLocalTiles; ++i) tile_done[i] = 0;
         *abort_flag = 0;
         mbar_fence_init();
@@ -271,17 +269,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         // ---------------- producer: one thread keeps the ring full ----------------
         if (lane == 0) {
             int issued = 0;
-            bool aux_sent = false;
-            for (int g = 0; g <= n_groups; ++g) {
-                if (!aux_sent && (g == p.stages || g == n_groups)) {
-                    // the weights above do not depend on the previous kernel; x does
-                    asm volatile("griddepcontrol.wait;" ::: "memory");
-                    mbar_expect_tx(aux, (uint32_t)p.x_bytes + (KIND == kAbsmaxCodes ? 1024u : 0u));
-                    bulk_g2s(gen + a_xs, p.x, (uint32_t)p.x_bytes, aux);
-                    if (KIND == kAbsmaxCodes) bulk_g2s(gen + a_nmap, p.sp.nmap, 1024u, aux);
-                    aux_sent = true;
-                }
-                if (g == n_groups) break;
+            for (int g = 0; g < n_groups; ++g) {
                 const int s = g % p.stages;
                 if (g >= p.stages) {
                     if (*(volatile int*)abort_flag) break;
@@ -319,12 +307,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             // never leave the CTA with copies still landing in its shared memory
             for (int g = max(0, issued - p.stages); g < issued; ++g)
                 mbar_wait_bounded(&full[g % p.stages], (g / p.stages) & 1);
-            if (aux_sent) mbar_wait_bounded(aux, 0);
         }
         return;
     }
 
     // ---------------- consumers ----------------
+    // second-level code book: static data, fetched first so the latency hides behind the table build
+    float nmap_reg = 0.0f;
+    if (KIND == kAbsmaxCodes && tid < 256) nmap_reg = __ldg(p.sp.nmap + tid);
     {
         // every lane owns the table column of its own lane index; warp w fills the rows of the
         // byte values w, w + W, ...: low half = first weight of the byte (even k, HIGH nibble)
@@ -358,6 +348,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (win_ok[h])
                 for (unsigned i = tid; i < cnt; i += W * 32)
                     sts_f32(a_nabsw + (uint32_t)(h * kNabsWindow + i) * 4u, __ldg(p.sp.nabs + win_lo[h] + i));
+        }
+    }
+    if (KIND == kAbsmaxCodes && tid < 256) sts_f32(a_nmap + 4u * tid, nmap_reg);
+    // x is the only input that may come from the previous kernel on the stream: everything above
+    // (and the producer's weight copies) ran without waiting for it
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+        const int n16 = p.x_bytes >> 4;
+        const uint4* xg = reinterpret_cast<const uint4*>(p.x);
+        for (int i = tid; i < n16; i += W * 32) {
+            const uint4 v = __ldg(xg + i);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_xs + 16u * i), "r"(v.x),
+                         "r"(v.y), "r"(v.z), "r"(v.w)
+                         : "memory");
         }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
@@ -499,13 +503,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     }
     const int kb_step = (kStageItems - IPW) % p.KU;  // from a run's last item + 1 to the next run
     const int rt_step = (kStageItems - IPW) / p.KU;
-
-    // x (and the second-level code book) must have landed before the first product
-    if (!mbar_wait_bounded(aux, 0)) {
-        atomicExch(p.status, kStatusTimeoutFull);
-        *(volatile int*)abort_flag = 1;
-        return;
-    }
 
     bool failed = false;
     for (int g = 0; g < n_groups; ++g) {
