@@ -36,7 +36,7 @@ UNIT = "GB/s"
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # capture summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 26083840  # profiles/gemv_stream_cfg2_ncu.md
 
 
 def weight_bytes(n: int, k: int) -> int:
