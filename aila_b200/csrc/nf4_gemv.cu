@@ -23,6 +23,7 @@
 //
 // Roofline: HBM. Algorithmic bytes per weight: 0.5 (nibbles) + 1/64 (code) + 4/16384 (scale).
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "nf4_internal.h"
@@ -113,7 +114,7 @@ constexpr int kNabsWindow = 256;    // second-level scales kept in shared memory
 
 struct StreamParams {
     const uint8_t* units;
-    float qmap_v[16];       // NF4 code book by value
+    uint32_t pair_table[256];  // byte value -> bf16 pair of its two nibbles (high nibble first)
     ScaleParams sp;
     const uint16_t* x;
     uint16_t* y;
@@ -317,15 +318,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     if (KIND == kAbsmaxCodes && tid < 256) nmap_reg = __ldg(p.sp.nmap + tid);
     {
         // every lane owns the table column of its own lane index; warp w fills the rows of the
-        // byte values w, w + W, ...: low half = first weight of the byte (even k, HIGH nibble)
+        // byte values w, w + W, ... from the 256-entry pair table in the kernel parameters
+        // (warp-uniform constant loads)
 #pragma unroll 4
-        for (int b = warp; b < 256; b += W) {
-            const uint32_t hi = f32_to_bf16_bits(p.qmap_v[b >> 4]);
-            const uint32_t lo = f32_to_bf16_bits(p.qmap_v[b & 15]);
+        for (int b = warp; b < 256; b += W)
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(a_lut + (uint32_t)b * 256u + (uint32_t)lane * 4u),
-                         "r"(hi | (lo << 16))
+                         "r"(p.pair_table[b])
                          : "memory");
-        }
         for (int i = tid; i < kMaxLocalTiles * NP * W * 16; i += W * 32) sts_f32(a_slots + 4u * i, 0.0f);
     }
     // Second-level scales this CTA can need: one window of consecutive nested_absmax entries per
@@ -768,7 +767,21 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     if (!pl.ok) return cudaErrorInvalidConfiguration;
     StreamParams p;
     p.units = w.d_units;
-    for (int i = 0; i < 16; ++i) p.qmap_v[i] = w.h_qmap[i];
+    {
+        // bf16 (round-to-nearest-even) of the 16 code-book values, paired per byte value:
+        // low half = first weight of the byte (even k, HIGH nibble)
+        uint32_t qb[16];
+        for (int i = 0; i < 16; ++i) {
+            uint32_t u;
+            std::memcpy(&u, &w.h_qmap[i], 4);
+            if ((u & 0x7fffffffu) > 0x7f800000u) {
+                qb[i] = (u >> 16) | 0x40u;
+            } else {
+                qb[i] = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+            }
+        }
+        for (int b = 0; b < 256; ++b) p.pair_table[b] = qb[b >> 4] | (qb[b & 15] << 16);
+    }
     p.sp = w.scale_params();
     p.x = static_cast<const uint16_t*>(x);
     p.y = static_cast<uint16_t*>(y);
