@@ -114,6 +114,7 @@ def cpu_gate_up_baseline(min_seconds: float = 10.0, max_reps: int = 400):
     from aila_b200 import synth
     from oracle import nf4_oracle as O
     O.build()
+    O.set_num_threads(os.cpu_count() or 1)  # launchers such as torchrun pin OMP_NUM_THREADS=1
     g = synth.synth_linear(synth.seed_for(2, 0, "gate"), FF, H)
     u = synth.synth_linear(synth.seed_for(2, 0, "up"), FF, H)
     am = np.concatenate([O.expand_absmax(w.absmax_codes, w.nested_quant_map, w.nested_absmax,
@@ -147,6 +148,7 @@ def run_reference(args):
     from aila_b200 import synth
     from oracle import nf4_oracle as O
     O.build()
+    O.set_num_threads(os.cpu_count() or 1)  # launchers such as torchrun pin OMP_NUM_THREADS=1
     g = synth.synth_linear(synth.seed_for(2, 0, "gate"), FF, H)
     u = synth.synth_linear(synth.seed_for(2, 0, "up"), FF, H)
     am = np.concatenate([O.expand_absmax(w.absmax_codes, w.nested_quant_map, w.nested_absmax,
@@ -225,14 +227,44 @@ def tp_mlp_latency(rank, world, local, stream):
             assert be.gate_up_swiglu(gate_up, x, mid, M, local_ff)
             be.forward(dn, mid, part, M)
 
+        acc32 = torch.empty(M, H5, dtype=torch.float32, device=part.device) if M <= 64 else None
+
         def full():
             compute()
-            sharded.reduce_partials(part, None, M <= 64)
+            if acc32 is not None:  # fp32 exchange for decode-sized messages
+                acc32.copy_(part)
+                dist.all_reduce(acc32)
+                part.copy_(acc32)
+            else:
+                dist.all_reduce(part)
+
+        def graphed(fn):
+            """Replays fn from a CUDA graph when capture works (NCCL included), else eager."""
+            try:
+                with torch.cuda.stream(stream):
+                    fn()
+                    stream.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        fn()
+                return g.replay, "cuda graph"
+            except Exception:
+                torch.cuda.synchronize()
+                return fn, "eager"
 
         if world > 1:
             dist.barrier()
-        t_c = _time_stream(compute, stream, reps)
-        t_f = _time_stream(full, stream, reps) if world > 1 else t_c
+        run_c, how_c = graphed(compute)
+        t_c = _time_stream(run_c, stream, reps)
+        if world > 1:
+            dist.barrier()
+            run_f, how_f = graphed(full)
+            dist.barrier()
+            t_f = _time_stream(run_f, stream, reps)
+            out[f"M{M}_launch"] = f"compute: {how_c}; with all-reduce: {how_f}"
+        else:
+            t_f = t_c
+            out[f"M{M}_launch"] = how_c
         if world > 1:
             t = torch.tensor([t_c, t_f], device=torch.device("cuda", local))
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -348,6 +380,7 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        torch.set_num_threads(max(1, (os.cpu_count() or world) // world))  # torchrun pins 1
     pk = peaks()
     layers = args.layers
 
