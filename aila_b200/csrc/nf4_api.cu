@@ -54,6 +54,7 @@ void free_linear(AilaNf4Linear* l) {
     cudaFree(l->d_qmap);
     cudaFree(l->d_nmap);
     cudaFree(l->d_nabs);
+    cudaFree(l->d_cache_bf16);
     delete l;
 }
 
@@ -63,6 +64,28 @@ cudaError_t upload(T** dst, const T* src, size_t count, bool src_on_device) {
     if (e != cudaSuccess) return e;
     return cudaMemcpy(*dst, src, count * sizeof(T),
                       src_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice);
+}
+
+// AILA_BNB4_CACHE_DEQUANT=1 (same name and meaning as the reference flag read in
+// Bnb4BitLinear::finish_init, src/ops/Bnb4BitLinear.cpp:642-650): keep a bf16 copy of the whole
+// weight so seq_len > 1 calls skip the dequantisation pass, at four times the weight memory.
+bool cache_dequant_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("AILA_BNB4_CACHE_DEQUANT");
+        return e && e[0] != '\0' && e[0] != '0';
+    }();
+    return on;
+}
+
+AilaNf4Status maybe_cache_dequant(AilaNf4Linear* l) {
+    if (!cache_dequant_enabled()) return AILA_NF4_OK;
+    const size_t bytes = (size_t)l->N * (size_t)l->K * 2;
+    cudaError_t e = cudaMalloc(&l->d_cache_bf16, bytes + 256);
+    if (e != cudaSuccess) return nf4::cuda_fail(e, "cudaMalloc(bf16 weight cache)");
+    NF4_CUDA(nf4::launch_dequant_nk(*l, l->d_cache_bf16, 0));
+    NF4_CUDA(cudaDeviceSynchronize());
+    l->device_bytes += (int64_t)bytes;
+    return AILA_NF4_OK;
 }
 
 // Validation shared by create and create_shard: the checks of LoadBnb4BitWeightRef
@@ -198,6 +221,10 @@ AilaNf4Status create_slice(const AilaNf4WeightDesc* d, int64_t row0, int64_t row
     l->seg_nabs_base[0] = 0;
     l->seg_offset[0] = d->nested ? d->nested_offset : 0.0f;
 #undef NF4_TRY
+    {
+        const AilaNf4Status cst = maybe_cache_dequant(l);
+        if (cst != AILA_NF4_OK) return cleanup(cst);
+    }
     *out = l;
     return cleanup(AILA_NF4_OK);
 }
@@ -455,6 +482,13 @@ AILA_NF4_API AilaNf4Status aila_nf4_linear_create_fused_rows(AilaNf4Linear* cons
 #undef NF4_TRY
     l->device_bytes = (int64_t)l->units_bytes() + 16 * 4 +
                       (l->absmax_kind == nf4::kAbsmaxCodes ? 256 * 4 + l->nabs_count * 4 : 0);
+    {
+        const AilaNf4Status cst = maybe_cache_dequant(l);
+        if (cst != AILA_NF4_OK) {
+            free_linear(l);
+            return cst;
+        }
+    }
     *out = l;
     return AILA_NF4_OK;
 }
@@ -571,10 +605,14 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward(const AilaNf4Linear* l, AilaNf4Scrat
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, y, residual, 0, s);
-    st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);
-    if (st != AILA_NF4_OK) return st;
-    NF4_CUDA(nf4::launch_dequant_nk(*l, sc->d_weight, s));
-    return nf4::launch_gemm_bf16(sc->d_weight, x, y, residual, seq_len, l->N, l->K, 0, l->device,
+    const void* wsrc = l->d_cache_bf16;
+    if (!wsrc) {
+        st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);
+        if (st != AILA_NF4_OK) return st;
+        NF4_CUDA(nf4::launch_dequant_nk(*l, sc->d_weight, s));
+        wsrc = sc->d_weight;
+    }
+    return nf4::launch_gemm_bf16(wsrc, x, y, residual, seq_len, l->N, l->K, 0, l->device,
                                  sc->sm_count, sc->d_status, s);
 }
 
@@ -592,11 +630,15 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, out, nullptr, ff_dim, s);
-    st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);
-    if (st != AILA_NF4_OK) return st;
-    NF4_CUDA(nf4::launch_dequant_nk(*l, sc->d_weight, s));
-    return nf4::launch_gemm_bf16(sc->d_weight, x, out, nullptr, seq_len, l->N, l->K, ff_dim,
-                                 l->device, sc->sm_count, sc->d_status, s);
+    const void* wsrc = l->d_cache_bf16;
+    if (!wsrc) {
+        st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);
+        if (st != AILA_NF4_OK) return st;
+        NF4_CUDA(nf4::launch_dequant_nk(*l, sc->d_weight, s));
+        wsrc = sc->d_weight;
+    }
+    return nf4::launch_gemm_bf16(wsrc, x, out, nullptr, seq_len, l->N, l->K, ff_dim, l->device,
+                                 sc->sm_count, sc->d_status, s);
 }
 
 AILA_NF4_API AilaNf4Status aila_nf4_forward_host(const AilaNf4Linear* l, AilaNf4Scratch* sc,

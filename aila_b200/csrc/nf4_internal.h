@@ -20,6 +20,7 @@ struct AilaNf4Linear {
     float* d_qmap = nullptr;     // [16]
     float* d_nmap = nullptr;     // [256]
     float* d_nabs = nullptr;     // concatenated nested_absmax
+    void* d_cache_bf16 = nullptr;  // optional bf16 [N][K] copy (AILA_BNB4_CACHE_DEQUANT=1)
     int64_t nabs_count = 0;
     float h_qmap[16] = {0};
     int nbs = 256;

@@ -1,0 +1,55 @@
+// Compile-and-link check of the C++ adapter (include/aila_nf4_linear.hpp) against libaila_nf4.so.
+// Mirrors how the reference backends use Bnb4BitLinear (src/models/Qwen3Bnb4Backend.cpp:186-243,
+// :339-418). With a GPU it also runs a tiny forward; without one it checks the error behaviour.
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "aila_nf4_linear.hpp"
+
+using aila::nf4::Bnb4BitLinear;
+using aila::nf4::Bnb4BitLinearScratch;
+using aila::nf4::Context;
+using aila::nf4::TensorView;
+
+int main() {
+    const int N = 32, K = 128;
+    std::vector<uint8_t> packed(N * K / 2, 0x7F);
+    std::vector<float> absmax(N * K / 64, 1.0f), qmap(16);
+    for (int i = 0; i < 16; ++i) qmap[i] = (i - 7) / 8.0f;
+    AilaNf4WeightDesc d;
+    std::memset(&d, 0, sizeof(d));
+    d.out_features = N;
+    d.in_features = K;
+    d.blocksize = 64;
+    d.nested = 0;
+    d.packed_weight = packed.data();
+    d.absmax = absmax.data();
+    d.quant_map = qmap.data();
+    d.pointers_on_device = 0;
+
+    Context ctx;
+    Bnb4BitLinear q, k, fused;
+    std::string err;
+    const bool ok = q.init(ctx, d, &err);
+    if (!ok) {
+        // no usable GPU: init reports the failure through the bool + message, like the reference
+        std::printf("init failed as expected without a GPU: %s\n", err.c_str());
+        if (err.empty()) return 2;
+        bool threw = false;
+        try {
+            Bnb4BitLinearScratch s;
+            TensorView x, y;
+            q.forward(ctx, s, x, y, 0);
+        } catch (const std::runtime_error& e) {
+            threw = std::strstr(e.what(), "seq_len") != nullptr;
+        }
+        return threw ? 0 : 3;
+    }
+    if (!k.init(ctx, d, &err)) return 4;
+    if (!fused.init_fused_rows(ctx, q, k, &err)) return 5;
+    if (fused.out_features() != 2 * N || fused.in_features() != K) return 6;
+    std::printf("adapter ok on a GPU: fused %d x %d\n", fused.out_features(), fused.in_features());
+    return 0;
+}

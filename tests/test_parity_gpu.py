@@ -355,3 +355,35 @@ def test_forward_error_behaviour(nf4, scratch):
         l.forward(scratch, x.float(), y, 1)
     with pytest.raises(RuntimeError, match="seq_len"):
         l.forward(scratch, x, y, 0)
+
+
+def test_cache_dequant_env_mode(oracle, tmp_path):
+    """AILA_BNB4_CACHE_DEQUANT=1 (the reference's flag, Bnb4BitLinear.cpp:642-650): the bf16
+    weight cache gives the same prefill result as the per-call dequantisation route. The flag is
+    read once per process, so the check runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "cache_mode.py"
+    script.write_text(
+        "import sys, torch, numpy as np\n"
+        f"sys.path.insert(0, {os.path.dirname(os.path.dirname(os.path.abspath(__file__)))!r})\n"
+        "from aila_b200 import synth\n"
+        "from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch\n"
+        "w = synth.synth_linear(77, 272, 448)\n"
+        "l = Bnb4BitLinear(); assert l.init(w, 0), l.last_error\n"
+        "assert l.device_bytes() > 272 * 448 * 2\n"
+        "s = Bnb4BitLinearScratch(0)\n"
+        "x = synth.gaussian_activation(78, 200, 448).cuda()\n"
+        "y = torch.empty(200, 272, dtype=torch.bfloat16, device='cuda')\n"
+        "l.forward(s, x, y, 200); torch.cuda.synchronize(); s.check()\n"
+        "np.save(sys.argv[1], y.cpu().view(torch.uint16).numpy())\n")
+    out = tmp_path / "y.npy"
+    env = dict(os.environ, AILA_BNB4_CACHE_DEQUANT="1")
+    subprocess.run([sys.executable, str(script), str(out)], check=True, env=env, timeout=300)
+    got = np.load(out)
+    w = make_weight(77, 272, 448)
+    x = _act(78, 200, 448)
+    want = oracle.forward(w.packed, w.quant_map, oracle_absmax(oracle, w), bf16_bits(x), 200, 272,
+                          448, 64)
+    assert_close_norm(got, want, REL, "prefill with bf16 weight cache")
