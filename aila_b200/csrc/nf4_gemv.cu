@@ -104,7 +104,7 @@ gemv_simple_kernel(const uint8_t* __restrict__ units, const float* __restrict__ 
 #define NF4_IPW 2
 #endif
 constexpr int kConsumerWarps = NF4_W;
-constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
+constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;  // + producer warp + finalizer warp
 constexpr int kItemsPerWarp = NF4_IPW;   // work items a consumer warp takes from one stage
 constexpr int kStageItems = kConsumerWarps * kItemsPerWarp;
 constexpr int kMaxStages = 24;
@@ -114,7 +114,7 @@ constexpr int kNabsWindow = 256;    // second-level scales kept in shared memory
 
 struct StreamParams {
     const uint8_t* units;
-    uint32_t pair_table[256];  // byte value -> bf16 pair of its two nibbles (high nibble first)
+    const float* qmap;      // [16] first-level code book
     ScaleParams sp;
     const uint16_t* x;
     uint16_t* y;
@@ -124,6 +124,9 @@ struct StreamParams {
     int* status;
     int total_items;        // work items (units, or gate/up unit pairs), < 2^31
     int slice_q, slice_r;   // total_items = slice_q * grid + slice_r
+    uint32_t div_g_m, div_ku_m;  // multiply-shift division by the grid size and by KU
+    int div_g_s, div_ku_s;
+    int kb_step, rt_step;   // (stage items - items per warp) mod / div KU
     int n_out;              // rows written (ff when paired)
     int K;
     int KU;
@@ -134,6 +137,9 @@ struct StreamParams {
     int x_in_b;             // 1: x lives above the table (large K), 0: below it
     int smem_bytes;         // dynamic shared memory of the launch
     int n_rows;             // rows of the linear (for clamping the padded rows of the last tile)
+#ifdef AILA_NF4_TRACE
+    int trace_idx;
+#endif
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1,
@@ -144,6 +150,16 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// first tile of a chain: accumulator operands are the constant zero (no register initialisation)
+__device__ __forceinline__ void mma_bf16_16816_init(float (&c)[4], uint32_t a0, uint32_t a1,
+                                                    uint32_t a2, uint32_t a3, uint32_t b0,
+                                                    uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -169,18 +185,6 @@ __device__ __forceinline__ uint2 lds_v2(uint32_t a) {
     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
     return v;
 }
-// 8-byte load executed only by lanes whose `pred_zero` is 0; the others get zeros
-__device__ __forceinline__ uint2 lds_v2_if_zero(uint32_t a, int pred_zero) {
-    uint2 v;
-    asm volatile(
-        "{\n\t.reg .pred q;\n\t"
-        "setp.eq.u32 q, %3, 0;\n\t"
-        "mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\t"
-        "@q ld.shared.v2.u32 {%0, %1}, [%2];\n\t}"
-        : "=&r"(v.x), "=&r"(v.y)
-        : "r"(a), "r"(pred_zero));
-    return v;
-}
 __device__ __forceinline__ void sts_f32(uint32_t a, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
 }
@@ -194,13 +198,41 @@ __device__ __forceinline__ uint32_t lut_pair(uint32_t word, uint32_t lane_base) 
     return lds_u32(__byte_perm(word, lane_base, 0x7604 | (BYTE << 4)));
 }
 
-// First work item of CTA c: floor(total * c / G) in 32-bit arithmetic, with total = q*G + r.
-__device__ __forceinline__ int slice_begin(int q, int r, int c, int G) {
-    return q * c + (int)(((unsigned)r * (unsigned)c) / (unsigned)G);
+// n / d for 0 <= n < 2^31 as (n * m) >> s, with s = 31 + ceil(log2 d) and m = ceil(2^s / d) < 2^32:
+// n*m / 2^s exceeds n/d by less than 2^31 / 2^s <= 1/d, which cannot carry into the next integer.
+__host__ __device__ __forceinline__ int fast_div(int n, uint32_t m, int s) {
+    return (int)(((unsigned long long)(unsigned)n * m) >> s);
 }
+void make_fast_div(uint32_t d, uint32_t* m, int* s) {
+    int l = 0;
+    while ((1ull << l) < d) ++l;
+    *s = 31 + l;
+    *m = (uint32_t)(((1ull << *s) + d - 1) / d);
+}
+
+// First work item of CTA c: floor(total * c / G) in 32-bit arithmetic, with total = q*G + r.
+__device__ __forceinline__ int slice_begin(const StreamParams& p, int c) {
+    return p.slice_q * c + fast_div(p.slice_r * c, p.div_g_m, p.div_g_s);
+}
+
+#ifdef AILA_NF4_TRACE
+__device__ unsigned long long g_trace[32][160][96];
+#define NF4_TRACE(slot)                                                              \
+    do {                                                                             \
+        unsigned long long t_;                                                       \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                       \
+        g_trace[p.trace_idx][blockIdx.x % 160][2 * (slot)] = t_;                     \
+        g_trace[p.trace_idx][blockIdx.x % 160][2 * (slot) + 1] = (unsigned long long)clock64(); \
+    } while (0)
+#else
+#define NF4_TRACE(slot) do {} while (0)
+#endif
 
 template <int KIND, bool PAIRED>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
+#ifdef AILA_NF4_TRACE
+    if (threadIdx.x == 0) { NF4_TRACE(0); g_trace[p.trace_idx][blockIdx.x % 160][30] = 0; }
+#endif
     constexpr int NP = PAIRED ? 2 : 1;
     constexpr int W = kConsumerWarps;
     constexpr int IPW = kItemsPerWarp;
@@ -213,12 +245,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     // table    = [64 KB, 128 KB)
     // region B = [128 KB, ...): x (if large), ring of stages
     const uint32_t base = smem_u32(smem_raw);
-    const uint32_t a_bar = (base + 15u) & ~15u;                 // full[kMaxStages], empty[], aux
-    const uint32_t a_tile = a_bar + 400;                         // tile_done[kMaxLocalTiles], abort
+    const uint32_t a_bar = (base + 15u) & ~15u;                 // full[kMaxStages], empty[], abort flag
+    const uint32_t a_tile = a_bar + 400;                         // tile_bar[kMaxLocalTiles]
     static_assert((2 * kMaxStages + 1) * 8 <= 400, "barrier block");
+    static_assert(kMaxLocalTiles * 8 <= 64, "tile barrier block");
     const uint32_t a_nmap = a_tile + 64;
     const uint32_t a_nabsw = a_nmap + 1024;                      // [2][kNabsWindow] second-level scales
-    const uint32_t a_slots = a_nabsw + 2 * kNabsWindow * 4;      // [tile][pair][warp][16] floats
+    const uint32_t a_ptab = a_nabsw + 2 * kNabsWindow * 4;       // [256] byte value -> bf16 pair
+    const uint32_t a_slots = a_ptab + 1024;                      // [tile][pair][warp][16] floats
     const uint32_t a_xs_small = a_slots + kMaxLocalTiles * NP * W * 64;
     const uint32_t a_lut = 65536u;
     const uint32_t a_xs = p.x_in_b ? 131072u : a_xs_small;
@@ -226,20 +260,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     uint8_t* gen = smem_raw - base;  // generic pointer to shared-window address 0
     uint64_t* full = reinterpret_cast<uint64_t*>(gen + a_bar);
     uint64_t* empty = full + kMaxStages;
-    int* tile_done = reinterpret_cast<int*>(gen + a_tile);
-    int* abort_flag = tile_done + kMaxLocalTiles;
+    uint64_t* tile_bar = reinterpret_cast<uint64_t*>(gen + a_tile);
+    int* abort_flag = reinterpret_cast<int*>(empty + kMaxStages);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int G = gridDim.x;
     const int c = blockIdx.x;
-    const int i0 = slice_begin(p.slice_q, p.slice_r, c, G);
-    const int i1 = slice_begin(p.slice_q, p.slice_r, c + 1, G);
+    const int i0 = slice_begin(p, c);
+    const int i1 = slice_begin(p, c + 1);
     const int len = i1 - i0;
     const int n_groups = (len + kStageItems - 1) / kStageItems;
-    const int rt_first = i0 / p.KU;
-    const int rt_last = (i1 - 1) / p.KU;
+    const int rt_first = fast_div(i0, p.div_ku_m, p.div_ku_s);
+    const int rt_last = fast_div(i1 - 1, p.div_ku_m, p.div_ku_s);
     const int n_local = rt_last - rt_first + 1;
     // Traversal order: the slice's LAST row tile first, then the rest from the front. Both row
     // tiles that may be shared with a neighbouring CTA are then finished early, and their
@@ -253,138 +287,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         if (tid == 0) atomicExch(p.status, kStatusBadArgument);
         return;
     }
-    if (tid == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], W);
-        }
-        for (int i = 0; i < kMaxLocalTiles; ++i) tile_done[i] = 0;
-        *abort_flag = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
     // let a dependent launch begin its own set-up; it waits for our completion before reading
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (warp == W) {
-        // ---------------- producer: one thread keeps the ring full ----------------
-        if (lane == 0) {
-            int issued = 0;
-            for (int g = 0; g < n_groups; ++g) {
-                const int s = g % p.stages;
-                if (g >= p.stages) {
-                    if (*(volatile int*)abort_flag) break;
-                    if (!mbar_wait_bounded(&empty[s], ((g / p.stages) - 1) & 1)) {
-                        atomicExch(p.status, kStatusTimeoutEmpty);
-                        *(volatile int*)abort_flag = 1;
-                        break;
-                    }
-                }
-                const int v0 = g * kStageItems;
-                const int cnt = min(kStageItems, len - v0);
-                uint8_t* dst = gen + a_ring + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full[s], (uint32_t)cnt * unit_stride * NP);
-                // up to two contiguous pieces (the traversal wraps from the tail tile to the front)
-                const int n1 = v0 < tail_len ? min(cnt, tail_len - v0) : 0;
-                if (n1 > 0) {
-                    const size_t it = (size_t)(tail0 + v0);
-                    bulk_g2s(dst, p.units + it * unit_stride, (uint32_t)n1 * unit_stride, &full[s]);
-                    if (PAIRED)
-                        bulk_g2s(dst + half_bytes,
-                                 p.units + (it + (size_t)p.pair_rt_offset * p.KU) * unit_stride,
-                                 (uint32_t)n1 * unit_stride, &full[s]);
-                }
-                if (cnt > n1) {
-                    const size_t it = (size_t)(i0 + (v0 + n1 - tail_len));
-                    bulk_g2s(dst + n1 * unit_stride, p.units + it * unit_stride,
-                             (uint32_t)(cnt - n1) * unit_stride, &full[s]);
-                    if (PAIRED)
-                        bulk_g2s(dst + half_bytes + n1 * unit_stride,
-                                 p.units + (it + (size_t)p.pair_rt_offset * p.KU) * unit_stride,
-                                 (uint32_t)(cnt - n1) * unit_stride, &full[s]);
-                }
-                issued = g + 1;
-            }
-            // never leave the CTA with copies still landing in its shared memory
-            for (int g = max(0, issued - p.stages); g < issued; ++g)
-                mbar_wait_bounded(&full[g % p.stages], (g / p.stages) & 1);
-        }
-        return;
-    }
-
-    // ---------------- consumers ----------------
-    // second-level code book: static data, fetched first so the latency hides behind the table build
-    float nmap_reg = 0.0f;
-    if (KIND == kAbsmaxCodes && tid < 256) nmap_reg = __ldg(p.sp.nmap + tid);
-    {
-        // every lane owns the table column of its own lane index; warp w fills the rows of the
-        // byte values w, w + W, ... from the 256-entry pair table in the kernel parameters
-        // (warp-uniform constant loads)
-#pragma unroll 4
-        for (int b = warp; b < 256; b += W)
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(a_lut + (uint32_t)b * 256u + (uint32_t)lane * 4u),
-                         "r"(p.pair_table[b])
-                         : "memory");
-        for (int i = tid; i < kMaxLocalTiles * NP * W * 16; i += W * 32) sts_f32(a_slots + 4u * i, 0.0f);
-    }
-    // Second-level scales this CTA can need: one window of consecutive nested_absmax entries per
-    // half (gate/plain rows, up rows), copied to shared memory so the absmax chain has no global
-    // load in it. A window that does not fit is read from global memory instead.
-    unsigned win_lo[NP];
-    bool win_ok[NP];
-#pragma unroll
-    for (int h = 0; h < NP; ++h) {
-        win_lo[h] = 0;
-        win_ok[h] = false;
-        if (KIND == kAbsmaxCodes) {
-            const int n_a = min((rt_first + h * p.pair_rt_offset) * kTileRows, p.n_rows - 1);
-            const int n_b = min((rt_last + h * p.pair_rt_offset) * kTileRows + kTileRows - 1, p.n_rows - 1);
-            const unsigned f_lo = segment_row(p.sp, n_a).flat;
-            const unsigned f_hi = segment_row(p.sp, n_b).flat + ((unsigned)(p.KU - 1) >> p.sp.blk_shift);
-            win_lo[h] = f_lo >> p.sp.nbs_shift;
-            const unsigned cnt = (f_hi >> p.sp.nbs_shift) - win_lo[h] + 1;
-            win_ok[h] = cnt <= (unsigned)kNabsWindow;
-            if (win_ok[h])
-                for (unsigned i = tid; i < cnt; i += W * 32)
-                    sts_f32(a_nabsw + (uint32_t)(h * kNabsWindow + i) * 4u, __ldg(p.sp.nabs + win_lo[h] + i));
-        }
-    }
-    if (KIND == kAbsmaxCodes && tid < 256) sts_f32(a_nmap + 4u * tid, nmap_reg);
-    // x is the only input that may come from the previous kernel on the stream: everything above
-    // (and the producer's weight copies) ran without waiting for it
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    {
-        const int n16 = p.x_bytes >> 4;
-        const uint4* xg = reinterpret_cast<const uint4*>(p.x);
-        for (int i = tid; i < n16; i += W * 32) {
-            const uint4 v = __ldg(xg + i);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a_xs + 16u * i), "r"(v.x),
-                         "r"(v.y), "r"(v.z), "r"(v.w)
-                         : "memory");
-        }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
-
-    const int gq = lane >> 2;  // row inside the tile (and row + 8)
-    const int t = lane & 3;
-    const uint32_t lane_base = a_lut + ((uint32_t)lane << 2);
-    const uint32_t w_off = (uint32_t)(gq * 32 + 8 * t);  // this lane's 8 bytes inside a unit
-    // absmax decode: lane (half, r) owns row r of the gate/plain unit (half 0) or of the up
-    // unit (half 1); its flat block index base follows the row tile
-    const int dhalf = PAIRED ? (lane >> 4) : 0;
-    const int drow = lane & 15;
-    const uint32_t code_off = (uint32_t)(dhalf * half_bytes + kUnitNibbleBytes + drow);
-    const bool my_win_ok = win_ok[PAIRED ? dhalf : 0];
-    const unsigned my_win_lo = win_lo[PAIRED ? dhalf : 0];
-    const uint32_t my_win = a_nabsw + (uint32_t)((PAIRED ? dhalf : 0) * kNabsWindow) * 4u;
-
-    float acc[NP][2];
-#pragma unroll
-    for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
-    int cur_li = -1;
-    unsigned done_mask = 0;  // local tiles this warp has signed off
-
-    // ---- completing a row tile: the warp that signs off last sums the per-warp slots ----
+    // ---- completing a row tile (finalizer warp): sum the per-warp slots, then either write the
+    // rows or, for a tile shared with a neighbouring CTA, publish the partial sums ----
     auto finalize_tile = [&](int li) {
         const int r = lane & 15;
         const int rtile = rt_first + li;
@@ -421,7 +328,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #pragma unroll
                 for (int h = 0; h < NP; ++h) v[h] = 0.0f;
                 for (int cc = c_lo; cc <= c_hi; ++cc) {
-                    const int cc_first = slice_begin(p.slice_q, p.slice_r, cc, G) / p.KU;
+                    const int cc_first = fast_div(slice_begin(p, cc), p.div_ku_m, p.div_ku_s);
                     const int hs = (rtile == cc_first) ? 0 : 1;
 #pragma unroll
                     for (int h = 0; h < NP; ++h)
@@ -446,20 +353,266 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             }
         }
     };
+
+    if (warp == W) {
+        // ---------------- producer: sets up the barriers, then one thread keeps the ring full ----
+        if (lane == 0) NF4_TRACE(45);
+        if (lane < p.stages) {
+            mbar_init(&full[lane], 1);
+            mbar_init(&empty[lane], W);
+        }
+        if (lane < kMaxLocalTiles) mbar_init(&tile_bar[lane], W);
+        if (lane == 0) *abort_flag = 0;
+        mbar_fence_init();
+        __syncwarp();
+        // the other warps pick the initialised barriers up at their first CTA-wide barrier; the
+        // producer does not wait for them
+        asm volatile("bar.arrive 2, %0;" ::"n"(kStreamThreads) : "memory");
+        if (lane == 0) {
+            int issued = 0;
+            int s = 0;
+            uint32_t ph = 0;  // (g / stages) & 1
+            for (int g = 0; g < n_groups; ++g) {
+                if (g >= p.stages) {
+                    if (*(volatile int*)abort_flag) break;
+                    if (!mbar_wait_bounded(&empty[s], ph ^ 1u)) {
+                        atomicExch(p.status, kStatusTimeoutEmpty);
+                        *(volatile int*)abort_flag = 1;
+                        break;
+                    }
+                }
+                if (g < 8) NF4_TRACE(16 + g);
+                const int v0 = g * kStageItems;
+                const int cnt = min(kStageItems, len - v0);
+                uint8_t* dst = gen + a_ring + (size_t)s * stage_bytes;
+                mbar_expect_tx(&full[s], (uint32_t)cnt * unit_stride * NP);
+                // up to two contiguous pieces (the traversal wraps from the tail tile to the front)
+                const int n1 = v0 < tail_len ? min(cnt, tail_len - v0) : 0;
+                if (n1 > 0) {
+                    const size_t it = (size_t)(tail0 + v0);
+                    bulk_g2s(dst, p.units + it * unit_stride, (uint32_t)n1 * unit_stride, &full[s]);
+                    if (PAIRED)
+                        bulk_g2s(dst + half_bytes,
+                                 p.units + (it + (size_t)p.pair_rt_offset * p.KU) * unit_stride,
+                                 (uint32_t)n1 * unit_stride, &full[s]);
+                }
+                if (cnt > n1) {
+                    const size_t it = (size_t)(i0 + (v0 + n1 - tail_len));
+                    bulk_g2s(dst + n1 * unit_stride, p.units + it * unit_stride,
+                             (uint32_t)(cnt - n1) * unit_stride, &full[s]);
+                    if (PAIRED)
+                        bulk_g2s(dst + half_bytes + n1 * unit_stride,
+                                 p.units + (it + (size_t)p.pair_rt_offset * p.KU) * unit_stride,
+                                 (uint32_t)(cnt - n1) * unit_stride, &full[s]);
+                }
+                issued = g + 1;
+                if (++s == p.stages) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+            // never leave the CTA with copies still landing in its shared memory
+            // (walk back from the last issued group: s, ph describe group `issued`)
+            for (int g = issued - 1; g >= max(0, issued - p.stages); --g) {
+                if (--s < 0) {
+                    s = p.stages - 1;
+                    ph ^= 1u;
+                }
+                mbar_wait_bounded(&full[s], ph);
+            }
+        }
+        return;
+    }
+
+    if (warp == W + 1) {
+        // ---------------- finalizer: completes row tiles off the consumers' critical path -------
+        if (lane == 0) NF4_TRACE(46);
+        asm volatile("bar.sync 2, %0;" ::"n"(kStreamThreads) : "memory");
+        // tiles complete in traversal order: the slice's last tile, then the others from the front
+        for (int q = 0; q < n_local; ++q) {
+            const int li = (q == 0) ? n_local - 1 : q - 1;
+            bool ok = mbar_try_wait(&tile_bar[li], 0);
+            if (!ok) {
+                const long long t0 = clock64();
+                while (!ok) {
+#pragma unroll 1
+                    for (int i = 0; i < 64 && !ok; ++i) {
+                        __nanosleep(200);
+                        ok = mbar_try_wait(&tile_bar[li], 0);
+                    }
+                    if (ok) break;
+                    if (*(volatile int*)abort_flag) break;
+                    if (clock64() - t0 > kSpinLimitCycles) {
+                        atomicExch(p.status, kStatusTimeoutFull);
+                        break;
+                    }
+                }
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            finalize_tile(li);
+#ifdef AILA_NF4_TRACE
+            if (lane == 0 && q < 8) NF4_TRACE(32 + q);
+#endif
+        }
+#ifdef AILA_NF4_TRACE
+        if (lane == 0) {
+            unsigned long long t_;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
+            atomicMax(&g_trace[p.trace_idx][blockIdx.x % 160][30], t_);
+        }
+#endif
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    if (tid == 0) NF4_TRACE(40);
+    // static inputs first: their latency overlaps the set-up arithmetic below
+    float nmap_reg = 0.0f, q_hi = 0.0f, q_lo = 0.0f;
+    if (tid < 256) {
+        if (KIND == kAbsmaxCodes) nmap_reg = __ldg(p.sp.nmap + tid);
+        q_hi = __ldg(p.qmap + (tid >> 4));
+        q_lo = __ldg(p.qmap + (tid & 15));
+    }
+    // Second-level scales this CTA can need: one window of consecutive nested_absmax entries per
+    // half (gate/plain rows, up rows), copied to shared memory so the absmax chain has no global
+    // load in it. A window that does not fit is read from global memory instead.
+    unsigned win_lo[NP];
+    bool win_ok[NP];
+    float win_reg[NP];
+#pragma unroll
+    for (int h = 0; h < NP; ++h) {
+        win_lo[h] = 0;
+        win_ok[h] = false;
+        win_reg[h] = 0.0f;
+        if (KIND == kAbsmaxCodes) {
+            const int n_a = min((rt_first + h * p.pair_rt_offset) * kTileRows, p.n_rows - 1);
+            const int n_b = min((rt_last + h * p.pair_rt_offset) * kTileRows + kTileRows - 1, p.n_rows - 1);
+            const unsigned f_lo = segment_row(p.sp, n_a).flat;
+            const unsigned f_hi = segment_row(p.sp, n_b).flat + ((unsigned)(p.KU - 1) >> p.sp.blk_shift);
+            win_lo[h] = f_lo >> p.sp.nbs_shift;
+            const unsigned cnt = (f_hi >> p.sp.nbs_shift) - win_lo[h] + 1;
+            win_ok[h] = cnt <= (unsigned)kNabsWindow;
+            static_assert(kNabsWindow <= W * 32, "one window entry per consumer thread");
+            if (win_ok[h] && (unsigned)tid < cnt) win_reg[h] = __ldg(p.sp.nabs + win_lo[h] + tid);
+        }
+    }
+    if (tid == 0) NF4_TRACE(41);
+    for (int i = tid; i < kMaxLocalTiles * NP * W * 16; i += W * 32) sts_f32(a_slots + 4u * i, 0.0f);
+    if (tid == 0) NF4_TRACE(42);
+
+    const int gq = lane >> 2;  // row inside the tile (and row + 8)
+    const int t = lane & 3;
+    const uint32_t lane_base = a_lut + ((uint32_t)lane << 2);
+    const uint32_t w_off = (uint32_t)(gq * 32 + 8 * t);  // this lane's 8 bytes inside a unit
+    // absmax decode: lane (half, r) owns row r of the gate/plain unit (half 0) or of the up
+    // unit (half 1); its flat block index base follows the row tile
+    const int dhalf = PAIRED ? (lane >> 4) : 0;
+    const int drow = lane & 15;
+    const uint32_t code_off = (uint32_t)(dhalf * half_bytes + kUnitNibbleBytes + drow);
+    const bool my_win_ok = dhalf ? win_ok[NP - 1] : win_ok[0];
+    const unsigned my_win_lo = dhalf ? win_lo[NP - 1] : win_lo[0];
+    const uint32_t my_win = a_nabsw + (uint32_t)((PAIRED ? dhalf : 0) * kNabsWindow) * 4u;
+
+    float acc[NP][2];
+#pragma unroll
+    for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
+    int cur_li = -1;
+    unsigned done_mask = 0;  // local tiles this warp has signed off
+
+    // position of this warp's first item of the current group; its IPW items are consecutive
+    int v = warp * IPW;
+    int kb = 0, rt = rt_first;
+    unsigned d_flat = 0;
+    float d_off = 0.0f;
+    auto locate = [&](int vv) {  // (kb, rt) of virtual position vv
+        const int it = vv < tail_len ? tail0 + vv : i0 + (vv - tail_len);
+        rt = fast_div(it, p.div_ku_m, p.div_ku_s);
+        kb = it - rt * p.KU;
+    };
+    auto refresh = [&]() {  // absmax row base of this lane for row tile rt
+        if (KIND == kAbsmaxCodes) {
+            // rows past the end of the linear (padding of the last tile) borrow the last row's scale
+            const int n = min((rt + dhalf * p.pair_rt_offset) * kTileRows + drow, p.n_rows - 1);
+            const SegmentRow sr = segment_row(p.sp, n);
+            d_flat = sr.flat;
+            d_off = sr.offset;
+        }
+    };
+    if (v < len) {
+        locate(v);
+        refresh();
+    }
+    const int kb_step = p.kb_step;  // from a run's last item + 1 to the next run
+    const int rt_step = p.rt_step;
+
+    if (tid == 0) NF4_TRACE(43);
+    // the loaded static inputs go to shared memory; after the CTA-wide barrier the table is built
+    if (tid < 256) {
+        // byte value tid -> bf16 pair of its two nibbles; low half = first weight (HIGH nibble)
+        const uint32_t ptab_reg = (uint32_t)f32_to_bf16_bits(q_hi) | ((uint32_t)f32_to_bf16_bits(q_lo) << 16);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(a_ptab + 4u * tid), "r"(ptab_reg) : "memory");
+        if (KIND == kAbsmaxCodes) sts_f32(a_nmap + 4u * tid, nmap_reg);
+    }
+    if (KIND == kAbsmaxCodes) {
+#pragma unroll
+        for (int h = 0; h < NP; ++h)
+            if (win_ok[h] && tid < kNabsWindow) sts_f32(a_nabsw + (uint32_t)(h * kNabsWindow + tid) * 4u, win_reg[h]);
+    }
+    if (tid == 0) NF4_TRACE(44);
+    asm volatile("bar.sync 2, %0;" ::"n"(kStreamThreads) : "memory");
+    if (tid == 0) NF4_TRACE(1);
+    // x is the only input that may come from the previous kernel on the stream: everything above
+    // (and the producer's weight copies) ran without waiting for it
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) NF4_TRACE(3);
+    // element k = 64*kb + 16*j + 4*t + e goes to fragment order: 16-byte slot (kb*2 + j/2)*4 + t
+    // holds tiles j = 2*(j/2) and +1 for lane column t
+    const int n8 = p.x_bytes >> 3;
+    const uint2* xg = reinterpret_cast<const uint2*>(p.x);
+    auto slot_of = [&](int q4) {
+        const int kbx = q4 >> 4, j = (q4 >> 2) & 3, tt = q4 & 3;
+        return a_xs + (uint32_t)((((kbx * 2 + (j >> 1)) * 4 + tt) * 2 + (j & 1)) * 8);
+    };
+    auto sts_x = [&](int q4, uint2 xv) {
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(slot_of(q4)), "r"(xv.x), "r"(xv.y) : "memory");
+    };
+    // the first two pieces per thread are fetched now and stored after the table build, which
+    // runs under their latency
+    uint2 xv0 = make_uint2(0u, 0u), xv1 = make_uint2(0u, 0u);
+    if (tid < n8) xv0 = __ldg(xg + tid);
+    if (tid + W * 32 < n8) xv1 = __ldg(xg + tid + W * 32);
+    {
+        // Table rows are 128 bytes (one word per lane) on a 256-byte pitch. One 16-byte store per
+        // lane fills four rows: lane l writes piece l % 8 of row 4*r4 + l / 8.
+        for (int r4 = warp; r4 < 64; r4 += W) {
+            const int b = r4 * 4 + (lane >> 3);
+            const uint32_t pv = lds_u32(a_ptab + 4u * (uint32_t)b);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a_lut + (uint32_t)b * 256u +
+                                                                         (uint32_t)(lane & 7) * 16u),
+                         "r"(pv)
+                         : "memory");
+        }
+    }
+    if (tid == 0) NF4_TRACE(2);
+    if (tid < n8) sts_x(tid, xv0);
+    if (tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
+    for (int q4 = tid + 2 * W * 32; q4 < n8; q4 += 2 * W * 32) {
+        const int q5 = q4 + W * 32;
+        const uint2 v0 = __ldg(xg + q4);
+        uint2 v1 = make_uint2(0u, 0u);
+        if (q5 < n8) v1 = __ldg(xg + q5);
+        sts_x(q4, v0);
+        if (q5 < n8) sts_x(q5, v1);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+    if (tid == 0) NF4_TRACE(4);
+
     // every warp signs off every local tile exactly once, after its last contribution to it
     auto sign_off = [&](int li) {
         __syncwarp();
-        int old = 0;
-        if (lane == 0) {
-            __threadfence_block();
-            old = atomicAdd(&tile_done[li], 1);
-        }
-        old = __shfl_sync(0xffffffffu, old, 0);
+        if (lane == 0) mbar_arrive(&tile_bar[li]);
         done_mask |= 1u << li;
-        if (old == W - 1) {
-            __threadfence_block();
-            finalize_tile(li);
-        }
     };
     auto flush_current = [&]() {
         if (cur_li >= 0) {
@@ -477,53 +630,32 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
     };
 
-    // position of this warp's first item of the current group; its IPW items are consecutive
-    int v = warp * IPW;
-    int kb = 0, rt = rt_first;
-    unsigned d_flat = 0;
-    float d_off = 0.0f;
-    auto locate = [&](int vv) {  // (kb, rt) of virtual position vv
-        const int it = vv < tail_len ? tail0 + vv : i0 + (vv - tail_len);
-        rt = it / p.KU;
-        kb = it - rt * p.KU;
-    };
-    auto refresh = [&]() {  // absmax row base of this lane for row tile rt
-        if (KIND == kAbsmaxCodes) {
-            // rows past the end of the linear (padding of the last tile) borrow the last row's scale
-            const int n = min((rt + dhalf * p.pair_rt_offset) * kTileRows + drow, p.n_rows - 1);
-            const SegmentRow sr = segment_row(p.sp, n);
-            d_flat = sr.flat;
-            d_off = sr.offset;
-        }
-    };
-    if (v < len) {
-        locate(v);
-        refresh();
-    }
-    const int kb_step = (kStageItems - IPW) % p.KU;  // from a run's last item + 1 to the next run
-    const int rt_step = (kStageItems - IPW) / p.KU;
-
     bool failed = false;
+    int s = 0;
+    uint32_t ph = 0;  // (g / stages) & 1
     for (int g = 0; g < n_groups; ++g) {
-        const int s = g % p.stages;
-        if (!mbar_wait_bounded(&full[s], (g / p.stages) & 1)) {
+        if (!mbar_wait_bounded(&full[s], ph)) {
             atomicExch(p.status, kStatusTimeoutFull);
             *(volatile int*)abort_flag = 1;
             failed = true;
             break;
         }
+        if (tid == 0 && g < 8) NF4_TRACE(5 + g);
         uint32_t ua = a_ring + (uint32_t)s * stage_bytes + (uint32_t)(warp * IPW) * unit_stride;
         const int nvalid = min(IPW, len - v);
 #pragma unroll
         for (int i = 0; i < IPW; ++i) {
             if (i < nvalid) {
                 // ---- one work item: unit (rt, kb) [and its up partner] ----
-                const uint32_t xa = a_xs + (uint32_t)kb * 128u + 8u * t;
-                uint2 xf[4];
-                // x fragments (batch column 0) live in the four lanes with gq == 0; the other
-                // columns of the 8-wide tile stay zero. 8 bytes per tile: x[64kb + 16j + 4t ..]
-#pragma unroll
-                for (int j = 0; j < 4; ++j) xf[j] = lds_v2_if_zero(xa + 32u * j, gq);
+                // x fragments: two 16-byte loads per lane (tiles j = 0,1 and j = 2,3). All eight
+                // lanes that share t read the same address (a broadcast), so the 8-wide tile
+                // carries x in every batch column; only column 0 is read back.
+                const uint32_t xa = a_xs + (uint32_t)kb * 128u + 16u * t;
+                uint4 xq0, xq1;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(xq0.x), "=r"(xq0.y), "=r"(xq0.z), "=r"(xq0.w) : "r"(xa));
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(xq1.x), "=r"(xq1.y), "=r"(xq1.z), "=r"(xq1.w) : "r"(xa + 64u));
                 float am0[NP], am1[NP];
                 if (KIND == kAbsmaxCodes) {
                     const unsigned code = lds_u8(ua + code_off);
@@ -549,8 +681,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 for (int h = 0; h < NP; ++h) {
                     const uint2 l = lds_v2(ua + h * half_bytes + w_off);
                     const uint2 u = lds_v2(ua + h * half_bytes + w_off + 256u);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) c0[h][e] = c1[h][e] = 0.0f;
                     // all 16 table lookups first (independent loads), then the four tiles:
                     // j = 0: bytes 0,1 of .x ; j = 1: bytes 2,3 of .x ; j = 2,3: .y
                     uint32_t a[16];
@@ -562,10 +692,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     a[10] = lut_pair<1>(l.y, lane_base); a[11] = lut_pair<1>(u.y, lane_base);
                     a[12] = lut_pair<2>(l.y, lane_base); a[13] = lut_pair<2>(u.y, lane_base);
                     a[14] = lut_pair<3>(l.y, lane_base); a[15] = lut_pair<3>(u.y, lane_base);
-                    mma_bf16_16816(c0[h], a[0], a[1], a[2], a[3], xf[0].x, xf[0].y);
-                    mma_bf16_16816(c1[h], a[4], a[5], a[6], a[7], xf[1].x, xf[1].y);
-                    mma_bf16_16816(c0[h], a[8], a[9], a[10], a[11], xf[2].x, xf[2].y);
-                    mma_bf16_16816(c1[h], a[12], a[13], a[14], a[15], xf[3].x, xf[3].y);
+                    mma_bf16_16816_init(c0[h], a[0], a[1], a[2], a[3], xq0.x, xq0.y);
+                    mma_bf16_16816_init(c1[h], a[4], a[5], a[6], a[7], xq0.z, xq0.w);
+                    mma_bf16_16816(c0[h], a[8], a[9], a[10], a[11], xq1.x, xq1.y);
+                    mma_bf16_16816(c1[h], a[12], a[13], a[14], a[15], xq1.z, xq1.w);
                 }
                 // ---- accumulate into the current row tile (switching tiles is rare) ----
                 const int li = rt - rt_first;
@@ -602,6 +732,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         // the stage's shared memory is no longer needed by this warp
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+        if (tid == 0 && g < 8) NF4_TRACE(24 + g);
+        if (++s == p.stages) {
+            s = 0;
+            ph ^= 1u;
+        }
         // ---- first item of this warp's run in the next group ----
         // (kb, rt) now describe position v + nvalid of the traversal
         const int vend = v + nvalid;
@@ -623,11 +758,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         }
     }
     if (failed) return;
+    if (tid == 0) NF4_TRACE(13);
     // last contribution of this warp, then sign off whatever it never touched
     flush_current();
     cur_li = -1;
     for (int q = 0; q < n_local; ++q)
         if (!((done_mask >> q) & 1u)) sign_off(q);
+#ifdef AILA_NF4_TRACE
+    if (tid == 0) NF4_TRACE(14);
+    if (lane == 0) {
+        unsigned long long t_;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
+        atomicMax(&g_trace[p.trace_idx][blockIdx.x % 160][30], t_);
+    }
+#endif
 }
 
 struct StreamPlan {
@@ -648,7 +792,7 @@ StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int
     const int x_bytes = (int)((w.K * 2 + 15) / 16 * 16);
     // region A (below the table, which sits at shared address 64 KB): barriers, counters, code
     // book, slots and x if it fits; region B (from 128 KB): x otherwise, then the ring
-    const int a_used = 2048 + 16 + 400 + 64 + 1024 + 2 * kNabsWindow * 4 +
+    const int a_used = 2048 + 16 + 400 + 64 + 1024 + 2 * kNabsWindow * 4 + 1024 +
                        kMaxLocalTiles * np * kConsumerWarps * 64;
     pl.x_in_b = (a_used + x_bytes > 65536) ? 1 : 0;
     const int b_capacity = 227 * 1024 - 131072;
@@ -767,21 +911,7 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     if (!pl.ok) return cudaErrorInvalidConfiguration;
     StreamParams p;
     p.units = w.d_units;
-    {
-        // bf16 (round-to-nearest-even) of the 16 code-book values, paired per byte value:
-        // low half = first weight of the byte (even k, HIGH nibble)
-        uint32_t qb[16];
-        for (int i = 0; i < 16; ++i) {
-            uint32_t u;
-            std::memcpy(&u, &w.h_qmap[i], 4);
-            if ((u & 0x7fffffffu) > 0x7f800000u) {
-                qb[i] = (u >> 16) | 0x40u;
-            } else {
-                qb[i] = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
-            }
-        }
-        for (int b = 0; b < 256; ++b) p.pair_table[b] = qb[b >> 4] | (qb[b & 15] << 16);
-    }
+    p.qmap = w.d_qmap;
     p.sp = w.scale_params();
     p.x = static_cast<const uint16_t*>(x);
     p.y = static_cast<uint16_t*>(y);
@@ -793,6 +923,10 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.total_items = rt_work * w.KU;
     p.slice_q = p.total_items / pl.grid;
     p.slice_r = p.total_items % pl.grid;
+    make_fast_div((uint32_t)pl.grid, &p.div_g_m, &p.div_g_s);
+    make_fast_div((uint32_t)w.KU, &p.div_ku_m, &p.div_ku_s);
+    p.kb_step = (kStageItems - kItemsPerWarp) % w.KU;
+    p.rt_step = (kStageItems - kItemsPerWarp) / w.KU;
     p.n_out = paired ? (int)ff_pair : (int)w.N;
     p.K = (int)w.K;
     p.KU = w.KU;
@@ -803,6 +937,10 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.x_in_b = pl.x_in_b;
     p.smem_bytes = pl.smem;
     p.n_rows = (int)w.N;
+#ifdef AILA_NF4_TRACE
+    static int trace_counter = 0;
+    p.trace_idx = trace_counter++ % 32;
+#endif
     if (w.absmax_kind == kAbsmaxCodes)
         return paired ? launch_stream_t<kAbsmaxCodes, true>(p, pl.grid, pl.smem, s)
                       : launch_stream_t<kAbsmaxCodes, false>(p, pl.grid, pl.smem, s);
@@ -856,3 +994,9 @@ AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, v
 }
 
 }  // namespace nf4
+
+#ifdef AILA_NF4_TRACE
+extern "C" __attribute__((visibility("default"))) int aila_nf4_debug_trace(void* dst) {
+    return (int)cudaMemcpyFromSymbol(dst, nf4::g_trace, sizeof(nf4::g_trace));
+}
+#endif
