@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -47,12 +48,67 @@ struct DeviceGuard {
     }
 };
 
+// Code-book tables (the 16-entry first-level map, the 256-entry second-level map) are the same
+// in every layer of a model. One device copy per distinct content and device is shared by all
+// linears that use it, so back-to-back launches for different layers find the table in L2
+// instead of fetching a private copy from HBM at every kernel start.
+struct InternedTable {
+    int device = 0;
+    std::vector<uint32_t> bits;
+    float* ptr = nullptr;
+    int refs = 0;
+};
+std::mutex g_intern_mutex;
+std::vector<InternedTable> g_interned;
+
+cudaError_t intern_table(float** dst, const float* src, size_t count, bool src_on_device,
+                         int device) {
+    std::vector<uint32_t> bits(count);
+    cudaError_t e = cudaMemcpy(bits.data(), src, count * 4,
+                               src_on_device ? cudaMemcpyDeviceToHost : cudaMemcpyHostToHost);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(g_intern_mutex);
+    for (auto& t : g_interned)
+        if (t.device == device && t.bits == bits) {
+            ++t.refs;
+            *dst = t.ptr;
+            return cudaSuccess;
+        }
+    InternedTable t;
+    t.device = device;
+    e = cudaMalloc(reinterpret_cast<void**>(&t.ptr), count * 4 + 16);
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpy(t.ptr, bits.data(), count * 4, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(t.ptr);
+        return e;
+    }
+    t.bits = std::move(bits);
+    t.refs = 1;
+    *dst = t.ptr;
+    g_interned.push_back(std::move(t));
+    return cudaSuccess;
+}
+
+void release_table(float* ptr) {
+    if (!ptr) return;
+    std::lock_guard<std::mutex> lock(g_intern_mutex);
+    for (size_t i = 0; i < g_interned.size(); ++i)
+        if (g_interned[i].ptr == ptr) {
+            if (--g_interned[i].refs == 0) {
+                cudaFree(ptr);
+                g_interned.erase(g_interned.begin() + (long)i);
+            }
+            return;
+        }
+}
+
 void free_linear(AilaNf4Linear* l) {
     if (!l) return;
     DeviceGuard g(l->device);
     cudaFree(l->d_units);
-    cudaFree(l->d_qmap);
-    cudaFree(l->d_nmap);
+    release_table(l->d_qmap);
+    release_table(l->d_nmap);
     cudaFree(l->d_nabs);
     cudaFree(l->d_cache_bf16);
     delete l;
@@ -171,11 +227,11 @@ AilaNf4Status create_slice(const AilaNf4WeightDesc* d, int64_t row0, int64_t row
     } while (0)
 
     NF4_TRY(cudaMalloc(reinterpret_cast<void**>(&l->d_units), l->units_bytes() + 16));
-    NF4_TRY(upload(&l->d_qmap, d->quant_map, 16, dev_src));
+    NF4_TRY(intern_table(&l->d_qmap, d->quant_map, 16, dev_src, l->device));
     NF4_TRY(cudaMemcpy(l->h_qmap, d->quant_map, 16 * sizeof(float),
                        dev_src ? cudaMemcpyDeviceToHost : cudaMemcpyHostToHost));
     if (d->nested) {
-        NF4_TRY(upload(&l->d_nmap, d->nested_quant_map, 256, dev_src));
+        NF4_TRY(intern_table(&l->d_nmap, d->nested_quant_map, 256, dev_src, l->device));
         NF4_TRY(upload(&l->d_nabs, d->nested_absmax, (size_t)d->nested_absmax_count, dev_src));
         l->nabs_count = d->nested_absmax_count;
     }
@@ -431,7 +487,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_linear_create_fused_rows(AilaNf4Linear* cons
         if (e__ != cudaSuccess) return bail(nf4::cuda_fail(e__, #call)); \
     } while (0)
     NF4_TRY(cudaMalloc(reinterpret_cast<void**>(&l->d_units), l->units_bytes() + 16));
-    NF4_TRY(upload(&l->d_qmap, first->d_qmap, 16, true));
+    NF4_TRY(intern_table(&l->d_qmap, first->d_qmap, 16, true, l->device));
     if (l->absmax_kind == nf4::kAbsmaxCodes) {
         // the second-level code book must be the same table in every source
         std::vector<float> ref(256), cur(256);
@@ -442,7 +498,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_linear_create_fused_rows(AilaNf4Linear* cons
                 return bail(fail(AILA_NF4_ERR_UNSUPPORTED,
                                  "fused sources use different nested quant maps"));
         }
-        NF4_TRY(upload(&l->d_nmap, first->d_nmap, 256, true));
+        NF4_TRY(intern_table(&l->d_nmap, first->d_nmap, 256, true, l->device));
         NF4_TRY(cudaMalloc(reinterpret_cast<void**>(&l->d_nabs), (size_t)total_nabs * 4 + 16));
         l->nabs_count = total_nabs;
     }

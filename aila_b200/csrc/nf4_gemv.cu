@@ -111,6 +111,7 @@ constexpr int kMaxStages = 24;
 constexpr int kMaxLocalTiles = 8;  // row tiles one CTA slice may touch
 constexpr int kMaxGridMult = 8;     // grid <= 8 x SM count
 constexpr int kNabsWindow = 256;    // second-level scales kept in shared memory per half
+constexpr int kPairSkewBytes = 64;  // shared-memory distance added between a stage's gate and up units
 
 struct StreamParams {
     const uint8_t* units;
@@ -126,7 +127,7 @@ struct StreamParams {
     int slice_q, slice_r;   // total_items = slice_q * grid + slice_r
     uint32_t div_g_m, div_ku_m;  // multiply-shift division by the grid size and by KU
     int div_g_s, div_ku_s;
-    int kb_step, rt_step;   // (stage items - items per warp) mod / div KU
+    int kb_step, rt_step;   // consumer warp count mod / div KU (a warp's items are that far apart)
     int n_out;              // rows written (ff when paired)
     int K;
     int KU;
@@ -231,14 +232,22 @@ __device__ unsigned long long g_trace[32][160][96];
 template <int KIND, bool PAIRED>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
 #ifdef AILA_NF4_TRACE
-    if (threadIdx.x == 0) { NF4_TRACE(0); g_trace[p.trace_idx][blockIdx.x % 160][30] = 0; }
+    if (threadIdx.x == 0) {
+        NF4_TRACE(0);
+        g_trace[p.trace_idx][blockIdx.x % 160][30] = 0;
+        unsigned smid_;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
+        g_trace[p.trace_idx][blockIdx.x % 160][94] = smid_;
+    }
 #endif
     constexpr int NP = PAIRED ? 2 : 1;
     constexpr int W = kConsumerWarps;
     constexpr int IPW = kItemsPerWarp;
     constexpr int unit_stride = (KIND == kAbsmaxCodes) ? kUnitStrideCodes : kUnitStrideF32;
-    constexpr int half_bytes = kStageItems * unit_stride;  // one stage of gate (or plain) units
-    constexpr int stage_bytes = half_bytes * NP;
+    // one stage of gate (or plain) units; the up units follow 64 bytes (16 banks) further so that
+    // the two halves' absmax bytes never meet in one bank
+    constexpr int half_bytes = kStageItems * unit_stride + (PAIRED ? kPairSkewBytes : 0);
+    constexpr int stage_bytes = kStageItems * unit_stride * NP + (PAIRED ? kPairSkewBytes : 0);
 
     // ---- shared-memory map (absolute shared-window addresses) ----
     // region A = [base, 64 KB): barriers, tile counters, code book, per-warp slots, x (if small)
@@ -249,10 +258,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const uint32_t a_tile = a_bar + 400;                         // tile_bar[kMaxLocalTiles]
     static_assert((2 * kMaxStages + 1) * 8 <= 400, "barrier block");
     static_assert(kMaxLocalTiles * 8 <= 64, "tile barrier block");
-    const uint32_t a_nmap = a_tile + 64;
+    const uint32_t a_info = a_tile + 64;                         // per half: window base, window valid
+    const uint32_t a_nmap = a_info + 16;
     const uint32_t a_nabsw = a_nmap + 1024;                      // [2][kNabsWindow] second-level scales
     const uint32_t a_ptab = a_nabsw + 2 * kNabsWindow * 4;       // [256] byte value -> bf16 pair
-    const uint32_t a_slots = a_ptab + 1024;                      // [tile][pair][warp][16] floats
+    const uint32_t a_tinfo = a_ptab + 1024;                      // [tile][lane] absmax row base, offset
+    const uint32_t a_slots = a_tinfo + kMaxLocalTiles * 32 * 8;  // [tile][pair][warp][16] floats
     const uint32_t a_xs_small = a_slots + kMaxLocalTiles * NP * W * 64;
     const uint32_t a_lut = 65536u;
     const uint32_t a_xs = p.x_in_b ? 131072u : a_xs_small;
@@ -266,6 +277,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    // static tables (shared by every launch that uses the same code books): requested before
+    // anything else, consumed after the set-up arithmetic
+    float nmap_reg = 0.0f, q_hi = 0.0f, q_lo = 0.0f;
+    if (tid < 256) {
+        if (KIND == kAbsmaxCodes) nmap_reg = __ldg(p.sp.nmap + tid);
+        q_hi = __ldg(p.qmap + (tid >> 4));
+        q_lo = __ldg(p.qmap + (tid & 15));
+    }
     const int G = gridDim.x;
     const int c = blockIdx.x;
     const int i0 = slice_begin(p, c);
@@ -467,52 +486,52 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 
     // ---------------- consumers ----------------
     if (tid == 0) NF4_TRACE(40);
-    // static inputs first: their latency overlaps the set-up arithmetic below
-    float nmap_reg = 0.0f, q_hi = 0.0f, q_lo = 0.0f;
-    if (tid < 256) {
-        if (KIND == kAbsmaxCodes) nmap_reg = __ldg(p.sp.nmap + tid);
-        q_hi = __ldg(p.qmap + (tid >> 4));
-        q_lo = __ldg(p.qmap + (tid & 15));
-    }
     // Second-level scales this CTA can need: one window of consecutive nested_absmax entries per
     // half (gate/plain rows, up rows), copied to shared memory so the absmax chain has no global
-    // load in it. A window that does not fit is read from global memory instead.
-    unsigned win_lo[NP];
-    bool win_ok[NP];
-    float win_reg[NP];
+    // load in it. A window that does not fit is read from global memory instead. Warp 8 + h
+    // prepares the window of half h and publishes its base and validity.
+    static_assert(W >= 8 + NP, "window warps");
+    static_assert(kNabsWindow == 256, "eight window entries per lane");
+    float win_reg[8];
+    unsigned wwin_lo = 0;
+    bool wwin_ok = false;
+    const int wh = warp - 8;  // the half this warp prepares, if in [0, NP)
+    if (KIND == kAbsmaxCodes && wh >= 0 && wh < NP) {
+        const int n_a = min((rt_first + wh * p.pair_rt_offset) * kTileRows, p.n_rows - 1);
+        const int n_b = min((rt_last + wh * p.pair_rt_offset) * kTileRows + kTileRows - 1, p.n_rows - 1);
+        const unsigned f_lo = segment_row(p.sp, n_a).flat;
+        const unsigned f_hi = segment_row(p.sp, n_b).flat + ((unsigned)(p.KU - 1) >> p.sp.blk_shift);
+        wwin_lo = f_lo >> p.sp.nbs_shift;
+        const unsigned cnt = (f_hi >> p.sp.nbs_shift) - wwin_lo + 1;
+        wwin_ok = cnt <= (unsigned)kNabsWindow;
 #pragma unroll
-    for (int h = 0; h < NP; ++h) {
-        win_lo[h] = 0;
-        win_ok[h] = false;
-        win_reg[h] = 0.0f;
-        if (KIND == kAbsmaxCodes) {
-            const int n_a = min((rt_first + h * p.pair_rt_offset) * kTileRows, p.n_rows - 1);
-            const int n_b = min((rt_last + h * p.pair_rt_offset) * kTileRows + kTileRows - 1, p.n_rows - 1);
-            const unsigned f_lo = segment_row(p.sp, n_a).flat;
-            const unsigned f_hi = segment_row(p.sp, n_b).flat + ((unsigned)(p.KU - 1) >> p.sp.blk_shift);
-            win_lo[h] = f_lo >> p.sp.nbs_shift;
-            const unsigned cnt = (f_hi >> p.sp.nbs_shift) - win_lo[h] + 1;
-            win_ok[h] = cnt <= (unsigned)kNabsWindow;
-            static_assert(kNabsWindow <= W * 32, "one window entry per consumer thread");
-            if (win_ok[h] && (unsigned)tid < cnt) win_reg[h] = __ldg(p.sp.nabs + win_lo[h] + tid);
+        for (int i = 0; i < 8; ++i) {
+            win_reg[i] = 0.0f;
+            if (wwin_ok && (unsigned)(lane + 32 * i) < cnt) win_reg[i] = __ldg(p.sp.nabs + wwin_lo + lane + 32 * i);
         }
     }
-    if (tid == 0) NF4_TRACE(41);
-    for (int i = tid; i < kMaxLocalTiles * NP * W * 16; i += W * 32) sts_f32(a_slots + 4u * i, 0.0f);
+    {
+        constexpr int kSlotVecs = kMaxLocalTiles * NP * W * 16 / 4;
+#pragma unroll
+        for (int i = 0; i < (kSlotVecs + W * 32 - 1) / (W * 32); ++i) {
+            const int q = tid + i * W * 32;
+            if (q < kSlotVecs)
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a_slots + 16u * q), "r"(0u) : "memory");
+        }
+    }
     if (tid == 0) NF4_TRACE(42);
 
     const int gq = lane >> 2;  // row inside the tile (and row + 8)
     const int t = lane & 3;
     const uint32_t lane_base = a_lut + ((uint32_t)lane << 2);
     const uint32_t w_off = (uint32_t)(gq * 32 + 8 * t);  // this lane's 8 bytes inside a unit
-    // absmax decode: lane (half, r) owns row r of the gate/plain unit (half 0) or of the up
-    // unit (half 1); its flat block index base follows the row tile
-    const int dhalf = PAIRED ? (lane >> 4) : 0;
-    const int drow = lane & 15;
+    // absmax decode: the four lanes of a quad (same gq) decode the four scales that the quad's
+    // lane t = 0 applies: lane t owns row gq + 8*(t & 1) of the gate/plain unit (t < 2) or of the
+    // up unit (t >= 2); an unpaired launch uses t = 0, 1 only
+    const int dhalf = PAIRED ? (t >> 1) : 0;
+    const int drow = gq + 8 * (t & 1);
     const uint32_t code_off = (uint32_t)(dhalf * half_bytes + kUnitNibbleBytes + drow);
-    const bool my_win_ok = dhalf ? win_ok[NP - 1] : win_ok[0];
-    const unsigned my_win_lo = dhalf ? win_lo[NP - 1] : win_lo[0];
-    const uint32_t my_win = a_nabsw + (uint32_t)((PAIRED ? dhalf : 0) * kNabsWindow) * 4u;
+    const uint32_t my_win = a_nabsw + (uint32_t)(dhalf * kNabsWindow) * 4u;
 
     float acc[NP][2];
 #pragma unroll
@@ -520,48 +539,80 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     int cur_li = -1;
     unsigned done_mask = 0;  // local tiles this warp has signed off
 
-    // position of this warp's first item of the current group; its IPW items are consecutive
-    int v = warp * IPW;
+    // The items of a CTA are dealt to the warps round-robin: this warp takes the traversal
+    // positions v = warp, warp + W, warp + 2W, ... (IPW of them in every stage), so the warps'
+    // item counts differ by at most one.
+    int v = warp;
     int kb = 0, rt = rt_first;
     unsigned d_flat = 0;
     float d_off = 0.0f;
-    auto locate = [&](int vv) {  // (kb, rt) of virtual position vv
+    auto locate = [&](int vv) {  // (kb, rt) of traversal position vv
         const int it = vv < tail_len ? tail0 + vv : i0 + (vv - tail_len);
         rt = fast_div(it, p.div_ku_m, p.div_ku_s);
         kb = it - rt * p.KU;
     };
+    // absmax row base and offset of this lane's row in every local tile: warp li prepares tile li
+    if (KIND == kAbsmaxCodes && warp < n_local) {
+        // rows past the end of the linear (padding of the last tile) borrow the last row's scale
+        const int n = min((rt_first + warp + dhalf * p.pair_rt_offset) * kTileRows + drow, p.n_rows - 1);
+        const SegmentRow sr = segment_row(p.sp, n);
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_tinfo + (uint32_t)(warp * 32 + lane) * 8u),
+                     "r"(sr.flat), "r"(__float_as_uint(sr.offset)) : "memory");
+    }
     auto refresh = [&]() {  // absmax row base of this lane for row tile rt
         if (KIND == kAbsmaxCodes) {
-            // rows past the end of the linear (padding of the last tile) borrow the last row's scale
-            const int n = min((rt + dhalf * p.pair_rt_offset) * kTileRows + drow, p.n_rows - 1);
-            const SegmentRow sr = segment_row(p.sp, n);
-            d_flat = sr.flat;
-            d_off = sr.offset;
+            const uint2 ti = lds_v2(a_tinfo + (uint32_t)((rt - rt_first) * 32 + lane) * 8u);
+            d_flat = ti.x;
+            d_off = __uint_as_float(ti.y);
         }
     };
-    if (v < len) {
-        locate(v);
-        refresh();
-    }
-    const int kb_step = p.kb_step;  // from a run's last item + 1 to the next run
+    if (v < len) locate(v);
+    const int kb_step = p.kb_step;  // from one item of this warp to its next
     const int rt_step = p.rt_step;
-
     if (tid == 0) NF4_TRACE(43);
-    // the loaded static inputs go to shared memory; after the CTA-wide barrier the table is built
+
+    // the static tables go to shared memory; after the CTA-wide barrier the lookup table is built
     if (tid < 256) {
         // byte value tid -> bf16 pair of its two nibbles; low half = first weight (HIGH nibble)
         const uint32_t ptab_reg = (uint32_t)f32_to_bf16_bits(q_hi) | ((uint32_t)f32_to_bf16_bits(q_lo) << 16);
         asm volatile("st.shared.u32 [%0], %1;" ::"r"(a_ptab + 4u * tid), "r"(ptab_reg) : "memory");
         if (KIND == kAbsmaxCodes) sts_f32(a_nmap + 4u * tid, nmap_reg);
     }
-    if (KIND == kAbsmaxCodes) {
-#pragma unroll
-        for (int h = 0; h < NP; ++h)
-            if (win_ok[h] && tid < kNabsWindow) sts_f32(a_nabsw + (uint32_t)(h * kNabsWindow + tid) * 4u, win_reg[h]);
-    }
+    if (KIND == kAbsmaxCodes && wh >= 0 && wh < NP && lane == 0)
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_info + 8u * wh), "r"(wwin_lo), "r"(wwin_ok ? 1u : 0u) : "memory");
     if (tid == 0) NF4_TRACE(44);
     asm volatile("bar.sync 2, %0;" ::"n"(kStreamThreads) : "memory");
     if (tid == 0) NF4_TRACE(1);
+    unsigned my_win_lo = 0;
+    bool my_win_ok = false;
+    if (KIND == kAbsmaxCodes) {
+        const uint2 info = lds_v2(a_info + 8u * dhalf);
+        my_win_lo = info.x;
+        my_win_ok = info.y != 0u;
+    }
+    {
+        // Table rows are 128 bytes (one word per lane) on a 256-byte pitch. One 16-byte store per
+        // lane fills four rows: lane l writes piece l % 8 of row 4*r4 + l / 8.
+        static_assert(64 % W == 0, "table rows per warp");
+        uint32_t pv[64 / W];
+#pragma unroll
+        for (int i = 0; i < 64 / W; ++i)
+            pv[i] = lds_u32(a_ptab + 4u * (uint32_t)((warp + i * W) * 4 + (lane >> 3)));
+#pragma unroll
+        for (int i = 0; i < 64 / W; ++i) {
+            const int b = (warp + i * W) * 4 + (lane >> 3);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a_lut + (uint32_t)b * 256u +
+                                                                         (uint32_t)(lane & 7) * 16u),
+                         "r"(pv[i])
+                         : "memory");
+        }
+    }
+    if (tid == 0) NF4_TRACE(2);
+    if (KIND == kAbsmaxCodes && wh >= 0 && wh < NP && wwin_ok) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            sts_f32(a_nabsw + (uint32_t)(wh * kNabsWindow + lane + 32 * i) * 4u, win_reg[i]);
+    }
     // x is the only input that may come from the previous kernel on the stream: everything above
     // (and the producer's weight copies) ran without waiting for it
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -577,24 +628,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     auto sts_x = [&](int q4, uint2 xv) {
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(slot_of(q4)), "r"(xv.x), "r"(xv.y) : "memory");
     };
-    // the first two pieces per thread are fetched now and stored after the table build, which
-    // runs under their latency
     uint2 xv0 = make_uint2(0u, 0u), xv1 = make_uint2(0u, 0u);
     if (tid < n8) xv0 = __ldg(xg + tid);
     if (tid + W * 32 < n8) xv1 = __ldg(xg + tid + W * 32);
-    {
-        // Table rows are 128 bytes (one word per lane) on a 256-byte pitch. One 16-byte store per
-        // lane fills four rows: lane l writes piece l % 8 of row 4*r4 + l / 8.
-        for (int r4 = warp; r4 < 64; r4 += W) {
-            const int b = r4 * 4 + (lane >> 3);
-            const uint32_t pv = lds_u32(a_ptab + 4u * (uint32_t)b);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a_lut + (uint32_t)b * 256u +
-                                                                         (uint32_t)(lane & 7) * 16u),
-                         "r"(pv)
-                         : "memory");
-        }
-    }
-    if (tid == 0) NF4_TRACE(2);
+
     if (tid < n8) sts_x(tid, xv0);
     if (tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
     for (int q4 = tid + 2 * W * 32; q4 < n8; q4 += 2 * W * 32) {
@@ -607,6 +644,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     }
     asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
     if (tid == 0) NF4_TRACE(4);
+    if (v < len) refresh();
 
     // every warp signs off every local tile exactly once, after its last contribution to it
     auto sign_off = [&](int li) {
@@ -630,6 +668,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
     };
 
+    uint4 xq0 = make_uint4(0u, 0u, 0u, 0u), xq1 = make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t x_lane = (gq == 0) ? 1u : 0u;
     bool failed = false;
     int s = 0;
     uint32_t ph = 0;  // (g / stages) & 1
@@ -641,21 +681,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             break;
         }
         if (tid == 0 && g < 8) NF4_TRACE(5 + g);
-        uint32_t ua = a_ring + (uint32_t)s * stage_bytes + (uint32_t)(warp * IPW) * unit_stride;
-        const int nvalid = min(IPW, len - v);
+        const uint32_t ua0 = a_ring + (uint32_t)s * stage_bytes + (uint32_t)warp * unit_stride;
 #pragma unroll
         for (int i = 0; i < IPW; ++i) {
-            if (i < nvalid) {
+            if (v < len) {
+                const uint32_t ua = ua0 + (uint32_t)(i * W) * unit_stride;
                 // ---- one work item: unit (rt, kb) [and its up partner] ----
-                // x fragments: two 16-byte loads per lane (tiles j = 0,1 and j = 2,3). All eight
-                // lanes that share t read the same address (a broadcast), so the 8-wide tile
-                // carries x in every batch column; only column 0 is read back.
+                // x fragments: two 16-byte loads (tiles j = 0,1 and j = 2,3) in the four lanes
+                // that hold batch column 0 of the tile; the other columns stay zero and are never
+                // read back. A 16-byte load is served a quarter warp at a time, so the
+                // predicated pair costs two shared-memory wavefronts instead of eight.
                 const uint32_t xa = a_xs + (uint32_t)kb * 128u + 16u * t;
-                uint4 xq0, xq1;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(xq0.x), "=r"(xq0.y), "=r"(xq0.z), "=r"(xq0.w) : "r"(xa));
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(xq1.x), "=r"(xq1.y), "=r"(xq1.z), "=r"(xq1.w) : "r"(xa + 64u));
+                asm volatile(
+                    "{\n\t.reg .pred q;\n\t"
+                    "setp.ne.u32 q, %9, 0;\n\t"
+                    "@q ld.shared.v4.u32 {%0,%1,%2,%3}, [%8];\n\t"
+                    "@q ld.shared.v4.u32 {%4,%5,%6,%7}, [%8+64];\n\t}"
+                    : "+r"(xq0.x), "+r"(xq0.y), "+r"(xq0.z), "+r"(xq0.w), "+r"(xq1.x), "+r"(xq1.y),
+                      "+r"(xq1.z), "+r"(xq1.w)
+                    : "r"(xa), "r"(x_lane));
                 float am0[NP], am1[NP];
                 if (KIND == kAbsmaxCodes) {
                     const unsigned code = lds_u8(ua + code_off);
@@ -664,10 +708,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     const float scale = my_win_ok ? lds_f32(my_win + (sidx - my_win_lo) * 4u)
                                                   : __ldg(p.sp.nabs + sidx);
                     const float am = __fadd_rn(__fmul_rn(lds_f32(a_nmap + 4u * code), scale), d_off);
+                    // lane t = 0 of each quad collects the quad's scales (the other lanes get
+                    // values they never use)
 #pragma unroll
                     for (int h = 0; h < NP; ++h) {
-                        am0[h] = __shfl_sync(0xffffffffu, am, h * 16 + gq);
-                        am1[h] = __shfl_sync(0xffffffffu, am, h * 16 + gq + 8);
+                        am0[h] = (h == 0) ? am : __shfl_down_sync(0xffffffffu, am, 2 * h);
+                        am1[h] = __shfl_down_sync(0xffffffffu, am, 2 * h + 1);
                     }
                 } else {
 #pragma unroll
@@ -701,7 +747,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 const int li = rt - rt_first;
                 if (li != cur_li) {
                     flush_current();
-                    if (v + i >= tail_len) {
+                    if (v >= tail_len) {
                         // the front part runs through the tiles in order and never returns to
                         // the slice's last tile: sign off what this warp will not touch again
                         for (int q = 0; q < li; ++q)
@@ -715,18 +761,23 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     acc[h][0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][0]);
                     acc[h][1] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][1]);
                 }
-                // ---- next item of the run ----
-                ua += unit_stride;
-                if (v + i + 1 == tail_len) {
-                    if (v + i + 1 < len) {
-                        locate(v + i + 1);  // wrapped from the tail tile to the front of the slice
-                        refresh();
+                // ---- this warp's next item: W positions further along the traversal ----
+                const int vn = v + W;
+                if (vn < len) {
+                    const int rt_old = rt;
+                    if (v < tail_len && vn >= tail_len) {
+                        locate(vn);  // wrapped from the tail tile to the front of the slice
+                    } else {
+                        kb += kb_step;
+                        rt += rt_step;
+                        if (kb >= p.KU) {
+                            kb -= p.KU;
+                            ++rt;
+                        }
                     }
-                } else if (++kb == p.KU) {
-                    kb = 0;
-                    ++rt;
-                    refresh();
+                    if (rt != rt_old) refresh();
                 }
+                v = vn;
             }
         }
         // the stage's shared memory is no longer needed by this warp
@@ -737,25 +788,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             s = 0;
             ph ^= 1u;
         }
-        // ---- first item of this warp's run in the next group ----
-        // (kb, rt) now describe position v + nvalid of the traversal
-        const int vend = v + nvalid;
-        v += kStageItems;
-        if (v < len) {
-            if (nvalid == IPW && !(vend < tail_len && v >= tail_len)) {
-                const int rt_old = rt;
-                kb += kb_step;
-                rt += rt_step;
-                if (kb >= p.KU) {
-                    kb -= p.KU;
-                    ++rt;
-                }
-                if (rt != rt_old) refresh();
-            } else {
-                locate(v);
-                refresh();
-            }
-        }
+        if (tid == 0 && g < 2) NF4_TRACE(11 + g);
     }
     if (failed) return;
     if (tid == 0) NF4_TRACE(13);
@@ -788,11 +821,12 @@ struct StreamPlan {
 StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int sm_count) {
     StreamPlan pl;
     const int np = paired ? 2 : 1;
-    const int stage_bytes = kStageItems * w.unit_stride * np;
+    const int stage_bytes = kStageItems * w.unit_stride * np + (paired ? kPairSkewBytes : 0);
     const int x_bytes = (int)((w.K * 2 + 15) / 16 * 16);
     // region A (below the table, which sits at shared address 64 KB): barriers, counters, code
     // book, slots and x if it fits; region B (from 128 KB): x otherwise, then the ring
-    const int a_used = 2048 + 16 + 400 + 64 + 1024 + 2 * kNabsWindow * 4 + 1024 +
+    const int a_used = 2048 + 16 + 400 + 64 + 16 + 1024 + 2 * kNabsWindow * 4 + 1024 +
+                       kMaxLocalTiles * 32 * 8 +
                        kMaxLocalTiles * np * kConsumerWarps * 64;
     pl.x_in_b = (a_used + x_bytes > 65536) ? 1 : 0;
     const int b_capacity = 227 * 1024 - 131072;
@@ -925,8 +959,8 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.slice_r = p.total_items % pl.grid;
     make_fast_div((uint32_t)pl.grid, &p.div_g_m, &p.div_g_s);
     make_fast_div((uint32_t)w.KU, &p.div_ku_m, &p.div_ku_s);
-    p.kb_step = (kStageItems - kItemsPerWarp) % w.KU;
-    p.rt_step = (kStageItems - kItemsPerWarp) / w.KU;
+    p.kb_step = kConsumerWarps % w.KU;
+    p.rt_step = kConsumerWarps / w.KU;
     p.n_out = paired ? (int)ff_pair : (int)w.N;
     p.K = (int)w.K;
     p.KU = w.KU;
