@@ -194,9 +194,18 @@ __device__ __forceinline__ void sts_f32(uint32_t a, float v) {
 // holds, for byte value b and lane l, the bf16 pair of b's two nibbles at b*256 + l*4: the 32
 // lanes of a warp always hit 32 different banks. `lane_base` = table address + l*4; ONE PRMT
 // splices the byte into bits [8,16) of it and the result is the load address.
+#ifndef NF4_EXP
+#define NF4_EXP 0
+#endif
 template <int BYTE>
 __device__ __forceinline__ uint32_t lut_pair(uint32_t word, uint32_t lane_base) {
+#if NF4_EXP == 1
+    return __byte_perm(word, lane_base, 0x7604 | (BYTE << 4));
+#elif NF4_EXP == 5 || (NF4_EXP >= 16 && (NF4_EXP & 1))
+    return word + BYTE;
+#else
     return lds_u32(__byte_perm(word, lane_base, 0x7604 | (BYTE << 4)));
+#endif
 }
 
 // n / d for 0 <= n < 2^31 as (n * m) >> s, with s = 31 + ceil(log2 d) and m = ceil(2^s / d) < 2^32:
@@ -309,8 +318,59 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     // let a dependent launch begin its own set-up; it waits for our completion before reading
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // ---- completing a row tile (finalizer warp): sum the per-warp slots, then either write the
-    // rows or, for a tile shared with a neighbouring CTA, publish the partial sums ----
+    // ---- completing a row tile (finalizer warp) ----
+    // write_rows: the epilogue of 16 output rows (lanes 0..15 hold one row each)
+    auto write_rows = [&](int rtile, const float (&v)[NP]) {
+        if (lane < 16) {
+            const int n = rtile * kTileRows + lane;
+            if (n < p.n_out) {
+                float o;
+                if (PAIRED) {
+                    const float gt = v[0], up = v[NP - 1];
+                    o = __fdividef(gt, 1.0f + __expf(-gt)) * up;
+                } else {
+                    o = v[0];
+                    if (p.residual) o += bf16_bits_to_f32(p.residual[n]);
+                }
+                p.y[n] = f32_to_bf16_bits(o);
+            }
+        }
+    };
+    // A tile shared with neighbouring CTAs: every contributor publishes its partial sums and adds
+    // its item count to the tile's counter; the contributor that completes the count sums all
+    // partial sums in CTA order (deterministic, nobody waits). The counter's old value is not
+    // looked at before the next tile has been waited for, so the round trip of the atomic stays
+    // off the finalizer's path.
+    int pend_li0 = -1, pend_li1 = -1;  // slot 0: the slice's first tile, slot 1: its last tile
+    int pend_old0 = 0, pend_old1 = 0;
+    auto tile_items = [&](int li) {  // this CTA's items in local tile li
+        const int t0 = (rt_first + li) * p.KU;
+        return min(i1, t0 + p.KU) - max(i0, t0);
+    };
+    auto resolve = [&](int& pend_li, int pend_old) {
+        const int li = pend_li;
+        if (li < 0) return;
+        pend_li = -1;
+        const int old = __shfl_sync(0xffffffffu, pend_old, 0);
+        if (old + tile_items(li) != p.KU) return;  // somebody else completes the tile
+        const int rtile = rt_first + li;
+        const int t0 = rtile * p.KU, t1 = t0 + p.KU;
+        int c_lo = c, c_hi = c;
+        while (c_lo > 0 && slice_begin(p, c_lo) > t0) --c_lo;
+        while (c_hi + 1 < G && slice_begin(p, c_hi + 1) < t1) ++c_hi;
+        float v[NP];
+#pragma unroll
+        for (int h = 0; h < NP; ++h) v[h] = 0.0f;
+        for (int cc = c_lo; cc <= c_hi; ++cc) {
+            const int cc_first = fast_div(slice_begin(p, cc), p.div_ku_m, p.div_ku_s);
+            const int hs = (rtile == cc_first) ? 0 : 1;
+#pragma unroll
+            for (int h = 0; h < NP; ++h)
+                v[h] += __ldcg(p.partials + (((size_t)cc * 2 + hs) * NP + h) * 16 + (lane & 15));
+        }
+        if (lane == 0) p.counters[rtile] = 0;
+        write_rows(rtile, v);
+    };
     auto finalize_tile = [&](int li) {
         const int r = lane & 15;
         const int rtile = rt_first + li;
@@ -318,58 +378,36 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #pragma unroll
         for (int h = 0; h < NP; ++h) {
             const uint32_t sl = a_slots + (uint32_t)(((li * NP + h) * W) * 16 + r) * 4u;
+            float part[W];
+#pragma unroll
+            for (int w = 0; w < W; ++w) part[w] = lds_f32(sl + w * 64);
             float sacc = 0.0f;
 #pragma unroll
-            for (int w = 0; w < W; ++w) sacc += lds_f32(sl + w * 64);
+            for (int w = 0; w < W; ++w) sacc += part[w];
             v[h] = sacc;
         }
-        const int t0 = rtile * p.KU, t1 = t0 + p.KU;
-        const bool is_full = (i0 <= t0) && (i1 >= t1);
-        bool write = is_full;
-        if (!is_full) {
-            // shared with neighbouring CTAs: publish, count, and let the last arriver sum all
-            // contributions in CTA order (deterministic, nobody waits)
-            const int hslot = (li == 0) ? 0 : 1;
-            if (lane < 16) {
-#pragma unroll
-                for (int h = 0; h < NP; ++h)
-                    p.partials[(((size_t)c * 2 + hslot) * NP + h) * 16 + r] = v[h];
-            }
-            __threadfence();
-            __syncwarp();
-            const int c_lo = (int)((((long long)t0 + 1) * G - 1) / p.total_items);
-            const int c_hi = (int)(((long long)t1 * G - 1) / p.total_items);
-            int old = 0;
-            if (lane == 0) old = atomicAdd(p.counters + rtile, 1);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old == c_hi - c_lo) {
-                __threadfence();
-#pragma unroll
-                for (int h = 0; h < NP; ++h) v[h] = 0.0f;
-                for (int cc = c_lo; cc <= c_hi; ++cc) {
-                    const int cc_first = fast_div(slice_begin(p, cc), p.div_ku_m, p.div_ku_s);
-                    const int hs = (rtile == cc_first) ? 0 : 1;
-#pragma unroll
-                    for (int h = 0; h < NP; ++h)
-                        v[h] += __ldcg(p.partials + (((size_t)cc * 2 + hs) * NP + h) * 16 + r);
-                }
-                if (lane == 0) p.counters[rtile] = 0;
-                write = true;
-            }
+        const int items = tile_items(li);
+        if (items == p.KU) {
+            write_rows(rtile, v);
+            return;
         }
-        if (write && lane < 16) {
-            const int n = rtile * kTileRows + r;
-            if (n < p.n_out) {
-                float o;
-                if (PAIRED) {
-                    const float gt = v[0], up = v[NP - 1];
-                    o = (gt / (1.0f + __expf(-gt))) * up;
-                } else {
-                    o = v[0];
-                    if (p.residual) o += bf16_bits_to_f32(p.residual[n]);
-                }
-                p.y[n] = f32_to_bf16_bits(o);
-            }
+        const int hslot = (li == 0) ? 0 : 1;
+        if (lane < 16) {
+#pragma unroll
+            for (int h = 0; h < NP; ++h)
+                p.partials[(((size_t)c * 2 + hslot) * NP + h) * 16 + r] = v[h];
+        }
+        __syncwarp();
+        int old = 0;
+        if (lane == 0)
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;"
+                         : "=r"(old) : "l"(p.counters + rtile), "r"(items) : "memory");
+        if (hslot == 0) {
+            pend_li0 = li;
+            pend_old0 = old;
+        } else {
+            pend_li1 = li;
+            pend_old1 = old;
         }
     };
 
@@ -456,7 +494,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 while (!ok) {
 #pragma unroll 1
                     for (int i = 0; i < 64 && !ok; ++i) {
-                        __nanosleep(200);
+                        __nanosleep(40);
                         ok = mbar_try_wait(&tile_bar[li], 0);
                     }
                     if (ok) break;
@@ -469,11 +507,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) return;
+            // counters added to before the wait above have answered by now
+            resolve(pend_li0, pend_old0);
+            resolve(pend_li1, pend_old1);
             finalize_tile(li);
 #ifdef AILA_NF4_TRACE
             if (lane == 0 && q < 8) NF4_TRACE(32 + q);
 #endif
         }
+        resolve(pend_li0, pend_old0);
+        resolve(pend_li1, pend_old1);
 #ifdef AILA_NF4_TRACE
         if (lane == 0) {
             unsigned long long t_;
@@ -684,7 +727,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         const uint32_t ua0 = a_ring + (uint32_t)s * stage_bytes + (uint32_t)warp * unit_stride;
 #pragma unroll
         for (int i = 0; i < IPW; ++i) {
-            if (v < len) {
+            if (v < len && NF4_EXP == 6) {
+                acc[0][0] += __uint_as_float(ua0 + v);
+                v += W;
+            } else if (v < len) {
                 const uint32_t ua = ua0 + (uint32_t)(i * W) * unit_stride;
                 // ---- one work item: unit (rt, kb) [and its up partner] ----
                 // x fragments: two 16-byte loads (tiles j = 0,1 and j = 2,3) in the four lanes
@@ -692,6 +738,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 // read back. A 16-byte load is served a quarter warp at a time, so the
                 // predicated pair costs two shared-memory wavefronts instead of eight.
                 const uint32_t xa = a_xs + (uint32_t)kb * 128u + 16u * t;
+                if (!(NF4_EXP >= 16 && (NF4_EXP & 32)))
                 asm volatile(
                     "{\n\t.reg .pred q;\n\t"
                     "setp.ne.u32 q, %9, 0;\n\t"
@@ -701,7 +748,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                       "+r"(xq1.z), "+r"(xq1.w)
                     : "r"(xa), "r"(x_lane));
                 float am0[NP], am1[NP];
-                if (KIND == kAbsmaxCodes) {
+                if (NF4_EXP == 3 || (NF4_EXP >= 16 && (NF4_EXP & 4))) {
+#pragma unroll
+                    for (int h = 0; h < NP; ++h) am0[h] = am1[h] = 1.0f + kb;
+                } else if (KIND == kAbsmaxCodes) {
                     const unsigned code = lds_u8(ua + code_off);
                     const unsigned flat = d_flat + ((unsigned)kb >> p.sp.blk_shift);
                     const unsigned sidx = flat >> p.sp.nbs_shift;
@@ -723,26 +773,53 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     }
                 }
                 float c0[NP][4], c1[NP][4];
+                // both halves' packed weights first, then all table lookups (independent loads),
+                // then the tiles: j = 0: bytes 0,1 of .x ; j = 1: bytes 2,3 of .x ; j = 2,3: .y
+                uint2 wl[NP], wu[NP];
 #pragma unroll
                 for (int h = 0; h < NP; ++h) {
-                    const uint2 l = lds_v2(ua + h * half_bytes + w_off);
-                    const uint2 u = lds_v2(ua + h * half_bytes + w_off + 256u);
-                    // all 16 table lookups first (independent loads), then the four tiles:
-                    // j = 0: bytes 0,1 of .x ; j = 1: bytes 2,3 of .x ; j = 2,3: .y
-                    uint32_t a[16];
-                    a[0] = lut_pair<0>(l.x, lane_base);  a[1] = lut_pair<0>(u.x, lane_base);
-                    a[2] = lut_pair<1>(l.x, lane_base);  a[3] = lut_pair<1>(u.x, lane_base);
-                    a[4] = lut_pair<2>(l.x, lane_base);  a[5] = lut_pair<2>(u.x, lane_base);
-                    a[6] = lut_pair<3>(l.x, lane_base);  a[7] = lut_pair<3>(u.x, lane_base);
-                    a[8] = lut_pair<0>(l.y, lane_base);  a[9] = lut_pair<0>(u.y, lane_base);
-                    a[10] = lut_pair<1>(l.y, lane_base); a[11] = lut_pair<1>(u.y, lane_base);
-                    a[12] = lut_pair<2>(l.y, lane_base); a[13] = lut_pair<2>(u.y, lane_base);
-                    a[14] = lut_pair<3>(l.y, lane_base); a[15] = lut_pair<3>(u.y, lane_base);
-                    mma_bf16_16816_init(c0[h], a[0], a[1], a[2], a[3], xq0.x, xq0.y);
-                    mma_bf16_16816_init(c1[h], a[4], a[5], a[6], a[7], xq0.z, xq0.w);
-                    mma_bf16_16816(c0[h], a[8], a[9], a[10], a[11], xq1.x, xq1.y);
-                    mma_bf16_16816(c1[h], a[12], a[13], a[14], a[15], xq1.z, xq1.w);
+#if NF4_EXP == 4 || (NF4_EXP >= 16 && (NF4_EXP & 8))
+                    wl[h] = make_uint2(ua * 2654435761u, kb * 40503u + h);
+                    wu[h] = make_uint2(ua * 2246822519u, kb * 3266489917u + h);
+#else
+                    wl[h] = lds_v2(ua + h * half_bytes + w_off);
+                    wu[h] = lds_v2(ua + h * half_bytes + w_off + 256u);
+#endif
                 }
+                uint32_t a[NP][16];
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    const uint2 l = wl[h], u = wu[h];
+                    a[h][0] = lut_pair<0>(l.x, lane_base);  a[h][1] = lut_pair<0>(u.x, lane_base);
+                    a[h][2] = lut_pair<1>(l.x, lane_base);  a[h][3] = lut_pair<1>(u.x, lane_base);
+                    a[h][4] = lut_pair<2>(l.x, lane_base);  a[h][5] = lut_pair<2>(u.x, lane_base);
+                    a[h][6] = lut_pair<3>(l.x, lane_base);  a[h][7] = lut_pair<3>(u.x, lane_base);
+                    a[h][8] = lut_pair<0>(l.y, lane_base);  a[h][9] = lut_pair<0>(u.y, lane_base);
+                    a[h][10] = lut_pair<1>(l.y, lane_base); a[h][11] = lut_pair<1>(u.y, lane_base);
+                    a[h][12] = lut_pair<2>(l.y, lane_base); a[h][13] = lut_pair<2>(u.y, lane_base);
+                    a[h][14] = lut_pair<3>(l.y, lane_base); a[h][15] = lut_pair<3>(u.y, lane_base);
+                }
+#if NF4_EXP == 2 || (NF4_EXP >= 16 && (NF4_EXP & 2))
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    uint32_t z0 = 0, z1 = 0;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) { z0 ^= a[h][q]; z1 ^= a[h][8 + q]; }
+                    c0[h][0] = __uint_as_float(z0 ^ xq0.x); c0[h][2] = __uint_as_float(z1 ^ xq1.y);
+                    c1[h][0] = __uint_as_float(z0 + xq0.z); c1[h][2] = __uint_as_float(z1 + xq1.w);
+                }
+#else
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    mma_bf16_16816_init(c0[h], a[h][0], a[h][1], a[h][2], a[h][3], xq0.x, xq0.y);
+                    mma_bf16_16816_init(c1[h], a[h][4], a[h][5], a[h][6], a[h][7], xq0.z, xq0.w);
+                }
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    mma_bf16_16816(c0[h], a[h][8], a[h][9], a[h][10], a[h][11], xq1.x, xq1.y);
+                    mma_bf16_16816(c1[h], a[h][12], a[h][13], a[h][14], a[h][15], xq1.z, xq1.w);
+                }
+#endif
                 // ---- accumulate into the current row tile (switching tiles is rare) ----
                 const int li = rt - rt_first;
                 if (li != cur_li) {
