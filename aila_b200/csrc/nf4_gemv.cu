@@ -111,6 +111,10 @@ constexpr int kMaxStages = 24;
 constexpr int kMaxLocalTiles = 8;  // row tiles one CTA slice may touch
 constexpr int kMaxGridMult = 8;     // grid <= 8 x SM count
 constexpr int kNabsWindow = 256;    // second-level scales kept in shared memory per half
+#ifndef NF4_EARLY
+#define NF4_EARLY 68
+#endif
+constexpr int kEarlyBytes = NF4_EARLY * 1024;  // ring bytes requested before x has been asked for
 constexpr int kPairSkewBytes = 64;  // shared-memory distance added between a stage's gate and up units
 
 struct StreamParams {
@@ -133,7 +137,8 @@ struct StreamParams {
     int KU;
     int unit_stride;
     int pair_rt_offset;     // paired: row-tile distance from a gate tile to its up tile
-    int stages;
+    int stages;             // ring depth = stages_b + stages_a
+    int stages_b;           // stages above the table (used first), the rest sit below it
     int x_bytes;            // K*2 rounded up to 16
     int x_in_b;             // 1: x lives above the table (large K), 0: below it
     int smem_bytes;         // dynamic shared memory of the launch
@@ -276,12 +281,18 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const uint32_t a_xs_small = a_slots + kMaxLocalTiles * NP * W * 64;
     const uint32_t a_lut = 65536u;
     const uint32_t a_xs = p.x_in_b ? 131072u : a_xs_small;
-    const uint32_t a_ring = 131072u + (p.x_in_b ? (uint32_t)p.x_bytes : 0u);
+    const uint32_t a_ring_b = 131072u + (p.x_in_b ? (uint32_t)p.x_bytes : 0u);
+    const uint32_t a_ring_a = (a_xs_small + (p.x_in_b ? 0u : (uint32_t)p.x_bytes) + 127u) & ~127u;
+    auto stage_addr = [&](int st) {
+        return st < p.stages_b ? a_ring_b + (uint32_t)st * stage_bytes
+                               : a_ring_a + (uint32_t)(st - p.stages_b) * stage_bytes;
+    };
     uint8_t* gen = smem_raw - base;  // generic pointer to shared-window address 0
     uint64_t* full = reinterpret_cast<uint64_t*>(gen + a_bar);
     uint64_t* empty = full + kMaxStages;
     uint64_t* tile_bar = reinterpret_cast<uint64_t*>(gen + a_tile);
     int* abort_flag = reinterpret_cast<int*>(empty + kMaxStages);
+    uint64_t* x_ready = reinterpret_cast<uint64_t*>(gen + a_bar + 392);  // x is in shared memory
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -310,8 +321,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const int tail_len = i1 - tail0;
     // virtual index v in [0, len): item = v < tail_len ? tail0 + v : i0 + (v - tail_len)
 
-    if (base > 2048u || base + (uint32_t)p.smem_bytes < a_ring + (uint32_t)p.stages * stage_bytes ||
-        a_xs_small + (p.x_in_b ? 0u : (uint32_t)p.x_bytes) > 65536u) {
+    if (base > 2048u || base + (uint32_t)p.smem_bytes < a_ring_b + (uint32_t)p.stages_b * stage_bytes ||
+        a_ring_a + (uint32_t)(p.stages - p.stages_b) * stage_bytes > 65536u) {
         if (tid == 0) atomicExch(p.status, kStatusBadArgument);
         return;
     }
@@ -419,6 +430,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             mbar_init(&empty[lane], W);
         }
         if (lane < kMaxLocalTiles) mbar_init(&tile_bar[lane], W);
+        if (lane == 0) mbar_init(x_ready, 1);
         if (lane == 0) *abort_flag = 0;
         mbar_fence_init();
         __syncwarp();
@@ -429,7 +441,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             int issued = 0;
             int s = 0;
             uint32_t ph = 0;  // (g / stages) & 1
+            const int early_stages = max(1, min(p.stages, kEarlyBytes / stage_bytes));
             for (int g = 0; g < n_groups; ++g) {
+                // Only the first stages are requested before x has arrived: the load of x slows
+                // down under the copies' traffic (measured), and it is the one load every
+                // consumer waits for once the previous kernel has finished.
+                if (g == early_stages && !mbar_wait_bounded(x_ready, 0)) break;
                 if (g >= p.stages) {
                     if (*(volatile int*)abort_flag) break;
                     if (!mbar_wait_bounded(&empty[s], ph ^ 1u)) {
@@ -441,7 +458,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 if (g < 8) NF4_TRACE(16 + g);
                 const int v0 = g * kStageItems;
                 const int cnt = min(kStageItems, len - v0);
-                uint8_t* dst = gen + a_ring + (size_t)s * stage_bytes;
+                uint8_t* dst = gen + stage_addr(s);
                 mbar_expect_tx(&full[s], (uint32_t)cnt * unit_stride * NP);
                 // up to two contiguous pieces (the traversal wraps from the tail tile to the front)
                 const int n1 = v0 < tail_len ? min(cnt, tail_len - v0) : 0;
@@ -686,6 +703,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         if (q5 < n8) sts_x(q5, v1);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+    if (tid == 0) mbar_arrive(x_ready);  // the producer may now fill the rest of the ring
     if (tid == 0) NF4_TRACE(4);
     if (v < len) refresh();
 
@@ -724,7 +742,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             break;
         }
         if (tid == 0 && g < 8) NF4_TRACE(5 + g);
-        const uint32_t ua0 = a_ring + (uint32_t)s * stage_bytes + (uint32_t)warp * unit_stride;
+        const uint32_t ua0 = stage_addr(s) + (uint32_t)warp * unit_stride;
 #pragma unroll
         for (int i = 0; i < IPW; ++i) {
             if (v < len && NF4_EXP == 6) {
@@ -887,6 +905,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 struct StreamPlan {
     int grid = 0;
     int stages = 0;
+    int stages_b = 0;
     int smem = 0;
     int x_in_b = 0;
     bool ok = false;
@@ -895,23 +914,45 @@ struct StreamPlan {
 // Grid and ring depth for one launch. The slice of a CTA may touch at most kMaxLocalTiles row
 // tiles; long outputs therefore get a grid that is a multiple of the SM count (CTAs never
 // wait on each other, so they need not be co-resident).
+// Shared memory the system keeps at the bottom of every block's window: the dynamic allocation
+// of a kernel without static shared memory starts right after it.
+int smem_window_base() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1024;
+    if (cached[dev] == 0) {
+        int r = 0;
+        if (cudaDeviceGetAttribute(&r, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess || r < 0)
+            r = 1024;
+        cached[dev] = r + 1;
+    }
+    return cached[dev] - 1;
+}
+
+constexpr int kStreamSmemBytes = 227 * 1024;  // every launch asks for the whole budget
+
 StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int sm_count) {
     StreamPlan pl;
     const int np = paired ? 2 : 1;
     const int stage_bytes = kStageItems * w.unit_stride * np + (paired ? kPairSkewBytes : 0);
     const int x_bytes = (int)((w.K * 2 + 15) / 16 * 16);
-    // region A (below the table, which sits at shared address 64 KB): barriers, counters, code
-    // book, slots and x if it fits; region B (from 128 KB): x otherwise, then the ring
-    const int a_used = 2048 + 16 + 400 + 64 + 16 + 1024 + 2 * kNabsWindow * 4 + 1024 +
-                       kMaxLocalTiles * 32 * 8 +
-                       kMaxLocalTiles * np * kConsumerWarps * 64;
-    pl.x_in_b = (a_used + x_bytes > 65536) ? 1 : 0;
-    const int b_capacity = 227 * 1024 - 131072;
-    const int ring_budget = b_capacity - (pl.x_in_b ? x_bytes : 0);
-    if (ring_budget < 2 * stage_bytes) return pl;
-    pl.stages = ring_budget / stage_bytes;
+    // Shared-window map: region A = [base, 64 KB): barriers, code books, tile tables, slots, x if
+    // it fits, then ring stages in what is left; table = [64 KB, 128 KB); region B = [128 KB,
+    // base + budget): x otherwise, then ring stages.
+    const int base = (smem_window_base() + 15) / 16 * 16;
+    const int a_fixed = base + 400 + 64 + 16 + 1024 + 2 * kNabsWindow * 4 + 1024 +
+                        kMaxLocalTiles * 32 * 8 + kMaxLocalTiles * np * kConsumerWarps * 64;
+    pl.x_in_b = (a_fixed + x_bytes > 65536) ? 1 : 0;
+    const int ring_a = (a_fixed + (pl.x_in_b ? 0 : x_bytes) + 127) / 128 * 128;
+    const int stages_a = ring_a < 65536 ? (65536 - ring_a) / stage_bytes : 0;
+    const int ring_b = 131072 + (pl.x_in_b ? x_bytes : 0);
+    const int end_b = smem_window_base() + kStreamSmemBytes;
+    pl.stages_b = end_b > ring_b ? (end_b - ring_b) / stage_bytes : 0;
+    if (pl.stages_b > kMaxStages) pl.stages_b = kMaxStages;
+    pl.stages = pl.stages_b + stages_a;
     if (pl.stages > kMaxStages) pl.stages = kMaxStages;
-    pl.smem = 131072 + (pl.x_in_b ? x_bytes : 0) + pl.stages * stage_bytes;
+    if (pl.stages < 2) return pl;
+    pl.smem = kStreamSmemBytes;
     const long long rt_work = paired ? ff_pair / kTileRows : w.RT;
     const long long total = rt_work * w.KU;
     if (total <= 0 || total >= (1ll << 31) || sm_count <= 0) return pl;
@@ -1045,6 +1086,7 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.pair_rt_offset = paired ? (int)(ff_pair / kTileRows) : 0;
     p.x_bytes = (int)((w.K * 2 + 15) / 16 * 16);
     p.stages = pl.stages;
+    p.stages_b = pl.stages_b;
     p.x_in_b = pl.x_in_b;
     p.smem_bytes = pl.smem;
     p.n_rows = (int)w.N;
