@@ -199,18 +199,9 @@ __device__ __forceinline__ void sts_f32(uint32_t a, float v) {
 // holds, for byte value b and lane l, the bf16 pair of b's two nibbles at b*256 + l*4: the 32
 // lanes of a warp always hit 32 different banks. `lane_base` = table address + l*4; ONE PRMT
 // splices the byte into bits [8,16) of it and the result is the load address.
-#ifndef NF4_EXP
-#define NF4_EXP 0
-#endif
 template <int BYTE>
 __device__ __forceinline__ uint32_t lut_pair(uint32_t word, uint32_t lane_base) {
-#if NF4_EXP == 1
-    return __byte_perm(word, lane_base, 0x7604 | (BYTE << 4));
-#elif NF4_EXP == 5 || (NF4_EXP >= 16 && (NF4_EXP & 1))
-    return word + BYTE;
-#else
     return lds_u32(__byte_perm(word, lane_base, 0x7604 | (BYTE << 4)));
-#endif
 }
 
 // n / d for 0 <= n < 2^31 as (n * m) >> s, with s = 31 + ceil(log2 d) and m = ceil(2^s / d) < 2^32:
@@ -745,10 +736,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         const uint32_t ua0 = stage_addr(s) + (uint32_t)warp * unit_stride;
 #pragma unroll
         for (int i = 0; i < IPW; ++i) {
-            if (v < len && NF4_EXP == 6) {
-                acc[0][0] += __uint_as_float(ua0 + v);
-                v += W;
-            } else if (v < len) {
+            if (v < len) {
                 const uint32_t ua = ua0 + (uint32_t)(i * W) * unit_stride;
                 // ---- one work item: unit (rt, kb) [and its up partner] ----
                 // x fragments: two 16-byte loads (tiles j = 0,1 and j = 2,3) in the four lanes
@@ -756,7 +744,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 // read back. A 16-byte load is served a quarter warp at a time, so the
                 // predicated pair costs two shared-memory wavefronts instead of eight.
                 const uint32_t xa = a_xs + (uint32_t)kb * 128u + 16u * t;
-                if (!(NF4_EXP >= 16 && (NF4_EXP & 32)))
                 asm volatile(
                     "{\n\t.reg .pred q;\n\t"
                     "setp.ne.u32 q, %9, 0;\n\t"
@@ -766,10 +753,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                       "+r"(xq1.z), "+r"(xq1.w)
                     : "r"(xa), "r"(x_lane));
                 float am0[NP], am1[NP];
-                if (NF4_EXP == 3 || (NF4_EXP >= 16 && (NF4_EXP & 4))) {
-#pragma unroll
-                    for (int h = 0; h < NP; ++h) am0[h] = am1[h] = 1.0f + kb;
-                } else if (KIND == kAbsmaxCodes) {
+                if (KIND == kAbsmaxCodes) {
                     const unsigned code = lds_u8(ua + code_off);
                     const unsigned flat = d_flat + ((unsigned)kb >> p.sp.blk_shift);
                     const unsigned sidx = flat >> p.sp.nbs_shift;
@@ -796,13 +780,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 uint2 wl[NP], wu[NP];
 #pragma unroll
                 for (int h = 0; h < NP; ++h) {
-#if NF4_EXP == 4 || (NF4_EXP >= 16 && (NF4_EXP & 8))
-                    wl[h] = make_uint2(ua * 2654435761u, kb * 40503u + h);
-                    wu[h] = make_uint2(ua * 2246822519u, kb * 3266489917u + h);
-#else
                     wl[h] = lds_v2(ua + h * half_bytes + w_off);
                     wu[h] = lds_v2(ua + h * half_bytes + w_off + 256u);
-#endif
                 }
                 uint32_t a[NP][16];
 #pragma unroll
@@ -817,16 +796,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     a[h][12] = lut_pair<2>(l.y, lane_base); a[h][13] = lut_pair<2>(u.y, lane_base);
                     a[h][14] = lut_pair<3>(l.y, lane_base); a[h][15] = lut_pair<3>(u.y, lane_base);
                 }
-#if NF4_EXP == 2 || (NF4_EXP >= 16 && (NF4_EXP & 2))
-#pragma unroll
-                for (int h = 0; h < NP; ++h) {
-                    uint32_t z0 = 0, z1 = 0;
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) { z0 ^= a[h][q]; z1 ^= a[h][8 + q]; }
-                    c0[h][0] = __uint_as_float(z0 ^ xq0.x); c0[h][2] = __uint_as_float(z1 ^ xq1.y);
-                    c1[h][0] = __uint_as_float(z0 + xq0.z); c1[h][2] = __uint_as_float(z1 + xq1.w);
-                }
-#else
 #pragma unroll
                 for (int h = 0; h < NP; ++h) {
                     mma_bf16_16816_init(c0[h], a[h][0], a[h][1], a[h][2], a[h][3], xq0.x, xq0.y);
@@ -837,7 +806,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     mma_bf16_16816(c0[h], a[h][8], a[h][9], a[h][10], a[h][11], xq1.x, xq1.y);
                     mma_bf16_16816(c1[h], a[h][12], a[h][13], a[h][14], a[h][15], xq1.z, xq1.w);
                 }
-#endif
                 // ---- accumulate into the current row tile (switching tiles is rare) ----
                 const int li = rt - rt_first;
                 if (li != cur_li) {
