@@ -21,6 +21,7 @@ ERR_KERNEL_TIMEOUT = 6
 
 SHARD_ROWS = 0
 SHARD_COLS = 1
+IPC_HANDLE_BYTES = 64
 
 
 class WeightDesc(ctypes.Structure):
@@ -71,6 +72,12 @@ _SIGNATURES = {
     "aila_nf4_forward_gate_up_swiglu_host": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int,
                                                             ctypes.c_int64, _VP]),
     "aila_nf4_forward_decode_static": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP]),
+    "aila_nf4_peerbuf_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                               ctypes.c_int64, ctypes.POINTER(_VP)]),
+    "aila_nf4_peerbuf_export": (ctypes.c_int, [_VP, _VP]),
+    "aila_nf4_peerbuf_import": (ctypes.c_int, [_VP, ctypes.c_int, _VP]),
+    "aila_nf4_peerbuf_destroy": (None, [_VP]),
+    "aila_nf4_forward_decode_allreduce": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "aila_nf4_dequantize": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_dequantize_rowmajor": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_expand_absmax": (ctypes.c_int, [_VP, _VP, _VP]),

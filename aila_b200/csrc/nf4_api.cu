@@ -316,16 +316,7 @@ AilaNf4Status ensure_weight(AilaNf4Scratch* sc, size_t bytes) {
     return AILA_NF4_OK;
 }
 
-AilaNf4Status ensure_counters(AilaNf4Scratch* sc, size_t tiles) {
-    if (sc->counters_ints >= tiles) return AILA_NF4_OK;
-    if (sc->d_counters) NF4_CUDA(cudaFree(sc->d_counters));
-    sc->d_counters = nullptr;
-    sc->counters_ints = 0;
-    NF4_CUDA(cudaMalloc(reinterpret_cast<void**>(&sc->d_counters), tiles * sizeof(int)));
-    NF4_CUDA(cudaMemset(sc->d_counters, 0, tiles * sizeof(int)));
-    sc->counters_ints = tiles;
-    return AILA_NF4_OK;
-}
+using nf4::ensure_counters;
 
 AilaNf4Status ensure_io(void** buf, size_t* have, size_t need) {
     if (*have >= need) return AILA_NF4_OK;
@@ -362,6 +353,17 @@ AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void*
 
 // ---------------------------------------------------------------------------------------
 namespace nf4 {
+
+AilaNf4Status ensure_counters(AilaNf4Scratch* sc, size_t tiles) {
+    if (sc->counters_ints >= tiles) return AILA_NF4_OK;
+    if (sc->d_counters) NF4_CUDA(cudaFree(sc->d_counters));
+    sc->d_counters = nullptr;
+    sc->counters_ints = 0;
+    NF4_CUDA(cudaMalloc(reinterpret_cast<void**>(&sc->d_counters), tiles * sizeof(int)));
+    NF4_CUDA(cudaMemset(sc->d_counters, 0, tiles * sizeof(int)));
+    sc->counters_ints = tiles;
+    return AILA_NF4_OK;
+}
 
 AilaNf4Status fail(AilaNf4Status code, const std::string& message) {
     g_last_error = message;

@@ -118,6 +118,7 @@ enum KernelStatus : int {
     kStatusTimeoutEmpty = 2,  // producer gave up waiting for a free stage
     kStatusTimeoutTmem = 3,   // epilogue / MMA gave up waiting on a TMEM barrier
     kStatusBadArgument = 4,
+    kStatusTimeoutPeer = 5,   // a rank gave up waiting for another rank's rows
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

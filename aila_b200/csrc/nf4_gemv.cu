@@ -115,6 +115,7 @@ constexpr int kNabsWindow = 256;    // second-level scales kept in shared memory
 #define NF4_EARLY 68
 #endif
 constexpr int kEarlyBytes = NF4_EARLY * 1024;  // ring bytes requested before x has been asked for
+constexpr int kMaxPeerWorld = 8;
 constexpr int kPairSkewBytes = 64;  // shared-memory distance added between a stage's gate and up units
 
 struct StreamParams {
@@ -143,6 +144,16 @@ struct StreamParams {
     int x_in_b;             // 1: x lives above the table (large K), 0: below it
     int smem_bytes;         // dynamic shared memory of the launch
     int n_rows;             // rows of the linear (for clamping the padded rows of the last tile)
+    // row-parallel exchange (peer_world > 0): the epilogue stores the fp32 row sums of this
+    // rank into every rank's exchange buffer and adds one to that rank's arrival counter per
+    // row tile, instead of writing y
+    int peer_world;
+    int peer_rank;
+    long long peer_max_rows;
+    float* peer_part[kMaxPeerWorld];      // rank d's row area (all parities and source ranks)
+    unsigned* peer_flag[kMaxPeerWorld];   // rank d's arrival counters
+    unsigned* peer_ctrl;                  // this rank's {epoch, tiles done, reducer blocks done}
+    int n_row_tiles;                      // row tiles of the launch (all CTAs)
 #ifdef AILA_NF4_TRACE
     int trace_idx;
 #endif
@@ -322,7 +333,36 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 
     // ---- completing a row tile (finalizer warp) ----
     // write_rows: the epilogue of 16 output rows (lanes 0..15 hold one row each)
+    int peer_parity = -1;  // exchange half of this launch, read on first use
     auto write_rows = [&](int rtile, const float (&v)[NP]) {
+        if (!PAIRED && p.peer_world > 0) {
+            // Plain stores into every rank's memory (this rank's own included) and a
+            // system-scope fence per tile. The CTA that finishes the launch's LAST row tile then
+            // adds one to this rank's arrival counter on every rank: a rank that sees all its
+            // counters reach the epoch's target may read the rows. The exchange alternates
+            // between two halves of the buffers (parity of the epoch, which this rank's reducer
+            // advances).
+            if (peer_parity < 0) peer_parity = (int)(*(volatile unsigned*)p.peer_ctrl & 1u);
+            const size_t slice = ((size_t)peer_parity * p.peer_world + p.peer_rank) * (size_t)p.peer_max_rows;
+            const int n = rtile * kTileRows + lane;
+            if (lane < 16 && n < p.n_out) {
+                for (int d = 0; d < p.peer_world; ++d) p.peer_part[d][slice + n] = v[0];
+            }
+            __threadfence_system();
+            __syncwarp();
+            unsigned done = 0;
+            if (lane == 0) done = atomicAdd(p.peer_ctrl + 1, 1u);
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (done == (unsigned)p.n_row_tiles - 1u) {
+                if (lane == 0) p.peer_ctrl[1] = 0u;
+                __threadfence_system();
+                if (lane < p.peer_world)
+                    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(
+                                     p.peer_flag[lane] + peer_parity * p.peer_world + p.peer_rank)
+                                 : "memory");
+            }
+            return;
+        }
         if (lane < 16) {
             const int n = rtile * kTileRows + lane;
             if (n < p.n_out) {
@@ -332,7 +372,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     o = __fdividef(gt, 1.0f + __expf(-gt)) * up;
                 } else {
                     o = v[0];
-                    if (p.residual) o += bf16_bits_to_f32(p.residual[n]);
+                    if (p.residual) o += bf16_bits_to_f32(__ldcg(p.residual + n));
                 }
                 p.y[n] = f32_to_bf16_bits(o);
             }
@@ -493,6 +533,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         // ---------------- finalizer: completes row tiles off the consumers' critical path -------
         if (lane == 0) NF4_TRACE(46);
         asm volatile("bar.sync 2, %0;" ::"n"(kStreamThreads) : "memory");
+        // the exchange's epoch is advanced by the previous kernel on the stream
+        if (!PAIRED && p.peer_world > 0) asm volatile("griddepcontrol.wait;" ::: "memory");
         // tiles complete in traversal order: the slice's last tile, then the others from the front
         for (int q = 0; q < n_local; ++q) {
             const int li = (q == 0) ? n_local - 1 : q - 1;
@@ -680,16 +722,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(slot_of(q4)), "r"(xv.x), "r"(xv.y) : "memory");
     };
     uint2 xv0 = make_uint2(0u, 0u), xv1 = make_uint2(0u, 0u);
-    if (tid < n8) xv0 = __ldg(xg + tid);
-    if (tid + W * 32 < n8) xv1 = __ldg(xg + tid + W * 32);
+    if (tid < n8) xv0 = __ldcg(xg + tid);
+    if (tid + W * 32 < n8) xv1 = __ldcg(xg + tid + W * 32);
 
     if (tid < n8) sts_x(tid, xv0);
     if (tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
     for (int q4 = tid + 2 * W * 32; q4 < n8; q4 += 2 * W * 32) {
         const int q5 = q4 + W * 32;
-        const uint2 v0 = __ldg(xg + q4);
+        const uint2 v0 = __ldcg(xg + q4);
         uint2 v1 = make_uint2(0u, 0u);
-        if (q5 < n8) v1 = __ldg(xg + q5);
+        if (q5 < n8) v1 = __ldcg(xg + q5);
         sts_x(q4, v0);
         if (q5 < n8) sts_x(q5, v1);
     }
@@ -1025,7 +1067,8 @@ bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count
 }
 
 cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
-                               void* y, const void* residual, int64_t ff_pair, cudaStream_t s) {
+                               void* y, const void* residual, int64_t ff_pair, cudaStream_t s,
+                               const PeerTargets* peers) {
     const bool paired = ff_pair > 0;
     const StreamPlan pl = stream_plan(w, paired, ff_pair, scratch.sm_count);
     if (!pl.ok) return cudaErrorInvalidConfiguration;
@@ -1058,6 +1101,26 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.x_in_b = pl.x_in_b;
     p.smem_bytes = pl.smem;
     p.n_rows = (int)w.N;
+    p.peer_world = 0;
+    p.peer_rank = 0;
+    p.peer_max_rows = 0;
+    p.peer_ctrl = nullptr;
+    p.n_row_tiles = rt_work;
+    for (int d = 0; d < kMaxPeerWorld; ++d) {
+        p.peer_part[d] = nullptr;
+        p.peer_flag[d] = nullptr;
+    }
+    if (peers) {
+        if (paired || peers->world < 1 || peers->world > kMaxPeerWorld) return cudaErrorInvalidValue;
+        p.peer_world = peers->world;
+        p.peer_rank = peers->rank;
+        p.peer_max_rows = peers->max_rows;
+        p.peer_ctrl = peers->ctrl;
+        for (int d = 0; d < peers->world; ++d) {
+            p.peer_part[d] = peers->part_base[d];
+            p.peer_flag[d] = peers->flag_base[d];
+        }
+    }
 #ifdef AILA_NF4_TRACE
     static int trace_counter = 0;
     p.trace_idx = trace_counter++ % 32;

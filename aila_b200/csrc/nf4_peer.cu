@@ -1,0 +1,260 @@
+// Row-parallel decode over NVLink peer memory (net-new: the reference is single-device).
+//
+// A column-sharded linear (o_proj, down) gives every rank a partial y[N]; the ranks need their
+// sum. For M = 1 the message is tens of KB and a library all-reduce is latency-bound, so the
+// exchange is folded into the GEMV: the kernel's epilogue stores this rank's fp32 row sums
+// straight into EVERY rank's exchange buffer (plain peer stores through NVLink, its own buffer
+// included) behind system-scope fences, and the CTA that finishes the call's last row tile bumps
+// this rank's arrival counter on every rank. A small reducer kernel on each rank then waits
+// (bounded) until all its counters have reached the call's target and writes
+// y = bf16(sum over ranks in rank order (+ residual)): every rank gets the bit-identical result.
+//
+// Exchange buffer of one rank (one cudaMalloc, shared with the other processes through CUDA
+// IPC): [2 parities][world][max_rows] fp32 rows, [2][world] u32 arrival counters, then this
+// rank's control block {epoch, row tiles done, reducer blocks done}. Calls alternate between the
+// two parities (parity = epoch & 1): a rank can run ahead of a peer by less than one call (its
+// next reducer needs that peer's next rows), so two halves are enough. A rank's GEMV bumps its
+// counter on every rank ONCE per call (by the CTA that finishes the call's last row tile), so
+// the target of a call is (epoch >> 1) + 1; the reducer's last block advances the epoch. All
+// state lives on the device: the call sequence can be captured in a CUDA graph and replayed.
+// All ranks must issue the same calls in the same order.
+//
+// No load in this file or in the GEMV touches another GPU's memory: remote memory is only
+// written. No multicast object is created.
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "nf4_internal.h"
+
+struct AilaNf4PeerBuf {
+    int device = 0;
+    int rank = 0;
+    int world = 0;
+    int64_t max_rows = 0;
+    void* local = nullptr;      // this rank's buffer (cudaMalloc)
+    void* base[8] = {nullptr};  // every rank's buffer as mapped here (base[rank] == local)
+    bool imported[8] = {false};
+    size_t bytes = 0;
+};
+
+namespace nf4 {
+
+namespace {
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One thread per output row. The first `world` threads of every block wait for one rank's
+// counter each; a timeout is recorded and the block leaves without writing. The last block to
+// finish advances the epoch (every block has read it by then).
+__global__ void __launch_bounds__(256)
+peer_reduce_kernel(const float* __restrict__ part_base, const unsigned* __restrict__ flag_base,
+                   unsigned* ctrl, int world, long long max_rows, long long n,
+                   const uint16_t* __restrict__ residual, uint16_t* __restrict__ y, int* status) {
+    __shared__ int gave_up;
+    const unsigned epoch = *(volatile unsigned*)ctrl;
+    const unsigned parity = epoch & 1u;
+    const unsigned target = (epoch >> 1) + 1u;
+    if (threadIdx.x == 0) gave_up = 0;
+    __syncthreads();
+    if ((int)threadIdx.x < world) {
+        const unsigned* flag = flag_base + parity * world + threadIdx.x;
+        const long long t0 = clock64();
+        // wrap-safe "counter has reached target"
+        while ((int)(ld_acquire_sys(flag) - target) < 0) {
+            __nanosleep(100);
+            if (clock64() - t0 > kSpinLimitCycles) {
+                atomicExch(status, kStatusTimeoutPeer);
+                gave_up = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (!gave_up && row < n) {
+        const float* part = part_base + (size_t)parity * world * (size_t)max_rows;
+        float acc = 0.0f;
+        for (int r = 0; r < world; ++r) acc += __ldcg(part + (size_t)r * (size_t)max_rows + row);
+        if (residual) acc += bf16_bits_to_f32(residual[row]);
+        y[row] = f32_to_bf16_bits(acc);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned done = atomicAdd(ctrl + 2, 1u);
+        if (done == gridDim.x - 1) {
+            ctrl[2] = 0u;
+            __threadfence();
+            *(volatile unsigned*)ctrl = epoch + 1u;
+        }
+    }
+}
+
+size_t rows_floats(int world, int64_t max_rows) { return (size_t)2 * world * (size_t)max_rows; }
+
+size_t peerbuf_bytes(int world, int64_t max_rows) {
+    return rows_floats(world, max_rows) * 4 + (size_t)2 * world * 4 + 64 + 256;
+}
+
+float* part_base_of(void* base) { return static_cast<float*>(base); }
+
+unsigned* flag_base_of(void* base, int world, int64_t max_rows) {
+    return reinterpret_cast<unsigned*>(static_cast<float*>(base) + rows_floats(world, max_rows));
+}
+
+unsigned* ctrl_of(void* base, int world, int64_t max_rows) {
+    // 16 words after the counters' start keeps the control block off the counters' sector pair
+    return flag_base_of(base, world, max_rows) + 2 * 8;
+}
+
+}  // namespace
+
+cudaError_t launch_peer_reduce(const float* part_base, const unsigned* flag_base, unsigned* ctrl,
+                               int world, int64_t max_rows, int64_t n, const void* residual,
+                               void* y, int* d_status, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    peer_reduce_kernel<<<blocks, 256, 0, s>>>(part_base, flag_base, ctrl, world,
+                                              (long long)max_rows, (long long)n,
+                                              static_cast<const uint16_t*>(residual),
+                                              static_cast<uint16_t*>(y), d_status);
+    return cudaGetLastError();
+}
+
+}  // namespace nf4
+
+using nf4::fail;
+
+namespace {
+struct DevGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DevGuard(int device) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != device)
+            switched = (cudaSetDevice(device) == cudaSuccess);
+    }
+    ~DevGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+}  // namespace
+
+extern "C" {
+
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_create(int device, int rank, int world,
+                                                   int64_t max_rows, AilaNf4PeerBuf** out) {
+    if (!out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "out is NULL");
+    *out = nullptr;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "rank/world out of range (world <= 8)");
+    if (max_rows <= 0 || max_rows > (1ll << 28))
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "max_rows out of range");
+    DevGuard guard(device);
+    AilaNf4PeerBuf* b = new (std::nothrow) AilaNf4PeerBuf();
+    if (!b) return fail(AILA_NF4_ERR_OUT_OF_MEMORY, "host allocation failed");
+    b->device = device;
+    b->rank = rank;
+    b->world = world;
+    b->max_rows = (max_rows + 15) / 16 * 16;
+    b->bytes = nf4::peerbuf_bytes(world, b->max_rows);
+    cudaError_t e = cudaMalloc(&b->local, b->bytes);
+    if (e == cudaSuccess) e = cudaMemset(b->local, 0, b->bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(b->local);
+        delete b;
+        return nf4::cuda_fail(e, "peer buffer allocation");
+    }
+    b->base[rank] = b->local;
+    b->imported[rank] = true;
+    *out = b;
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_export(const AilaNf4PeerBuf* b, void* handle_out) {
+    if (!b || !handle_out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == AILA_NF4_IPC_HANDLE_BYTES, "IPC handle size");
+    DevGuard guard(b->device);
+    cudaIpcMemHandle_t h;
+    NF4_CUDA(cudaIpcGetMemHandle(&h, b->local));
+    std::memcpy(handle_out, &h, sizeof(h));
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_import(AilaNf4PeerBuf* b, int peer_rank,
+                                                   const void* handle) {
+    if (!b || !handle) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (peer_rank < 0 || peer_rank >= b->world || peer_rank == b->rank)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "peer_rank must name another rank of the group");
+    if (b->imported[peer_rank])
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "this peer's buffer is already mapped");
+    DevGuard guard(b->device);
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    NF4_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    b->base[peer_rank] = p;
+    b->imported[peer_rank] = true;
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API void aila_nf4_peerbuf_destroy(AilaNf4PeerBuf* b) {
+    if (!b) return;
+    DevGuard guard(b->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < b->world; ++r)
+        if (r != b->rank && b->imported[r] && b->base[r]) cudaIpcCloseMemHandle(b->base[r]);
+    cudaFree(b->local);
+    delete b;
+}
+
+AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear* l,
+                                                             AilaNf4Scratch* sc,
+                                                             AilaNf4PeerBuf* b, const void* x,
+                                                             void* y, const void* residual,
+                                                             void* stream) {
+    if (!l || !sc || !b || !x || !y) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (l->device != b->device || sc->device != b->device)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "linear, scratch and peer buffer must share a device");
+    if (l->N > b->max_rows)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT,
+                    "out_features " + std::to_string(l->N) + " exceeds the peer buffer's " +
+                        std::to_string(b->max_rows) + " rows");
+    for (int r = 0; r < b->world; ++r)
+        if (!b->imported[r])
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT,
+                        "peer buffer of rank " + std::to_string(r) + " has not been imported");
+    if (reinterpret_cast<uintptr_t>(x) & 15)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "x must be 16-byte aligned");
+    if (!nf4::gemv_stream_supported(*l, 0, sc->sm_count))
+        return fail(AILA_NF4_ERR_UNSUPPORTED, "shape not taken by the streaming decode kernel");
+    DevGuard guard(l->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    AilaNf4Status st = nf4::ensure_counters(sc, (size_t)l->RT);
+    if (st != AILA_NF4_OK) return st;
+    nf4::PeerTargets pt;
+    pt.world = b->world;
+    pt.rank = b->rank;
+    pt.max_rows = b->max_rows;
+    pt.ctrl = nf4::ctrl_of(b->local, b->world, b->max_rows);
+    for (int d = 0; d < 8; ++d) {
+        pt.part_base[d] = nullptr;
+        pt.flag_base[d] = nullptr;
+    }
+    for (int d = 0; d < b->world; ++d) {
+        pt.part_base[d] = nf4::part_base_of(b->base[d]);
+        pt.flag_base[d] = nf4::flag_base_of(b->base[d], b->world, b->max_rows);
+    }
+    NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, nullptr, nullptr, 0, s, &pt));
+    NF4_CUDA(nf4::launch_peer_reduce(nf4::part_base_of(b->local),
+                                     nf4::flag_base_of(b->local, b->world, b->max_rows), pt.ctrl,
+                                     b->world, b->max_rows, l->N, residual, y, sc->d_status, s));
+    return AILA_NF4_OK;
+}
+
+}  // extern "C"

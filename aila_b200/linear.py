@@ -211,6 +211,20 @@ class Bnb4BitLinear:
         _lib.check(_lib.load().aila_nf4_forward_decode_static(
             self._h, input.data_ptr(), output.data_ptr(), res, _stream_ptr(self.device)))
 
+    def forward_decode_allreduce(self, scratch: Bnb4BitLinearScratch, peers: "PeerBuffer",
+                                 input: torch.Tensor, output: torch.Tensor,
+                                 add_residual: torch.Tensor | None = None) -> None:
+        """seq_len == 1 forward of a column shard with the sum over ranks folded in: ``input`` is
+        this rank's column slice, ``output`` receives the full row sum on every rank."""
+        if input.dtype != torch.bfloat16 or output.dtype != torch.bfloat16:
+            raise RuntimeError("Bnb4BitLinear expects bf16 input/output tensors")
+        assert input.is_cuda and output.is_cuda and input.is_contiguous() and output.is_contiguous()
+        assert input.numel() >= self.in_features() and output.numel() >= self.out_features()
+        res = add_residual.data_ptr() if add_residual is not None else None
+        _lib.check(_lib.load().aila_nf4_forward_decode_allreduce(
+            self._h, scratch._h, peers._h, input.data_ptr(), output.data_ptr(), res,
+            _stream_ptr(self.device)))
+
     def dequantize_weight(self) -> torch.Tensor:
         """bf16 [in_features, out_features], the transposed layout of
         Bnb4BitLinear::dequantize_weight (Bnb4BitLinear.cpp:723-757)."""
@@ -232,6 +246,37 @@ class Bnb4BitLinear:
         _lib.check(_lib.load().aila_nf4_expand_absmax(self._h, out.data_ptr(),
                                                       _stream_ptr(self.device)))
         return out
+
+
+class PeerBuffer:
+    """One rank's exchange buffer for ``forward_decode_allreduce`` (aila_nf4_peerbuf_*)."""
+
+    def __init__(self, device: int, rank: int, world: int, max_rows: int):
+        self._h = ctypes.c_void_p()
+        self.rank, self.world = rank, world
+        _lib.check(_lib.load().aila_nf4_peerbuf_create(int(device), rank, world, max_rows,
+                                                       ctypes.byref(self._h)))
+
+    def export_handle(self) -> bytes:
+        buf = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        _lib.check(_lib.load().aila_nf4_peerbuf_export(self._h, buf))
+        return buf.raw
+
+    def import_handle(self, peer_rank: int, handle: bytes) -> None:
+        assert len(handle) == _lib.IPC_HANDLE_BYTES
+        buf = ctypes.create_string_buffer(handle, _lib.IPC_HANDLE_BYTES)
+        _lib.check(_lib.load().aila_nf4_peerbuf_import(self._h, peer_rank, buf))
+
+    def close(self) -> None:
+        if self._h:
+            _lib.load().aila_nf4_peerbuf_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def set_gemv_kernel(which: int) -> None:

@@ -85,6 +85,27 @@ class CudaBackend:
         return self._L.try_forward_decode_gate_up_swiglu(handle, self.scratch, x, out, ff,
                                                          seq_len=seq_len)
 
+    # -- fused decode exchange over NVLink peer memory -----------------------------------
+    def make_peer_buffer(self, group, max_rows: int):
+        """Creates this rank's exchange buffer and maps every other rank's (CUDA IPC handles
+        travel through the process group). Collective: every rank of ``group`` must call it."""
+        from .linear import PeerBuffer
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        buf = PeerBuffer(self.device, rank, world, max_rows)
+        mine = torch.frombuffer(bytearray(buf.export_handle()), dtype=torch.uint8)
+        mine = mine.to(torch.device("cuda", self.device))
+        handles = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(handles, mine, group=group)
+        for r, h in enumerate(handles):
+            if r != rank:
+                buf.import_handle(r, bytes(h.cpu().numpy().tobytes()))
+        dist.barrier(group=group)
+        return buf
+
+    def forward_allreduce(self, handle, peers, x: torch.Tensor, out: torch.Tensor,
+                          residual: torch.Tensor | None = None) -> None:
+        handle.forward_decode_allreduce(self.scratch, peers, x, out, residual)
+
 
 def _group_info(group):
     return dist.get_rank(group), dist.get_world_size(group)
@@ -112,18 +133,27 @@ class ColumnParallelNf4Linear:
 
 
 class RowParallelNf4Linear:
-    """y = sum_r x[:, rank's columns] W_r^T with one all-reduce (fp32 for small M)."""
+    """y = sum_r x[:, rank's columns] W_r^T with one all-reduce (fp32 for small M).
 
-    def __init__(self, w: Nf4Tensors, backend, group=None):
+    With ``peers`` (a buffer from ``backend.make_peer_buffer``) a single-row input takes the
+    fused route: the GEMV stores its fp32 row sums into every rank's exchange buffer and a small
+    kernel adds them up, with no library collective."""
+
+    def __init__(self, w: Nf4Tensors, backend, group=None, peers=None):
         self.rank, self.world = _group_info(group)
         self.group, self.backend = group, backend
         self.out_features, self.in_features = w.out_features, w.in_features
         self.local_in = w.in_features // self.world
         self.handle = backend.make_shard(w, COLS, self.rank, self.world)
+        self.peers = peers
 
     def forward(self, x_local: torch.Tensor, fp32_reduce: bool | None = None) -> torch.Tensor:
         """x_local: this rank's column slice [M, in/world]."""
         m = x_local.shape[0]
+        if m == 1 and self.peers is not None:
+            y = self.backend.empty(1, self.out_features)
+            self.backend.forward_allreduce(self.handle, self.peers, x_local, y)
+            return y
         part = self.backend.empty(m, self.out_features)
         self.backend.forward(self.handle, x_local, part, m)
         return reduce_partials(part, self.group, m <= 64 if fp32_reduce is None else fp32_reduce)
@@ -145,8 +175,10 @@ def reduce_partials(part: torch.Tensor, group, fp32: bool) -> torch.Tensor:
 class ShardedNf4Mlp:
     """SwiGLU MLP: gate|up row-sharded (SwiGLU local) -> down column-sharded -> one all-reduce."""
 
-    def __init__(self, gate: Nf4Tensors, up: Nf4Tensors, down: Nf4Tensors, backend, group=None):
+    def __init__(self, gate: Nf4Tensors, up: Nf4Tensors, down: Nf4Tensors, backend, group=None,
+                 peers=None):
         self.rank, self.world = _group_info(group)
+        self.peers = peers  # exchange buffer: single-row inputs skip the library all-reduce
         self.group, self.backend = group, backend
         if gate.out_features != up.out_features or gate.in_features != up.in_features:
             raise ValueError("gate and up must have the same shape")
@@ -168,5 +200,8 @@ class ShardedNf4Mlp:
             raise RuntimeError("fused gate+up+SiLU path not applicable to this shard "
                                "(ff / world must be a multiple of 16)")
         part = self.backend.empty(m, self.hidden)
+        if m == 1 and self.peers is not None:
+            self.backend.forward_allreduce(self.down, self.peers, mid, part)
+            return part
         self.backend.forward(self.down, mid, part, m)
         return reduce_partials(part, self.group, m <= 64)

@@ -215,6 +215,41 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_static(const AilaNf4Linear* l
                                                           void* stream);
 
 /*
+ * Row-parallel decode with the sum exchange folded into the GEMV. No reference counterpart
+ * (the reference runs on one device). For a linear that holds a COLUMN shard of the weight
+ * (aila_nf4_linear_create_shard, AILA_NF4_SHARD_COLS) every rank computes a partial y; the
+ * kernel stores its fp32 row sums straight into every rank's exchange buffer over NVLink
+ * (plain peer stores, no multicast object, no load from another GPU's memory) and a small
+ * second kernel sums the ranks' rows in rank order: all ranks obtain the bit-identical
+ * y = bf16(sum_r W_r x_r (+ residual)).
+ *
+ * Set-up, once per process group (one process per GPU, all on one node): every rank creates an
+ * AilaNf4PeerBuf for `max_rows` >= the largest out_features it will be used with, exports its
+ * 64-byte handle, hands it to the other ranks by any host channel, and imports theirs.
+ * Rules: all ranks issue the same aila_nf4_forward_decode_allreduce calls in the same order;
+ * the calls of one buffer go to one stream per GPU; the sequence may be captured in a CUDA
+ * graph (all exchange state lives on the device). A rank that waits more than about a second
+ * for another rank records AILA_NF4_ERR_KERNEL_TIMEOUT for aila_nf4_scratch_check; after that
+ * the buffers of the group must be recreated.
+ */
+typedef struct AilaNf4PeerBuf AilaNf4PeerBuf;
+#define AILA_NF4_IPC_HANDLE_BYTES 64
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_create(int device, int rank, int world,
+                                                   int64_t max_rows, AilaNf4PeerBuf** out);
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_export(const AilaNf4PeerBuf* buf, void* handle_out);
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_import(AilaNf4PeerBuf* buf, int peer_rank,
+                                                   const void* handle);
+AILA_NF4_API void aila_nf4_peerbuf_destroy(AilaNf4PeerBuf* buf);
+/* seq_len == 1 only; x is this rank's column slice [in_features / world] (bf16, 16-byte
+ * aligned), y receives all out_features rows. */
+AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear* linear,
+                                                             AilaNf4Scratch* scratch,
+                                                             AilaNf4PeerBuf* buf,
+                                                             const void* x_bf16, void* y_bf16,
+                                                             const void* residual_bf16,
+                                                             void* stream);
+
+/*
  * Whole-weight dequantisation into the TRANSPOSED bf16 matrix Wt[in][out], bit-equal to
  * Bnb4BitLinear::dequantize_weight (src/ops/Bnb4BitLinear.cpp:723-757):
  * Wt[k*out + n] = bf16(quant_map[nibble(n,k)] * absmax(n, k/blocksize)).

@@ -387,3 +387,40 @@ def test_cache_dequant_env_mode(oracle, tmp_path):
     want = oracle.forward(w.packed, w.quant_map, oracle_absmax(oracle, w), bf16_bits(x), 200, 272,
                           448, 64)
     assert_close_norm(got, want, REL, "prefill with bf16 weight cache")
+
+
+def test_dependent_decode_launches_in_cuda_graph(nf4):
+    """A chain of decode launches where each consumes the previous one's output, captured in a
+    CUDA graph and replayed: with programmatic dependent launch the consumer kernel is already
+    resident while its input is being written, so its loads of x must not come from a
+    non-coherent cache. Every replay (the first included) must reproduce the eager results."""
+    H, FF = 1024, 2048
+    g, u, d = make_weight(1, FF, H), make_weight(2, FF, H), make_weight(3, H, FF)
+    Bnb4BitLinear = nf4.Bnb4BitLinear
+    lg, lu, gu, ld = Bnb4BitLinear(), Bnb4BitLinear(), Bnb4BitLinear(), Bnb4BitLinear()
+    assert lg.init(g, 0) and lu.init(u, 0) and gu.init_fused_rows(lg, lu) and ld.init(d, 0)
+    sc = nf4.Bnb4BitLinearScratch(0)
+    x = synth.gaussian_activation(11, 1, H).cuda()
+
+    def mlp(inp):
+        mid = torch.empty(1, FF, dtype=torch.bfloat16, device="cuda")
+        assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(gu, sc, inp, mid, FF)
+        y = torch.empty(1, H, dtype=torch.bfloat16, device="cuda")
+        ld.forward(sc, mid, y, 1, add_residual=inp)
+        return y
+
+    y0 = mlp(x)
+    torch.cuda.synchronize()
+    y1 = mlp(y0)
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            ya = mlp(x)
+            yb = mlp(ya)
+        for _ in range(3):
+            gr.replay()
+            st.synchronize()
+            assert torch.equal(ya, y0) and torch.equal(yb, y1)
+    sc.check()

@@ -43,7 +43,37 @@ def _worker(rank, world, port, q):
             y = mlp.forward(x)
             torch.cuda.synchronize()
             outs[M] = y.cpu().view(torch.uint16).numpy()
+        # fused exchange: the down projection stores its row sums into every rank's buffer over
+        # NVLink and a small kernel adds them up - several eager calls (the exchange alternates
+        # between two buffer halves), then the same calls replayed from a CUDA graph
+        peers = be.make_peer_buffer(None, H)
+        fused = sharded.ShardedNf4Mlp(gate, up, down, be, peers=peers)
+        x1 = synth.gaussian_activation(11, 1, H).cuda()
+        ys = [fused.forward(x1) for _ in range(5)]
+        torch.cuda.synchronize()
         be.scratch.check()
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                yg = fused.forward(x1)
+                yg2 = fused.forward(yg[:, :H].contiguous())
+            for _ in range(3):
+                g.replay()
+            st.synchronize()
+        be.scratch.check()
+        y_chain = fused.forward(fused.forward(x1)[:, :H].contiguous())
+        torch.cuda.synchronize()
+        be.scratch.check()
+        same = all(torch.equal(ys[0], t) for t in ys[1:]) and torch.equal(ys[0], yg) \
+            and torch.equal(y_chain, yg2)
+        mine = ys[0].clone()
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        same = same and all(torch.equal(mine, t) for t in everyone)
+        outs["fused"] = ys[0].cpu().view(torch.uint16).numpy()
+        outs["fused_consistent"] = bool(same)
+        peers.close()
         if rank == 0:
             q.put(("ok", outs))
         dist.barrier()
@@ -73,6 +103,8 @@ def test_sharded_mlp_nccl(oracle, world):
     gate, up, down = make_weight(1, FF, H), make_weight(2, FF, H), make_weight(3, H, FF)
     packed = np.concatenate([gate.packed, up.packed])
     am = np.concatenate([oracle_absmax(oracle, gate), oracle_absmax(oracle, up)])
+    assert res[1].pop("fused_consistent"), "fused exchange: results differ between calls or ranks"
+    fused_bits = res[1].pop("fused")
     for M, got in res[1].items():
         x = synth.gaussian_activation(10 + M, M, H).view(torch.uint16).numpy()
         if M == 1:
@@ -83,3 +115,8 @@ def test_sharded_mlp_nccl(oracle, world):
                                           mid, M, H, FF, 64))
         err = np.abs(bits_to_f32(got) - want).max()
         assert err <= 2e-2 * np.abs(want).max(), (M, err)
+        if M == 1:
+            err = np.abs(bits_to_f32(fused_bits) - want).max()
+            assert err <= 2e-2 * np.abs(want).max(), ("fused", err)
+            # (not bit-equal to the library route, which rounds every rank's partial sum to bf16
+            # before the all-reduce; the fused route adds the fp32 partial sums and rounds once)
