@@ -44,6 +44,15 @@ class WeightDesc(ctypes.Structure):
     ]
 
 
+class StTensorView(ctypes.Structure):
+    """AilaStTensorView."""
+    _fields_ = [("dtype", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * 8), ("data", ctypes.c_void_p),
+                ("nbytes", ctypes.c_int64)]
+
+
+ST_DTYPES = ("unknown", "U8", "I8", "F16", "BF16", "F32", "F64", "I32", "I64", "BOOL")
+
 # name -> (restype, argtypes); every symbol include/aila_nf4.h declares
 _VP = ctypes.c_void_p
 _SIGNATURES = {
@@ -78,6 +87,13 @@ _SIGNATURES = {
     "aila_nf4_peerbuf_import": (ctypes.c_int, [_VP, ctypes.c_int, _VP]),
     "aila_nf4_peerbuf_destroy": (None, [_VP]),
     "aila_nf4_forward_decode_allreduce": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
+    "aila_st_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_VP)]),
+    "aila_st_close": (None, [_VP]),
+    "aila_st_tensor_count": (ctypes.c_int64, [_VP]),
+    "aila_st_tensor_name": (ctypes.c_char_p, [_VP, ctypes.c_int64]),
+    "aila_st_find": (ctypes.c_int, [_VP, ctypes.c_char_p, ctypes.POINTER(StTensorView)]),
+    "aila_st_load_bnb4_weight": (ctypes.c_int, [_VP, ctypes.c_char_p, ctypes.c_int,
+                                                ctypes.POINTER(WeightDesc)]),
     "aila_nf4_dequantize": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_dequantize_rowmajor": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_expand_absmax": (ctypes.c_int, [_VP, _VP, _VP]),

@@ -334,33 +334,39 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     // ---- completing a row tile (finalizer warp) ----
     // write_rows: the epilogue of 16 output rows (lanes 0..15 hold one row each)
     int peer_parity = -1;  // exchange half of this launch, read on first use
+    int peer_tiles = 0;    // row tiles this CTA has stored into the exchange buffers
+    // After a CTA's last tile: one system-scope fence, then the tiles are counted; the CTA that
+    // completes the launch's count adds one to this rank's arrival counter on every rank. A rank
+    // that sees all its counters reach the epoch's target may read the rows.
+    auto peer_publish = [&]() {
+        if (PAIRED || p.peer_world == 0 || peer_tiles == 0) return;
+        __threadfence_system();
+        __syncwarp();
+        unsigned done = 0;
+        if (lane == 0) done = atomicAdd(p.peer_ctrl + 1, (unsigned)peer_tiles);
+        done = __shfl_sync(0xffffffffu, done, 0);
+        if (done + (unsigned)peer_tiles == (unsigned)p.n_row_tiles) {
+            if (lane == 0) p.peer_ctrl[1] = 0u;
+            __threadfence_system();
+            if (lane < p.peer_world)
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(
+                                 p.peer_flag[lane] + peer_parity * p.peer_world + p.peer_rank)
+                             : "memory");
+        }
+    };
     auto write_rows = [&](int rtile, const float (&v)[NP]) {
         if (!PAIRED && p.peer_world > 0) {
-            // Plain stores into every rank's memory (this rank's own included) and a
-            // system-scope fence per tile. The CTA that finishes the launch's LAST row tile then
-            // adds one to this rank's arrival counter on every rank: a rank that sees all its
-            // counters reach the epoch's target may read the rows. The exchange alternates
-            // between two halves of the buffers (parity of the epoch, which this rank's reducer
-            // advances).
+            // Row-parallel exchange: plain stores into every rank's memory (this rank's own
+            // included); the fence and the arrival accounting follow once per CTA
+            // (peer_publish). The exchange alternates between two halves of the buffers
+            // (parity of the epoch, which this rank's reducer advances).
             if (peer_parity < 0) peer_parity = (int)(*(volatile unsigned*)p.peer_ctrl & 1u);
             const size_t slice = ((size_t)peer_parity * p.peer_world + p.peer_rank) * (size_t)p.peer_max_rows;
             const int n = rtile * kTileRows + lane;
             if (lane < 16 && n < p.n_out) {
                 for (int d = 0; d < p.peer_world; ++d) p.peer_part[d][slice + n] = v[0];
             }
-            __threadfence_system();
-            __syncwarp();
-            unsigned done = 0;
-            if (lane == 0) done = atomicAdd(p.peer_ctrl + 1, 1u);
-            done = __shfl_sync(0xffffffffu, done, 0);
-            if (done == (unsigned)p.n_row_tiles - 1u) {
-                if (lane == 0) p.peer_ctrl[1] = 0u;
-                __threadfence_system();
-                if (lane < p.peer_world)
-                    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(
-                                     p.peer_flag[lane] + peer_parity * p.peer_world + p.peer_rank)
-                                 : "memory");
-            }
+            ++peer_tiles;
             return;
         }
         if (lane < 16) {
@@ -567,6 +573,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         }
         resolve(pend_li0, pend_old0);
         resolve(pend_li1, pend_old1);
+        peer_publish();
 #ifdef AILA_NF4_TRACE
         if (lane == 0) {
             unsigned long long t_;

@@ -97,10 +97,16 @@ class Bnb4BitLinear:
         """Rank ``rank`` of ``world`` of the weight: rows (mode 0) or input columns (mode 1)."""
         return self._create(weight, device, (mode, rank, world))
 
+    def init_from_desc(self, desc: _lib.WeightDesc, shard: tuple[int, int, int] | None = None) -> bool:
+        """From a ready descriptor, e.g. ``SafetensorsFile.load_bnb4_weight_ref`` (the
+        reference's LoadBnb4BitWeightRef + init pair); ``shard`` = (mode, rank, world). The
+        memory the descriptor points to must stay valid until this call returns."""
+        return self._create(desc, int(desc.device), shard)
+
     def _create(self, weight, device, shard) -> bool:
         lib = _lib.load()
         keep: list = []
-        d = self._desc(weight, device, keep)
+        d = weight if isinstance(weight, _lib.WeightDesc) else self._desc(weight, device, keep)
         h = ctypes.c_void_p()
         if shard is None:
             st = lib.aila_nf4_linear_create(ctypes.byref(d), ctypes.byref(h))

@@ -250,6 +250,41 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear
                                                              void* stream);
 
 /*
+ * Checkpoint front-end (host side, no GPU work): a memory-mapped safetensors file and the
+ * assembly of one bitsandbytes 4-bit weight into an AilaNf4WeightDesc whose pointers lie
+ * inside the mapping, ready for aila_nf4_linear_create (keep the file open until the create
+ * call has returned). Replaces, for this path, LoadSafetensors + LoadBnb4BitWeightRef
+ * (reference src/utils/SafeTensors.hpp:127-140, src/utils/SafeTensors.cpp:154-222 and
+ * :370-489): same side-tensor names (<w>.absmax, <w>.quant_map, <w>.nested_absmax,
+ * <w>.nested_quant_map, <w>.quant_state.bitsandbytes__nf4), same dtype rules, same size
+ * invariants, same quant_state JSON keys; a violated rule returns
+ * AILA_NF4_ERR_INVALID_ARGUMENT (AILA_NF4_ERR_UNSUPPORTED for a quant_type other than nf4)
+ * with the reference's wording in aila_nf4_last_error().
+ */
+typedef struct AilaStFile AilaStFile;
+typedef enum AilaStDtype {
+    AILA_ST_DTYPE_UNKNOWN = 0, AILA_ST_U8, AILA_ST_I8, AILA_ST_F16, AILA_ST_BF16, AILA_ST_F32,
+    AILA_ST_F64, AILA_ST_I32, AILA_ST_I64, AILA_ST_BOOL
+} AilaStDtype;
+#define AILA_ST_MAX_RANK 8
+typedef struct AilaStTensorView {
+    int32_t dtype;                 /* AilaStDtype */
+    int32_t rank;
+    int64_t shape[AILA_ST_MAX_RANK];
+    const void* data;              /* inside the mapping; valid until aila_st_close */
+    int64_t nbytes;
+} AilaStTensorView;
+AILA_NF4_API AilaNf4Status aila_st_open(const char* path, AilaStFile** out);
+AILA_NF4_API void aila_st_close(AilaStFile* file);
+AILA_NF4_API int64_t aila_st_tensor_count(const AilaStFile* file);
+AILA_NF4_API const char* aila_st_tensor_name(const AilaStFile* file, int64_t index);
+/* AILA_NF4_NOT_APPLICABLE when the file holds no tensor of that name. */
+AILA_NF4_API AilaNf4Status aila_st_find(const AilaStFile* file, const char* name,
+                                        AilaStTensorView* out);
+AILA_NF4_API AilaNf4Status aila_st_load_bnb4_weight(const AilaStFile* file, const char* name,
+                                                    int device, AilaNf4WeightDesc* out);
+
+/*
  * Whole-weight dequantisation into the TRANSPOSED bf16 matrix Wt[in][out], bit-equal to
  * Bnb4BitLinear::dequantize_weight (src/ops/Bnb4BitLinear.cpp:723-757):
  * Wt[k*out + n] = bf16(quant_map[nibble(n,k)] * absmax(n, k/blocksize)).

@@ -63,6 +63,37 @@ struct Bnb4BitLinearScratch {
     }
 };
 
+// One memory-mapped safetensors file; stands where the reference keeps a ModelWeights
+// (src/utils/SafeTensors.hpp:86-121) for the purpose of finding bitsandbytes weights.
+struct SafetensorsFile {
+    AilaStFile* handle = nullptr;
+
+    SafetensorsFile() = default;
+    explicit SafetensorsFile(const std::string& path) {
+        if (aila_st_open(path.c_str(), &handle) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+    }
+    SafetensorsFile(const SafetensorsFile&) = delete;
+    SafetensorsFile& operator=(const SafetensorsFile&) = delete;
+    ~SafetensorsFile() { aila_st_close(handle); }
+
+    bool has(const std::string& name) const {
+        AilaStTensorView v;
+        return aila_st_find(handle, name.c_str(), &v) == AILA_NF4_OK;
+    }
+};
+
+// LoadBnb4BitWeightRef (reference src/utils/SafeTensors.hpp:136-140, .cpp:370-489): assembles
+// and checks the view of weight `name`; false + message when a rule is violated. The view
+// points into the mapped file: keep `weights` alive until Bnb4BitLinear::init has returned.
+inline bool LoadBnb4BitWeightRef(Context& ctx, SafetensorsFile& weights, const std::string& name,
+                                 AilaNf4WeightDesc& out, std::string* error_message = nullptr) {
+    if (aila_st_load_bnb4_weight(weights.handle, name.c_str(), ctx.device, &out) == AILA_NF4_OK)
+        return true;
+    if (error_message) *error_message = aila_nf4_last_error();
+    return false;
+}
+
 class Bnb4BitLinear {
 public:
     Bnb4BitLinear() = default;

@@ -32,6 +32,20 @@ int main() {
     Context ctx;
     Bnb4BitLinear q, k, fused;
     std::string err;
+    {
+        // the loader half of the interface: a missing file throws, a missing weight reports
+        bool threw = false;
+        try {
+            aila::nf4::SafetensorsFile nofile("/nonexistent/model.safetensors");
+        } catch (const std::runtime_error&) {
+            threw = true;
+        }
+        if (!threw) return 7;
+        aila::nf4::SafetensorsFile empty;
+        AilaNf4WeightDesc view;
+        if (aila::nf4::LoadBnb4BitWeightRef(ctx, empty, "w", view, &err) || err.empty()) return 8;
+        err.clear();
+    }
     const bool ok = q.init(ctx, d, &err);
     if (!ok) {
         // no usable GPU: init reports the failure through the bool + message, like the reference

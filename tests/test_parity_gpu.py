@@ -424,3 +424,25 @@ def test_dependent_decode_launches_in_cuda_graph(nf4):
             st.synchronize()
             assert torch.equal(ya, y0) and torch.equal(yb, y1)
     sc.check()
+
+
+def test_linear_from_checkpoint_file(nf4, oracle, tmp_path):
+    """safetensors file -> aila_st_load_bnb4_weight -> aila_nf4_linear_create: the weight goes from
+    the mapped file straight into the device layout; dequantised values are bit-equal to the
+    oracle's and to a linear created from the same tensors in memory."""
+    from aila_b200 import checkpoint
+    N, K = 80, 384
+    w = make_weight(91, N, K, 64, True)
+    path = tmp_path / "m.safetensors"
+    tensors = {"pad": np.zeros(3, dtype=np.uint8)}  # odd-sized neighbour: unaligned tensor data
+    tensors.update(checkpoint.bnb4_checkpoint_tensors("model.layers.3.self_attn.o_proj.weight", w))
+    checkpoint.write_safetensors(str(path), tensors)
+    with checkpoint.SafetensorsFile(str(path)) as f:
+        lin = nf4.Bnb4BitLinear()
+        assert lin.init_from_desc(f.load_bnb4_weight_ref("model.layers.3.self_attn.o_proj.weight", 0)), \
+            lin.last_error
+    direct = _lin(nf4, w)
+    got = lin.dequantize_weight().cpu().view(torch.uint16).numpy()
+    assert np.array_equal(got, direct.dequantize_weight().cpu().view(torch.uint16).numpy())
+    want = oracle.dequantize_kn(w.packed, w.quant_map, oracle_absmax(oracle, w), N, K, 64)
+    assert np.array_equal(got, want.reshape(K, N))
