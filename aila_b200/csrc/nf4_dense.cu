@@ -1,0 +1,286 @@
+// Dense bf16 linear: the unquantised projection that sits next to the NF4 linears in the decode
+// stack (the lm_head, 29 % of the bytes of a decode step in the 4B configuration), and a greedy
+// argmax over its logits.
+//
+// Role in the reference: class Linear (src/ops/Ops.hpp:16-31, src/ops/Linear.cpp:172-256), a
+// library matmul y = x W^T with W bf16 [out][in], fp32 accumulation, bf16 output; called for the
+// last token's hidden state (src/models/Qwen3Bnb4Backend.cpp:432-439); ops::argmax
+// (src/ops/SamplingOps.cpp:321-365) picks the token on the device.
+//
+// seq_len == 1: a streaming GEMV, HBM-bound (2 bytes per weight): every warp owns four
+// consecutive rows, reads them with 16-byte non-allocating loads (eight loads in flight per
+// lane), x sits in shared memory, fp32 accumulation, one shuffle reduction per row.
+// seq_len > 1: the tcgen05 GEMM of the prefill route (the weight already has its [out][in] bf16
+// layout).
+#include <new>
+#include <string>
+
+#include "nf4_internal.h"
+
+struct AilaDenseLinear {
+    int device = 0;
+    int64_t N = 0, K = 0;
+    uint16_t* d_w = nullptr;  // [N][K] bf16
+};
+
+namespace nf4 {
+namespace {
+
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w}, xx[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        acc = fmaf(__uint_as_float(ww[i] << 16), __uint_as_float(xx[i] << 16), acc);
+        acc = fmaf(__uint_as_float(ww[i] & 0xffff0000u), __uint_as_float(xx[i] & 0xffff0000u), acc);
+    }
+    return acc;
+}
+
+constexpr int kDenseWarps = 8;
+constexpr int kDenseRows = 4;  // rows per warp
+
+// K % 8 == 0, rows 16-byte aligned. Dynamic shared memory: x, K bf16.
+__global__ void __launch_bounds__(kDenseWarps * 32)
+dense_gemv_kernel(const uint16_t* __restrict__ w, const uint16_t* __restrict__ x,
+                  uint16_t* __restrict__ y, const uint16_t* __restrict__ residual, long long N, int K) {
+    extern __shared__ __align__(16) uint8_t dense_smem[];
+    uint4* xs = reinterpret_cast<uint4*>(dense_smem);
+    const int k16 = K >> 3;  // 16-byte pieces per row
+    // x may have been written by the previous kernel on the stream: coherent (L2) loads
+    for (int i = threadIdx.x; i < k16; i += blockDim.x) xs[i] = __ldcg(reinterpret_cast<const uint4*>(x) + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long r0 = ((long long)blockIdx.x * kDenseWarps + warp) * kDenseRows;
+    if (r0 >= N) return;
+    const uint4* rows[kDenseRows];
+#pragma unroll
+    for (int r = 0; r < kDenseRows; ++r) {
+        const long long rr = (r0 + r < N) ? r0 + r : N - 1;  // clamp: the tail warp re-reads a row
+        rows[r] = reinterpret_cast<const uint4*>(w + rr * K);
+    }
+    float acc[kDenseRows] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int i = lane;
+    for (; i + 32 < k16; i += 64) {
+        uint4 a[kDenseRows], b[kDenseRows];
+#pragma unroll
+        for (int r = 0; r < kDenseRows; ++r) {
+            a[r] = ldg_stream16(rows[r] + i);
+            b[r] = ldg_stream16(rows[r] + i + 32);
+        }
+        const uint4 xa = xs[i], xb = xs[i + 32];
+#pragma unroll
+        for (int r = 0; r < kDenseRows; ++r) acc[r] = dot8(b[r], xb, dot8(a[r], xa, acc[r]));
+    }
+    for (; i < k16; i += 32) {
+        const uint4 xa = xs[i];
+#pragma unroll
+        for (int r = 0; r < kDenseRows; ++r) acc[r] = dot8(ldg_stream16(rows[r] + i), xa, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kDenseRows; ++r)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+    if (lane < kDenseRows && r0 + lane < N) {
+        float v = acc[0];
+#pragma unroll
+        for (int r = 1; r < kDenseRows; ++r)
+            if (lane == r) v = acc[r];
+        if (residual) v += bf16_bits_to_f32(__ldcg(residual + r0 + lane));
+        y[r0 + lane] = f32_to_bf16_bits(v);
+    }
+}
+
+// Any K (scalar loads): one warp per row. The slow path for shapes the vector kernel does not take.
+__global__ void __launch_bounds__(256)
+dense_gemv_generic_kernel(const uint16_t* __restrict__ w, const uint16_t* __restrict__ x,
+                          uint16_t* __restrict__ y, const uint16_t* __restrict__ residual,
+                          long long N, int K) {
+    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= N) return;
+    float acc = 0.0f;
+    for (int k = lane; k < K; k += 32)
+        acc = fmaf(bf16_bits_to_f32(w[row * K + k]), bf16_bits_to_f32(__ldcg(x + k)), acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        if (residual) acc += bf16_bits_to_f32(__ldcg(residual + row));
+        y[row] = f32_to_bf16_bits(acc);
+    }
+}
+
+// Greedy token choice over bf16 logits: the largest value, the smallest index among equals
+// (NaN never wins). One block, like the reference's single work-group.
+__global__ void __launch_bounds__(1024)
+argmax_bf16_kernel(const uint16_t* __restrict__ logits, long long n, int* __restrict__ out) {
+    __shared__ float s_val[32];
+    __shared__ long long s_idx[32];
+    float best = -INFINITY;
+    long long best_i = 0x7fffffffffffffffll;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = bf16_bits_to_f32(__ldcg(logits + i));
+        if (v > best || (v == best && i < best_i)) {
+            best = v;
+            best_i = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) {
+            best = ov;
+            best_i = oi;
+        }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+        s_val[warp] = best;
+        s_idx[warp] = best_i;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? s_val[lane] : -INFINITY;
+        best_i = lane < nw ? s_idx[lane] : 0x7fffffffffffffffll;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const long long oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best || (ov == best && oi < best_i)) {
+                best = ov;
+                best_i = oi;
+            }
+        }
+        // all values NaN or -inf: index 0, as a plain "first element wins" scan would give
+        if (lane == 0) *out = (int)(best_i == 0x7fffffffffffffffll ? 0 : best_i);
+    }
+}
+
+}  // namespace
+}  // namespace nf4
+
+using nf4::fail;
+
+namespace {
+struct DenseDevGuard {
+    int prev = -1;
+    bool switched = false;
+    cudaError_t err = cudaSuccess;
+    explicit DenseDevGuard(int device) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) {
+            err = cudaSetDevice(device);
+            switched = (err == cudaSuccess);
+        }
+    }
+    ~DenseDevGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+}  // namespace
+
+extern "C" {
+
+AILA_NF4_API AilaNf4Status aila_dense_linear_create(const void* weight_bf16, int64_t out_features,
+                                                    int64_t in_features, int weight_on_device,
+                                                    int device, AilaDenseLinear** out) {
+    if (!out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "out is NULL");
+    *out = nullptr;
+    if (!weight_bf16) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "weight pointer is NULL");
+    if (out_features <= 0 || in_features <= 0 || in_features > (1 << 30) ||
+        out_features > (1ll << 40) / in_features)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Linear: in_features/out_features out of range");
+    DenseDevGuard guard(device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    AilaDenseLinear* l = new (std::nothrow) AilaDenseLinear();
+    if (!l) return fail(AILA_NF4_ERR_OUT_OF_MEMORY, "host allocation failed");
+    l->device = device;
+    l->N = out_features;
+    l->K = in_features;
+    const size_t bytes = (size_t)out_features * (size_t)in_features * 2;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&l->d_w), bytes + 256);
+    if (e == cudaSuccess)
+        e = cudaMemcpy(l->d_w, weight_bf16, bytes,
+                       weight_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(l->d_w);
+        delete l;
+        return nf4::cuda_fail(e, "dense weight upload");
+    }
+    *out = l;
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API void aila_dense_linear_destroy(AilaDenseLinear* l) {
+    if (!l) return;
+    DenseDevGuard guard(l->device);
+    cudaFree(l->d_w);
+    delete l;
+}
+
+AILA_NF4_API int64_t aila_dense_linear_in_features(const AilaDenseLinear* l) { return l ? l->K : 0; }
+AILA_NF4_API int64_t aila_dense_linear_out_features(const AilaDenseLinear* l) { return l ? l->N : 0; }
+
+AILA_NF4_API AilaNf4Status aila_dense_linear_forward(const AilaDenseLinear* l, AilaNf4Scratch* sc,
+                                                     const void* x, void* y, int seq_len,
+                                                     const void* residual, void* stream) {
+    if (!l) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "linear handle is NULL");
+    if (!sc) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "scratch handle is NULL");
+    if (!x || !y) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Linear expects bf16 input/output tensors");
+    if (seq_len <= 0) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Linear::forward: seq_len must be positive");
+    if (sc->device != l->device)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "scratch and linear live on different devices");
+    DenseDevGuard guard(l->device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (seq_len > 1)
+        return nf4::launch_gemm_bf16(l->d_w, x, y, residual, seq_len, l->N, l->K, 0, l->device,
+                                     sc->sm_count, sc->d_status, s);
+    const uint16_t* w = l->d_w;
+    const uint16_t* xp = static_cast<const uint16_t*>(x);
+    uint16_t* yp = static_cast<uint16_t*>(y);
+    const uint16_t* rp = static_cast<const uint16_t*>(residual);
+    const size_t smem = (size_t)l->K * 2;
+    const bool vec = (l->K % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && smem <= 200 * 1024;
+    if (vec) {
+        if (smem > 48 * 1024) {
+            static bool raised[64] = {false};
+            if (l->device < 64 && !raised[l->device]) {
+                NF4_CUDA(cudaFuncSetAttribute(nf4::dense_gemv_kernel,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                raised[l->device] = true;
+            }
+        }
+        const long long rows_per_block = nf4::kDenseWarps * nf4::kDenseRows;
+        const unsigned blocks = (unsigned)((l->N + rows_per_block - 1) / rows_per_block);
+        nf4::dense_gemv_kernel<<<blocks, nf4::kDenseWarps * 32, smem, s>>>(w, xp, yp, rp, (long long)l->N, (int)l->K);
+    } else {
+        const unsigned blocks = (unsigned)((l->N + 7) / 8);
+        nf4::dense_gemv_generic_kernel<<<blocks, 256, 0, s>>>(w, xp, yp, rp, (long long)l->N, (int)l->K);
+    }
+    NF4_CUDA(cudaGetLastError());
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, int32_t* d_result,
+                                            int device, void* stream) {
+    if (!logits_bf16 || !d_result) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (n <= 0 || n > 0x7fffffffll) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "argmax: vocab size out of range");
+    DenseDevGuard guard(device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    nf4::argmax_bf16_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(logits_bf16), (long long)n, d_result);
+    NF4_CUDA(cudaGetLastError());
+    return AILA_NF4_OK;
+}
+
+}  // extern "C"

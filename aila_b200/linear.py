@@ -254,6 +254,64 @@ class Bnb4BitLinear:
         return out
 
 
+class Linear:
+    """Dense bf16 linear (reference class Linear, src/ops/Ops.hpp:16-31): ``init`` with a
+    [out_features, in_features] bf16 weight, ``forward(scratch, input, output, seq_len)``."""
+
+    def __init__(self):
+        self._h = None
+        self.device = None
+
+    def init(self, weight: torch.Tensor, in_features: int, out_features: int, device: int = 0) -> None:
+        if weight.dtype != torch.bfloat16 or tuple(weight.shape) != (out_features, in_features):
+            raise RuntimeError("Linear::init expects a bf16 [out_features, in_features] weight")
+        weight = weight.contiguous()
+        h = ctypes.c_void_p()
+        _lib.check(_lib.load().aila_dense_linear_create(weight.data_ptr(), out_features, in_features,
+                                                        1 if weight.is_cuda else 0, int(device),
+                                                        ctypes.byref(h)))
+        self.close()
+        self._h = h
+        self.device = torch.device("cuda", device)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.load().aila_dense_linear_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def in_features(self) -> int:
+        return int(_lib.load().aila_dense_linear_in_features(self._h))
+
+    def out_features(self) -> int:
+        return int(_lib.load().aila_dense_linear_out_features(self._h))
+
+    def forward(self, scratch: Bnb4BitLinearScratch, input: torch.Tensor, output: torch.Tensor,
+                seq_len: int, add_residual: torch.Tensor | None = None) -> None:
+        if input.dtype != torch.bfloat16 or output.dtype != torch.bfloat16:
+            raise RuntimeError("Linear expects bf16 input/output tensors")
+        assert input.is_cuda and output.is_cuda and input.is_contiguous() and output.is_contiguous()
+        assert input.numel() >= seq_len * self.in_features()
+        assert output.numel() >= seq_len * self.out_features()
+        res = add_residual.data_ptr() if add_residual is not None else None
+        _lib.check(_lib.load().aila_dense_linear_forward(self._h, scratch._h, input.data_ptr(),
+                                                         output.data_ptr(), seq_len, res,
+                                                         _stream_ptr(self.device)))
+
+
+def argmax(logits: torch.Tensor, vocab_size: int, result: torch.Tensor) -> None:
+    """ops::argmax (src/ops/SamplingOps.cpp:321-365): greedy token over bf16 logits, written to
+    the int32 device tensor ``result``."""
+    assert logits.dtype == torch.bfloat16 and logits.is_cuda and result.dtype == torch.int32
+    _lib.check(_lib.load().aila_argmax_bf16(logits.data_ptr(), vocab_size, result.data_ptr(),
+                                            logits.device.index, _stream_ptr(logits.device)))
+
+
 class PeerBuffer:
     """One rank's exchange buffer for ``forward_decode_allreduce`` (aila_nf4_peerbuf_*)."""
 

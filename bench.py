@@ -300,16 +300,17 @@ def decode_stack(local, stream):
     """cfg4: the NF4 linears of one decode step of a 36-layer GQA transformer (hidden 2560, q 4096,
     k/v 1024, ff 9728): per layer fused qkv 2560->6144, o 4096->2560, fused gate|up+SiLU
     2560->2x9728, down 9728->2560; each linear gets its own N(0,1) input. One CUDA graph of 144
-    launches, 1.87 GB of weights per step. (The bf16 lm_head of cfg4 is not part of this library.)"""
+    launches, 1.87 GB of weights per step; then the same plus the bf16 lm_head 2560->151936
+    (0.78 GB, dense GEMV) and the greedy argmax over its logits."""
     import dataclasses
 
     import numpy as np
     import torch
 
     from aila_b200 import synth
-    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch
+    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch, Linear, argmax
     dev = torch.device("cuda", local)
-    HID, Q, KV, F = 2560, 4096, 1024, 9728
+    HID, Q, KV, F, VOCAB = 2560, 4096, 1024, 9728, 151936
     shapes = {"q": (Q, HID), "k": (KV, HID), "v": (KV, HID), "o": (HID, Q), "gate": (F, HID),
               "up": (F, HID), "down": (HID, F)}
     base = {k: synth.synth_linear(synth.seed_for(4, 0, k), *v) for k, v in shapes.items()}
@@ -361,13 +362,57 @@ def decode_stack(local, stream):
             step()
     us = _time_stream(graph.replay, stream, 20)
     scratch.check()
+    # the bf16 lm_head of the same model and the token choice, alone and behind the stack
+    g = torch.Generator().manual_seed(synth.seed_for(4, 0, "lm_head"))
+    head_w = (torch.randn(VOCAB, HID, generator=g) * 0.02).to(torch.bfloat16)
+    head = Linear()
+    head.init(head_w, HID, VOCAB, local)
+    del head_w
+    logits = torch.empty(1, VOCAB, dtype=torch.bfloat16, device=dev)
+    token = torch.zeros(1, dtype=torch.int32, device=dev)
+    # three more heads so that consecutive timed launches do not find the weight in L2
+    heads = [head]
+    for _ in range(3):
+        h = Linear()
+        h.init((torch.randn(VOCAB, HID, generator=g) * 0.02).to(torch.bfloat16), HID, VOCAB, local)
+        heads.append(h)
+
+    def head_only():
+        for h in heads:
+            h.forward(scratch, x_h, logits, 1)
+
+    def full_step():
+        step()
+        head.forward(scratch, y_h, logits, 1)
+        argmax(logits, VOCAB, token)
+
+    with torch.cuda.stream(stream):
+        head_only()
+        full_step()
+        stream.synchronize()
+        g_head = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_head, stream=stream):
+            head_only()
+        g_full = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_full, stream=stream):
+            full_step()
+    us_head = _time_stream(g_head.replay, stream, 10) / len(heads)
+    us_full = _time_stream(g_full.replay, stream, 20)
+    head_bytes = VOCAB * HID * 2
     wbytes = 36 * (weight_bytes(Q + 2 * KV, HID) + weight_bytes(HID, Q) + 2 * weight_bytes(F, HID) +
                    weight_bytes(HID, F))
     pk = peaks()
     return {"workload": "cfg4 NF4 linear stack, M=1: 36 x {qkv 2560->6144, o 4096->2560, "
                         "gate|up+SiLU 2560->2x9728, down 9728->2560}", "launches_per_step": 144,
             "weight_bytes_per_step": wbytes, "us_per_step": us, "weight_GBps": wbytes / us / 1e3,
-            "frac_of_measured_hbm": wbytes / us / 1e3 / pk["hbm"]}
+            "frac_of_measured_hbm": wbytes / us / 1e3 / pk["hbm"],
+            "lm_head": {"workload": "bf16 dense GEMV 2560 -> 151936, 4 distinct weights in turn",
+                        "us": us_head, "weight_GBps": head_bytes / us_head / 1e3,
+                        "frac_of_measured_hbm": head_bytes / us_head / 1e3 / pk["hbm"]},
+            "with_lm_head_and_argmax": {"us_per_step": us_full,
+                                        "weight_bytes_per_step": wbytes + head_bytes,
+                                        "weight_GBps": (wbytes + head_bytes) / us_full / 1e3,
+                                        "frac_of_measured_hbm": (wbytes + head_bytes) / us_full / 1e3 / pk["hbm"]}}
 
 # ------------------------------------------------------------------------------------------
 def main():

@@ -250,6 +250,32 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear
                                                              void* stream);
 
 /*
+ * Dense bf16 linear y = x W^T (+ residual), W bf16 [out_features][in_features]: the unquantised
+ * projection next to the NF4 linears (the lm_head). Replaces class Linear for this use
+ * (reference src/ops/Ops.hpp:16-31: init(ctx, weight, in_features, out_features) and
+ * forward(ctx, input, output, seq_len); src/ops/Linear.cpp:172-256; call site
+ * src/models/Qwen3Bnb4Backend.cpp:432-439). seq_len == 1 runs an HBM-bound streaming GEMV,
+ * seq_len > 1 the tcgen05 GEMM (needs in_features % 64 == 0). The weight is copied at creation.
+ * The bias / GELU variants of the reference class (vision and audio towers) are not built.
+ */
+typedef struct AilaDenseLinear AilaDenseLinear;
+AILA_NF4_API AilaNf4Status aila_dense_linear_create(const void* weight_bf16, int64_t out_features,
+                                                    int64_t in_features, int weight_on_device,
+                                                    int device, AilaDenseLinear** out);
+AILA_NF4_API void aila_dense_linear_destroy(AilaDenseLinear* linear);
+AILA_NF4_API int64_t aila_dense_linear_in_features(const AilaDenseLinear* linear);
+AILA_NF4_API int64_t aila_dense_linear_out_features(const AilaDenseLinear* linear);
+AILA_NF4_API AilaNf4Status aila_dense_linear_forward(const AilaDenseLinear* linear,
+                                                     AilaNf4Scratch* scratch, const void* x_bf16,
+                                                     void* y_bf16, int seq_len,
+                                                     const void* residual_bf16, void* stream);
+/* Greedy token choice over n bf16 logits on the device (reference ops::argmax,
+ * src/ops/SamplingOps.cpp:321-365): index of the largest value, the smallest index among equal
+ * values, written to *d_result (device memory). */
+AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, int32_t* d_result,
+                                            int device, void* stream);
+
+/*
  * Checkpoint front-end (host side, no GPU work): a memory-mapped safetensors file and the
  * assembly of one bitsandbytes 4-bit weight into an AilaNf4WeightDesc whose pointers lie
  * inside the mapping, ready for aila_nf4_linear_create (keep the file open until the create

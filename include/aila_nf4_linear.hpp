@@ -63,6 +63,50 @@ struct Bnb4BitLinearScratch {
     }
 };
 
+// Dense bf16 linear (reference class Linear, src/ops/Ops.hpp:16-31): weight [out_features,
+// in_features] bf16 in host or device memory, copied at init. forward throws like the reference
+// operator on a contract violation.
+class Linear {
+public:
+    Linear() = default;
+    Linear(const Linear&) = delete;
+    Linear& operator=(const Linear&) = delete;
+    ~Linear() { aila_dense_linear_destroy(handle_); }
+
+    void init(Context& ctx, const void* weight_bf16, int in_features, int out_features,
+              bool weight_on_device = true) {
+        AilaDenseLinear* fresh = nullptr;
+        if (aila_dense_linear_create(weight_bf16, out_features, in_features, weight_on_device ? 1 : 0,
+                                     ctx.device, &fresh) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+        aila_dense_linear_destroy(handle_);
+        handle_ = fresh;
+    }
+
+    void forward(Context& ctx, Bnb4BitLinearScratch& scratch, TensorView& input, TensorView& output,
+                 int seq_len, const void* add_residual = nullptr) {
+        if (!input.is_bf16() || !output.is_bf16())
+            throw std::runtime_error("Linear expects bf16 input/output tensors");
+        scratch.open(ctx);
+        if (aila_dense_linear_forward(handle_, scratch.handle, input.data(), output.data(), seq_len,
+                                      add_residual, ctx.stream) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+    }
+
+    int in_features() const { return (int)aila_dense_linear_in_features(handle_); }
+    int out_features() const { return (int)aila_dense_linear_out_features(handle_); }
+
+private:
+    AilaDenseLinear* handle_ = nullptr;
+};
+
+// ops::argmax (reference src/ops/SamplingOps.cpp:321-365): greedy token over bf16 logits,
+// written to device memory.
+inline void argmax(Context& ctx, TensorView& logits, int vocab_size, int* d_result) {
+    if (aila_argmax_bf16(logits.data(), vocab_size, d_result, ctx.device, ctx.stream) != AILA_NF4_OK)
+        throw std::runtime_error(aila_nf4_last_error());
+}
+
 // One memory-mapped safetensors file; stands where the reference keeps a ModelWeights
 // (src/utils/SafeTensors.hpp:86-121) for the purpose of finding bitsandbytes weights.
 struct SafetensorsFile {

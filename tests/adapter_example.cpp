@@ -46,6 +46,17 @@ int main() {
         if (aila::nf4::LoadBnb4BitWeightRef(ctx, empty, "w", view, &err) || err.empty()) return 8;
         err.clear();
     }
+    {
+        // the dense linear keeps the reference's throwing behaviour
+        aila::nf4::Linear head;
+        bool threw = false;
+        try {
+            head.init(ctx, nullptr, 8, 8, false);
+        } catch (const std::runtime_error&) {
+            threw = true;
+        }
+        if (!threw) return 9;
+    }
     const bool ok = q.init(ctx, d, &err);
     if (!ok) {
         // no usable GPU: init reports the failure through the bool + message, like the reference

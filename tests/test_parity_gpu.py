@@ -446,3 +446,72 @@ def test_linear_from_checkpoint_file(nf4, oracle, tmp_path):
     assert np.array_equal(got, direct.dequantize_weight().cpu().view(torch.uint16).numpy())
     want = oracle.dequantize_kn(w.packed, w.quant_map, oracle_absmax(oracle, w), N, K, 64)
     assert np.array_equal(got, want.reshape(K, N))
+
+
+# ---------------------------------------------------------------- dense bf16 linear (lm_head)
+def _dense_weight(seed, N, K):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("N,K", [(32, 64), (1000, 2560), (37, 264), (130, 100), (5, 8), (4099, 4096)])
+def test_dense_linear_decode(nf4, oracle, scratch, N, K):
+    """seq_len == 1 of the dense linear against the CPU oracle (bf16 weights, fp32 accumulation,
+    one bf16 rounding); (130, 100) has K % 8 != 0 and takes the scalar kernel."""
+    w = _dense_weight(7000 + N + K, N, K)
+    lin = nf4.Linear()
+    lin.init(w, K, N, 0)
+    assert (lin.in_features(), lin.out_features()) == (K, N)
+    x = _act(7100 + N, 1, K)
+    y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+    lin.forward(scratch, x.cuda(), y, 1)
+    want = oracle.gemm_bf16w(bf16_bits(w), bf16_bits(x), 1, N, K)
+    assert_close_norm(bf16_bits(y.cpu()), want, REL)
+    # fp32 products of bf16 values are exact and both sides accumulate in fp32: the results may
+    # differ by summation order only
+    assert np.abs(bits_to_f32(bf16_bits(y.cpu())) - bits_to_f32(want)).max() <= \
+        4e-3 * np.abs(bits_to_f32(want)).max() + 1e-6
+    res = _act(7200 + N, 1, N)
+    lin.forward(scratch, x.cuda(), y, 1, add_residual=res.cuda())
+    want_r = bits_to_f32(want) + bits_to_f32(bf16_bits(res))
+    assert np.abs(bits_to_f32(bf16_bits(y.cpu())) - want_r).max() <= 2e-2 * np.abs(want_r).max()
+
+
+def test_dense_linear_prefill(nf4, oracle, scratch):
+    N, K, M = 640, 512, 96
+    w = _dense_weight(7301, N, K)
+    lin = nf4.Linear()
+    lin.init(w.cuda(), K, N, 0)  # device-resident weight
+    x = _act(7302, M, K)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    lin.forward(scratch, x.cuda(), y, M)
+    want = oracle.gemm_bf16w(bf16_bits(w), bf16_bits(x), M, N, K)
+    assert_close_norm(bf16_bits(y.cpu()), want, REL)
+
+
+def test_dense_linear_errors(nf4, scratch):
+    lin = nf4.Linear()
+    with pytest.raises(RuntimeError):
+        lin.init(torch.zeros(4, 8), 8, 4, 0)  # not bf16
+    lin.init(_dense_weight(1, 16, 40), 40, 16, 0)
+    x = torch.zeros(2, 40, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(2, 16, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        lin.forward(scratch, x.float(), y, 1)
+    from aila_b200 import _lib
+    with pytest.raises(_lib.Nf4Error):
+        lin.forward(scratch, x, y, 2)  # in_features % 64 != 0: the GEMM does not take it
+
+
+def test_argmax_bf16(nf4):
+    g = torch.Generator().manual_seed(5)
+    for n in (1, 7, 1024, 151936):
+        logits = torch.randn(n, generator=g).to(torch.bfloat16)
+        if n > 100:
+            logits[n // 3] = 9.0
+            logits[n // 2] = 9.0  # a tie: the smaller index wins
+        out = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+        nf4.argmax(logits.cuda(), n, out)
+        f = logits.float()
+        want = int(torch.nonzero(f == f.max())[0])
+        assert int(out.item()) == want
