@@ -328,6 +328,27 @@ AilaNf4Status ensure_io(void** buf, size_t* have, size_t need) {
     return AILA_NF4_OK;
 }
 
+// Small batches (2 .. AILA_NF4_DECODE_ROWS_MAX rows, default 6; 0 or 1 turns it off): one decode
+// launch per row instead of the dequantise + GEMM route, when the streaming kernel takes the
+// shape and no bf16 weight cache exists (with a cache the GEMM has nothing to dequantise).
+int decode_rows_max() {
+    static const int v = [] {
+        const char* e = std::getenv("AILA_NF4_DECODE_ROWS_MAX");
+        if (!e || !*e) return 6;  // measured crossover on B200: 7 rows
+        const int n = std::atoi(e);
+        return n < 0 ? 0 : (n > 64 ? 64 : n);
+    }();
+    return v;
+}
+
+bool use_row_loop(const AilaNf4Linear* l, const AilaNf4Scratch* sc, const void* x, int seq_len,
+                  int64_t ff_pair) {
+    if (seq_len < 2 || seq_len > decode_rows_max() || l->d_cache_bf16) return false;
+    if (gemv_kernel_choice() == 1) return false;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (l->K * 2) % 16) return false;
+    return nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
+}
+
 // seq_len == 1: decode kernels. ff_pair > 0 selects the gate/up pair kernel.
 AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void* x, void* y,
                          const void* residual, int64_t ff_pair, cudaStream_t s) {
@@ -663,6 +684,19 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward(const AilaNf4Linear* l, AilaNf4Scrat
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, y, residual, 0, s);
+    if (use_row_loop(l, sc, x, seq_len, 0)) {
+        // a few rows: one streaming GEMV per row reads 0.52 B per weight and row (the later rows
+        // from L2), the dequantise + GEMM route moves 4.5 B per weight whatever the row count
+        const char* xb = static_cast<const char*>(x);
+        char* yb = static_cast<char*>(y);
+        const char* rb = static_cast<const char*>(residual);
+        for (int m = 0; m < seq_len; ++m) {
+            st = run_decode(l, sc, xb + (size_t)m * l->K * 2, yb + (size_t)m * l->N * 2,
+                            rb ? rb + (size_t)m * l->N * 2 : nullptr, 0, s);
+            if (st != AILA_NF4_OK) return st;
+        }
+        return AILA_NF4_OK;
+    }
     const void* wsrc = l->d_cache_bf16;
     if (!wsrc) {
         st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);
@@ -688,6 +722,16 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, out, nullptr, ff_dim, s);
+    if (use_row_loop(l, sc, x, seq_len, ff_dim)) {
+        const char* xb = static_cast<const char*>(x);
+        char* ob = static_cast<char*>(out);
+        for (int m = 0; m < seq_len; ++m) {
+            st = run_decode(l, sc, xb + (size_t)m * l->K * 2, ob + (size_t)m * ff_dim * 2, nullptr,
+                            ff_dim, s);
+            if (st != AILA_NF4_OK) return st;
+        }
+        return AILA_NF4_OK;
+    }
     const void* wsrc = l->d_cache_bf16;
     if (!wsrc) {
         st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);

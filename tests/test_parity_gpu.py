@@ -515,3 +515,20 @@ def test_argmax_bf16(nf4):
         f = logits.float()
         want = int(torch.nonzero(f == f.max())[0])
         assert int(out.item()) == want
+
+
+@pytest.mark.parametrize("M", [2, 5, 6, 7])
+def test_small_batch_routes_agree(nf4, oracle, scratch, M):
+    """2..6 rows take one decode launch per row, 7 and more the dequantise + GEMM route: both
+    must meet the bound against the oracle's forward for the same input."""
+    N, K = 272, 512
+    w = make_weight(8100 + M, N, K)
+    lin = _lin(nf4, w)
+    x = _act(8200 + M, M, K)
+    res = _act(8300 + M, M, N)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    lin.forward(scratch, x.cuda(), y, M, add_residual=res.cuda())
+    want = bits_to_f32(oracle.forward(w.packed, w.quant_map, oracle_absmax(oracle, w), bf16_bits(x),
+                                      M, N, K, 64)) + bits_to_f32(bf16_bits(res))
+    got = bits_to_f32(bf16_bits(y.cpu()))
+    assert np.abs(got - want).max() <= REL * np.abs(want).max()
