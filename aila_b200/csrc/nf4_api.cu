@@ -328,20 +328,21 @@ AilaNf4Status ensure_io(void** buf, size_t* have, size_t need) {
     return AILA_NF4_OK;
 }
 
-// Small batches (2 .. AILA_NF4_DECODE_ROWS_MAX rows, default 6; 0 or 1 turns it off): one decode
-// launch per row instead of the dequantise + GEMM route, when the streaming kernel takes the
-// shape and no bf16 weight cache exists (with a cache the GEMM has nothing to dequantise).
+// Small batches (2 .. AILA_NF4_DECODE_ROWS_MAX rows; 0 or 1 turns it off): batched decode
+// launches of up to eight rows each instead of the dequantise + GEMM route, when the streaming
+// kernel takes the shape and no bf16 weight cache exists (with a cache the GEMM has nothing to
+// dequantise).
 int decode_rows_max() {
     static const int v = [] {
         const char* e = std::getenv("AILA_NF4_DECODE_ROWS_MAX");
-        if (!e || !*e) return 6;  // measured crossover on B200: 7 rows
+        if (!e || !*e) return 32;
         const int n = std::atoi(e);
         return n < 0 ? 0 : (n > 64 ? 64 : n);
     }();
     return v;
 }
 
-bool use_row_loop(const AilaNf4Linear* l, const AilaNf4Scratch* sc, const void* x, int seq_len,
+bool use_batched_decode(const AilaNf4Linear* l, const AilaNf4Scratch* sc, const void* x, int seq_len,
                   int64_t ff_pair) {
     if (seq_len < 2 || seq_len > decode_rows_max() || l->d_cache_bf16) return false;
     if (gemv_kernel_choice() == 1) return false;
@@ -351,7 +352,7 @@ bool use_row_loop(const AilaNf4Linear* l, const AilaNf4Scratch* sc, const void* 
 
 // seq_len == 1: decode kernels. ff_pair > 0 selects the gate/up pair kernel.
 AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void* x, void* y,
-                         const void* residual, int64_t ff_pair, cudaStream_t s) {
+                         const void* residual, int64_t ff_pair, cudaStream_t s, int m_rows = 1) {
     const int choice = gemv_kernel_choice();
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     bool stream_ok = aligned && nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
@@ -363,8 +364,10 @@ AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void*
         const size_t tiles = (size_t)(ff_pair > 0 ? ff_pair / nf4::kTileRows : l->RT);
         AilaNf4Status st = ensure_counters(sc, tiles);
         if (st != AILA_NF4_OK) return st;
-        NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, y, residual, ff_pair, s));
+        NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, y, residual, ff_pair, s, nullptr, m_rows));
     } else {
+        if (m_rows != 1)
+            return nf4::fail(AILA_NF4_ERR_UNSUPPORTED, "batched decode needs the streaming kernel");
         NF4_CUDA(nf4::launch_gemv_simple(*l, x, y, residual, ff_pair, s));
     }
     return AILA_NF4_OK;
@@ -684,15 +687,17 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward(const AilaNf4Linear* l, AilaNf4Scrat
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, y, residual, 0, s);
-    if (use_row_loop(l, sc, x, seq_len, 0)) {
-        // a few rows: one streaming GEMV per row reads 0.52 B per weight and row (the later rows
-        // from L2), the dequantise + GEMM route moves 4.5 B per weight whatever the row count
+    if (use_batched_decode(l, sc, x, seq_len, 0)) {
+        // a few rows: the batched decode kernel carries up to eight rows through the tensor-core
+        // tile's batch columns and reads 0.52 B per weight per launch; the dequantise + GEMM
+        // route moves 4.5 B per weight whatever the row count
         const char* xb = static_cast<const char*>(x);
         char* yb = static_cast<char*>(y);
         const char* rb = static_cast<const char*>(residual);
-        for (int m = 0; m < seq_len; ++m) {
+        for (int m = 0; m < seq_len; m += 8) {
+            const int rows = seq_len - m < 8 ? seq_len - m : 8;
             st = run_decode(l, sc, xb + (size_t)m * l->K * 2, yb + (size_t)m * l->N * 2,
-                            rb ? rb + (size_t)m * l->N * 2 : nullptr, 0, s);
+                            rb ? rb + (size_t)m * l->N * 2 : nullptr, 0, s, rows);
             if (st != AILA_NF4_OK) return st;
         }
         return AILA_NF4_OK;
@@ -722,12 +727,13 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, out, nullptr, ff_dim, s);
-    if (use_row_loop(l, sc, x, seq_len, ff_dim)) {
+    if (use_batched_decode(l, sc, x, seq_len, ff_dim)) {
         const char* xb = static_cast<const char*>(x);
         char* ob = static_cast<char*>(out);
-        for (int m = 0; m < seq_len; ++m) {
+        for (int m = 0; m < seq_len; m += 8) {
+            const int rows = seq_len - m < 8 ? seq_len - m : 8;
             st = run_decode(l, sc, xb + (size_t)m * l->K * 2, ob + (size_t)m * ff_dim * 2, nullptr,
-                            ff_dim, s);
+                            ff_dim, s, rows);
             if (st != AILA_NF4_OK) return st;
         }
         return AILA_NF4_OK;

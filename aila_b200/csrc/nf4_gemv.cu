@@ -144,6 +144,7 @@ struct StreamParams {
     int x_in_b;             // 1: x lives above the table (large K), 0: below it
     int smem_bytes;         // dynamic shared memory of the launch
     int n_rows;             // rows of the linear (for clamping the padded rows of the last tile)
+    int m_rows;             // batch rows of x / y handled by this launch (1; 2..8 in the batched kernel)
     // row-parallel exchange (peer_world > 0): the epilogue stores the fp32 row sums of this
     // rank into every rank's exchange buffer and adds one to that rank's arrival counter per
     // row tile, instead of writing y
@@ -245,7 +246,13 @@ __device__ unsigned long long g_trace[32][160][96];
 #define NF4_TRACE(slot) do {} while (0)
 #endif
 
-template <int KIND, bool PAIRED>
+// BATCH: up to eight rows of x ride in the eight batch columns of the tensor-core tile, so the
+// weights are read and dequantised once for all of them. Differences from the single-row kernel:
+// x fragments come straight from global memory (L2) per work item, every lane keeps 2x2
+// accumulators per half, warps add their tile sums into one shared fp32 tile with shared-memory
+// atomics (the order of these additions is not fixed: last-bit differences between runs), and
+// the epilogue writes [rows][out] outputs.
+template <int KIND, bool PAIRED, bool BATCH>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
 #ifdef AILA_NF4_TRACE
     if (threadIdx.x == 0) {
@@ -419,6 +426,90 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         if (lane == 0) p.counters[rtile] = 0;
         write_rows(rtile, v);
     };
+    // ---- batched variants: a tile is 16 rows x 8 batch columns, lane l holds the four entries
+    // 4l .. 4l+3 of its row-major order ----
+    auto write_rows_b = [&](int rtile, const float (&v)[NP][4]) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int idx = lane * 4 + e, r = idx >> 3, m = idx & 7;
+            const int n = rtile * kTileRows + r;
+            if (m < p.m_rows && n < p.n_out) {
+                float o;
+                if (PAIRED) {
+                    const float gt = v[0][e], up = v[NP - 1][e];
+                    o = __fdividef(gt, 1.0f + __expf(-gt)) * up;
+                } else {
+                    o = v[0][e];
+                    if (p.residual) o += bf16_bits_to_f32(__ldcg(p.residual + (size_t)m * p.n_out + n));
+                }
+                p.y[(size_t)m * p.n_out + n] = f32_to_bf16_bits(o);
+            }
+        }
+    };
+    auto resolve_b = [&](int& pend_li, int pend_old) {
+        const int li = pend_li;
+        if (li < 0) return;
+        pend_li = -1;
+        const int old = __shfl_sync(0xffffffffu, pend_old, 0);
+        if (old + tile_items(li) != p.KU) return;
+        const int rtile = rt_first + li;
+        const int t0 = rtile * p.KU, t1 = t0 + p.KU;
+        int c_lo = c, c_hi = c;
+        while (c_lo > 0 && slice_begin(p, c_lo) > t0) --c_lo;
+        while (c_hi + 1 < G && slice_begin(p, c_hi + 1) < t1) ++c_hi;
+        float v[NP][4];
+#pragma unroll
+        for (int h = 0; h < NP; ++h)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[h][e] = 0.0f;
+        for (int cc = c_lo; cc <= c_hi; ++cc) {
+            const int cc_first = fast_div(slice_begin(p, cc), p.div_ku_m, p.div_ku_s);
+            const int hs = (rtile == cc_first) ? 0 : 1;
+#pragma unroll
+            for (int h = 0; h < NP; ++h) {
+                const float4 q = __ldcg(reinterpret_cast<const float4*>(
+                    p.partials + (((size_t)cc * 2 + hs) * NP + h) * 128) + lane);
+                v[h][0] += q.x; v[h][1] += q.y; v[h][2] += q.z; v[h][3] += q.w;
+            }
+        }
+        if (lane == 0) p.counters[rtile] = 0;
+        write_rows_b(rtile, v);
+    };
+    auto finalize_tile_b = [&](int li) {
+        const int rtile = rt_first + li;
+        float v[NP][4];
+#pragma unroll
+        for (int h = 0; h < NP; ++h) {
+            uint4 q;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                         : "r"(a_slots + (uint32_t)((li * NP + h) * 128 + lane * 4) * 4u));
+            v[h][0] = __uint_as_float(q.x); v[h][1] = __uint_as_float(q.y);
+            v[h][2] = __uint_as_float(q.z); v[h][3] = __uint_as_float(q.w);
+        }
+        const int items = tile_items(li);
+        if (items == p.KU) {
+            write_rows_b(rtile, v);
+            return;
+        }
+        const int hslot = (li == 0) ? 0 : 1;
+#pragma unroll
+        for (int h = 0; h < NP; ++h)
+            reinterpret_cast<float4*>(p.partials + (((size_t)c * 2 + hslot) * NP + h) * 128)[lane] =
+                make_float4(v[h][0], v[h][1], v[h][2], v[h][3]);
+        __syncwarp();
+        int old = 0;
+        if (lane == 0)
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;"
+                         : "=r"(old) : "l"(p.counters + rtile), "r"(items) : "memory");
+        if (hslot == 0) {
+            pend_li0 = li;
+            pend_old0 = old;
+        } else {
+            pend_li1 = li;
+            pend_old1 = old;
+        }
+    };
     auto finalize_tile = [&](int li) {
         const int r = lane & 15;
         const int rtile = rt_first + li;
@@ -564,15 +655,26 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) return;
             // counters added to before the wait above have answered by now
-            resolve(pend_li0, pend_old0);
-            resolve(pend_li1, pend_old1);
-            finalize_tile(li);
+            if (BATCH) {
+                resolve_b(pend_li0, pend_old0);
+                resolve_b(pend_li1, pend_old1);
+                finalize_tile_b(li);
+            } else {
+                resolve(pend_li0, pend_old0);
+                resolve(pend_li1, pend_old1);
+                finalize_tile(li);
+            }
 #ifdef AILA_NF4_TRACE
             if (lane == 0 && q < 8) NF4_TRACE(32 + q);
 #endif
         }
-        resolve(pend_li0, pend_old0);
-        resolve(pend_li1, pend_old1);
+        if (BATCH) {
+            resolve_b(pend_li0, pend_old0);
+            resolve_b(pend_li1, pend_old1);
+        } else {
+            resolve(pend_li0, pend_old0);
+            resolve(pend_li1, pend_old1);
+        }
         peer_publish();
 #ifdef AILA_NF4_TRACE
         if (lane == 0) {
@@ -633,9 +735,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const uint32_t code_off = (uint32_t)(dhalf * half_bytes + kUnitNibbleBytes + drow);
     const uint32_t my_win = a_nabsw + (uint32_t)(dhalf * kNabsWindow) * 4u;
 
-    float acc[NP][2];
+    // single row: [h][row gq / gq + 8] in lanes t = 0; batched: [h][2 * (row) + (column 2t / 2t+1)]
+    constexpr int NACC = BATCH ? 4 : 2;
+    float acc[NP][NACC];
 #pragma unroll
-    for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
+    for (int h = 0; h < NP; ++h)
+#pragma unroll
+        for (int e = 0; e < NACC; ++e) acc[h][e] = 0.0f;
     int cur_li = -1;
     unsigned done_mask = 0;  // local tiles this warp has signed off
 
@@ -729,12 +835,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(slot_of(q4)), "r"(xv.x), "r"(xv.y) : "memory");
     };
     uint2 xv0 = make_uint2(0u, 0u), xv1 = make_uint2(0u, 0u);
-    if (tid < n8) xv0 = __ldcg(xg + tid);
-    if (tid + W * 32 < n8) xv1 = __ldcg(xg + tid + W * 32);
+    if (!BATCH && tid < n8) xv0 = __ldcg(xg + tid);
+    if (!BATCH && tid + W * 32 < n8) xv1 = __ldcg(xg + tid + W * 32);
 
-    if (tid < n8) sts_x(tid, xv0);
-    if (tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
-    for (int q4 = tid + 2 * W * 32; q4 < n8; q4 += 2 * W * 32) {
+    if (!BATCH && tid < n8) sts_x(tid, xv0);
+    if (!BATCH && tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
+    for (int q4 = tid + 2 * W * 32; !BATCH && q4 < n8; q4 += 2 * W * 32) {
         const int q5 = q4 + W * 32;
         const uint2 v0 = __ldcg(xg + q4);
         uint2 v1 = make_uint2(0u, 0u);
@@ -755,7 +861,18 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     };
     auto flush_current = [&]() {
         if (cur_li >= 0) {
-            if (t == 0) {
+            if constexpr (BATCH) {
+                // every warp adds its share of the tile into one fp32 tile [16 rows][8 columns]
+#pragma unroll
+                for (int h = 0; h < NP; ++h) {
+                    const uint32_t tb = a_slots + (uint32_t)((cur_li * NP + h) * 128) * 4u;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t idx = (uint32_t)((gq + 8 * (e >> 1)) * 8 + 2 * t + (e & 1));
+                        asm volatile("red.shared.add.f32 [%0], %1;" ::"r"(tb + 4u * idx), "f"(acc[h][e]) : "memory");
+                    }
+                }
+            } else if (t == 0) {
 #pragma unroll
                 for (int h = 0; h < NP; ++h) {
                     const uint32_t sl = a_slots + (uint32_t)(((cur_li * NP + h) * W + warp) * 16) * 4u;
@@ -766,7 +883,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             sign_off(cur_li);
         }
 #pragma unroll
-        for (int h = 0; h < NP; ++h) acc[h][0] = acc[h][1] = 0.0f;
+        for (int h = 0; h < NP; ++h)
+#pragma unroll
+            for (int e = 0; e < NACC; ++e) acc[h][e] = 0.0f;
     };
 
     uint4 xq0 = make_uint4(0u, 0u, 0u, 0u), xq1 = make_uint4(0u, 0u, 0u, 0u);
@@ -792,15 +911,30 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 // that hold batch column 0 of the tile; the other columns stay zero and are never
                 // read back. A 16-byte load is served a quarter warp at a time, so the
                 // predicated pair costs two shared-memory wavefronts instead of eight.
+                if (BATCH) {
+                    // batch row gq of x, straight from L2 (coherent loads: x may be the previous
+                    // kernel's output): tile j wants k = 64 kb + 16 j + 4 t + {0..3}
+                    const uint2* xr = reinterpret_cast<const uint2*>(p.x + (size_t)gq * p.K + (size_t)kb * 64 + 4 * t);
+                    uint2 xb0 = make_uint2(0u, 0u), xb1 = xb0, xb2 = xb0, xb3 = xb0;
+                    if (gq < p.m_rows) {
+                        xb0 = __ldcg(xr);
+                        xb1 = __ldcg(xr + 4);
+                        xb2 = __ldcg(xr + 8);
+                        xb3 = __ldcg(xr + 12);
+                    }
+                    xq0 = make_uint4(xb0.x, xb0.y, xb1.x, xb1.y);
+                    xq1 = make_uint4(xb2.x, xb2.y, xb3.x, xb3.y);
+                } else {
                 const uint32_t xa = a_xs + (uint32_t)kb * 128u + 16u * t;
-                asm volatile(
-                    "{\n\t.reg .pred q;\n\t"
-                    "setp.ne.u32 q, %9, 0;\n\t"
-                    "@q ld.shared.v4.u32 {%0,%1,%2,%3}, [%8];\n\t"
-                    "@q ld.shared.v4.u32 {%4,%5,%6,%7}, [%8+64];\n\t}"
-                    : "+r"(xq0.x), "+r"(xq0.y), "+r"(xq0.z), "+r"(xq0.w), "+r"(xq1.x), "+r"(xq1.y),
-                      "+r"(xq1.z), "+r"(xq1.w)
-                    : "r"(xa), "r"(x_lane));
+                    asm volatile(
+                        "{\n\t.reg .pred q;\n\t"
+                        "setp.ne.u32 q, %9, 0;\n\t"
+                        "@q ld.shared.v4.u32 {%0,%1,%2,%3}, [%8];\n\t"
+                        "@q ld.shared.v4.u32 {%4,%5,%6,%7}, [%8+64];\n\t}"
+                        : "+r"(xq0.x), "+r"(xq0.y), "+r"(xq0.z), "+r"(xq0.w), "+r"(xq1.x), "+r"(xq1.y),
+                          "+r"(xq1.z), "+r"(xq1.w)
+                        : "r"(xa), "r"(x_lane));
+                }
                 float am0[NP], am1[NP];
                 if (KIND == kAbsmaxCodes) {
                     const unsigned code = lds_u8(ua + code_off);
@@ -813,8 +947,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     // values they never use)
 #pragma unroll
                     for (int h = 0; h < NP; ++h) {
-                        am0[h] = (h == 0) ? am : __shfl_down_sync(0xffffffffu, am, 2 * h);
-                        am1[h] = __shfl_down_sync(0xffffffffu, am, 2 * h + 1);
+                        if (BATCH) {  // every lane of the quad uses all four scales
+                            am0[h] = __shfl_sync(0xffffffffu, am, (lane & ~3) | (2 * h));
+                            am1[h] = __shfl_sync(0xffffffffu, am, (lane & ~3) | (2 * h + 1));
+                        } else {
+                            am0[h] = (h == 0) ? am : __shfl_down_sync(0xffffffffu, am, 2 * h);
+                            am1[h] = __shfl_down_sync(0xffffffffu, am, 2 * h + 1);
+                        }
                     }
                 } else {
 #pragma unroll
@@ -870,8 +1009,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 }
 #pragma unroll
                 for (int h = 0; h < NP; ++h) {
-                    acc[h][0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][0]);
-                    acc[h][1] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][1]);
+                    if constexpr (BATCH) {
+                        acc[h][0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][0]);
+                        acc[h][1] = fmaf(am0[h], c0[h][1] + c1[h][1], acc[h][1]);
+                        acc[h][2] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][2]);
+                        acc[h][3] = fmaf(am1[h], c0[h][3] + c1[h][3], acc[h][3]);
+                    } else {
+                        acc[h][0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][0]);
+                        acc[h][1] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][1]);
+                    }
                 }
                 // ---- this warp's next item: W positions further along the traversal ----
                 const int vn = v + W;
@@ -988,13 +1134,13 @@ StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int
     return pl;
 }
 
-template <int KIND, bool PAIRED>
+template <int KIND, bool PAIRED, bool BATCH>
 cudaError_t launch_stream_t(const StreamParams& p, int grid, int smem, cudaStream_t s) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<KIND, PAIRED>,
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<KIND, PAIRED, BATCH>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
@@ -1016,7 +1162,7 @@ cudaError_t launch_stream_t(const StreamParams& p, int grid, int smem, cudaStrea
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<KIND, PAIRED>, p);
+    return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<KIND, PAIRED, BATCH>, p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1065,7 +1211,8 @@ cudaError_t launch_gemv_simple(const AilaNf4Linear& w, const void* x, void* y,
 }
 
 size_t gemv_stream_partials_floats(int sm_count) {
-    return (size_t)sm_count * kMaxGridMult * 2 * 2 * 16;
+    // per CTA: two shared tiles x two halves x (16 rows x up to 8 batch columns)
+    return (size_t)sm_count * kMaxGridMult * 2 * 2 * 128;
 }
 
 bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count) {
@@ -1075,7 +1222,7 @@ bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count
 
 cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
                                void* y, const void* residual, int64_t ff_pair, cudaStream_t s,
-                               const PeerTargets* peers) {
+                               const PeerTargets* peers, int m_rows) {
     const bool paired = ff_pair > 0;
     const StreamPlan pl = stream_plan(w, paired, ff_pair, scratch.sm_count);
     if (!pl.ok) return cudaErrorInvalidConfiguration;
@@ -1108,6 +1255,8 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.x_in_b = pl.x_in_b;
     p.smem_bytes = pl.smem;
     p.n_rows = (int)w.N;
+    if (m_rows < 1 || m_rows > 8 || (m_rows > 1 && peers)) return cudaErrorInvalidValue;
+    p.m_rows = m_rows;
     p.peer_world = 0;
     p.peer_rank = 0;
     p.peer_max_rows = 0;
@@ -1132,11 +1281,19 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     static int trace_counter = 0;
     p.trace_idx = trace_counter++ % 32;
 #endif
-    if (w.absmax_kind == kAbsmaxCodes)
-        return paired ? launch_stream_t<kAbsmaxCodes, true>(p, pl.grid, pl.smem, s)
-                      : launch_stream_t<kAbsmaxCodes, false>(p, pl.grid, pl.smem, s);
-    return paired ? launch_stream_t<kAbsmaxF32, true>(p, pl.grid, pl.smem, s)
-                  : launch_stream_t<kAbsmaxF32, false>(p, pl.grid, pl.smem, s);
+    const bool batch = m_rows > 1;
+    if (w.absmax_kind == kAbsmaxCodes) {
+        if (batch)
+            return paired ? launch_stream_t<kAbsmaxCodes, true, true>(p, pl.grid, pl.smem, s)
+                          : launch_stream_t<kAbsmaxCodes, false, true>(p, pl.grid, pl.smem, s);
+        return paired ? launch_stream_t<kAbsmaxCodes, true, false>(p, pl.grid, pl.smem, s)
+                      : launch_stream_t<kAbsmaxCodes, false, false>(p, pl.grid, pl.smem, s);
+    }
+    if (batch)
+        return paired ? launch_stream_t<kAbsmaxF32, true, true>(p, pl.grid, pl.smem, s)
+                      : launch_stream_t<kAbsmaxF32, false, true>(p, pl.grid, pl.smem, s);
+    return paired ? launch_stream_t<kAbsmaxF32, true, false>(p, pl.grid, pl.smem, s)
+                  : launch_stream_t<kAbsmaxF32, false, false>(p, pl.grid, pl.smem, s);
 }
 
 // Decode GEMV on the static work space: no allocation of any kind. The first call on a device

@@ -119,7 +119,7 @@ struct PeerTargets {
 };
 cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
                                void* y, const void* residual, int64_t ff_pair, cudaStream_t s,
-                               const PeerTargets* peers = nullptr);
+                               const PeerTargets* peers = nullptr, int m_rows = 1);
 bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);

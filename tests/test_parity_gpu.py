@@ -517,10 +517,10 @@ def test_argmax_bf16(nf4):
         assert int(out.item()) == want
 
 
-@pytest.mark.parametrize("M", [2, 5, 6, 7])
+@pytest.mark.parametrize("M", [2, 5, 8, 9, 17, 32, 33])
 def test_small_batch_routes_agree(nf4, oracle, scratch, M):
-    """2..6 rows take one decode launch per row, 7 and more the dequantise + GEMM route: both
-    must meet the bound against the oracle's forward for the same input."""
+    """2..32 rows take the batched decode kernel (eight rows per launch), more rows the
+    dequantise + GEMM route: both must meet the bound against the oracle's forward."""
     N, K = 272, 512
     w = make_weight(8100 + M, N, K)
     lin = _lin(nf4, w)
@@ -532,3 +532,37 @@ def test_small_batch_routes_agree(nf4, oracle, scratch, M):
                                       M, N, K, 64)) + bits_to_f32(bf16_bits(res))
     got = bits_to_f32(bf16_bits(y.cpu()))
     assert np.abs(got - want).max() <= REL * np.abs(want).max()
+
+
+@pytest.mark.parametrize("N,K,nested,M", [(16, 64, True, 2), (100, 448, False, 3), (2560, 9728, True, 8),
+                                          (6144, 2560, True, 5), (33, 128, True, 7)])
+def test_batched_decode_rows_match_single_rows(nf4, scratch, N, K, nested, M):
+    """Every row of a batched decode launch against the single-row kernel on the same row: the
+    same dequantised operands and fp32 accumulation, different summation order across warps."""
+    w = make_weight(8400 + N + M, N, K, 64, nested)
+    lin = _lin(nf4, w)
+    x = _act(8500 + N, M, K).cuda()
+    yb = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    lin.forward(scratch, x, yb, M)
+    ys = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    for m in range(M):
+        lin.forward(scratch, x[m:m + 1].contiguous(), ys[m:m + 1], 1)
+    torch.cuda.synchronize()
+    a, b = yb.float().cpu().numpy(), ys.float().cpu().numpy()
+    assert np.abs(a - b).max() <= 1e-2 * np.abs(b).max() + 1e-6
+
+
+@pytest.mark.parametrize("M", [2, 8, 11])
+def test_batched_gate_up_swiglu(nf4, oracle, scratch, M):
+    H, FF = 512, 1040
+    g, u = make_weight(8601, FF, H), make_weight(8602, FF, H)
+    lg, lu, f = _lin(nf4, g), _lin(nf4, u), nf4.Bnb4BitLinear()
+    assert f.init_fused_rows(lg, lu)
+    x = _act(8603 + M, M, H)
+    out = torch.empty(M, FF, dtype=torch.bfloat16, device="cuda")
+    assert nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x.cuda(), out, FF, seq_len=M)
+    packed = np.concatenate([g.packed, u.packed])
+    am = np.concatenate([oracle_absmax(oracle, g), oracle_absmax(oracle, u)])
+    xb = bf16_bits(x)
+    want = np.stack([oracle.gemv_gate_up_swiglu(packed, g.quant_map, am, xb[m], FF, H, 64) for m in range(M)])
+    assert_close_norm(bf16_bits(out.cpu()), want, REL)
