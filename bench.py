@@ -362,6 +362,32 @@ def decode_stack(local, stream):
             step()
     us = _time_stream(graph.replay, stream, 20)
     scratch.check()
+    # small batches through the batched decode kernel (eight rows per launch)
+    batch = {}
+    for M in (4, 8, 16, 32):
+        xb_h = synth.gaussian_activation(4100 + M, M, HID).to(dev)
+        xb_q = synth.gaussian_activation(4200 + M, M, Q).to(dev)
+        xb_f = synth.gaussian_activation(4300 + M, M, F).to(dev)
+        yb_qkv = torch.empty(M, Q + 2 * KV, dtype=torch.bfloat16, device=dev)
+        yb_h = torch.empty(M, HID, dtype=torch.bfloat16, device=dev)
+        yb_f = torch.empty(M, F, dtype=torch.bfloat16, device=dev)
+
+        def step_m():
+            for qkv, o, gu, dn in layers:
+                qkv.forward(scratch, xb_h, yb_qkv, M)
+                o.forward(scratch, xb_q, yb_h, M)
+                assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(gu, scratch, xb_h, yb_f, F, seq_len=M)
+                dn.forward(scratch, xb_f, yb_h, M)
+
+        with torch.cuda.stream(stream):
+            step_m()
+            stream.synchronize()
+            gm = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gm, stream=stream):
+                step_m()
+        batch[f"M{M}_us_per_step"] = _time_stream(gm.replay, stream, 10)
+        del gm
+    scratch.check()
     # the bf16 lm_head of the same model and the token choice, alone and behind the stack
     g = torch.Generator().manual_seed(synth.seed_for(4, 0, "lm_head"))
     head_w = (torch.randn(VOCAB, HID, generator=g) * 0.02).to(torch.bfloat16)
@@ -406,6 +432,7 @@ def decode_stack(local, stream):
                         "gate|up+SiLU 2560->2x9728, down 9728->2560}", "launches_per_step": 144,
             "weight_bytes_per_step": wbytes, "us_per_step": us, "weight_GBps": wbytes / us / 1e3,
             "frac_of_measured_hbm": wbytes / us / 1e3 / pk["hbm"],
+            "small_batch": batch,
             "lm_head": {"workload": "bf16 dense GEMV 2560 -> 151936, 4 distinct weights in turn",
                         "us": us_head, "weight_GBps": head_bytes / us_head / 1e3,
                         "frac_of_measured_hbm": head_bytes / us_head / 1e3 / pk["hbm"]},
