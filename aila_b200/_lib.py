@@ -53,6 +53,12 @@ class StTensorView(ctypes.Structure):
 
 ST_DTYPES = ("unknown", "U8", "I8", "F16", "BF16", "F32", "F64", "I32", "I64", "BOOL")
 
+class RmsNorm(ctypes.Structure):
+    """AilaNf4RmsNorm."""
+    _fields_ = [("add_bf16", ctypes.c_void_p), ("weight_bf16", ctypes.c_void_p),
+                ("eps", ctypes.c_float), ("hidden_out_bf16", ctypes.c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/aila_nf4.h declares
 _VP = ctypes.c_void_p
 _SIGNATURES = {
@@ -87,6 +93,11 @@ _SIGNATURES = {
     "aila_nf4_peerbuf_import": (ctypes.c_int, [_VP, ctypes.c_int, _VP]),
     "aila_nf4_peerbuf_destroy": (None, [_VP]),
     "aila_nf4_forward_decode_allreduce": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
+    "aila_nf4_forward_rmsnorm": (ctypes.c_int, [_VP, _VP, _VP, ctypes.POINTER(RmsNorm), _VP, _VP, _VP]),
+    "aila_nf4_forward_gate_up_swiglu_rmsnorm": (ctypes.c_int, [_VP, _VP, _VP, ctypes.POINTER(RmsNorm),
+                                                               _VP, ctypes.c_int64, _VP]),
+    "aila_add_rms_norm": (ctypes.c_int, [_VP, _VP, _VP, ctypes.c_float, ctypes.c_int, ctypes.c_int,
+                                         _VP, _VP, ctypes.c_int, _VP]),
     "aila_dense_linear_create": (ctypes.c_int, [_VP, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
                                                 ctypes.c_int, ctypes.POINTER(_VP)]),
     "aila_dense_linear_destroy": (None, [_VP]),

@@ -352,7 +352,8 @@ bool use_batched_decode(const AilaNf4Linear* l, const AilaNf4Scratch* sc, const 
 
 // seq_len == 1: decode kernels. ff_pair > 0 selects the gate/up pair kernel.
 AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void* x, void* y,
-                         const void* residual, int64_t ff_pair, cudaStream_t s, int m_rows = 1) {
+                         const void* residual, int64_t ff_pair, cudaStream_t s, int m_rows = 1,
+                         const nf4::NormInput* norm = nullptr) {
     const int choice = gemv_kernel_choice();
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     bool stream_ok = aligned && nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
@@ -364,8 +365,11 @@ AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void*
         const size_t tiles = (size_t)(ff_pair > 0 ? ff_pair / nf4::kTileRows : l->RT);
         AilaNf4Status st = ensure_counters(sc, tiles);
         if (st != AILA_NF4_OK) return st;
-        NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, y, residual, ff_pair, s, nullptr, m_rows));
+        NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, y, residual, ff_pair, s, nullptr, m_rows, norm));
     } else {
+        if (norm)
+            return nf4::fail(AILA_NF4_NOT_APPLICABLE,
+                             "the fused RMSNorm input needs the streaming decode kernel");
         if (m_rows != 1)
             return nf4::fail(AILA_NF4_ERR_UNSUPPORTED, "batched decode needs the streaming kernel");
         NF4_CUDA(nf4::launch_gemv_simple(*l, x, y, residual, ff_pair, s));
@@ -747,6 +751,56 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
     }
     return nf4::launch_gemm_bf16(wsrc, x, out, nullptr, seq_len, l->N, l->K, ff_dim, l->device,
                                  sc->sm_count, sc->d_status, s);
+}
+
+namespace {
+AilaNf4Status check_norm(const AilaNf4Linear* l, const void* x, const AilaNf4RmsNorm* norm,
+                         nf4::NormInput* out) {
+    if (!norm || !norm->weight_bf16)
+        return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "RMSNorm weight is NULL");
+    if (!(norm->eps >= 0.0f)) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "RMSNorm eps must be >= 0");
+    if (norm->hidden_out_bf16 && (norm->hidden_out_bf16 == x || norm->hidden_out_bf16 == norm->add_bf16))
+        return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT,
+                         "hidden_out must not alias x or the added tensor (every CTA reads them)");
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(norm->weight_bf16) |
+                           reinterpret_cast<uintptr_t>(norm->add_bf16) |
+                           reinterpret_cast<uintptr_t>(norm->hidden_out_bf16);
+    if (bits & 7) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "RMSNorm tensors must be 8-byte aligned");
+    (void)l;
+    out->add = norm->add_bf16;
+    out->weight = norm->weight_bf16;
+    out->hidden_out = norm->hidden_out_bf16;
+    out->eps = norm->eps;
+    return AILA_NF4_OK;
+}
+}  // namespace
+
+AILA_NF4_API AilaNf4Status aila_nf4_forward_rmsnorm(const AilaNf4Linear* l, AilaNf4Scratch* sc,
+                                                    const void* x, const AilaNf4RmsNorm* norm,
+                                                    void* y, const void* residual, void* stream) {
+    AilaNf4Status st = check_forward_args(l, sc, x, y, 1);
+    if (st != AILA_NF4_OK) return st;
+    nf4::NormInput ni;
+    if ((st = check_norm(l, x, norm, &ni)) != AILA_NF4_OK) return st;
+    DeviceGuard guard(l->device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    return run_decode(l, sc, x, y, residual, 0, static_cast<cudaStream_t>(stream), 1, &ni);
+}
+
+AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_rmsnorm(
+    const AilaNf4Linear* l, AilaNf4Scratch* sc, const void* x, const AilaNf4RmsNorm* norm, void* out,
+    int64_t ff_dim, void* stream) {
+    AilaNf4Status st = check_forward_args(l, sc, x, out, 1);
+    if (st != AILA_NF4_OK) return st;
+    if (ff_dim <= 0 || l->N != 2 * ff_dim)
+        return nf4::fail(AILA_NF4_NOT_APPLICABLE, "out_features != 2 * ff_dim");
+    if (ff_dim % nf4::kTileRows != 0)
+        return nf4::fail(AILA_NF4_NOT_APPLICABLE, "ff_dim is not a multiple of 16");
+    nf4::NormInput ni;
+    if ((st = check_norm(l, x, norm, &ni)) != AILA_NF4_OK) return st;
+    DeviceGuard guard(l->device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    return run_decode(l, sc, x, out, nullptr, ff_dim, static_cast<cudaStream_t>(stream), 1, &ni);
 }
 
 AILA_NF4_API AilaNf4Status aila_nf4_forward_host(const AilaNf4Linear* l, AilaNf4Scratch* sc,

@@ -165,6 +165,36 @@ argmax_bf16_kernel(const uint16_t* __restrict__ logits, long long n, int* __rest
     }
 }
 
+// Residual add + RMSNorm, one block per row (ops::fused_add_rms_norm / rms_norm,
+// src/ops/NormOps.cpp:141-260): v = x + add in fp32, hidden_out = bf16(v),
+// normed = bf16(v * rsqrt(mean(v^2) + eps) * w). hidden_out may alias x (each element is read and
+// written by the same thread).
+__global__ void __launch_bounds__(256)
+add_rms_norm_kernel(const uint16_t* x, const uint16_t* __restrict__ add,
+                    const uint16_t* __restrict__ w, float eps, int H, uint16_t* hidden_out,
+                    uint16_t* __restrict__ normed) {
+    __shared__ float warp_sum[8];
+    const size_t row = (size_t)blockIdx.x * H;
+    float ss = 0.0f;
+    for (int k = threadIdx.x; k < H; k += blockDim.x) {
+        const float v = bf16_bits_to_f32(__ldcg(x + row + k)) + (add ? bf16_bits_to_f32(__ldcg(add + row + k)) : 0.0f);
+        ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += warp_sum[i];
+    const float inv_rms = rsqrtf(total / (float)H + eps);
+    for (int k = threadIdx.x; k < H; k += blockDim.x) {
+        const float v = bf16_bits_to_f32(__ldcg(x + row + k)) + (add ? bf16_bits_to_f32(__ldcg(add + row + k)) : 0.0f);
+        if (hidden_out) hidden_out[row + k] = f32_to_bf16_bits(v);
+        normed[row + k] = f32_to_bf16_bits(v * inv_rms * bf16_bits_to_f32(w[k]));
+    }
+}
+
 }  // namespace
 }  // namespace nf4
 
@@ -279,6 +309,25 @@ AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, 
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     nf4::argmax_bf16_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(logits_bf16), (long long)n, d_result);
+    NF4_CUDA(cudaGetLastError());
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API AilaNf4Status aila_add_rms_norm(const void* x_bf16, const void* add_bf16,
+                                             const void* weight_bf16, float eps, int rows,
+                                             int hidden_size, void* hidden_out_bf16,
+                                             void* normed_out_bf16, int device, void* stream) {
+    if (!x_bf16 || !weight_bf16 || !normed_out_bf16)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (rows <= 0 || hidden_size <= 0) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "rows and hidden_size must be positive");
+    if (hidden_out_bf16 && hidden_out_bf16 == add_bf16)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "hidden_out may alias x but not the added tensor");
+    DenseDevGuard guard(device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    nf4::add_rms_norm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(x_bf16), static_cast<const uint16_t*>(add_bf16),
+        static_cast<const uint16_t*>(weight_bf16), eps, hidden_size,
+        static_cast<uint16_t*>(hidden_out_bf16), static_cast<uint16_t*>(normed_out_bf16));
     NF4_CUDA(cudaGetLastError());
     return AILA_NF4_OK;
 }

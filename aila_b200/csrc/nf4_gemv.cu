@@ -145,6 +145,13 @@ struct StreamParams {
     int smem_bytes;         // dynamic shared memory of the launch
     int n_rows;             // rows of the linear (for clamping the padded rows of the last tile)
     int m_rows;             // batch rows of x / y handled by this launch (1; 2..8 in the batched kernel)
+    // residual add + RMSNorm folded into the staging of x (single-row kernel, norm_w != NULL):
+    // v = x + norm_add (fp32), the linear's input is bf16(v * rsqrt(mean(v^2) + eps) * norm_w),
+    // CTA 0 writes bf16(v) to norm_hidden_out
+    const uint16_t* norm_add;
+    const uint16_t* norm_w;
+    uint16_t* norm_hidden_out;
+    float norm_eps;
     // row-parallel exchange (peer_world > 0): the epilogue stores the fp32 row sums of this
     // rank into every rank's exchange buffer and adds one to that rank's arrival counter per
     // row tile, instead of writing y
@@ -282,7 +289,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     static_assert((2 * kMaxStages + 1) * 8 <= 400, "barrier block");
     static_assert(kMaxLocalTiles * 8 <= 64, "tile barrier block");
     const uint32_t a_info = a_tile + 64;                         // per half: window base, window valid
-    const uint32_t a_nmap = a_info + 16;
+    const uint32_t a_red = a_info + 16;                          // [W] per-warp sums of the RMSNorm
+    const uint32_t a_nmap = a_red + 64;
     const uint32_t a_nabsw = a_nmap + 1024;                      // [2][kNabsWindow] second-level scales
     const uint32_t a_ptab = a_nabsw + 2 * kNabsWindow * 4;       // [256] byte value -> bf16 pair
     const uint32_t a_tinfo = a_ptab + 1024;                      // [tile][lane] absmax row base, offset
@@ -834,13 +842,76 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     auto sts_x = [&](int q4, uint2 xv) {
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(slot_of(q4)), "r"(xv.x), "r"(xv.y) : "memory");
     };
+    if (!BATCH && p.norm_w != nullptr) {
+        // ---- residual add + RMSNorm while staging x ----
+        static_assert(W <= 16, "per-warp sums");
+        const uint2* ag = reinterpret_cast<const uint2*>(p.norm_add);
+        const uint2* wg = reinterpret_cast<const uint2*>(p.norm_w);
+        auto load_v = [&](int q4, float (&vv)[4]) {
+            const uint2 a = __ldcg(xg + q4);
+            uint2 b = make_uint2(0u, 0u);
+            if (ag) b = __ldcg(ag + q4);
+            vv[0] = __uint_as_float(a.x << 16) + __uint_as_float(b.x << 16);
+            vv[1] = __uint_as_float(a.x & 0xffff0000u) + __uint_as_float(b.x & 0xffff0000u);
+            vv[2] = __uint_as_float(a.y << 16) + __uint_as_float(b.y << 16);
+            vv[3] = __uint_as_float(a.y & 0xffff0000u) + __uint_as_float(b.y & 0xffff0000u);
+        };
+        auto sq = [](const float (&vv)[4]) { return vv[0] * vv[0] + vv[1] * vv[1] + vv[2] * vv[2] + vv[3] * vv[3]; };
+        float v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
+        float ss = 0.0f;
+        if (tid < n8) {
+            load_v(tid, v0);
+            ss += sq(v0);
+        }
+        if (tid + W * 32 < n8) {
+            load_v(tid + W * 32, v1);
+            ss += sq(v1);
+        }
+        for (int q4 = tid + 2 * W * 32; q4 < n8; q4 += W * 32) {
+            float vv[4];
+            load_v(q4, vv);
+            ss += sq(vv);
+        }
+        // the same fixed reduction order in every CTA: shuffle tree, then the warp sums in order
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sts_f32(a_red + 4u * warp, ss);
+        asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) total += lds_f32(a_red + 4u * w);
+        const float inv_rms = rsqrtf(total / (float)p.K + p.norm_eps);
+        auto emit = [&](int q4, const float (&vv)[4]) {
+            const uint2 wq = __ldg(wg + q4);
+            const float w0 = __uint_as_float(wq.x << 16), w1 = __uint_as_float(wq.x & 0xffff0000u);
+            const float w2 = __uint_as_float(wq.y << 16), w3 = __uint_as_float(wq.y & 0xffff0000u);
+            uint2 o;
+            o.x = (uint32_t)f32_to_bf16_bits(vv[0] * inv_rms * w0) | ((uint32_t)f32_to_bf16_bits(vv[1] * inv_rms * w1) << 16);
+            o.y = (uint32_t)f32_to_bf16_bits(vv[2] * inv_rms * w2) | ((uint32_t)f32_to_bf16_bits(vv[3] * inv_rms * w3) << 16);
+            sts_x(q4, o);
+            if (c == 0 && p.norm_hidden_out) {
+                uint2 hq;
+                hq.x = (uint32_t)f32_to_bf16_bits(vv[0]) | ((uint32_t)f32_to_bf16_bits(vv[1]) << 16);
+                hq.y = (uint32_t)f32_to_bf16_bits(vv[2]) | ((uint32_t)f32_to_bf16_bits(vv[3]) << 16);
+                reinterpret_cast<uint2*>(p.norm_hidden_out)[q4] = hq;
+            }
+        };
+        if (tid < n8) emit(tid, v0);
+        if (tid + W * 32 < n8) emit(tid + W * 32, v1);
+        for (int q4 = tid + 2 * W * 32; q4 < n8; q4 += W * 32) {
+            float vv[4];
+            load_v(q4, vv);
+            emit(q4, vv);
+        }
+    }
+    const bool plain_x = !BATCH && p.norm_w == nullptr;
     uint2 xv0 = make_uint2(0u, 0u), xv1 = make_uint2(0u, 0u);
-    if (!BATCH && tid < n8) xv0 = __ldcg(xg + tid);
-    if (!BATCH && tid + W * 32 < n8) xv1 = __ldcg(xg + tid + W * 32);
+    if (plain_x && tid < n8) xv0 = __ldcg(xg + tid);
+    if (plain_x && tid + W * 32 < n8) xv1 = __ldcg(xg + tid + W * 32);
 
-    if (!BATCH && tid < n8) sts_x(tid, xv0);
-    if (!BATCH && tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
-    for (int q4 = tid + 2 * W * 32; !BATCH && q4 < n8; q4 += 2 * W * 32) {
+    if (plain_x && tid < n8) sts_x(tid, xv0);
+    if (plain_x && tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
+    for (int q4 = tid + 2 * W * 32; plain_x && q4 < n8; q4 += 2 * W * 32) {
         const int q5 = q4 + W * 32;
         const uint2 v0 = __ldcg(xg + q4);
         uint2 v1 = make_uint2(0u, 0u);
@@ -1103,7 +1174,7 @@ StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int
     // it fits, then ring stages in what is left; table = [64 KB, 128 KB); region B = [128 KB,
     // base + budget): x otherwise, then ring stages.
     const int base = (smem_window_base() + 15) / 16 * 16;
-    const int a_fixed = base + 400 + 64 + 16 + 1024 + 2 * kNabsWindow * 4 + 1024 +
+    const int a_fixed = base + 400 + 64 + 16 + 64 + 1024 + 2 * kNabsWindow * 4 + 1024 +
                         kMaxLocalTiles * 32 * 8 + kMaxLocalTiles * np * kConsumerWarps * 64;
     pl.x_in_b = (a_fixed + x_bytes > 65536) ? 1 : 0;
     const int ring_a = (a_fixed + (pl.x_in_b ? 0 : x_bytes) + 127) / 128 * 128;
@@ -1222,7 +1293,7 @@ bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count
 
 cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
                                void* y, const void* residual, int64_t ff_pair, cudaStream_t s,
-                               const PeerTargets* peers, int m_rows) {
+                               const PeerTargets* peers, int m_rows, const NormInput* norm) {
     const bool paired = ff_pair > 0;
     const StreamPlan pl = stream_plan(w, paired, ff_pair, scratch.sm_count);
     if (!pl.ok) return cudaErrorInvalidConfiguration;
@@ -1255,8 +1326,12 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.x_in_b = pl.x_in_b;
     p.smem_bytes = pl.smem;
     p.n_rows = (int)w.N;
-    if (m_rows < 1 || m_rows > 8 || (m_rows > 1 && peers)) return cudaErrorInvalidValue;
+    if (m_rows < 1 || m_rows > 8 || (m_rows > 1 && (peers || norm))) return cudaErrorInvalidValue;
     p.m_rows = m_rows;
+    p.norm_add = norm ? static_cast<const uint16_t*>(norm->add) : nullptr;
+    p.norm_w = norm ? static_cast<const uint16_t*>(norm->weight) : nullptr;
+    p.norm_hidden_out = norm ? static_cast<uint16_t*>(norm->hidden_out) : nullptr;
+    p.norm_eps = norm ? norm->eps : 0.0f;
     p.peer_world = 0;
     p.peer_rank = 0;
     p.peer_max_rows = 0;

@@ -117,9 +117,17 @@ struct PeerTargets {
     unsigned* flag_base[8];
     unsigned* ctrl;
 };
+// Residual add + RMSNorm folded into the staging of x (single-row launches): weight != NULL.
+struct NormInput {
+    const void* add;     // bf16 [K] added to x first, or NULL
+    const void* weight;  // bf16 [K]
+    void* hidden_out;    // bf16 [K] receives bf16(x + add), or NULL; must not alias x or add
+    float eps;
+};
 cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
                                void* y, const void* residual, int64_t ff_pair, cudaStream_t s,
-                               const PeerTargets* peers = nullptr, int m_rows = 1);
+                               const PeerTargets* peers = nullptr, int m_rows = 1,
+                               const NormInput* norm = nullptr);
 bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);

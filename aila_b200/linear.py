@@ -193,6 +193,49 @@ class Bnb4BitLinear:
         _lib.check(st)
         return True
 
+    @staticmethod
+    def _norm(weight: torch.Tensor, eps: float, add: torch.Tensor | None,
+              hidden_out: torch.Tensor | None) -> _lib.RmsNorm:
+        n = _lib.RmsNorm()
+        n.add_bf16 = add.data_ptr() if add is not None else None
+        n.weight_bf16 = weight.data_ptr()
+        n.eps = float(eps)
+        n.hidden_out_bf16 = hidden_out.data_ptr() if hidden_out is not None else None
+        return n
+
+    def forward_rmsnorm(self, scratch: Bnb4BitLinearScratch, input: torch.Tensor,
+                        norm_weight: torch.Tensor, eps: float, output: torch.Tensor,
+                        add: torch.Tensor | None = None, hidden_out: torch.Tensor | None = None,
+                        add_residual: torch.Tensor | None = None) -> bool:
+        """ops::fused_add_rms_norm (NormOps.cpp:141-260) folded into a seq_len == 1 forward:
+        the linear sees rmsnorm(input + add) * norm_weight, ``hidden_out`` receives input + add.
+        False = not applicable here (run ``add_rms_norm`` and ``forward`` separately)."""
+        n = self._norm(norm_weight, eps, add, hidden_out)
+        res = add_residual.data_ptr() if add_residual is not None else None
+        st = _lib.load().aila_nf4_forward_rmsnorm(self._h, scratch._h, input.data_ptr(),
+                                                  ctypes.byref(n), output.data_ptr(), res,
+                                                  _stream_ptr(self.device))
+        if st == _lib.NOT_APPLICABLE:
+            return False
+        _lib.check(st)
+        return True
+
+    @staticmethod
+    def try_forward_decode_gate_up_swiglu_rmsnorm(fused_gate_up: "Bnb4BitLinear",
+                                                  scratch: Bnb4BitLinearScratch, input: torch.Tensor,
+                                                  norm_weight: torch.Tensor, eps: float,
+                                                  output: torch.Tensor, ff_dim: int,
+                                                  add: torch.Tensor | None = None,
+                                                  hidden_out: torch.Tensor | None = None) -> bool:
+        n = Bnb4BitLinear._norm(norm_weight, eps, add, hidden_out)
+        st = _lib.load().aila_nf4_forward_gate_up_swiglu_rmsnorm(
+            fused_gate_up._h, scratch._h, input.data_ptr(), ctypes.byref(n), output.data_ptr(),
+            ff_dim, _stream_ptr(fused_gate_up.device))
+        if st == _lib.NOT_APPLICABLE:
+            return False
+        _lib.check(st)
+        return True
+
     def forward_host(self, scratch: Bnb4BitLinearScratch, x_host: torch.Tensor,
                      y_host: torch.Tensor, seq_len: int) -> None:
         """forward with (pinned) host tensors; copies in, runs, copies out, waits."""
@@ -302,6 +345,17 @@ class Linear:
         _lib.check(_lib.load().aila_dense_linear_forward(self._h, scratch._h, input.data_ptr(),
                                                          output.data_ptr(), seq_len, res,
                                                          _stream_ptr(self.device)))
+
+
+def add_rms_norm(x: torch.Tensor, add: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                 hidden_out: torch.Tensor | None, normed_out: torch.Tensor) -> None:
+    """ops::fused_add_rms_norm / rms_norm (NormOps.cpp:141-260) as its own launch, any row count:
+    hidden_out = x + add (may alias x), normed_out = rmsnorm(x + add) * weight."""
+    rows, hidden = x.shape
+    _lib.check(_lib.load().aila_add_rms_norm(
+        x.data_ptr(), add.data_ptr() if add is not None else None, weight.data_ptr(), float(eps),
+        rows, hidden, hidden_out.data_ptr() if hidden_out is not None else None,
+        normed_out.data_ptr(), x.device.index, _stream_ptr(x.device)))
 
 
 def argmax(logits: torch.Tensor, vocab_size: int, result: torch.Tensor) -> None:

@@ -250,6 +250,34 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear
                                                              void* stream);
 
 /*
+ * Residual add + RMSNorm in front of a decode linear, folded into the linear's launch
+ * (reference: ops::fused_add_rms_norm, src/ops/NormOps.cpp:141-260, launched before the qkv and
+ * gate|up linears at src/models/Qwen3Bnb4Backend.cpp:403 and :422). With v = x + add (fp32, not
+ * rounded): the linear's input is bf16(v * rsqrt(mean(v^2) + eps) * weight) and hidden_out, if
+ * given, receives bf16(v) - the updated residual stream. seq_len == 1 only.
+ * hidden_out must not alias x or add (every thread block of the launch reads them);
+ * aila_add_rms_norm below is the stand-alone operator (any row count, hidden_out may alias x)
+ * for the cases these entry points answer with AILA_NF4_NOT_APPLICABLE.
+ */
+typedef struct AilaNf4RmsNorm {
+    const void* add_bf16;     /* [in_features] added to x first, or NULL                 */
+    const void* weight_bf16;  /* [in_features] RMSNorm weight                            */
+    float eps;
+    void* hidden_out_bf16;    /* [in_features] receives bf16(x + add), or NULL           */
+} AilaNf4RmsNorm;
+AILA_NF4_API AilaNf4Status aila_nf4_forward_rmsnorm(const AilaNf4Linear* linear,
+                                                    AilaNf4Scratch* scratch, const void* x_bf16,
+                                                    const AilaNf4RmsNorm* norm, void* y_bf16,
+                                                    const void* residual_bf16, void* stream);
+AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_rmsnorm(
+    const AilaNf4Linear* fused_gate_up, AilaNf4Scratch* scratch, const void* x_bf16,
+    const AilaNf4RmsNorm* norm, void* out_bf16, int64_t ff_dim, void* stream);
+AILA_NF4_API AilaNf4Status aila_add_rms_norm(const void* x_bf16, const void* add_bf16,
+                                             const void* weight_bf16, float eps, int rows,
+                                             int hidden_size, void* hidden_out_bf16,
+                                             void* normed_out_bf16, int device, void* stream);
+
+/*
  * Dense bf16 linear y = x W^T (+ residual), W bf16 [out_features][in_features]: the unquantised
  * projection next to the NF4 linears (the lm_head). Replaces class Linear for this use
  * (reference src/ops/Ops.hpp:16-31: init(ctx, weight, in_features, out_features) and

@@ -304,6 +304,28 @@ void nf4o_swiglu_rows(const bf16_t* gate_up, int64_t M, int64_t ff, bf16_t* out)
     }
 }
 
+/* Residual add + RMSNorm in front of a linear. NormOps.cpp:141-260 (ops::fused_add_rms_norm):
+ * v = float(in) + float(residual) in fp32 (not rounded), sum of v^2 over the row,
+ * inv_rms = 1/sqrt(sum / H + eps), hidden_out = bf16(v), normed = bf16(v * inv_rms * float(w)).
+ * residual may be NULL (plain RMSNorm, NormOps.cpp rms_norm). The summation here is sequential in
+ * double so that it is a tight reference for any fp32 reduction order. */
+void nf4o_add_rms_norm(const bf16_t* in, const bf16_t* residual, const bf16_t* weight, float eps,
+                       int64_t M, int64_t H, bf16_t* hidden_out, bf16_t* normed_out) {
+    for (int64_t m = 0; m < M; ++m) {
+        double sum = 0.0;
+        for (int64_t k = 0; k < H; ++k) {
+            const float v = bf16_to_f32(in[m * H + k]) + (residual ? bf16_to_f32(residual[m * H + k]) : 0.0f);
+            sum += (double)v * (double)v;
+        }
+        const float inv_rms = 1.0f / sqrtf((float)(sum / (double)H) + eps);
+        for (int64_t k = 0; k < H; ++k) {
+            const float v = bf16_to_f32(in[m * H + k]) + (residual ? bf16_to_f32(residual[m * H + k]) : 0.0f);
+            if (hidden_out) hidden_out[m * H + k] = f32_to_bf16(v);
+            normed_out[m * H + k] = f32_to_bf16(v * inv_rms * bf16_to_f32(weight[k]));
+        }
+    }
+}
+
 /* Row concatenation of already-expanded linears. Bnb4BitLinear.cpp:604-615
  * (init_fused_rows_impl): packed bytes and fp32 absmax of each source are appended. The
  * caller concatenates; this helper only exists so tests exercise the same byte arithmetic. */

@@ -151,6 +151,18 @@ def swiglu_rows(gate_up_bf16, M, ff) -> np.ndarray:
     return out
 
 
+def add_rms_norm(x_bf16, residual_bf16, weight_bf16, eps, M, H):
+    """(hidden_out, normed) of ops::fused_add_rms_norm (NormOps.cpp:141-260); residual may be None."""
+    x = _c(x_bf16, np.uint16).reshape(M, H)
+    r = _c(residual_bf16, np.uint16).reshape(M, H) if residual_bf16 is not None else None
+    w = _c(weight_bf16, np.uint16).reshape(H)
+    hidden = np.empty((M, H), np.uint16)
+    normed = np.empty((M, H), np.uint16)
+    lib().nf4o_add_rms_norm(_p(x), _p(r) if r is not None else None, _p(w), ctypes.c_float(eps),
+                            ctypes.c_int64(M), ctypes.c_int64(H), _p(hidden), _p(normed))
+    return hidden, normed
+
+
 def forward(packed, qmap, absmax, x_bf16, M, N, K, blocksize) -> np.ndarray:
     """What Bnb4BitLinear::forward (Bnb4BitLinear.cpp:799-949) returns for [M,K] input:
     the decode GEMV for M == 1 (:813-818), otherwise bf16-rounded weights followed by a

@@ -566,3 +566,76 @@ def test_batched_gate_up_swiglu(nf4, oracle, scratch, M):
     xb = bf16_bits(x)
     want = np.stack([oracle.gemv_gate_up_swiglu(packed, g.quant_map, am, xb[m], FF, H, 64) for m in range(M)])
     assert_close_norm(bf16_bits(out.cpu()), want, REL)
+
+
+# ---------------------------------------------------------------- RMSNorm around the linears
+def _bf16_ulp_close(got_bits, want_bits, max_ulp=1):
+    """bf16 results that differ by at most `max_ulp` units in the last place (same sign)."""
+    g, w = got_bits.astype(np.int32), want_bits.astype(np.int32)
+    return np.abs(g - w).max() <= max_ulp
+
+
+@pytest.mark.parametrize("rows,H,with_add", [(1, 2560, True), (3, 1024, True), (2, 100, False), (1, 5120, True)])
+def test_add_rms_norm(nf4, oracle, rows, H, with_add):
+    x, add = _act(9001 + H, rows, H), (_act(9002 + H, rows, H) if with_add else None)
+    g = torch.Generator().manual_seed(9003)
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    xc = x.cuda()
+    hidden = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
+    normed = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
+    nf4.add_rms_norm(xc, add.cuda() if with_add else None, w.cuda(), 1e-6, hidden, normed)
+    want_h, want_n = oracle.add_rms_norm(bf16_bits(x), bf16_bits(add) if with_add else None, bf16_bits(w),
+                                         1e-6, rows, H)
+    assert np.array_equal(bf16_bits(hidden.cpu()), want_h)           # one exact fp32 add, one rounding
+    assert _bf16_ulp_close(bf16_bits(normed.cpu()), want_n)            # reduction order, rsqrt: 1 ulp
+    nf4.add_rms_norm(xc, add.cuda() if with_add else None, w.cuda(), 1e-6, xc, normed)  # in place
+    assert np.array_equal(bf16_bits(xc.cpu()), want_h)
+
+
+@pytest.mark.parametrize("N,K", [(272, 512), (6144, 2560), (2560, 9728)])
+def test_forward_with_folded_rms_norm(nf4, oracle, scratch, N, K):
+    """aila_nf4_forward_rmsnorm against (stand-alone RMSNorm kernel -> plain forward): the linear
+    must see the same normalised input up to one bf16 ulp, and hidden_out the same residual
+    stream; and against the oracle chain within the output bound."""
+    w = make_weight(9100 + N, N, K)
+    lin = _lin(nf4, w)
+    x, add = _act(9101 + N, 1, K), _act(9102 + N, 1, K)
+    g = torch.Generator().manual_seed(9103)
+    nw = (1.0 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16)
+    res = _act(9104 + N, 1, N)
+    y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+    hidden = torch.empty(1, K, dtype=torch.bfloat16, device="cuda")
+    assert lin.forward_rmsnorm(scratch, x.cuda(), nw.cuda(), 1e-6, y, add=add.cuda(), hidden_out=hidden,
+                               add_residual=res.cuda())
+    want_h, want_n = oracle.add_rms_norm(bf16_bits(x), bf16_bits(add), bf16_bits(nw), 1e-6, 1, K)
+    assert np.array_equal(bf16_bits(hidden.cpu()), want_h)
+    want = bits_to_f32(oracle.gemv(w.packed, w.quant_map, oracle_absmax(oracle, w), want_n.reshape(-1),
+                                   N, K, 64)) + bits_to_f32(bf16_bits(res)).reshape(-1)
+    got = bits_to_f32(bf16_bits(y.cpu())).reshape(-1)
+    assert np.abs(got - want).max() <= REL * np.abs(want).max()
+    # the unfused pair of launches gives (nearly) the same output
+    normed = torch.empty(1, K, dtype=torch.bfloat16, device="cuda")
+    nf4.add_rms_norm(x.cuda(), add.cuda(), nw.cuda(), 1e-6, None, normed)
+    y2 = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+    lin.forward(scratch, normed, y2, 1, add_residual=res.cuda())
+    assert np.abs(got - y2.float().cpu().numpy().reshape(-1)).max() <= 5e-3 * np.abs(want).max()
+    with pytest.raises(Exception):
+        lin.forward_rmsnorm(scratch, hidden, nw.cuda(), 1e-6, y, hidden_out=hidden)  # aliasing
+
+
+def test_gate_up_swiglu_with_folded_rms_norm(nf4, oracle, scratch):
+    H, FF = 1024, 2048
+    g, u = make_weight(9201, FF, H), make_weight(9202, FF, H)
+    lg, lu, f = _lin(nf4, g), _lin(nf4, u), nf4.Bnb4BitLinear()
+    assert f.init_fused_rows(lg, lu)
+    x = _act(9203, 1, H)
+    gen = torch.Generator().manual_seed(9204)
+    nw = (1.0 + 0.1 * torch.randn(H, generator=gen)).to(torch.bfloat16)
+    out = torch.empty(1, FF, dtype=torch.bfloat16, device="cuda")
+    assert nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu_rmsnorm(f, scratch, x.cuda(), nw.cuda(),
+                                                                       1e-6, out, FF)
+    _, want_n = oracle.add_rms_norm(bf16_bits(x), None, bf16_bits(nw), 1e-6, 1, H)
+    packed = np.concatenate([g.packed, u.packed])
+    am = np.concatenate([oracle_absmax(oracle, g), oracle_absmax(oracle, u)])
+    want = oracle.gemv_gate_up_swiglu(packed, g.quant_map, am, want_n.reshape(-1), FF, H, 64)
+    assert_close_norm(bf16_bits(out.cpu()).reshape(-1), want, REL)
