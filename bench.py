@@ -271,27 +271,37 @@ def tp_mlp_latency(rank, world, local, stream):
             t_c, t_f = float(t[0]), float(t[1])
         out[f"M{M}_compute_us"] = t_c
         out[f"M{M}_with_allreduce_us"] = t_f
-        if world > 1 and M == 1:
+        if world > 1 and M == 1 and os.environ.get("AILA_BENCH_FUSED_TP", "1") != "0":
             # the exchange folded into the down GEMV: fp32 row sums stored into every rank's
-            # buffer over NVLink, summed by a small kernel (no library collective)
-            peers = be.make_peer_buffer(None, H5)
-            y1 = be.empty(1, H5)
+            # buffer over NVLink, summed by a small kernel (no library collective). A failure on
+            # any rank is reported instead of the number; the collectives below stay matched.
+            t_x, how_x, err = 0.0, "", ""
+            peers = None
+            try:
+                peers = be.make_peer_buffer(None, H5)
+                y1 = be.empty(1, H5)
 
-            def fused():
-                assert be.gate_up_swiglu(gate_up, x, mid, 1, local_ff)
-                be.forward_allreduce(dn, peers, mid, y1)
+                def fused():
+                    assert be.gate_up_swiglu(gate_up, x, mid, 1, local_ff)
+                    be.forward_allreduce(dn, peers, mid, y1)
 
+                run_x, how_x = graphed(fused)
+                t_x = _time_stream(run_x, stream, reps)
+                torch.cuda.synchronize()
+                be.scratch.check()
+            except Exception as e:  # noqa: BLE001
+                err = repr(e)[:200]
+            t = torch.tensor([t_x, 0.0 if err else 1.0], device=torch.device("cuda", local))
+            dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
+            dist.all_reduce(t[1:], op=dist.ReduceOp.MIN)
+            if float(t[1]) > 0.5:
+                out["M1_fused_exchange_us"] = float(t[0])
+                out["M1_fused_launch"] = how_x
+            else:
+                out["M1_fused_exchange_error"] = err or "failed on another rank"
             dist.barrier()
-            run_x, how_x = graphed(fused)
-            dist.barrier()
-            t_x = _time_stream(run_x, stream, reps)
-            t = torch.tensor([t_x], device=torch.device("cuda", local))
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            out["M1_fused_exchange_us"] = float(t[0])
-            out["M1_fused_launch"] = how_x
-            torch.cuda.synchronize()
-            dist.barrier()
-            peers.close()
+            if peers is not None:
+                peers.close()
     be.scratch.check()
     return out
 
