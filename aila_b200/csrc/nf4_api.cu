@@ -803,6 +803,21 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_rmsnorm(
     return run_decode(l, sc, x, out, nullptr, ff_dim, static_cast<cudaStream_t>(stream), 1, &ni);
 }
 
+namespace {
+// A page-locked host buffer that the GPU can address (cudaHostAlloc / cudaHostRegister memory
+// under unified addressing): the kernels then write the result straight into it and the
+// device-to-host copy of the host entry points is skipped. NULL for pageable memory.
+void* device_view_of_host(const void* host_ptr) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host_ptr) != cudaSuccess) {
+        cudaGetLastError();  // pageable memory reports an error on some drivers: not a failure
+        return nullptr;
+    }
+    if (attr.type != cudaMemoryTypeHost || !attr.devicePointer) return nullptr;
+    return attr.devicePointer;
+}
+}  // namespace
+
 AILA_NF4_API AilaNf4Status aila_nf4_forward_host(const AilaNf4Linear* l, AilaNf4Scratch* sc,
                                                  const void* x_host, void* y_host, int seq_len,
                                                  void* stream) {
@@ -815,9 +830,11 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_host(const AilaNf4Linear* l, AilaNf4
     if ((st = ensure_io(&sc->d_io_in, &sc->io_in_bytes, in_b)) != AILA_NF4_OK) return st;
     if ((st = ensure_io(&sc->d_io_out, &sc->io_out_bytes, out_b)) != AILA_NF4_OK) return st;
     NF4_CUDA(cudaMemcpyAsync(sc->d_io_in, x_host, in_b, cudaMemcpyHostToDevice, s));
-    st = aila_nf4_forward(l, sc, sc->d_io_in, sc->d_io_out, seq_len, nullptr, stream);
+    // single-row results (tens of KB) go straight into GPU-addressable host memory
+    void* y_direct = seq_len == 1 ? device_view_of_host(y_host) : nullptr;
+    st = aila_nf4_forward(l, sc, sc->d_io_in, y_direct ? y_direct : sc->d_io_out, seq_len, nullptr, stream);
     if (st != AILA_NF4_OK) return st;
-    NF4_CUDA(cudaMemcpyAsync(y_host, sc->d_io_out, out_b, cudaMemcpyDeviceToHost, s));
+    if (!y_direct) NF4_CUDA(cudaMemcpyAsync(y_host, sc->d_io_out, out_b, cudaMemcpyDeviceToHost, s));
     NF4_CUDA(cudaStreamSynchronize(s));
     return AILA_NF4_OK;
 }
@@ -835,9 +852,11 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_host(
     if ((st = ensure_io(&sc->d_io_in, &sc->io_in_bytes, in_b)) != AILA_NF4_OK) return st;
     if ((st = ensure_io(&sc->d_io_out, &sc->io_out_bytes, out_b)) != AILA_NF4_OK) return st;
     NF4_CUDA(cudaMemcpyAsync(sc->d_io_in, x_host, in_b, cudaMemcpyHostToDevice, s));
-    st = aila_nf4_forward_gate_up_swiglu(l, sc, sc->d_io_in, sc->d_io_out, seq_len, ff_dim, stream);
+    void* out_direct = seq_len == 1 ? device_view_of_host(out_host) : nullptr;
+    st = aila_nf4_forward_gate_up_swiglu(l, sc, sc->d_io_in, out_direct ? out_direct : sc->d_io_out,
+                                         seq_len, ff_dim, stream);
     if (st != AILA_NF4_OK) return st;
-    NF4_CUDA(cudaMemcpyAsync(out_host, sc->d_io_out, out_b, cudaMemcpyDeviceToHost, s));
+    if (!out_direct) NF4_CUDA(cudaMemcpyAsync(out_host, sc->d_io_out, out_b, cudaMemcpyDeviceToHost, s));
     NF4_CUDA(cudaStreamSynchronize(s));
     return AILA_NF4_OK;
 }

@@ -36,7 +36,7 @@ UNIT = "GB/s"
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # capture summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 26083840  # profiles/gemv_stream_cfg2_ncu.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 25750528  # profiles/gemv_stream_cfg2_ncu.md
 
 
 def weight_bytes(n: int, k: int) -> int:
@@ -669,8 +669,9 @@ def main():
                      "frac_of_nominal_8TBps": achieved / 8000.0},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": layers * 2 * H,
                 "d2h_bytes_per_step": layers * 2 * FF,
-                "note": "aila_nf4_forward_gate_up_swiglu_host per layer: pinned H2D of x, kernel, "
-                        "D2H of y, stream sync"},
+                "note": "aila_nf4_forward_gate_up_swiglu_host per layer: pinned H2D copy of x, kernel "
+                        "whose epilogue stores y straight into the pinned host buffer (the D2H "
+                        "bytes cross PCIe as the kernel's stores), stream sync"},
         "gpu_launches": args.steps * layers,
         "clocks": clocks.summary(),
         "step_ms_min_max": [min(step_ms), max(step_ms)],
