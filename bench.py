@@ -277,21 +277,34 @@ def tp_mlp_latency(rank, world, local, stream):
             # any rank is reported instead of the number; the collectives below stay matched.
             t_x, how_x, err = 0.0, "", ""
             peers = None
-            try:
+            dev_t = torch.device("cuda", local)
+            y1 = be.empty(1, H5)
+
+            def fused():
+                assert be.gate_up_swiglu(gate_up, x, mid, 1, local_ff)
+                be.forward_allreduce(dn, peers, mid, y1)
+
+            try:  # set-up and one checked call; every rank must get through it before any timing
                 peers = be.make_peer_buffer(None, H5)
-                y1 = be.empty(1, H5)
-
-                def fused():
-                    assert be.gate_up_swiglu(gate_up, x, mid, 1, local_ff)
-                    be.forward_allreduce(dn, peers, mid, y1)
-
-                run_x, how_x = graphed(fused)
-                t_x = _time_stream(run_x, stream, reps)
-                torch.cuda.synchronize()
+                with torch.cuda.stream(stream):
+                    fused()
+                    stream.synchronize()
                 be.scratch.check()
             except Exception as e:  # noqa: BLE001
                 err = repr(e)[:200]
-            t = torch.tensor([t_x, 0.0 if err else 1.0], device=torch.device("cuda", local))
+            ok = torch.tensor([0.0 if err else 1.0], device=dev_t)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if float(ok[0]) > 0.5:
+                try:
+                    run_x, how_x = graphed(fused)
+                    t_x = _time_stream(run_x, stream, reps)
+                    torch.cuda.synchronize()
+                    be.scratch.check()
+                except Exception as e:  # noqa: BLE001
+                    err = repr(e)[:200]
+            elif not err:
+                err = "set-up failed on another rank"
+            t = torch.tensor([t_x, 0.0 if err else 1.0], device=dev_t)
             dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
             dist.all_reduce(t[1:], op=dist.ReduceOp.MIN)
             if float(t[1]) > 0.5:
