@@ -153,15 +153,15 @@ struct StreamParams {
     uint16_t* norm_hidden_out;
     float norm_eps;
     // row-parallel exchange (peer_world > 0): the epilogue stores the fp32 row sums of this
-    // rank into every rank's exchange buffer and adds one to that rank's arrival counter per
-    // row tile, instead of writing y
+    // rank into every rank's exchange buffer as 8-byte words {value, tag = epoch + 1}; a reader
+    // that finds the call's tag in a word has the value (one naturally aligned 64-bit access)
     int peer_world;
     int peer_rank;
     long long peer_max_rows;
-    float* peer_part[kMaxPeerWorld];      // rank d's row area (all parities and source ranks)
-    unsigned* peer_flag[kMaxPeerWorld];   // rank d's arrival counters
-    unsigned* peer_ctrl;                  // this rank's {epoch, tiles done, reducer blocks done}
+    unsigned long long* peer_part[kMaxPeerWorld];  // rank d's row area (all parities and source ranks)
+    unsigned* peer_ctrl;                  // this rank's {epoch, unused, CTAs / reducer blocks done}
     int n_row_tiles;                      // row tiles of the launch (all CTAs)
+    int peer_inline;                      // 1: the CTAs also sum the ranks' rows and write y
 #ifdef AILA_NF4_TRACE
     int trace_idx;
 #endif
@@ -349,39 +349,78 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     // ---- completing a row tile (finalizer warp) ----
     // write_rows: the epilogue of 16 output rows (lanes 0..15 hold one row each)
     int peer_parity = -1;  // exchange half of this launch, read on first use
-    int peer_tiles = 0;    // row tiles this CTA has stored into the exchange buffers
-    // After a CTA's last tile: one system-scope fence, then the tiles are counted; the CTA that
-    // completes the launch's count adds one to this rank's arrival counter on every rank. A rank
-    // that sees all its counters reach the epoch's target may read the rows.
-    auto peer_publish = [&]() {
-        if (PAIRED || p.peer_world == 0 || peer_tiles == 0) return;
-        __threadfence_system();
+    unsigned peer_epoch = 0;
+    auto peer_read_epoch = [&]() {
+        if (peer_parity < 0) {
+            peer_epoch = *(volatile unsigned*)p.peer_ctrl;
+            peer_parity = (int)(peer_epoch & 1u);
+        }
+    };
+    // One launch does the whole exchange when every CTA of the grid is resident at once (grid <=
+    // SM count): each CTA's finalizer warp sums the ranks' rows of its share of the output in rank
+    // order as soon as every rank's word carries the call's tag (bounded wait per word), adds the
+    // residual and writes y. The CTA that finishes last advances the epoch. A CTA only waits
+    // after it has published its own rows, and this rank's words need nothing but the resident
+    // CTAs of this grid.
+    auto peer_reduce_inline = [&]() {
+        peer_read_epoch();
+        const unsigned tag = peer_epoch + 1u;
+        const int per = (p.n_out + G - 1) / G;
+        const int r0 = c * per, r1 = min(p.n_out, r0 + per);
+        const unsigned long long* part =
+            p.peer_part[p.peer_rank] + (size_t)peer_parity * p.peer_world * (size_t)p.peer_max_rows;
+        bool ok = true;
+        for (int r = r0 + lane; r < r1 && ok; r += 32) {
+            float acc = 0.0f;
+            for (int src = 0; src < p.peer_world && ok; ++src) {
+                const unsigned long long* word = part + (size_t)src * (size_t)p.peer_max_rows + r;
+                unsigned long long q;
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(q) : "l"(word) : "memory");
+                if ((unsigned)(q >> 32) != tag) {
+                    const long long t0 = clock64();
+                    do {
+                        __nanosleep(40);
+                        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(q) : "l"(word) : "memory");
+                        if (*(volatile int*)abort_flag || clock64() - t0 > kSpinLimitCycles) {
+                            atomicExch(p.status, kStatusTimeoutPeer);
+                            ok = false;
+                            break;
+                        }
+                    } while ((unsigned)(q >> 32) != tag);
+                }
+                acc += __uint_as_float((unsigned)q);
+            }
+            if (ok) {
+                if (p.residual) acc += bf16_bits_to_f32(__ldcg(p.residual + r));
+                p.y[r] = f32_to_bf16_bits(acc);
+            }
+        }
         __syncwarp();
-        unsigned done = 0;
-        if (lane == 0) done = atomicAdd(p.peer_ctrl + 1, (unsigned)peer_tiles);
-        done = __shfl_sync(0xffffffffu, done, 0);
-        if (done + (unsigned)peer_tiles == (unsigned)p.n_row_tiles) {
-            if (lane == 0) p.peer_ctrl[1] = 0u;
-            __threadfence_system();
-            if (lane < p.peer_world)
-                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(
-                                 p.peer_flag[lane] + peer_parity * p.peer_world + p.peer_rank)
-                             : "memory");
+        if (lane == 0) {
+            __threadfence();
+            const unsigned done = atomicAdd(p.peer_ctrl + 2, 1u);
+            if (done == (unsigned)G - 1u) {
+                p.peer_ctrl[2] = 0u;
+                __threadfence();
+                *(volatile unsigned*)p.peer_ctrl = peer_epoch + 1u;
+            }
         }
     };
     auto write_rows = [&](int rtile, const float (&v)[NP]) {
         if (!PAIRED && p.peer_world > 0) {
-            // Row-parallel exchange: plain stores into every rank's memory (this rank's own
-            // included); the fence and the arrival accounting follow once per CTA
-            // (peer_publish). The exchange alternates between two halves of the buffers
-            // (parity of the epoch, which this rank's reducer advances).
-            if (peer_parity < 0) peer_parity = (int)(*(volatile unsigned*)p.peer_ctrl & 1u);
+            // Row-parallel exchange: one 8-byte store {value, tag} per row into every rank's
+            // memory (this rank's own included). No fence and no counter: the tag arrives with
+            // the value. The exchange alternates between two halves of the buffers (parity of
+            // the epoch, which this rank advances when the call's sums have been written).
+            peer_read_epoch();
             const size_t slice = ((size_t)peer_parity * p.peer_world + p.peer_rank) * (size_t)p.peer_max_rows;
             const int n = rtile * kTileRows + lane;
             if (lane < 16 && n < p.n_out) {
-                for (int d = 0; d < p.peer_world; ++d) p.peer_part[d][slice + n] = v[0];
+                const unsigned long long word =
+                    ((unsigned long long)(peer_epoch + 1u) << 32) | (unsigned long long)__float_as_uint(v[0]);
+                for (int d = 0; d < p.peer_world; ++d)
+                    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.peer_part[d] + slice + n), "l"(word) : "memory");
             }
-            ++peer_tiles;
             return;
         }
         if (lane < 16) {
@@ -683,7 +722,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             resolve(pend_li0, pend_old0);
             resolve(pend_li1, pend_old1);
         }
-        peer_publish();
+        if (!PAIRED && !BATCH && p.peer_world > 0 && p.peer_inline) peer_reduce_inline();
 #ifdef AILA_NF4_TRACE
         if (lane == 0) {
             unsigned long long t_;
@@ -1286,6 +1325,11 @@ size_t gemv_stream_partials_floats(int sm_count) {
     return (size_t)sm_count * kMaxGridMult * 2 * 2 * 128;
 }
 
+int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count) {
+    const StreamPlan pl = stream_plan(w, ff_pair > 0, ff_pair, sm_count);
+    return pl.ok ? pl.grid : 0;
+}
+
 bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count) {
     if (w.K > 65535 * 4) return false;
     return stream_plan(w, ff_pair > 0, ff_pair, sm_count).ok;
@@ -1336,10 +1380,10 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.peer_rank = 0;
     p.peer_max_rows = 0;
     p.peer_ctrl = nullptr;
+    p.peer_inline = 0;
     p.n_row_tiles = rt_work;
     for (int d = 0; d < kMaxPeerWorld; ++d) {
         p.peer_part[d] = nullptr;
-        p.peer_flag[d] = nullptr;
     }
     if (peers) {
         if (paired || peers->world < 1 || peers->world > kMaxPeerWorld) return cudaErrorInvalidValue;
@@ -1347,9 +1391,9 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
         p.peer_rank = peers->rank;
         p.peer_max_rows = peers->max_rows;
         p.peer_ctrl = peers->ctrl;
+        p.peer_inline = peers->inline_reduce ? 1 : 0;
         for (int d = 0; d < peers->world; ++d) {
             p.peer_part[d] = peers->part_base[d];
-            p.peer_flag[d] = peers->flag_base[d];
         }
     }
 #ifdef AILA_NF4_TRACE

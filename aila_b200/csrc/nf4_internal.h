@@ -105,17 +105,17 @@ cudaError_t launch_gemv_simple(const AilaNf4Linear& w, const void* x, void* y,
                                const void* residual, int64_t ff_pair, cudaStream_t s);
 size_t gemv_stream_partials_floats(int sm_count);
 // Row-parallel exchange of one launch: where this rank's fp32 row sums go on every rank (its
-// own included). part_base[d] / flag_base[d] are rank d's row area and arrival counters as
-// mapped in this process; ctrl is this rank's own control block {epoch, tiles done, reducer
-// blocks done}. Row slice and counter of (parity, source rank): part_base + (parity * world +
-// rank) * max_rows, flag_base + parity * world + rank.
+// own included), as 8-byte words {value, tag}. part_base[d] is rank d's row area as mapped in
+// this process; the word of (parity, source rank, row) sits at
+// part_base + (parity * world + rank) * max_rows + row. ctrl is this rank's own control block
+// {epoch, unused, CTAs or reducer blocks done}.
 struct PeerTargets {
     int world;
     int rank;
     long long max_rows;
-    float* part_base[8];
-    unsigned* flag_base[8];
+    unsigned long long* part_base[8];
     unsigned* ctrl;
+    bool inline_reduce;  // the GEMV's CTAs also sum the ranks' rows (grid <= SM count only)
 };
 // Residual add + RMSNorm folded into the staging of x (single-row launches): weight != NULL.
 struct NormInput {
@@ -129,16 +129,17 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
                                const PeerTargets* peers = nullptr, int m_rows = 1,
                                const NormInput* norm = nullptr);
 bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);
+int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);  // 0: shape not taken
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);
 
 // nf4_peer.cu ---------------------------------------------------------------------------
-// y[n] = bf16(sum over ranks of part[parity][rank][n] (+ residual[n])) once every rank's
-// counter of the current parity has reached the epoch's target; waits are bounded and report
-// kStatusTimeoutPeer. The last block advances the epoch.
-cudaError_t launch_peer_reduce(const float* part_base, const unsigned* flag_base, unsigned* ctrl,
-                               int world, int64_t max_rows, int64_t n, const void* residual,
-                               void* y, int* d_status, cudaStream_t s);
+// y[n] = bf16(sum over ranks of the tagged words [parity][rank][n] (+ residual[n])), each word
+// waited for (bounded, kStatusTimeoutPeer) until it carries the call's tag. The last block
+// advances the epoch.
+cudaError_t launch_peer_reduce(const unsigned long long* part_base, unsigned* ctrl, int world,
+                               int64_t max_rows, int64_t n, const void* residual, void* y,
+                               int* d_status, cudaStream_t s);
 AilaNf4Status ensure_counters(AilaNf4Scratch* sc, size_t tiles);
 
 // nf4_gemm.cu ---------------------------------------------------------------------------

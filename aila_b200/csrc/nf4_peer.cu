@@ -4,23 +4,25 @@
 // sum. For M = 1 the message is tens of KB and a library all-reduce is latency-bound, so the
 // exchange is folded into the GEMV: the kernel's epilogue stores this rank's fp32 row sums
 // straight into EVERY rank's exchange buffer (plain peer stores through NVLink, its own buffer
-// included) behind system-scope fences, and the CTA that finishes the call's last row tile bumps
-// this rank's arrival counter on every rank. A small reducer kernel on each rank then waits
-// (bounded) until all its counters have reached the call's target and writes
-// y = bf16(sum over ranks in rank order (+ residual)): every rank gets the bit-identical result.
+// included) as 8-byte words {value, tag}, tag = epoch + 1. A naturally aligned 64-bit store is
+// seen whole or not at all, so a reader that finds the call's tag in a word has its value: no
+// fence, no counter, one NVLink store latency. The rank sum (rank order, + residual, one bf16
+// rounding: every rank gets the bit-identical result) is done by the GEMV's own CTAs when the
+// whole grid is resident at once, otherwise by a small second kernel; readers wait per word,
+// bounded.
 //
 // Exchange buffer of one rank (one cudaMalloc, shared with the other processes through CUDA
-// IPC): [2 parities][world][max_rows] fp32 rows, [2][world] u32 arrival counters, then this
-// rank's control block {epoch, row tiles done, reducer blocks done}. Calls alternate between the
-// two parities (parity = epoch & 1): a rank can run ahead of a peer by less than one call (its
-// next reducer needs that peer's next rows), so two halves are enough. A rank's GEMV bumps its
-// counter on every rank ONCE per call (by the CTA that finishes the call's last row tile), so
-// the target of a call is (epoch >> 1) + 1; the reducer's last block advances the epoch. All
-// state lives on the device: the call sequence can be captured in a CUDA graph and replayed.
-// All ranks must issue the same calls in the same order.
+// IPC): [2 parities][world][max_rows] 8-byte words, then this rank's control block {epoch,
+// unused, CTAs / reducer blocks done}. Calls alternate between the two parities (parity = epoch
+// & 1): a rank can run ahead of a peer by less than one call (its next sum needs that peer's
+// next rows, which the peer sends only after it has finished reading the current ones), so two
+// halves are enough; the tag tells the halves' successive uses apart. The last CTA (or reducer
+// block) of a call advances the epoch. All state lives on the device: the call sequence can be
+// captured in a CUDA graph and replayed. All ranks must issue the same calls in the same order.
 //
 // No load in this file or in the GEMV touches another GPU's memory: remote memory is only
 // written. No multicast object is created.
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -42,46 +44,47 @@ namespace nf4 {
 
 namespace {
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 
-// One thread per output row. The first `world` threads of every block wait for one rank's
-// counter each; a timeout is recorded and the block leaves without writing. The last block to
-// finish advances the epoch (every block has read it by then).
+// One thread per output row: wait (bounded) for every rank's word of the row, sum in rank order.
+// The last block to finish advances the epoch (every block has read it by then).
 __global__ void __launch_bounds__(256)
-peer_reduce_kernel(const float* __restrict__ part_base, const unsigned* __restrict__ flag_base,
-                   unsigned* ctrl, int world, long long max_rows, long long n,
-                   const uint16_t* __restrict__ residual, uint16_t* __restrict__ y, int* status) {
-    __shared__ int gave_up;
+peer_reduce_kernel(const unsigned long long* __restrict__ part_base, unsigned* ctrl, int world,
+                   long long max_rows, long long n, const uint16_t* __restrict__ residual,
+                   uint16_t* __restrict__ y, int* status) {
     const unsigned epoch = *(volatile unsigned*)ctrl;
     const unsigned parity = epoch & 1u;
-    const unsigned target = (epoch >> 1) + 1u;
-    if (threadIdx.x == 0) gave_up = 0;
-    __syncthreads();
-    if ((int)threadIdx.x < world) {
-        const unsigned* flag = flag_base + parity * world + threadIdx.x;
-        const long long t0 = clock64();
-        // wrap-safe "counter has reached target"
-        while ((int)(ld_acquire_sys(flag) - target) < 0) {
-            __nanosleep(100);
-            if (clock64() - t0 > kSpinLimitCycles) {
-                atomicExch(status, kStatusTimeoutPeer);
-                gave_up = 1;
-                break;
-            }
-        }
-    }
-    __syncthreads();
+    const unsigned tag = epoch + 1u;
     const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (!gave_up && row < n) {
-        const float* part = part_base + (size_t)parity * world * (size_t)max_rows;
+    if (row < n) {
+        const unsigned long long* part = part_base + (size_t)parity * world * (size_t)max_rows;
         float acc = 0.0f;
-        for (int r = 0; r < world; ++r) acc += __ldcg(part + (size_t)r * (size_t)max_rows + row);
-        if (residual) acc += bf16_bits_to_f32(residual[row]);
-        y[row] = f32_to_bf16_bits(acc);
+        bool ok = true;
+        for (int r = 0; r < world && ok; ++r) {
+            const unsigned long long* word = part + (size_t)r * (size_t)max_rows + row;
+            unsigned long long q = ld_relaxed_sys_u64(word);
+            if ((unsigned)(q >> 32) != tag) {
+                const long long t0 = clock64();
+                do {
+                    __nanosleep(40);
+                    q = ld_relaxed_sys_u64(word);
+                    if (clock64() - t0 > kSpinLimitCycles) {
+                        atomicExch(status, kStatusTimeoutPeer);
+                        ok = false;
+                        break;
+                    }
+                } while ((unsigned)(q >> 32) != tag);
+            }
+            acc += __uint_as_float((unsigned)q);
+        }
+        if (ok) {
+            if (residual) acc += bf16_bits_to_f32(residual[row]);
+            y[row] = f32_to_bf16_bits(acc);
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -95,33 +98,25 @@ peer_reduce_kernel(const float* __restrict__ part_base, const unsigned* __restri
     }
 }
 
-size_t rows_floats(int world, int64_t max_rows) { return (size_t)2 * world * (size_t)max_rows; }
+size_t rows_words(int world, int64_t max_rows) { return (size_t)2 * world * (size_t)max_rows; }
 
-size_t peerbuf_bytes(int world, int64_t max_rows) {
-    return rows_floats(world, max_rows) * 4 + (size_t)2 * world * 4 + 64 + 256;
-}
+size_t peerbuf_bytes(int world, int64_t max_rows) { return rows_words(world, max_rows) * 8 + 64 + 256; }
 
-float* part_base_of(void* base) { return static_cast<float*>(base); }
-
-unsigned* flag_base_of(void* base, int world, int64_t max_rows) {
-    return reinterpret_cast<unsigned*>(static_cast<float*>(base) + rows_floats(world, max_rows));
-}
+unsigned long long* part_base_of(void* base) { return static_cast<unsigned long long*>(base); }
 
 unsigned* ctrl_of(void* base, int world, int64_t max_rows) {
-    // 16 words after the counters' start keeps the control block off the counters' sector pair
-    return flag_base_of(base, world, max_rows) + 2 * 8;
+    return reinterpret_cast<unsigned*>(static_cast<unsigned long long*>(base) + rows_words(world, max_rows));
 }
 
 }  // namespace
 
-cudaError_t launch_peer_reduce(const float* part_base, const unsigned* flag_base, unsigned* ctrl,
-                               int world, int64_t max_rows, int64_t n, const void* residual,
-                               void* y, int* d_status, cudaStream_t s) {
+cudaError_t launch_peer_reduce(const unsigned long long* part_base, unsigned* ctrl, int world,
+                               int64_t max_rows, int64_t n, const void* residual, void* y,
+                               int* d_status, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    peer_reduce_kernel<<<blocks, 256, 0, s>>>(part_base, flag_base, ctrl, world,
-                                              (long long)max_rows, (long long)n,
-                                              static_cast<const uint16_t*>(residual),
+    peer_reduce_kernel<<<blocks, 256, 0, s>>>(part_base, ctrl, world, (long long)max_rows,
+                                              (long long)n, static_cast<const uint16_t*>(residual),
                                               static_cast<uint16_t*>(y), d_status);
     return cudaGetLastError();
 }
@@ -242,18 +237,23 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear
     pt.rank = b->rank;
     pt.max_rows = b->max_rows;
     pt.ctrl = nf4::ctrl_of(b->local, b->world, b->max_rows);
-    for (int d = 0; d < 8; ++d) {
-        pt.part_base[d] = nullptr;
-        pt.flag_base[d] = nullptr;
-    }
-    for (int d = 0; d < b->world; ++d) {
-        pt.part_base[d] = nf4::part_base_of(b->base[d]);
-        pt.flag_base[d] = nf4::flag_base_of(b->base[d], b->world, b->max_rows);
+    for (int d = 0; d < 8; ++d) pt.part_base[d] = nullptr;
+    for (int d = 0; d < b->world; ++d) pt.part_base[d] = nf4::part_base_of(b->base[d]);
+    // One launch when all CTAs of the grid are resident together (they wait for each other's
+    // rows through the arrival counters); otherwise the GEMV publishes and a second kernel sums.
+    static const bool allow_inline = [] {
+        const char* e = std::getenv("AILA_NF4_PEER_INLINE");
+        return !(e && e[0] == '0');
+    }();
+    const int grid = nf4::gemv_stream_grid(*l, 0, sc->sm_count);
+    pt.inline_reduce = allow_inline && grid > 0 && grid <= sc->sm_count;
+    if (pt.inline_reduce) {
+        NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, y, residual, 0, s, &pt));
+        return AILA_NF4_OK;
     }
     NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, nullptr, nullptr, 0, s, &pt));
-    NF4_CUDA(nf4::launch_peer_reduce(nf4::part_base_of(b->local),
-                                     nf4::flag_base_of(b->local, b->world, b->max_rows), pt.ctrl,
-                                     b->world, b->max_rows, l->N, residual, y, sc->d_status, s));
+    NF4_CUDA(nf4::launch_peer_reduce(nf4::part_base_of(b->local), pt.ctrl, b->world, b->max_rows,
+                                     l->N, residual, y, sc->d_status, s));
     return AILA_NF4_OK;
 }
 

@@ -219,8 +219,9 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_static(const AilaNf4Linear* l
  * (the reference runs on one device). For a linear that holds a COLUMN shard of the weight
  * (aila_nf4_linear_create_shard, AILA_NF4_SHARD_COLS) every rank computes a partial y; the
  * kernel stores its fp32 row sums straight into every rank's exchange buffer over NVLink
- * (plain peer stores, no multicast object, no load from another GPU's memory) and a small
- * second kernel sums the ranks' rows in rank order: all ranks obtain the bit-identical
+ * (plain peer stores of 8-byte {value, tag} words; no multicast object, no load from another
+ * GPU's memory) and the ranks' rows are summed in rank order - by the same launch when its grid
+ * is one thread block per SM, else by a small second kernel: all ranks obtain the bit-identical
  * y = bf16(sum_r W_r x_r (+ residual)).
  *
  * Set-up, once per process group (one process per GPU, all on one node): every rank creates an

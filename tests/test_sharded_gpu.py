@@ -71,6 +71,21 @@ def _worker(rank, world, port, q):
         everyone = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(everyone, mine)
         same = same and all(torch.equal(mine, t) for t in everyone)
+        # a tall, narrow row-parallel linear: its grid exceeds the SM count, so the exchange takes
+        # the two-kernel form (publish, then a reducer kernel) instead of the single launch
+        tall = make_weight(4, 20000, 128 * world)
+        rp = sharded.RowParallelNf4Linear(tall, be, peers=None)
+        peers_tall = be.make_peer_buffer(None, 20000)
+        rp_fused = sharded.RowParallelNf4Linear(tall, be, peers=peers_tall)
+        xt = synth.gaussian_activation(12, 1, 128 * world).cuda()
+        xt_local = xt[:, rank * 128:(rank + 1) * 128].contiguous()
+        yt_ref = rp.forward(xt_local)
+        yt = [rp_fused.forward(xt_local) for _ in range(3)]
+        torch.cuda.synchronize()
+        be.scratch.check()
+        tall_err = float((yt[0].float() - yt_ref.float()).abs().max() / yt_ref.float().abs().max())
+        same = same and all(torch.equal(yt[0], t) for t in yt[1:]) and tall_err < 1e-2
+        peers_tall.close()
         outs["fused"] = ys[0].cpu().view(torch.uint16).numpy()
         outs["fused_consistent"] = bool(same)
         peers.close()
