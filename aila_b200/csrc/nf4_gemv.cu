@@ -759,7 +759,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (wwin_ok && (unsigned)(lane + 32 * i) < cnt) win_reg[i] = __ldg(p.sp.nabs + wwin_lo + lane + 32 * i);
         }
     }
-    {
+    auto zero_slots = [&]() {
         constexpr int kSlotVecs = kMaxLocalTiles * NP * W * 16 / 4;
 #pragma unroll
         for (int i = 0; i < (kSlotVecs + W * 32 - 1) / (W * 32); ++i) {
@@ -767,7 +767,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             if (q < kSlotVecs)
                 asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a_slots + 16u * q), "r"(0u) : "memory");
         }
-    }
+    };
     if (tid == 0) NF4_TRACE(42);
 
     const int gq = lane >> 2;  // row inside the tile (and row + 8)
@@ -804,14 +804,18 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         rt = fast_div(it, p.div_ku_m, p.div_ku_s);
         kb = it - rt * p.KU;
     };
+    // Set-up that nothing needs before the first work item: it runs after the loads of x have been
+    // issued, under their latency (x can only be asked for once the previous kernel is done).
     // absmax row base and offset of this lane's row in every local tile: warp li prepares tile li
-    if (KIND == kAbsmaxCodes && warp < n_local) {
+    auto tile_tables = [&]() {
+      if (KIND == kAbsmaxCodes && warp < n_local) {
         // rows past the end of the linear (padding of the last tile) borrow the last row's scale
         const int n = min((rt_first + warp + dhalf * p.pair_rt_offset) * kTileRows + drow, p.n_rows - 1);
         const SegmentRow sr = segment_row(p.sp, n);
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_tinfo + (uint32_t)(warp * 32 + lane) * 8u),
                      "r"(sr.flat), "r"(__float_as_uint(sr.offset)) : "memory");
-    }
+      }
+    };
     auto refresh = [&]() {  // absmax row base of this lane for row tile rt
         if (KIND == kAbsmaxCodes) {
             const uint2 ti = lds_v2(a_tinfo + (uint32_t)((rt - rt_first) * 32 + lane) * 8u);
@@ -819,7 +823,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             d_off = __uint_as_float(ti.y);
         }
     };
-    if (v < len) locate(v);
+    auto late_setup = [&]() {
+        zero_slots();
+        tile_tables();
+        if (v < len) locate(v);
+    };
     const int kb_step = p.kb_step;  // from one item of this warp to its next
     const int rt_step = p.rt_step;
     if (tid == 0) NF4_TRACE(43);
@@ -881,6 +889,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     auto sts_x = [&](int q4, uint2 xv) {
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(slot_of(q4)), "r"(xv.x), "r"(xv.y) : "memory");
     };
+    if (BATCH || p.norm_w != nullptr) late_setup();
     if (!BATCH && p.norm_w != nullptr) {
         // ---- residual add + RMSNorm while staging x ----
         static_assert(W <= 16, "per-warp sums");
@@ -947,6 +956,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     uint2 xv0 = make_uint2(0u, 0u), xv1 = make_uint2(0u, 0u);
     if (plain_x && tid < n8) xv0 = __ldcg(xg + tid);
     if (plain_x && tid + W * 32 < n8) xv1 = __ldcg(xg + tid + W * 32);
+    if (plain_x) late_setup();
 
     if (plain_x && tid < n8) sts_x(tid, xv0);
     if (plain_x && tid + W * 32 < n8) sts_x(tid + W * 32, xv1);
