@@ -59,6 +59,13 @@ class RmsNorm(ctypes.Structure):
                 ("eps", ctypes.c_float), ("hidden_out_bf16", ctypes.c_void_p)]
 
 
+class ChainOp(ctypes.Structure):
+    """AilaNf4ChainOp."""
+    _fields_ = [("linear", ctypes.c_void_p), ("ff_dim", ctypes.c_int64), ("x_bf16", ctypes.c_void_p),
+                ("y_bf16", ctypes.c_void_p), ("residual_bf16", ctypes.c_void_p),
+                ("norm", ctypes.POINTER(RmsNorm))]
+
+
 # name -> (restype, argtypes); every symbol include/aila_nf4.h declares
 _VP = ctypes.c_void_p
 _SIGNATURES = {
@@ -116,6 +123,13 @@ _SIGNATURES = {
     "aila_nf4_dequantize_rowmajor": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_expand_absmax": (ctypes.c_int, [_VP, _VP, _VP]),
     "aila_nf4_set_gemv_kernel": (ctypes.c_int, [ctypes.c_int]),
+    "aila_nf4_chain_create": (ctypes.c_int, [_VP, ctypes.POINTER(ChainOp), ctypes.c_int,
+                                             ctypes.POINTER(_VP)]),
+    "aila_nf4_chain_destroy": (None, [_VP]),
+    "aila_nf4_chain_length": (ctypes.c_int, [_VP]),
+    "aila_nf4_chain_run": (ctypes.c_int, [_VP, _VP]),
+    "aila_nf4_chain_run_host": (ctypes.c_int, [_VP, _VP, _VP, _VP]),
+    "aila_nf4_scratch_set_wait_limit": (ctypes.c_int, [_VP, ctypes.c_int64]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

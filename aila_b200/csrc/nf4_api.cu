@@ -19,7 +19,7 @@ int gemv_kernel_choice() {
     if (g_gemv_kernel < 0) {
         const char* e = std::getenv("AILA_NF4_GEMV_KERNEL");
         int v = e ? std::atoi(e) : 0;
-        g_gemv_kernel = (v >= 0 && v <= 2) ? v : 0;
+        g_gemv_kernel = (v >= 0 && v <= 3) ? v : 0;
     }
     return g_gemv_kernel;
 }
@@ -356,6 +356,15 @@ AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void*
                          const nf4::NormInput* norm = nullptr) {
     const int choice = gemv_kernel_choice();
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    // the chained kernel, as a one-operation launch, is the default single-row route
+    const bool chain_ok = m_rows == 1 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 &&
+                          nf4::gemv_chain_supported(*l, ff_pair, *sc) &&
+                          !(norm && l->K > 11520);
+    if (choice == 3 && !chain_ok)
+        return nf4::fail(AILA_NF4_ERR_UNSUPPORTED,
+                         "chained decode kernel was forced but does not take this call");
+    if ((choice == 0 || choice == 3) && chain_ok)
+        return nf4::launch_gemv_chain_single(*l, *sc, x, y, residual, ff_pair, norm, s);
     bool stream_ok = aligned && nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
     if (choice == 1) stream_ok = false;
     if (choice == 2 && !stream_ok)
@@ -625,6 +634,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_scratch_create(int device, AilaNf4Scratch** 
         return bail(e, "cudaMalloc(status)");
     if ((e = cudaMemset(sc->d_status, 0, 64)) != cudaSuccess) return bail(e, "cudaMemset(status)");
     AilaNf4Status st = ensure_counters(sc, 1 << 14);
+    if (st == AILA_NF4_OK) st = nf4::ensure_chain_scratch(sc);
     if (st != AILA_NF4_OK) {
         aila_nf4_scratch_destroy(sc);
         return st;
@@ -643,6 +653,7 @@ AILA_NF4_API void aila_nf4_scratch_destroy(AilaNf4Scratch* sc) {
     cudaFree(sc->d_weight);
     cudaFree(sc->d_io_in);
     cudaFree(sc->d_io_out);
+    cudaFree(sc->d_chain_ctrl);
     delete sc;
 }
 
@@ -674,6 +685,8 @@ AILA_NF4_API AilaNf4Status aila_nf4_scratch_check(AilaNf4Scratch* sc, void* stre
     NF4_CUDA(cudaStreamSynchronize(s));
     if (host != 0) {
         NF4_CUDA(cudaMemsetAsync(sc->d_status, 0, sizeof(int), s));
+        // the chained kernel's "somebody gave up" word: later launches start clean
+        if (sc->d_chain_ctrl) NF4_CUDA(cudaMemsetAsync(sc->d_chain_ctrl + 2, 0, sizeof(unsigned), s));
         NF4_CUDA(cudaStreamSynchronize(s));
         return nf4::fail(AILA_NF4_ERR_KERNEL_TIMEOUT,
                          "a bounded device-side wait expired (code " + std::to_string(host) + ")");
@@ -901,9 +914,16 @@ AILA_NF4_API AilaNf4Status aila_nf4_expand_absmax(const AilaNf4Linear* l, void* 
     return AILA_NF4_OK;
 }
 
+AILA_NF4_API AilaNf4Status aila_nf4_scratch_set_wait_limit(AilaNf4Scratch* sc, int64_t sm_cycles) {
+    if (!sc) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "scratch handle is NULL");
+    if (sm_cycles <= 0) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "wait limit must be positive");
+    sc->wait_limit_cycles = (long long)sm_cycles;
+    return AILA_NF4_OK;
+}
+
 AILA_NF4_API AilaNf4Status aila_nf4_set_gemv_kernel(int which) {
-    if (which < 0 || which > 2)
-        return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "gemv kernel selector must be 0, 1 or 2");
+    if (which < 0 || which > 3)
+        return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "gemv kernel selector must be 0, 1, 2 or 3");
     g_gemv_kernel = which;
     return AILA_NF4_OK;
 }

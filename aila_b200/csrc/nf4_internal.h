@@ -56,6 +56,14 @@ struct AilaNf4Scratch {
     void* d_io_out = nullptr;
     size_t io_out_bytes = 0;
     int sm_count = 0;
+    // exchange space of the chained decode kernel (one allocation, d_chain_ctrl is its base):
+    // control words {epoch, CTAs done, abort}, one token per CTA, partial-sum words, x words
+    unsigned* d_chain_ctrl = nullptr;
+    unsigned long long* d_chain_tok = nullptr;
+    unsigned long long* d_chain_p = nullptr;
+    unsigned long long* d_chain_x = nullptr;
+    long long chain_xwords = 0;
+    long long wait_limit_cycles = 2000000000LL;  // bound of every device-side wait of the chained kernel
 };
 
 namespace nf4 {
@@ -132,6 +140,15 @@ bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count
 int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);  // 0: shape not taken
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);
+
+// nf4_chain.cu --------------------------------------------------------------------------
+// The chained decode kernel: one cooperative launch walks a list of linears. A one-operation
+// launch serves aila_nf4_forward and its siblings.
+bool gemv_chain_supported(const AilaNf4Linear& w, int64_t ff_pair, const AilaNf4Scratch& sc);
+AilaNf4Status launch_gemv_chain_single(const AilaNf4Linear& w, AilaNf4Scratch& sc, const void* x,
+                                       void* y, const void* residual, int64_t ff_pair,
+                                       const NormInput* norm, cudaStream_t s);
+AilaNf4Status ensure_chain_scratch(AilaNf4Scratch* sc);
 
 // nf4_peer.cu ---------------------------------------------------------------------------
 // y[n] = bf16(sum over ranks of the tagged words [parity][rank][n] (+ residual[n])), each word

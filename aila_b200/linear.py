@@ -40,6 +40,10 @@ class Bnb4BitLinearScratch:
         """Raises if a bounded wait inside a kernel expired since the last check."""
         _lib.check(_lib.load().aila_nf4_scratch_check(self._h, _stream_ptr(self.device)))
 
+    def set_wait_limit(self, sm_cycles: int) -> None:
+        """Bound (SM clock cycles) of every device-side wait of the chained decode kernel."""
+        _lib.check(_lib.load().aila_nf4_scratch_set_wait_limit(self._h, int(sm_cycles)))
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             _lib.load().aila_nf4_scratch_destroy(self._h)
@@ -397,6 +401,65 @@ class PeerBuffer:
             pass
 
 
+class DecodeChain:
+    """A run of seq_len == 1 linears executed by ONE launch (aila_nf4_chain_*): the calls the
+    reference's decode step makes back to back (Qwen3Bnb4Backend.cpp:400-418). ``ops`` is a list
+    of dicts with keys ``linear`` (Bnb4BitLinear), and optionally ``ff_dim`` (> 0: fused gate|up
+    + SwiGLU), ``x`` (input tensor; omitted = the previous operation's output), ``y`` (output
+    tensor), ``residual`` and ``norm`` = dict(weight=, eps=, add=None, hidden_out=None)."""
+
+    def __init__(self, scratch: Bnb4BitLinearScratch, ops: list[dict]):
+        lib = _lib.load()
+        self.scratch = scratch
+        self.device = scratch.device
+        self._keep = []
+        arr = (_lib.ChainOp * len(ops))()
+        for i, o in enumerate(ops):
+            for k in ("x", "y", "residual"):
+                tns = o.get(k)
+                if tns is not None:
+                    assert tns.dtype == torch.bfloat16 and tns.is_cuda and tns.is_contiguous()
+                    self._keep.append(tns)
+            arr[i].linear = o["linear"]._h
+            arr[i].ff_dim = int(o.get("ff_dim", 0))
+            arr[i].x_bf16 = o["x"].data_ptr() if o.get("x") is not None else None
+            arr[i].y_bf16 = o["y"].data_ptr() if o.get("y") is not None else None
+            arr[i].residual_bf16 = o["residual"].data_ptr() if o.get("residual") is not None else None
+            nd = o.get("norm")
+            if nd is not None:
+                n = Bnb4BitLinear._norm(nd["weight"], nd["eps"], nd.get("add"), nd.get("hidden_out"))
+                self._keep += [n, nd["weight"], nd.get("add"), nd.get("hidden_out")]
+                arr[i].norm = ctypes.pointer(n)
+            self._keep.append(o["linear"])
+        h = ctypes.c_void_p()
+        _lib.check(lib.aila_nf4_chain_create(scratch._h, arr, len(ops), ctypes.byref(h)))
+        self._h = h
+
+    def run(self) -> None:
+        _lib.check(_lib.load().aila_nf4_chain_run(self._h, _stream_ptr(self.device)))
+
+    def run_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """x of the first operation from (pinned) host memory, y of the last back to host memory,
+        one synchronisation."""
+        _lib.check(_lib.load().aila_nf4_chain_run_host(self._h, x_host.data_ptr(), y_host.data_ptr(),
+                                                       _stream_ptr(self.device)))
+
+    def __len__(self) -> int:
+        return int(_lib.load().aila_nf4_chain_length(self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.load().aila_nf4_chain_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def set_gemv_kernel(which: int) -> None:
-    """0 automatic, 1 plain CUDA-core kernel, 2 streaming tensor-core kernel."""
+    """0 automatic, 1 plain CUDA-core kernel, 2 streaming kernel with a shared-memory ring,
+    3 the chained kernel as a one-operation launch."""
     _lib.check(_lib.load().aila_nf4_set_gemv_kernel(which))

@@ -279,6 +279,50 @@ AILA_NF4_API AilaNf4Status aila_add_rms_norm(const void* x_bf16, const void* add
                                              void* normed_out_bf16, int device, void* stream);
 
 /*
+ * A chain of decode (seq_len == 1) linears run by ONE kernel launch. Replaces the sequence of
+ * Bnb4BitLinear::forward / try_forward_decode_gate_up_swiglu calls that the reference's decode
+ * step issues back to back (src/models/Qwen3Bnb4Backend.cpp:400-418: o_proj, fused add+RMSNorm,
+ * gate_up + SwiGLU, down_proj; src/models/Qwen35HybridBnb4Backend.cpp:2140-2197), where every
+ * call is one queue submission. The operations run in list order; operation i may take the
+ * output of operation i-1 as its input (x_bf16 == NULL, or x_bf16 equal to the previous
+ * operation's y_bf16), optionally through the residual add + RMSNorm of AilaNf4RmsNorm. An
+ * operation with an input of its own still starts only after the previous one has finished.
+ * Rules: all linears share their code books (quant_map, nested_quant_map) and the scratch's
+ * device; in_features of a linked operation equals the previous output size; at most 160
+ * operations; in_features <= 49,000 (x lives in shared memory). Buffers named in the list must
+ * stay valid for the life of the chain; an operation must not read, through a pointer of its own,
+ * memory that an earlier operation of the same chain writes (use the link instead).
+ * The launch is cooperative (one thread block per SM, all resident) and every device-side wait is
+ * bounded (aila_nf4_scratch_set_wait_limit); a wait that runs out is reported by
+ * aila_nf4_scratch_check as AILA_NF4_ERR_KERNEL_TIMEOUT. One chain launch at a time per scratch.
+ * Creation is synchronous (load time); aila_nf4_chain_run only enqueues and may be captured in a
+ * CUDA graph.
+ */
+typedef struct AilaNf4Chain AilaNf4Chain;
+typedef struct AilaNf4ChainOp {
+    const AilaNf4Linear* linear;
+    int64_t ff_dim;             /* > 0: fused gate|up linear, output silu(gate) .* up [ff_dim]   */
+    const void* x_bf16;         /* [in_features] device memory; NULL: the previous output        */
+    void* y_bf16;               /* [out] device memory; may be NULL when the next op consumes it */
+    const void* residual_bf16;  /* [out] added before the rounding, or NULL (not with ff_dim)    */
+    const AilaNf4RmsNorm* norm;        /* residual add + RMSNorm in front of the linear, or NULL */
+} AilaNf4ChainOp;
+AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const AilaNf4ChainOp* ops,
+                                                 int n_ops, AilaNf4Chain** out);
+AILA_NF4_API void aila_nf4_chain_destroy(AilaNf4Chain* chain);
+AILA_NF4_API int aila_nf4_chain_length(const AilaNf4Chain* chain);
+AILA_NF4_API AilaNf4Status aila_nf4_chain_run(AilaNf4Chain* chain, void* stream);
+/* Same with HOST buffers at both ends: copies x of the first operation (in_features bf16) to
+ * the device buffer named in the list, runs the chain, copies the last operation's y back and
+ * waits for it. One copy in, one launch, one copy out, one synchronisation for the whole chain. */
+AILA_NF4_API AilaNf4Status aila_nf4_chain_run_host(AilaNf4Chain* chain, const void* x_host_bf16,
+                                                   void* y_host_bf16, void* stream);
+/* Bound, in SM clock cycles, of every device-side wait of the chained decode kernel (default
+ * 2e9, about a second). Takes effect at the next launch. No reference counterpart. */
+AILA_NF4_API AilaNf4Status aila_nf4_scratch_set_wait_limit(AilaNf4Scratch* scratch,
+                                                           int64_t sm_cycles);
+
+/*
  * Dense bf16 linear y = x W^T (+ residual), W bf16 [out_features][in_features]: the unquantised
  * projection next to the NF4 linears (the lm_head). Replaces class Linear for this use
  * (reference src/ops/Ops.hpp:16-31: init(ctx, weight, in_features, out_features) and
@@ -357,7 +401,8 @@ AILA_NF4_API AilaNf4Status aila_nf4_expand_absmax(const AilaNf4Linear* linear, v
 /*
  * Kernel selection for the seq_len == 1 route, for A/B measurement: 0 = automatic,
  * 1 = plain CUDA-core kernel (fp32 weights, exactly the reference's arithmetic up to
- * summation order), 2 = streaming tensor-core kernel. Process-wide; also settable with the
+ * summation order), 2 = streaming tensor-core kernel with a shared-memory ring, 3 = the chained
+ * kernel as a one-operation launch (what automatic picks when it takes the call). Process-wide; also settable with the
  * environment variable AILA_NF4_GEMV_KERNEL read at first use.
  */
 AILA_NF4_API AilaNf4Status aila_nf4_set_gemv_kernel(int which);

@@ -87,7 +87,7 @@ GEMV_SHAPES = [(16, 64), (40, 128), (48, 448), (100, 512), (256, 2560), (2560, 9
                (9728, 2560), (6144, 2560), (2560, 4096)]
 
 
-@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("kernel", [1, 2, 3])
 @pytest.mark.parametrize("N,K", GEMV_SHAPES)
 def test_gemv(nf4, oracle, scratch, kernel, N, K):
     w = make_weight(1000 + N + K, N, K)
@@ -129,7 +129,7 @@ def test_gemv_non_nested(nf4, oracle, scratch):
     w = make_weight(41, N, K, 64, nested=False)
     l = _lin(nf4, w)
     x = _act(42, 1, K)
-    for kernel in (1, 2):
+    for kernel in (1, 2, 3):
         y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
         nf4.set_gemv_kernel(kernel)
         try:
@@ -187,7 +187,7 @@ def test_fused_rows_rejects_mismatch(nf4):
     assert "2 to 4" in f.last_error
 
 
-@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("kernel", [1, 2, 3])
 @pytest.mark.parametrize("ff,K", [(64, 512), (1216, 2560), (9728, 2560)])
 def test_gate_up_swiglu_decode(nf4, oracle, scratch, kernel, ff, K):
     ws = [make_weight(2000 + ff, ff, K), make_weight(2001 + ff, ff, K)]
