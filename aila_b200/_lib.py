@@ -94,6 +94,7 @@ _SIGNATURES = {
     "aila_nf4_forward_gate_up_swiglu_host": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int,
                                                             ctypes.c_int64, _VP]),
     "aila_nf4_forward_decode_static": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP]),
+    "aila_nf4_static_check": (ctypes.c_int, [ctypes.c_int, _VP]),
     "aila_nf4_peerbuf_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                ctypes.c_int64, ctypes.POINTER(_VP)]),
     "aila_nf4_peerbuf_export": (ctypes.c_int, [_VP, _VP]),

@@ -356,20 +356,21 @@ AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void*
                          const nf4::NormInput* norm = nullptr) {
     const int choice = gemv_kernel_choice();
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-    // the chained kernel, as a one-operation launch, is the default single-row route
+    // One operation per launch: the ring kernel starts faster than the chained kernel (which pays
+    // for a cooperative launch and builds for a whole list), so it is the first choice here; the
+    // chained kernel as a one-operation launch takes what the ring kernel does not.
     const bool chain_ok = m_rows == 1 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 &&
-                          nf4::gemv_chain_supported(*l, ff_pair, *sc) &&
-                          !(norm && l->K > 11520);
+                          nf4::gemv_chain_supported(*l, ff_pair, *sc) && !(norm && l->K > 11520);
+    bool stream_ok = aligned && nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
+    if (choice == 1 || choice == 3) stream_ok = false;
     if (choice == 3 && !chain_ok)
         return nf4::fail(AILA_NF4_ERR_UNSUPPORTED,
                          "chained decode kernel was forced but does not take this call");
-    if ((choice == 0 || choice == 3) && chain_ok)
-        return nf4::launch_gemv_chain_single(*l, *sc, x, y, residual, ff_pair, norm, s);
-    bool stream_ok = aligned && nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
-    if (choice == 1) stream_ok = false;
     if (choice == 2 && !stream_ok)
         return nf4::fail(AILA_NF4_ERR_UNSUPPORTED,
                          "streaming decode kernel was forced but does not take this shape");
+    if (!stream_ok && chain_ok && choice != 1 && choice != 2)
+        return nf4::launch_gemv_chain_single(*l, *sc, x, y, residual, ff_pair, norm, s);
     if (stream_ok) {
         const size_t tiles = (size_t)(ff_pair > 0 ? ff_pair / nf4::kTileRows : l->RT);
         AilaNf4Status st = ensure_counters(sc, tiles);
@@ -883,6 +884,12 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_static(const AilaNf4Linear* l
     DeviceGuard guard(l->device);
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     return nf4::launch_gemv_stream_static(*l, x, y, residual, static_cast<cudaStream_t>(stream));
+}
+
+AILA_NF4_API AilaNf4Status aila_nf4_static_check(int device, void* stream) {
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
+    return nf4::check_gemv_stream_static(static_cast<cudaStream_t>(stream));
 }
 
 AILA_NF4_API AilaNf4Status aila_nf4_dequantize(const AilaNf4Linear* l, void* out_kn, void* stream) {

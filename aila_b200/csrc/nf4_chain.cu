@@ -98,9 +98,9 @@ struct ChainParams {
     int n_ops;
     const float* qmap;            // [16]
     const float* nmap;            // [256] or NULL
-    unsigned long long* xbuf;     // [4][xwords] exchange words {bf16 pair, tag}, slot = tag & 3
+    unsigned long long* xbuf;     // [8][xwords] exchange words {bf16 pair, tag}, slot = tag & 7
     long long xwords;
-    unsigned long long* pbuf;     // [4][grid][32] partial sums {f32, tag}, slot = tag & 3
+    unsigned long long* pbuf;     // [8][grid][32] partial sums {f32, tag}, slot = tag & 7
     unsigned long long* tokens;   // [kChainMaxGrid] {0, tag of the last operation whose finalize phase the CTA left}
     unsigned* ctrl;               // {epoch, CTAs done, abort}
     int* status;
@@ -194,6 +194,7 @@ void make_fast_div(uint32_t d, uint32_t* m, int* s) {
     *m = (uint32_t)(((1ull << *s) + d - 1) / d);
 }
 
+// First work item of CTA c: floor(total * c / grid) in 32-bit arithmetic, with total = q*grid + r.
 __device__ __forceinline__ int slice_begin(const ChainOpDev& op, int c) {
     return op.slice_q * c + fast_div(op.slice_r * c, op.div_g_m, op.div_g_s);
 }
@@ -259,7 +260,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
     const uint32_t a_slots = a_nmap + 1024;        // [kRing][warp][2][32] floats
     const uint32_t a_seg = a_slots + kRing * kChainWarps * 2 * 32 * 4;  // [kRing][warp][2] pair whose sums the slot holds, or -1
     const uint32_t a_xbar = a_seg + kRing * kChainWarps * 2 * 4;        // [2] mbarriers: x buffer granted / filled
-    const uint32_t a_desc = a_xbar + 16;
+    const uint32_t a_rflag = a_xbar + 16;               // [8] tag of the operation that may write exchange slot tag & 7
+    const uint32_t a_desc = a_rflag + 32;
     const int n_ops = p.n_ops;
     const int xbufs = p.x_buffers;
     if (base > 2048u || a_desc + (uint32_t)n_ops * kDescBytes > kLutAddr ||
@@ -295,6 +297,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                     (uint32_t)f32_to_bf16_bits(q_hi) | ((uint32_t)f32_to_bf16_bits(q_lo) << 16));
             sts_f32(a_nmap + 4u * tid, nm);
         }
+        if (tid < 8) sts_u32(a_rflag + 4u * tid, 0u);
         if (tid == 0) {
             *abort_flag = 0;
             mbar_init(reinterpret_cast<uint64_t*>(gen + a_xbar), 32);  // every lane of the granting warp arrives
@@ -399,17 +402,19 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         if (o.publish) {
             const uint32_t hi = __shfl_down_sync(0xffffffffu, bits, 1);
             if (valid && !(row & 1))
-                st_relaxed_u64(p.xbuf + (size_t)(tg & 3u) * (size_t)p.xwords + (n >> 1),
+                st_relaxed_u64(p.xbuf + (size_t)(tg & 7u) * (size_t)p.xwords + (n >> 1),
                                ((unsigned long long)tg << 32) | (unsigned long long)(bits | (hi << 16)));
         }
     };
-    // Exchange slots (x words, partial sums) are used round-robin over four operations. Before a
-    // warp writes slot tag & 3 every CTA must have left the finalize phase of the operation three
-    // back (it has then read all words of the one four back). Tokens only grow.
+    // Exchange slots (x words, partial sums) are used round-robin over eight operations. Before a
+    // warp writes slot tag & 7 every CTA must have left the finalize phase of the operation seven
+    // back (it has then read all words of the one eight back). Tokens only grow. The finalizer
+    // warp checks ahead of time and leaves the operation's tag in a shared-memory flag; a warp
+    // that does not find it there reads the tokens itself.
     auto ring_ok = [&](int oj) {
-        if (oj < 3) return true;
-        const unsigned need = tag_of(oj) - 3u;
-        // all tokens in one round trip; only a token that lags is waited for
+        if (oj < 7) return true;
+        if (lds_u32(a_rflag + 4u * (uint32_t)(oj & 7)) == tag_of(oj)) return true;
+        const unsigned need = tag_of(oj) - 7u;
         unsigned long long tk[kChainMaxGrid / 32];
 #pragma unroll
         for (int i = 0; i < kChainMaxGrid / 32; ++i) {
@@ -432,135 +437,145 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         // finalizer warp: finishes the pairs of each operation while the consumers run ahead
         // =====================================================================================
         for (int oj = 0; oj < min(xbufs, n_ops); ++oj) x_grant(oj, false);  // the first buffers are free
+        int flag_next = 7;  // first operation whose exchange slot has not been cleared for writing yet
         for (int oi = 0; oi < n_ops; ++oi) {
             const ChainOpDev& op = desc(oi);
             const unsigned tag = tag_of(oi);
-            bar_sync(kBarDone + (oi & (kRing - 1)), kChainThreads);
+            const int r = oi & (kRing - 1);
+            // exchange slots that may be written by now: operation oj needs every token >= tag(oj) - 7
+            if (flag_next < n_ops && flag_next <= oi + 3) {
+                int behind = 0x7fffffff;  // tokens relative to the first operation of this launch
+                unsigned long long tk[kChainMaxGrid / 32];  // (all loads in flight together)
+#pragma unroll
+                for (int i = 0; i < kChainMaxGrid / 32; ++i) {
+                    tk[i] = ~0ull >> 1;
+                    if (lane + 32 * i < G) tk[i] = ld_relaxed_u64(p.tokens + lane + 32 * i);
+                }
+#pragma unroll
+                for (int i = 0; i < kChainMaxGrid / 32; ++i)
+                    if (lane + 32 * i < G) behind = min(behind, (int)((unsigned)(tk[i] >> 32) - tag_of(0)));
+#pragma unroll
+                for (int sh = 16; sh > 0; sh >>= 1) behind = min(behind, __shfl_xor_sync(0xffffffffu, behind, sh));
+                while (flag_next < n_ops && behind >= flag_next - 7) {
+                    if (lane == 0) sts_u32(a_rflag + 4u * (uint32_t)(flag_next & 7), tag_of(flag_next));
+                    ++flag_next;
+                }
+            }
+            bar_sync(kBarDone + r, kChainThreads);
             const bool aborted = is_aborted();
             // every consumer is through with operation oi: its x buffer goes to operation oi + xbufs
             if (oi + xbufs < n_ops) x_grant(oi + xbufs, aborted);
-            const int KB = op.KB;
+            // Add up the consumers' slots pair by pair, in slot order (warp 0 slot 0, warp 0 slot 1,
+            // warp 1 slot 0, ...; the pairs in them never decrease), and finish every pair.
             const int i0 = slice_begin(op, c), i1 = slice_begin(op, c + 1);
-            const uint32_t slots = a_slots + (uint32_t)(oi & (kRing - 1)) * (kChainWarps * 256u);
-            const uint32_t segs = a_seg + (uint32_t)(oi & (kRing - 1)) * (kChainWarps * 8u);
             if (!aborted && i1 > i0) {
-                const int p_first = fast_div(i0, op.div_kb_m, op.div_kb_s);
-                const int p_last = fast_div(i1 - 1, op.div_kb_m, op.div_kb_s);
-                // the slots that hold sums of a pair, added in warp order
-                const int seg0 = (int)lds_u32(segs + (uint32_t)(min(lane, kConsumerWarps - 1) * 2) * 4u);
-                const int seg1 = (int)lds_u32(segs + (uint32_t)(min(lane, kConsumerWarps - 1) * 2 + 1) * 4u);
+                const int KB = op.KB;
+                const uint32_t slots = a_slots + (uint32_t)r * (kChainWarps * 256u);
+                const uint32_t segs = a_seg + (uint32_t)r * (kChainWarps * 8u);
+                constexpr int NQ = kConsumerWarps * 2;
+                // all tags first (the same word for every lane): which slots hold sums, where pairs start
+                int tq[NQ];
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) tq[q] = (int)lds_u32(segs + 4u * (uint32_t)q);
+                unsigned valid = 0u, first = 0u;
+                {
+                    int cur = -1;
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q)
+                        if (tq[q] >= 0) {
+                            valid |= 1u << q;
+                            if (tq[q] != cur) first |= 1u << q;
+                            cur = tq[q];
+                        }
+                }
                 // what the epilogue needs, read from the descriptor once
                 const int e_swiglu = op.swiglu, e_n_out = op.n_out, e_pair_offset = op.pair_offset;
                 const int e_n_tiles = op.n_tiles, e_publish = op.publish;
                 uint16_t* const e_y = op.y;
                 const uint16_t* const e_res = op.residual;
-                unsigned long long* const e_xw = p.xbuf + (size_t)(tag & 3u) * (size_t)p.xwords;
+                unsigned long long* const e_xw = p.xbuf + (size_t)(tag & 7u) * (size_t)p.xwords;
                 const int row = lane & 15;
                 const bool hl = lane < 16;
-                auto finish = [&](int pr, float v) {
+                auto finish = [&](int pr, float val) {
                     int n;
-                    bool valid;
+                    bool ok_row;
                     float out;
                     if (e_swiglu) {
-                        const float up = __shfl_down_sync(0xffffffffu, v, 16);
+                        const float up = __shfl_down_sync(0xffffffffu, val, 16);
                         n = pr * kTileRows + row;
-                        valid = hl && n < e_n_out;
-                        out = __fdividef(v, 1.0f + __expf(-v)) * up;
+                        ok_row = hl && n < e_n_out;
+                        out = __fdividef(val, 1.0f + __expf(-val)) * up;
                     } else {
                         const int tile = pr + (hl ? 0 : e_pair_offset);
                         n = tile * kTileRows + row;
-                        valid = tile < e_n_tiles && n < e_n_out;
-                        out = v;
-                        if (valid && e_res) out += bf16_bits_to_f32(__ldcg(e_res + n));
+                        ok_row = tile < e_n_tiles && n < e_n_out;
+                        out = val;
+                        if (ok_row && e_res) out += bf16_bits_to_f32(__ldcg(e_res + n));
                     }
                     const uint32_t bits = f32_to_bf16_bits(out);
-                    if (valid && e_y) e_y[n] = (uint16_t)bits;
+                    if (ok_row && e_y) e_y[n] = (uint16_t)bits;
                     if (e_publish) {
-                        const uint32_t hi = __shfl_down_sync(0xffffffffu, bits, 1);
-                        if (valid && !(row & 1))
+                        const uint32_t hi16 = __shfl_down_sync(0xffffffffu, bits, 1);
+                        if (ok_row && !(row & 1))
                             st_relaxed_u64(e_xw + (n >> 1),
-                                           ((unsigned long long)tag << 32) | (unsigned long long)(bits | (hi << 16)));
+                                           ((unsigned long long)tag << 32) | (unsigned long long)(bits | (hi16 << 16)));
                     }
                 };
                 int checked = 0;  // 1: the exchange slots of this operation may be written
-                // Four pairs at a time, so that the shared-memory loads of one pair do not wait for
-                // the previous pair's arithmetic (this warp shares the load/store unit with fifteen
-                // busy consumer warps: every access is slow, but they overlap).
-                constexpr int NB = 4, NS = 6;
-                for (int pb = p_first; pb <= p_last && checked >= 0; pb += NB) {
-                    unsigned mk[NB];
-                    float v[NB];
-                    float part[NB][NS];
+                while (first != 0u && checked >= 0) {
+                    const int q0 = __ffs((int)first) - 1;
+                    first &= first - 1u;
+                    // the pair's slots: the valid ones from q0 up to the next pair's first slot
+                    const unsigned upto = first != 0u ? ((1u << (__ffs((int)first) - 1)) - 1u) : 0xffffffffu;
+                    unsigned run = valid & upto & ~((1u << q0) - 1u);
+                    // up to six slots with independent loads, any further ones after them, in slot order
+                    float part[6];
 #pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        const int pr = pb + b;
-                        const unsigned low = (1u << kConsumerWarps) - 1u;
-                        const unsigned m0 = __ballot_sync(0xffffffffu, seg0 == pr) & low;
-                        const unsigned m1 = __ballot_sync(0xffffffffu, seg1 == pr) & low;
-                        // (a warp's two slots never hold the same pair: bit w of m0 | m1 << 16 names one slot)
-                        mk[b] = pr <= p_last ? (m0 | (m1 << 16)) : 0u;  // 0: finished inside one warp's range already
-                    }
-#pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        unsigned m = mk[b];
-#pragma unroll
-                        for (int q = 0; q < NS; ++q) {
-                            part[b][q] = 0.0f;
-                            if (m != 0u) {
-                                const int bit = __ffs((int)m) - 1;
-                                part[b][q] = lds_f32(slots + (uint32_t)(bit & 15) * 256u + (uint32_t)(bit >> 4) * 128u + 4u * lane);
-                                m &= m - 1u;
-                            }
+                    for (int k = 0; k < 6; ++k) {
+                        part[k] = 0.0f;
+                        if (run != 0u) {
+                            const int q = __ffs((int)run) - 1;
+                            run &= run - 1u;
+                            part[k] = lds_f32(slots + (uint32_t)q * 128u + 4u * lane);
                         }
                     }
+                    float sum = part[0];
 #pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        float sum = 0.0f;
+                    for (int k = 1; k < 6; ++k) sum += part[k];  // (absent slots add +0)
+                    for (; run != 0u; run &= run - 1u)
+                        sum += lds_f32(slots + (uint32_t)(__ffs((int)run) - 1) * 128u + 4u * lane);
+                    int pr = 0;
 #pragma unroll
-                        for (int q = 0; q < NS; ++q) sum += part[b][q];  // (absent slots add +0)
-                        unsigned m = mk[b];
-#pragma unroll
-                        for (int q = 0; q < NS; ++q) m &= m - 1u;
-                        for (; m != 0u; m &= m - 1u) {  // more than NS slots: the rest one by one
-                            const int bit = __ffs((int)m) - 1;
-                            sum += lds_f32(slots + (uint32_t)(bit & 15) * 256u + (uint32_t)(bit >> 4) * 128u + 4u * lane);
+                    for (int q = 0; q < NQ; ++q)
+                        if (q == q0) pr = tq[q];
+                    const int t0 = pr * KB, t1 = t0 + KB;
+                    const int lo = max(i0, t0), hi = min(i1, t1);
+                    const bool writes_ring = e_publish || hi - lo != KB;
+                    if (writes_ring && checked == 0) checked = ring_ok(oi) ? 1 : -1;
+                    if (writes_ring && checked < 0) break;
+                    if (hi - lo == KB) {
+                        finish(pr, sum);
+                    } else if (lo == t0) {
+                        // this CTA holds the pair's first item: add the later CTAs' sums in CTA order
+                        int cover = hi - lo;
+                        bool got = true;
+                        for (int cc = c + 1; cc < G && cover < KB && got; ++cc) {
+                            const int j0 = slice_begin(op, cc), j1 = slice_begin(op, cc + 1);
+                            const int s1 = min(j1, t1);
+                            if (s1 <= j0) continue;
+                            unsigned long long q;
+                            got = poll_word(p.pbuf + ((size_t)(tag & 7u) * G + cc) * 32 + lane, tag, false,
+                                            p.spin_limit, g_abort, q);
+                            sum += __uint_as_float((unsigned)q);
+                            cover += s1 - j0;
                         }
-                        v[b] = sum;
-                    }
-#pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        if (mk[b] == 0u || checked < 0) continue;
-                        const int pr = pb + b;
-                        const int t0 = pr * KB, t1 = t0 + KB;
-                        const int lo = max(i0, t0), hi = min(i1, t1);
-                        const bool writes_ring = e_publish || hi - lo != KB;
-                        if (writes_ring && checked == 0) checked = ring_ok(oi) ? 1 : -1;
-                        if (writes_ring && checked < 0) continue;
-                        if (hi - lo == KB) {
-                            finish(pr, v[b]);
-                        } else if (lo == t0) {
-                            // this CTA holds the pair's first item: add the later CTAs' sums in CTA order
-                            float sum = v[b];
-                            int cover = hi - lo;
-                            bool got = true;
-                            for (int cc = c + 1; cc < G && cover < KB && got; ++cc) {
-                                const int j0 = slice_begin(op, cc), j1 = slice_begin(op, cc + 1);
-                                const int s1 = min(j1, t1);
-                                if (s1 <= j0) continue;
-                                unsigned long long q;
-                                got = poll_word(p.pbuf + ((size_t)(tag & 3u) * G + cc) * 32 + lane, tag, false,
-                                                p.spin_limit, g_abort, q);
-                                sum += __uint_as_float((unsigned)q);
-                                cover += s1 - j0;
-                            }
-                            if (__all_sync(0xffffffffu, got))
-                                finish(pr, sum);
-                            else
-                                checked = -1;
-                        } else {
-                            st_relaxed_u64(p.pbuf + ((size_t)(tag & 3u) * G + c) * 32 + lane,
-                                           ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v[b]));
-                        }
+                        if (__all_sync(0xffffffffu, got))
+                            finish(pr, sum);
+                        else
+                            checked = -1;
+                    } else {
+                        st_relaxed_u64(p.pbuf + ((size_t)(tag & 7u) * G + c) * 32 + lane,
+                                       ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(sum));
                     }
                 }
                 if (checked < 0 && lane == 0) give_up(kStatusTimeoutFull);
@@ -568,8 +583,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             // this CTA has left the finalize phase of operation oi
             __syncwarp();
             if (lane == 0) st_relaxed_u64(p.tokens + c, (unsigned long long)tag << 32);
-            // these slots are free for operation oi + kRing
-            if (oi + kRing < n_ops) bar_arrive(kBarGo + (oi & (kRing - 1)), kChainThreads);
+            // the slots of this ring position are free for operation oi + kRing
+            if (oi + kRing < n_ops) bar_arrive(kBarGo + r, kChainThreads);
         }
         // ---- the CTA that finishes last advances the epoch (every CTA has read it by then) ----
         if (lane == 0) {
@@ -727,7 +742,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         if (stage) {
             const int n8 = o.K >> 2;  // 8-byte chunks of four elements
             const unsigned want = tg - 1u;  // the previous operation's words
-            const unsigned long long* xw = p.xbuf + (size_t)(want & 3u) * (size_t)p.xwords;
+            const unsigned long long* xw = p.xbuf + (size_t)(want & 7u) * (size_t)p.xwords;
             const uint2* xg = reinterpret_cast<const uint2*>(o.x_ext);
             // fetches up to kXBatch chunks of this thread, all loads issued before the first wait
             auto fetch = [&](int q_first, uint2 (&xv)[kXBatch]) {
@@ -946,16 +961,20 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 if (u < n) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
+                        // all sixteen table addresses first (one PRMT each: the byte goes into bits
+                        // [8,16) of the lane's base address), then the sixteen loads
                         uint32_t a[16];
                         const uint2 l = W[h][u][0], up = W[h][u][1];
-                        a[0] = lut_pair<0>(l.x, lane_base);   a[1] = lut_pair<0>(up.x, lane_base);
-                        a[2] = lut_pair<1>(l.x, lane_base);   a[3] = lut_pair<1>(up.x, lane_base);
-                        a[4] = lut_pair<2>(l.x, lane_base);   a[5] = lut_pair<2>(up.x, lane_base);
-                        a[6] = lut_pair<3>(l.x, lane_base);   a[7] = lut_pair<3>(up.x, lane_base);
-                        a[8] = lut_pair<0>(l.y, lane_base);   a[9] = lut_pair<0>(up.y, lane_base);
-                        a[10] = lut_pair<1>(l.y, lane_base);  a[11] = lut_pair<1>(up.y, lane_base);
-                        a[12] = lut_pair<2>(l.y, lane_base);  a[13] = lut_pair<2>(up.y, lane_base);
-                        a[14] = lut_pair<3>(l.y, lane_base);  a[15] = lut_pair<3>(up.y, lane_base);
+                        a[0] = __byte_perm(l.x, lane_base, 0x7604);   a[1] = __byte_perm(up.x, lane_base, 0x7604);
+                        a[2] = __byte_perm(l.x, lane_base, 0x7614);   a[3] = __byte_perm(up.x, lane_base, 0x7614);
+                        a[4] = __byte_perm(l.x, lane_base, 0x7624);   a[5] = __byte_perm(up.x, lane_base, 0x7624);
+                        a[6] = __byte_perm(l.x, lane_base, 0x7634);   a[7] = __byte_perm(up.x, lane_base, 0x7634);
+                        a[8] = __byte_perm(l.y, lane_base, 0x7604);   a[9] = __byte_perm(up.y, lane_base, 0x7604);
+                        a[10] = __byte_perm(l.y, lane_base, 0x7614);  a[11] = __byte_perm(up.y, lane_base, 0x7614);
+                        a[12] = __byte_perm(l.y, lane_base, 0x7624);  a[13] = __byte_perm(up.y, lane_base, 0x7624);
+                        a[14] = __byte_perm(l.y, lane_base, 0x7634);  a[15] = __byte_perm(up.y, lane_base, 0x7634);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) a[i] = lds_u32(a[i]);
                         // the registers of this unit are free: fetch the same unit of the next step
                         if (u < ld_n) load_half(h, u, h == 0 ? pl0 : pl1, ld_stride);
                         float d[4];
@@ -975,6 +994,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             if (ld_n > 0) prepare_scales(cross ? desc(oi + 1) : op, cross ? oi + 1 : oi, ld_pair, ld_kb0, ld_n, pl0, pl1);
             // leaving the pair: reduce over t, hand the 32 row sums over
             if (n_n == 0 || pair_n != pair) {
+
                 float v[2][2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
@@ -1122,6 +1142,7 @@ void chain_params_from_scratch(ChainParams* p, const AilaNf4Scratch& sc) {
     p->ctrl = sc.d_chain_ctrl;
     p->status = sc.d_status;
     p->spin_limit = sc.wait_limit_cycles;
+
 }
 
 }  // namespace
@@ -1166,11 +1187,12 @@ AilaNf4Status launch_gemv_chain_single(const AilaNf4Linear& w, AilaNf4Scratch& s
 AilaNf4Status ensure_chain_scratch(AilaNf4Scratch* sc) {
     if (sc->d_chain_x) return AILA_NF4_OK;
     const size_t xwords = 32768;  // in_features up to 65536
-    const size_t ctrl_b = 256, tok_b = (size_t)kChainMaxGrid * 8, p_b = (size_t)4 * kChainMaxGrid * 32 * 8;
-    const size_t x_b = 4 * xwords * 8;
+    const size_t ctrl_b = 256, tok_b = (size_t)kChainMaxGrid * 8, p_b = (size_t)8 * kChainMaxGrid * 32 * 8;
+    const size_t x_b = 8 * xwords * 8;
     uint8_t* base = nullptr;
     NF4_CUDA(cudaMalloc(reinterpret_cast<void**>(&base), ctrl_b + tok_b + p_b + x_b));
     NF4_CUDA(cudaMemset(base, 0, ctrl_b + tok_b + p_b + x_b));
+
     sc->d_chain_ctrl = reinterpret_cast<unsigned*>(base);
     sc->d_chain_tok = reinterpret_cast<unsigned long long*>(base + ctrl_b);
     sc->d_chain_p = reinterpret_cast<unsigned long long*>(base + ctrl_b + tok_b);

@@ -465,22 +465,6 @@ AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const v
         p.n_tiles = (int)((N + p.BN - 1) / p.BN);
         p.n_out = (int)N;
     }
-    if (const char* e = std::getenv("AILA_NF4_GEMM_MTILE")) {  // measurement override: 1 or 2
-        const int f = std::atoi(e);
-        if ((f == 1 || f == 2) && !(f == 2 && M <= BM)) p.mtile = f;
-    }
-    if (const char* e = std::getenv("AILA_NF4_GEMM_BN")) {  // measurement override: columns per tile
-        const int bn = std::atoi(e);
-        if (bn >= 16 && bn % 16 == 0) {
-            if (swiglu_ff > 0 && bn <= kMaxBN / 2) {
-                p.BN = 2 * bn;
-                p.n_tiles = (int)((swiglu_ff + bn - 1) / bn);
-            } else if (swiglu_ff == 0 && bn <= kMaxBN) {
-                p.BN = bn;
-                p.n_tiles = (int)((N + bn - 1) / bn);
-            }
-        }
-    }
     p.m_tiles = (M + BM * p.mtile - 1) / (BM * p.mtile);
     p.stages = p.mtile == 2 ? 3 : 4;
     // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4

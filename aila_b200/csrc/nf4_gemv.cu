@@ -97,24 +97,15 @@ gemv_simple_kernel(const uint8_t* __restrict__ units, const float* __restrict__ 
 // ------------------------------------------------------------------------------------------
 // gemv_stream
 // ------------------------------------------------------------------------------------------
-#ifndef NF4_W
-#define NF4_W 16
-#endif
-#ifndef NF4_IPW
-#define NF4_IPW 2
-#endif
-constexpr int kConsumerWarps = NF4_W;
+constexpr int kConsumerWarps = 16;
 constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;  // + producer warp + finalizer warp
-constexpr int kItemsPerWarp = NF4_IPW;   // work items a consumer warp takes from one stage
+constexpr int kItemsPerWarp = 2;   // work items a consumer warp takes from one stage
 constexpr int kStageItems = kConsumerWarps * kItemsPerWarp;
 constexpr int kMaxStages = 24;
 constexpr int kMaxLocalTiles = 8;  // row tiles one CTA slice may touch
 constexpr int kMaxGridMult = 8;     // grid <= 8 x SM count
 constexpr int kNabsWindow = 256;    // second-level scales kept in shared memory per half
-#ifndef NF4_EARLY
-#define NF4_EARLY 68
-#endif
-constexpr int kEarlyBytes = NF4_EARLY * 1024;  // ring bytes requested before x has been asked for
+constexpr int kEarlyBytes = 68 * 1024;  // ring bytes requested before x has been asked for
 constexpr int kMaxPeerWorld = 8;
 constexpr int kPairSkewBytes = 64;  // shared-memory distance added between a stage's gate and up units
 
@@ -162,9 +153,6 @@ struct StreamParams {
     unsigned* peer_ctrl;                  // this rank's {epoch, unused, CTAs / reducer blocks done}
     int n_row_tiles;                      // row tiles of the launch (all CTAs)
     int peer_inline;                      // 1: the CTAs also sum the ranks' rows and write y
-#ifdef AILA_NF4_TRACE
-    int trace_idx;
-#endif
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1,
@@ -240,18 +228,6 @@ __device__ __forceinline__ int slice_begin(const StreamParams& p, int c) {
     return p.slice_q * c + fast_div(p.slice_r * c, p.div_g_m, p.div_g_s);
 }
 
-#ifdef AILA_NF4_TRACE
-__device__ unsigned long long g_trace[32][160][96];
-#define NF4_TRACE(slot)                                                              \
-    do {                                                                             \
-        unsigned long long t_;                                                       \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                       \
-        g_trace[p.trace_idx][blockIdx.x % 160][2 * (slot)] = t_;                     \
-        g_trace[p.trace_idx][blockIdx.x % 160][2 * (slot) + 1] = (unsigned long long)clock64(); \
-    } while (0)
-#else
-#define NF4_TRACE(slot) do {} while (0)
-#endif
 
 // BATCH: up to eight rows of x ride in the eight batch columns of the tensor-core tile, so the
 // weights are read and dequantised once for all of them. Differences from the single-row kernel:
@@ -261,15 +237,6 @@ __device__ unsigned long long g_trace[32][160][96];
 // the epilogue writes [rows][out] outputs.
 template <int KIND, bool PAIRED, bool BATCH>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
-#ifdef AILA_NF4_TRACE
-    if (threadIdx.x == 0) {
-        NF4_TRACE(0);
-        g_trace[p.trace_idx][blockIdx.x % 160][30] = 0;
-        unsigned smid_;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
-        g_trace[p.trace_idx][blockIdx.x % 160][94] = smid_;
-    }
-#endif
     constexpr int NP = PAIRED ? 2 : 1;
     constexpr int W = kConsumerWarps;
     constexpr int IPW = kItemsPerWarp;
@@ -599,7 +566,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 
     if (warp == W) {
         // ---------------- producer: sets up the barriers, then one thread keeps the ring full ----
-        if (lane == 0) NF4_TRACE(45);
         if (lane < p.stages) {
             mbar_init(&full[lane], 1);
             mbar_init(&empty[lane], W);
@@ -630,7 +596,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                         break;
                     }
                 }
-                if (g < 8) NF4_TRACE(16 + g);
                 const int v0 = g * kStageItems;
                 const int cnt = min(kStageItems, len - v0);
                 uint8_t* dst = gen + stage_addr(s);
@@ -675,7 +640,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 
     if (warp == W + 1) {
         // ---------------- finalizer: completes row tiles off the consumers' critical path -------
-        if (lane == 0) NF4_TRACE(46);
         asm volatile("bar.sync 2, %0;" ::"n"(kStreamThreads) : "memory");
         // the exchange's epoch is advanced by the previous kernel on the stream
         if (!PAIRED && p.peer_world > 0) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -711,9 +675,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 resolve(pend_li1, pend_old1);
                 finalize_tile(li);
             }
-#ifdef AILA_NF4_TRACE
-            if (lane == 0 && q < 8) NF4_TRACE(32 + q);
-#endif
         }
         if (BATCH) {
             resolve_b(pend_li0, pend_old0);
@@ -723,18 +684,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             resolve(pend_li1, pend_old1);
         }
         if (!PAIRED && !BATCH && p.peer_world > 0 && p.peer_inline) peer_reduce_inline();
-#ifdef AILA_NF4_TRACE
-        if (lane == 0) {
-            unsigned long long t_;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
-            atomicMax(&g_trace[p.trace_idx][blockIdx.x % 160][30], t_);
-        }
-#endif
         return;
     }
 
     // ---------------- consumers ----------------
-    if (tid == 0) NF4_TRACE(40);
     // Second-level scales this CTA can need: one window of consecutive nested_absmax entries per
     // half (gate/plain rows, up rows), copied to shared memory so the absmax chain has no global
     // load in it. A window that does not fit is read from global memory instead. Warp 8 + h
@@ -768,7 +721,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a_slots + 16u * q), "r"(0u) : "memory");
         }
     };
-    if (tid == 0) NF4_TRACE(42);
 
     const int gq = lane >> 2;  // row inside the tile (and row + 8)
     const int t = lane & 3;
@@ -830,7 +782,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     };
     const int kb_step = p.kb_step;  // from one item of this warp to its next
     const int rt_step = p.rt_step;
-    if (tid == 0) NF4_TRACE(43);
 
     // the static tables go to shared memory; after the CTA-wide barrier the lookup table is built
     if (tid < 256) {
@@ -841,9 +792,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     }
     if (KIND == kAbsmaxCodes && wh >= 0 && wh < NP && lane == 0)
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a_info + 8u * wh), "r"(wwin_lo), "r"(wwin_ok ? 1u : 0u) : "memory");
-    if (tid == 0) NF4_TRACE(44);
     asm volatile("bar.sync 2, %0;" ::"n"(kStreamThreads) : "memory");
-    if (tid == 0) NF4_TRACE(1);
     unsigned my_win_lo = 0;
     bool my_win_ok = false;
     if (KIND == kAbsmaxCodes) {
@@ -868,7 +817,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                          : "memory");
         }
     }
-    if (tid == 0) NF4_TRACE(2);
     if (KIND == kAbsmaxCodes && wh >= 0 && wh < NP && wwin_ok) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
@@ -877,7 +825,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     // x is the only input that may come from the previous kernel on the stream: everything above
     // (and the producer's weight copies) ran without waiting for it
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (tid == 0) NF4_TRACE(3);
     // element k = 64*kb + 16*j + 4*t + e goes to fragment order: 16-byte slot (kb*2 + j/2)*4 + t
     // holds tiles j = 2*(j/2) and +1 for lane column t
     const int n8 = p.x_bytes >> 3;
@@ -970,7 +917,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     }
     asm volatile("bar.sync 1, %0;" ::"n"(W * 32) : "memory");
     if (tid == 0) mbar_arrive(x_ready);  // the producer may now fill the rest of the ring
-    if (tid == 0) NF4_TRACE(4);
     if (v < len) refresh();
 
     // every warp signs off every local tile exactly once, after its last contribution to it
@@ -1020,7 +966,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
             failed = true;
             break;
         }
-        if (tid == 0 && g < 8) NF4_TRACE(5 + g);
         const uint32_t ua0 = stage_addr(s) + (uint32_t)warp * unit_stride;
 #pragma unroll
         for (int i = 0; i < IPW; ++i) {
@@ -1161,28 +1106,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         // the stage's shared memory is no longer needed by this warp
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-        if (tid == 0 && g < 8) NF4_TRACE(24 + g);
         if (++s == p.stages) {
             s = 0;
             ph ^= 1u;
         }
-        if (tid == 0 && g < 2) NF4_TRACE(11 + g);
     }
     if (failed) return;
-    if (tid == 0) NF4_TRACE(13);
     // last contribution of this warp, then sign off whatever it never touched
     flush_current();
     cur_li = -1;
     for (int q = 0; q < n_local; ++q)
         if (!((done_mask >> q) & 1u)) sign_off(q);
-#ifdef AILA_NF4_TRACE
-    if (tid == 0) NF4_TRACE(14);
-    if (lane == 0) {
-        unsigned long long t_;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
-        atomicMax(&g_trace[p.trace_idx][blockIdx.x % 160][30], t_);
-    }
-#endif
 }
 
 struct StreamPlan {
@@ -1406,10 +1340,6 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
             p.peer_part[d] = peers->part_base[d];
         }
     }
-#ifdef AILA_NF4_TRACE
-    static int trace_counter = 0;
-    p.trace_idx = trace_counter++ % 32;
-#endif
     const bool batch = m_rows > 1;
     if (w.absmax_kind == kAbsmaxCodes) {
         if (batch)
@@ -1470,10 +1400,30 @@ AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, v
     return AILA_NF4_OK;
 }
 
+// Reads (and clears) the status word of the static work space on the current device: what
+// aila_nf4_scratch_check does for a scratch object. Allocates nothing.
+AilaNf4Status check_gemv_stream_static(cudaStream_t s) {
+    int dev = 0;
+    NF4_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(AILA_NF4_ERR_UNSUPPORTED, "device ordinal above 63");
+    StaticScratchHost host;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        host = g_static_host[dev];
+    }
+    if (!host.ptr) return AILA_NF4_OK;  // no call on this device yet
+    int code = 0;
+    NF4_CUDA(cudaMemcpyAsync(&code, host.ptr->status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    NF4_CUDA(cudaStreamSynchronize(s));
+    if (code != 0) {
+        NF4_CUDA(cudaMemsetAsync(host.ptr->status, 0, sizeof(int), s));
+        NF4_CUDA(cudaStreamSynchronize(s));
+        return fail(AILA_NF4_ERR_KERNEL_TIMEOUT,
+                    "aila_nf4_forward_decode_static: a bounded device-side wait expired (code " +
+                        std::to_string(code) + ")");
+    }
+    return AILA_NF4_OK;
+}
+
 }  // namespace nf4
 
-#ifdef AILA_NF4_TRACE
-extern "C" __attribute__((visibility("default"))) int aila_nf4_debug_trace(void* dst) {
-    return (int)cudaMemcpyFromSymbol(dst, nf4::g_trace, sizeof(nf4::g_trace));
-}
-#endif

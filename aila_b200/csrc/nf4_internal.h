@@ -140,6 +140,7 @@ bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count
 int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);  // 0: shape not taken
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);
+AilaNf4Status check_gemv_stream_static(cudaStream_t s);
 
 // nf4_chain.cu --------------------------------------------------------------------------
 // The chained decode kernel: one cooperative launch walks a list of linears. A one-operation

@@ -459,6 +459,14 @@ class DecodeChain:
             pass
 
 
+def static_check(device: int | torch.device = 0) -> None:
+    """Raises if a bounded wait inside a forward_decode_static kernel expired on this GPU since the
+    last check (aila_nf4_static_check: reads and clears the status word of the built-in work
+    space; allocates nothing)."""
+    dev = torch.device("cuda", device) if isinstance(device, int) else device
+    _lib.check(_lib.load().aila_nf4_static_check(dev.index or 0, _stream_ptr(dev)))
+
+
 def set_gemv_kernel(which: int) -> None:
     """0 automatic, 1 plain CUDA-core kernel, 2 streaming kernel with a shared-memory ring,
     3 the chained kernel as a one-operation launch."""

@@ -1,22 +1,30 @@
 #!/usr/bin/env python
 """Benchmark of the NF4 linear hot path on B200.
 
-Headline workload (BASELINE.json configs[1]): the fused gate+up+SiLU NF4 decode GEMV,
-M = 1, K = 2560, gate and up each 2560 -> 9728, blocksize 64 with double-quantised absmax.
-One STEP = one pass over LAYERS distinct copies of that fused weight (LAYERS * 25.7 MB, far
-larger than the 126 MB L2, so every pass streams from HBM), replayed from a CUDA graph.
+Headline workload: the fused gate+up+SiLU NF4 decode GEMV, M = 1, K = 2560, gate and up each
+2560 -> 9728, blocksize 64 with double-quantised absmax. One STEP = one pass over LAYERS distinct
+copies of that fused weight (LAYERS * 25.7 MB, far larger than the 126 MB L2, so every pass
+streams from HBM), run as ONE chained launch (aila_nf4_chain_run) replayed from a CUDA graph.
 
-  value     whole-job NF4 weight GB/s with inputs resident in HBM (all ranks' bytes / max time)
-  roofline  algorithmic bytes of one launch / average launch time, against the measured HBM peak
-  e2e       the same metric through the host-buffer C-ABI call (H2D x, kernel, D2H y per call)
-  prefill   the second half of BASELINE.json's metric: cfg3 NF4 prefill GEMM pair in TFLOP/s
+  value        whole-job NF4 weight GB/s with inputs resident in HBM (all ranks' bytes / max time)
+  roofline     algorithmic bytes of one operation / average time per operation inside the chained
+               launch, against the measured HBM peak
+  per_call     the same 36 operations as 36 separate C-ABI calls (one launch each)
+  cfg1         36 plain 2560 -> 9728 linears, chained
+  stack        the decode-step linear stack of a 36-layer GQA transformer (144 linears in one
+               chained launch) plus the bf16 lm_head and argmax
+  e2e          the headline metric through the host-buffer C-ABI call (H2D x, chain, D2H y, sync)
+  prefill      the second half of the metric: the M = 2048 NF4 prefill GEMM pair in TFLOP/s
+  tp           the sharded large-model linears (MLP, q, o) at M = 1 and M = 2048
   cpu_baseline / --impl reference: the CPU restatement of the reference kernels on host cores
 
 Usage: python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+       python bench.py --profile-case chain|per_call|batch|dense|prefill   (small runs for ncu)
 """
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import subprocess
@@ -28,15 +36,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-H, FF = 2560, 9728          # cfg2 / cfg3 shapes (Qwen3-4B MLP)
+H, FF = 2560, 9728          # Qwen3-4B MLP shapes
 LAYERS = 36
 PREFILL_M = 2048
 METRIC = "nf4_gemv_weight_bandwidth"
 UNIT = "GB/s"
+WORKLOAD = "cfg2 fused gate+up+SiLU NF4 GEMV, M=1, K=2560, 2x9728 rows, bs64 double-quant"
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
-# capture summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 25750528  # profiles/gemv_stream_cfg2_ncu.md
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per operation of the dominant kernel (one
+# capture of a chained launch, divided by its operations); None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_OP = None
 
 
 def weight_bytes(n: int, k: int) -> int:
@@ -47,6 +56,7 @@ def weight_bytes(n: int, k: int) -> int:
 
 GATE_UP_WEIGHT_BYTES = 2 * weight_bytes(FF, H)                 # 25,694,080
 GATE_UP_ALGO_BYTES = GATE_UP_WEIGHT_BYTES + 2 * H + 2 * FF     # + x + y = 25,718,656
+CFG1_ALGO_BYTES = weight_bytes(FF, H) + 2 * H + 2 * FF         # 12,871,616
 
 
 def peaks():
@@ -106,8 +116,10 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
-def cpu_gate_up_baseline(min_seconds: float = 10.0, max_reps: int = 400):
-    """Times the CPU restatement of the reference's fused gate+up+SiLU GEMV on all host cores."""
+# CPU arm: the C restatement of the reference kernels (the reference's SYCL sources cannot be
+# built in this image), all host cores
+# ------------------------------------------------------------------------------------------
+def _cpu_inputs():
     import numpy as np
     import torch
 
@@ -121,40 +133,62 @@ def cpu_gate_up_baseline(min_seconds: float = 10.0, max_reps: int = 400):
                                          w.nested_blocksize, w.nested_offset) for w in (g, u)])
     packed = np.concatenate([g.packed, u.packed])
     x = synth.gaussian_activation(2009, H).view(torch.uint16).numpy()
-    for _ in range(3):
-        O.gemv_gate_up_swiglu(packed, g.quant_map, am, x, FF, H, 64)
-    reps, t0, best = 0, time.perf_counter(), 1e9
-    while reps < max_reps and (time.perf_counter() - t0 < min_seconds or reps < 5):
-        t1 = time.perf_counter()
-        O.gemv_gate_up_swiglu(packed, g.quant_map, am, x, FF, H, 64)
-        best = min(best, time.perf_counter() - t1)
-        reps += 1
-    mean = (time.perf_counter() - t0) / reps
-    return dict(value=GATE_UP_WEIGHT_BYTES / mean / 1e9, unit=UNIT, cores=O.num_threads(),
-                kind="port", best_ms=best * 1e3, mean_ms=mean * 1e3,
-                sample=f"{reps} passes of one cfg2 fused gate+up+SiLU GEMV (2x[9728,2560] NF4), "
-                       f"scalar C port of the reference SYCL kernel, OpenMP over rows")
+    return O, g, packed, am, x
+
+
+def cpu_baselines(min_seconds: float = 8.0, max_reps: int = 400):
+    """cfg2 (the headline), cfg1 and a bounded sample of the prefill route on the host cores."""
+    import numpy as np
+    import torch
+    O, g, packed, am, x = _cpu_inputs()
+
+    def best_mean(fn, seconds):
+        for _ in range(2):
+            fn()
+        reps, t0, best = 0, time.perf_counter(), 1e9
+        while reps < max_reps and (time.perf_counter() - t0 < seconds or reps < 3):
+            t1 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t1)
+            reps += 1
+        return (time.perf_counter() - t0) / reps, best, reps
+
+    mean, best, reps = best_mean(lambda: O.gemv_gate_up_swiglu(packed, g.quant_map, am, x, FF, H, 64),
+                                 min_seconds)
+    out = dict(value=GATE_UP_WEIGHT_BYTES / mean / 1e9, unit=UNIT, cores=O.num_threads(), kind="port",
+               best_ms=best * 1e3, mean_ms=mean * 1e3,
+               build="gcc -O2 -march=x86-64-v3 -fopenmp -ffp-contract=off (oracle/Makefile)",
+               sample=f"{reps} passes of one cfg2 fused gate+up+SiLU GEMV (2x[9728,2560] NF4), "
+                      f"scalar C port of the reference SYCL kernel, OpenMP over rows")
+    half = packed[: packed.size // 2]
+    mean1, _, reps1 = best_mean(lambda: O.gemv(half, g.quant_map, am[: am.size // 2], x, FF, H, 64), 3.0)
+    out["cfg1"] = dict(value=weight_bytes(FF, H) / mean1 / 1e9, unit=UNIT, mean_ms=mean1 * 1e3,
+                       sample=f"{reps1} passes of one 2560->9728 GEMV")
+    # the reference's M > 1 route at blocksize 64: dequantise to bf16 (its kernel, transcribed), then
+    # a bf16 matmul with fp32 accumulation (torch CPU = oneDNN, the library family it calls)
+    m_cpu = 256
+    xs = torch.randn(m_cpu, H, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    w_nk = O.dequantize_nk(packed, g.quant_map, am, 2 * FF, H, 64)
+    t_deq = time.perf_counter() - t0
+    wt = torch.from_numpy(w_nk.view(np.int16).copy()).view(torch.bfloat16)
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    _ = xs @ wt.t()
+    t_mm = time.perf_counter() - t0
+    out["prefill_route"] = dict(value=2.0 * m_cpu * 2 * FF * H / (t_deq + t_mm) / 1e12, unit="TFLOP/s",
+                                dequant_ms=t_deq * 1e3, matmul_ms=t_mm * 1e3,
+                                sample=f"gate|up 2560->19456 at M={m_cpu} (1/8 of cfg3's rows): transcribed "
+                                       f"dequantize_weight + torch CPU bf16 matmul, one pass")
+    return out
 
 
 def run_reference(args):
-    """--impl reference: the reference's own algorithm on the host cores (CPU port; the SYCL
-    sources cannot be built in this image). Rank 0 only."""
+    """--impl reference: the reference's own algorithm on the host cores. Rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np
-    import torch
-
-    from aila_b200 import synth
-    from oracle import nf4_oracle as O
-    O.build()
-    O.set_num_threads(os.cpu_count() or 1)  # launchers such as torchrun pin OMP_NUM_THREADS=1
-    g = synth.synth_linear(synth.seed_for(2, 0, "gate"), FF, H)
-    u = synth.synth_linear(synth.seed_for(2, 0, "up"), FF, H)
-    am = np.concatenate([O.expand_absmax(w.absmax_codes, w.nested_quant_map, w.nested_absmax,
-                                         w.nested_blocksize, w.nested_offset) for w in (g, u)])
-    packed = np.concatenate([g.packed, u.packed])
-    x = synth.gaussian_activation(2009, H).view(torch.uint16).numpy()
+    O, g, packed, am, x = _cpu_inputs()
     for _ in range(max(args.warmup, 1)):
         O.gemv_gate_up_swiglu(packed, g.quant_map, am, x, FF, H, 64)
     t0 = time.perf_counter()
@@ -169,8 +203,7 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "cfg2 fused gate+up+SiLU NF4 GEMV, M=1, K=2560, 2x9728 rows, bs64 double-quant",
-                   "l2": "50 MB working set on host caches; CPU arm"},
+        "config": {"workload": WORKLOAD, "l2": "50 MB working set on host caches; CPU arm"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -179,8 +212,46 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-
 # ------------------------------------------------------------------------------------------
+def _rolled(w, shift):
+    """A copy of a quantised weight with its rows rotated: distinct memory, same value distribution."""
+    import numpy as np
+    if shift == 0:
+        return w
+    n, k = w.out_features, w.in_features
+    return dataclasses.replace(
+        w, packed=np.roll(np.asarray(w.packed).reshape(n, k // 2), shift, 0).reshape(-1),
+        absmax_codes=np.roll(np.asarray(w.absmax_codes).reshape(n, k // 64), shift, 0).reshape(-1))
+
+
+def _lin(w, local):
+    from aila_b200.linear import Bnb4BitLinear
+    l = Bnb4BitLinear()
+    assert l.init(w, local), l.last_error
+    return l
+
+
+def _fuse(*ls):
+    from aila_b200.linear import Bnb4BitLinear
+    f = Bnb4BitLinear()
+    assert f.init_fused_rows(*ls), f.last_error
+    for l in ls:
+        l.close()
+    return f
+
+
+def _graph(fn, stream):
+    """fn captured in a CUDA graph (after one eager run); returns the replay callable."""
+    import torch
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+    return g.replay
+
+
 def _time_stream(fn, stream, reps, warm=3):
     import torch
     with torch.cuda.stream(stream):
@@ -196,171 +267,190 @@ def _time_stream(fn, stream, reps, warm=3):
     return a.elapsed_time(b) * 1e3 / reps  # us
 
 
-def tp_mlp_latency(rank, world, local, stream):
-    """cfg5 MLP (hidden 5120, intermediate 25600) sharded over `world` GPUs: gate|up by rows with
-    local SwiGLU, down by columns, one all-reduce. Per-layer latency at M = 1 and M = 2048, with
-    and without the collective. Strong scaling: total work fixed, ideal = t(1)/world."""
+def _max_rel_err(got_bits, want_bits):
+    """max |got - want| / max |want| of two bf16 bit arrays."""
+    import numpy as np
+
+    def f32(a):
+        return (np.ascontiguousarray(a, np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    g, w = f32(got_bits), f32(want_bits)
+    return float(np.abs(g - w).max() / max(np.abs(w).max(), 1e-30))
+
+
+def _bits(t):
+    import torch
+    return t.detach().cpu().contiguous().view(torch.uint16).numpy()
+
+
+# ------------------------------------------------------------------------------------------
+def tp_linears(rank, world, local, stream):
+    """The large-model linears (hidden 5120, intermediate 25600; q 5120->8192, o 8192->5120) sharded
+    over `world` GPUs, at M = 1 and M = 2048. MLP: gate|up by rows with local SwiGLU, down by
+    columns, one sum exchange. q by rows (column-parallel, no exchange), o by columns (row-parallel,
+    one sum exchange). Strong scaling: total work fixed, ideal = t(1) / world. Every result is
+    compared with the CPU oracle on the UNSHARDED weights (M = 2048: sampled rows)."""
+    import numpy as np
     import torch
     import torch.distributed as dist
 
     from aila_b200 import sharded, synth
-    H5, FF5 = 5120, 25600
+    from oracle import nf4_oracle as O
+    O.build()
+    O.set_num_threads(max(1, (os.cpu_count() or world) // world))
+    H5, FF5, Q5 = 5120, 25600, 8192
+    dev = torch.device("cuda", local)
     gate = synth.synth_linear(synth.seed_for(5, 0, "gate"), FF5, H5)
     up = synth.synth_linear(synth.seed_for(5, 0, "up"), FF5, H5)
     down = synth.synth_linear(synth.seed_for(5, 0, "down"), H5, FF5)
+    wq = synth.synth_linear(synth.seed_for(5, 0, "q"), Q5, H5)
+    wo = synth.synth_linear(synth.seed_for(5, 0, "o"), H5, Q5)
     be = sharded.CudaBackend(local)
     be.scratch.ensure(2048, FF5, 2 * FF5 // world, True)
-    if world > 1:
-        mlp = sharded.ShardedNf4Mlp(gate, up, down, be)
-        gate_up, dn, local_ff = mlp.gate_up, mlp.down, mlp.local_ff
-    else:
-        g, u = be.make_shard(gate, 0, 0, 1), be.make_shard(up, 0, 0, 1)
-        gate_up, dn, local_ff = be.fuse(g, u), be.make_shard(down, 1, 0, 1), FF5
-    out = {"workload": "cfg5 MLP 5120 -> 2x25600 -> 5120, NF4; gate|up row-sharded + local SwiGLU, "
-                       "down column-sharded, one all-reduce", "world": world, "scaling": "strong"}
-    for M, reps in ((1, 200), (2048, 10)):
-        x = synth.gaussian_activation(5009 + M, M, H5).to(torch.device("cuda", local))
+    g_r, u_r = be.make_shard(gate, sharded.ROWS, rank, world), be.make_shard(up, sharded.ROWS, rank, world)
+    gate_up, local_ff = be.fuse(g_r, u_r), FF5 // world
+    dn = be.make_shard(down, sharded.COLS, rank, world)
+    q_r = be.make_shard(wq, sharded.ROWS, rank, world)
+    o_r = be.make_shard(wo, sharded.COLS, rank, world)
+    local_q = Q5 // world
+
+    def am(w):
+        return O.expand_absmax(w.absmax_codes, w.nested_quant_map, w.nested_absmax, w.nested_blocksize,
+                               w.nested_offset)
+
+    out = {"workload": "cfg5 linears: MLP 5120 -> 2x25600 -> 5120 (gate|up row-sharded + local SwiGLU, down "
+                       "column-sharded, one sum exchange), q 5120->8192 row-sharded, o 8192->5120 column-sharded",
+           "world": world, "scaling": "strong"}
+    parity = 0.0
+
+    def allmax(v):
+        if world == 1:
+            return float(v)
+        t = torch.tensor([float(v)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    peers = be.make_peer_buffer(None, H5) if world > 1 else None
+    for M, reps in ((1, 100), (2048, 10)):
+        x = synth.gaussian_activation(5009 + M, M, H5).to(dev)
+        xo = synth.gaussian_activation(5019 + M, M, Q5).to(dev)
+        xo_local = xo[:, rank * local_q:(rank + 1) * local_q].contiguous()
         mid = be.empty(M, local_ff)
         part = be.empty(M, H5)
+        yq = be.empty(M, local_q)
+        yo = be.empty(M, H5)
+        y_fused = be.empty(1, H5)
 
-        def compute():
+        def mlp_compute():
             assert be.gate_up_swiglu(gate_up, x, mid, M, local_ff)
             be.forward(dn, mid, part, M)
 
-        acc32 = torch.empty(M, H5, dtype=torch.float32, device=part.device) if M <= 64 else None
-
-        def full():
-            compute()
-            if acc32 is not None:  # fp32 exchange for decode-sized messages
-                acc32.copy_(part)
-                dist.all_reduce(acc32)
-                part.copy_(acc32)
+        def exchange(t):
+            if world == 1:
+                return
+            if M <= 64:  # fp32 exchange for decode-sized messages
+                acc = t.float()
+                dist.all_reduce(acc)
+                t.copy_(acc)
             else:
-                dist.all_reduce(part)
+                dist.all_reduce(t)
 
-        def graphed(fn):
-            """Replays fn from a CUDA graph when capture works (NCCL included), else eager."""
+        def mlp_full():
+            mlp_compute()
+            exchange(part)
+
+        def mlp_fused():
+            assert be.gate_up_swiglu(gate_up, x, mid, 1, local_ff)
+            be.forward_allreduce(dn, peers, mid, y_fused)
+
+        def q_proj():
+            be.forward(q_r, x, yq, M)
+
+        def o_compute():
+            be.forward(o_r, xo_local, yo, M)
+
+        def o_full():
+            o_compute()
+            exchange(yo)
+
+        def timed(fn):
             try:
-                with torch.cuda.stream(stream):
-                    fn()
-                    stream.synchronize()
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=stream):
-                        fn()
-                return g.replay, "cuda graph"
+                run = _graph(fn, stream)
             except Exception:
                 torch.cuda.synchronize()
-                return fn, "eager"
+                run = fn
+            if world > 1:
+                dist.barrier()
+            return allmax(_time_stream(run, stream, reps))
 
-        if world > 1:
-            dist.barrier()
-        run_c, how_c = graphed(compute)
-        t_c = _time_stream(run_c, stream, reps)
-        if world > 1:
-            dist.barrier()
-            run_f, how_f = graphed(full)
-            dist.barrier()
-            t_f = _time_stream(run_f, stream, reps)
-            out[f"M{M}_launch"] = f"compute: {how_c}; with all-reduce: {how_f}"
+        t_c, t_f = timed(mlp_compute), timed(mlp_full)
+        out[f"M{M}_mlp_compute_us"], out[f"M{M}_mlp_with_exchange_us"] = t_c, t_f
+        out[f"M{M}_mlp_collective_us"] = t_f - t_c
+        out[f"M{M}_q_us"] = timed(q_proj)
+        t_oc, t_of = timed(o_compute), timed(o_full)
+        out[f"M{M}_o_compute_us"], out[f"M{M}_o_with_exchange_us"] = t_oc, t_of
+        if M == 1 and world > 1:
+            out["M1_mlp_fused_exchange_us"] = timed(mlp_fused)
+        # ---- parity against the oracle on the unsharded weights
+        with torch.cuda.stream(stream):
+            mlp_full()
+            o_full()
+            q_proj()
+            if M == 1 and world > 1:
+                mlp_fused()
+            stream.synchronize()
+        be.scratch.check()
+        rows = [0] if M == 1 else [0, 1029, 2047]
+        xs, xos = _bits(x)[rows], _bits(xo)[rows]
+        gu_packed = np.concatenate([gate.packed, up.packed])
+        gu_am = np.concatenate([am(gate), am(up)])
+        if M == 1:
+            mid_w = O.gemv_gate_up_swiglu(gu_packed, gate.quant_map, gu_am, xs[0], FF5, H5, 64)
+            y_w = O.gemv(down.packed, down.quant_map, am(down), mid_w, H5, FF5, 64).reshape(1, -1)
+            q_w = O.gemv(wq.packed, wq.quant_map, am(wq), xs[0], Q5, H5, 64).reshape(1, -1)
+            o_w = O.gemv(wo.packed, wo.quant_map, am(wo), xos[0], H5, Q5, 64).reshape(1, -1)
         else:
-            t_f = t_c
-            out[f"M{M}_launch"] = how_c
-        if world > 1:
-            t = torch.tensor([t_c, t_f], device=torch.device("cuda", local))
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            t_c, t_f = float(t[0]), float(t[1])
-        out[f"M{M}_compute_us"] = t_c
-        out[f"M{M}_with_allreduce_us"] = t_f
-        if world > 1 and M == 1 and os.environ.get("AILA_BENCH_FUSED_TP", "1") != "0":
-            # the exchange folded into the down GEMV: fp32 row sums stored into every rank's
-            # buffer over NVLink, summed by a small kernel (no library collective). A failure on
-            # any rank is reported instead of the number; the collectives below stay matched.
-            t_x, how_x, err = 0.0, "", ""
-            peers = None
-            dev_t = torch.device("cuda", local)
-            y1 = be.empty(1, H5)
-
-            def fused():
-                assert be.gate_up_swiglu(gate_up, x, mid, 1, local_ff)
-                be.forward_allreduce(dn, peers, mid, y1)
-
-            try:  # set-up and one checked call; every rank must get through it before any timing
-                peers = be.make_peer_buffer(None, H5)
-                with torch.cuda.stream(stream):
-                    fused()
-                    stream.synchronize()
-                be.scratch.check()
-            except Exception as e:  # noqa: BLE001
-                err = repr(e)[:200]
-            ok = torch.tensor([0.0 if err else 1.0], device=dev_t)
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-            if float(ok[0]) > 0.5:
-                try:
-                    run_x, how_x = graphed(fused)
-                    t_x = _time_stream(run_x, stream, reps)
-                    torch.cuda.synchronize()
-                    be.scratch.check()
-                except Exception as e:  # noqa: BLE001
-                    err = repr(e)[:200]
-            elif not err:
-                err = "set-up failed on another rank"
-            t = torch.tensor([t_x, 0.0 if err else 1.0], device=dev_t)
-            dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
-            dist.all_reduce(t[1:], op=dist.ReduceOp.MIN)
-            if float(t[1]) > 0.5:
-                out["M1_fused_exchange_us"] = float(t[0])
-                out["M1_fused_launch"] = how_x
-            else:
-                out["M1_fused_exchange_error"] = err or "failed on another rank"
-            dist.barrier()
-            if peers is not None:
-                peers.close()
-    be.scratch.check()
+            # the reference's M > 1 route on the sampled rows: bf16-rounded weights, bf16 GEMM
+            n_r = len(rows)
+            w_gu = O.dequantize_nk(gu_packed, gate.quant_map, gu_am, 2 * FF5, H5, 64)
+            mid_w = O.swiglu_rows(O.gemm_bf16w(w_gu, xs, n_r, 2 * FF5, H5), n_r, FF5)
+            del w_gu
+            y_w = O.gemm_bf16w(O.dequantize_nk(down.packed, down.quant_map, am(down), H5, FF5, 64), mid_w,
+                               n_r, H5, FF5)
+            q_w = O.gemm_bf16w(O.dequantize_nk(wq.packed, wq.quant_map, am(wq), Q5, H5, 64), xs, n_r, Q5, H5)
+            o_w = O.gemm_bf16w(O.dequantize_nk(wo.packed, wo.quant_map, am(wo), H5, Q5, 64), xos, n_r, H5, Q5)
+        for i, r in enumerate(rows):
+            parity = max(parity, _max_rel_err(_bits(part)[r], y_w[i]), _max_rel_err(_bits(yo)[r], o_w[i]),
+                         _max_rel_err(_bits(yq)[r], q_w[i][rank * local_q:(rank + 1) * local_q]))
+            if M == 1 and world > 1:
+                parity = max(parity, _max_rel_err(_bits(y_fused)[0], y_w[i]))
+    out["parity_max_rel_err"] = allmax(parity)
+    out["parity_bound"] = 2e-2
+    if peers is not None:
+        dist.barrier()
+        peers.close()
     return out
 
 
-def decode_stack(local, stream):
+def decode_stack(local, stream, batches=(4, 8, 16, 32)):
     """cfg4: the NF4 linears of one decode step of a 36-layer GQA transformer (hidden 2560, q 4096,
     k/v 1024, ff 9728): per layer fused qkv 2560->6144, o 4096->2560, fused gate|up+SiLU
-    2560->2x9728, down 9728->2560; each linear gets its own N(0,1) input. One CUDA graph of 144
-    launches, 1.87 GB of weights per step; then the same plus the bf16 lm_head 2560->151936
-    (0.78 GB, dense GEMV) and the greedy argmax over its logits."""
-    import dataclasses
-
-    import numpy as np
+    2560->2x9728, down 9728->2560; each linear gets its own N(0,1) input. 144 operations, 1.87 GB
+    of weights per step: as one chained launch, as 144 separate calls, and followed by the bf16
+    lm_head 2560->151936 (0.78 GB, dense GEMV) and the greedy argmax over its logits."""
     import torch
 
     from aila_b200 import synth
-    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch, Linear, argmax
+    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch, DecodeChain, Linear, argmax
     dev = torch.device("cuda", local)
     HID, Q, KV, F, VOCAB = 2560, 4096, 1024, 9728, 151936
     shapes = {"q": (Q, HID), "k": (KV, HID), "v": (KV, HID), "o": (HID, Q), "gate": (F, HID),
               "up": (F, HID), "down": (HID, F)}
     base = {k: synth.synth_linear(synth.seed_for(4, 0, k), *v) for k, v in shapes.items()}
-
-    def rolled(w, shift):
-        n, k = w.out_features, w.in_features
-        return dataclasses.replace(
-            w, packed=np.roll(np.asarray(w.packed).reshape(n, k // 2), shift, 0).reshape(-1),
-            absmax_codes=np.roll(np.asarray(w.absmax_codes).reshape(n, k // 64), shift, 0).reshape(-1))
-
-    def lin(w):
-        l = Bnb4BitLinear()
-        assert l.init(w, local), l.last_error
-        return l
-
-    def fuse(*ls):
-        f = Bnb4BitLinear()
-        assert f.init_fused_rows(*ls), f.last_error
-        for l in ls:
-            l.close()
-        return f
-
     layers = []
     for i in range(36):
-        w = {k: rolled(v, 16 * i) for k, v in base.items()}
-        layers.append((fuse(lin(w["q"]), lin(w["k"]), lin(w["v"])), lin(w["o"]),
-                       fuse(lin(w["gate"]), lin(w["up"])), lin(w["down"])))
+        w = {k: _rolled(v, 16 * i) for k, v in base.items()}
+        layers.append((_fuse(_lin(w["q"], local), _lin(w["k"], local), _lin(w["v"], local)), _lin(w["o"], local),
+                       _fuse(_lin(w["gate"], local), _lin(w["up"], local)), _lin(w["down"], local)))
     scratch = Bnb4BitLinearScratch(local)
     scratch.ensure(1, F, 2 * F, False)
     x_h = synth.gaussian_activation(4009, 1, HID).to(dev)
@@ -369,25 +459,25 @@ def decode_stack(local, stream):
     y_qkv = torch.empty(1, Q + 2 * KV, dtype=torch.bfloat16, device=dev)
     y_h = torch.empty(1, HID, dtype=torch.bfloat16, device=dev)
     y_f = torch.empty(1, F, dtype=torch.bfloat16, device=dev)
+    ops = []
+    for qkv, o, gu, dn in layers:
+        ops += [dict(linear=qkv, x=x_h, y=y_qkv), dict(linear=o, x=x_q, y=y_h),
+                dict(linear=gu, ff_dim=F, x=x_h, y=y_f), dict(linear=dn, x=x_f, y=y_h)]
+    chain = DecodeChain(scratch, ops)
 
-    def step():
+    def per_call():
         for qkv, o, gu, dn in layers:
             qkv.forward(scratch, x_h, y_qkv, 1)
             o.forward(scratch, x_q, y_h, 1)
             assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(gu, scratch, x_h, y_f, F)
             dn.forward(scratch, x_f, y_h, 1)
 
-    with torch.cuda.stream(stream):
-        step()
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step()
-    us = _time_stream(graph.replay, stream, 20)
+    us = _time_stream(_graph(chain.run, stream), stream, 20)
+    us_calls = _time_stream(_graph(per_call, stream), stream, 10)
     scratch.check()
-    # small batches through the batched decode kernel (eight rows per launch)
+    # small batches (batched decode kernel, eight rows per launch)
     batch = {}
-    for M in (4, 8, 16, 32):
+    for M in batches:
         xb_h = synth.gaussian_activation(4100 + M, M, HID).to(dev)
         xb_q = synth.gaussian_activation(4200 + M, M, Q).to(dev)
         xb_f = synth.gaussian_activation(4300 + M, M, F).to(dev)
@@ -402,67 +492,110 @@ def decode_stack(local, stream):
                 assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(gu, scratch, xb_h, yb_f, F, seq_len=M)
                 dn.forward(scratch, xb_f, yb_h, M)
 
-        with torch.cuda.stream(stream):
-            step_m()
-            stream.synchronize()
-            gm = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gm, stream=stream):
-                step_m()
-        batch[f"M{M}_us_per_step"] = _time_stream(gm.replay, stream, 10)
-        del gm
+        batch[f"M{M}_us_per_step"] = _time_stream(_graph(step_m, stream), stream, 5)
     scratch.check()
-    # the bf16 lm_head of the same model and the token choice, alone and behind the stack
-    g = torch.Generator().manual_seed(synth.seed_for(4, 0, "lm_head"))
-    head_w = (torch.randn(VOCAB, HID, generator=g) * 0.02).to(torch.bfloat16)
-    head = Linear()
-    head.init(head_w, HID, VOCAB, local)
-    del head_w
+    # the bf16 lm_head of the same model and the token choice; four distinct heads so that
+    # consecutive timed launches do not find the weight in L2 (values drawn on the device)
+    g = torch.Generator(device=dev).manual_seed(synth.seed_for(4, 0, "lm_head"))
+    heads = []
+    for _ in range(4):
+        h = Linear()
+        h.init((torch.randn(VOCAB, HID, generator=g, device=dev) * 0.02).to(torch.bfloat16), HID, VOCAB, local)
+        heads.append(h)
     logits = torch.empty(1, VOCAB, dtype=torch.bfloat16, device=dev)
     token = torch.zeros(1, dtype=torch.int32, device=dev)
-    # three more heads so that consecutive timed launches do not find the weight in L2
-    heads = [head]
-    for _ in range(3):
-        h = Linear()
-        h.init((torch.randn(VOCAB, HID, generator=g) * 0.02).to(torch.bfloat16), HID, VOCAB, local)
-        heads.append(h)
 
     def head_only():
         for h in heads:
             h.forward(scratch, x_h, logits, 1)
 
     def full_step():
-        step()
-        head.forward(scratch, y_h, logits, 1)
+        chain.run()
+        heads[0].forward(scratch, y_h, logits, 1)
         argmax(logits, VOCAB, token)
 
-    with torch.cuda.stream(stream):
-        head_only()
-        full_step()
-        stream.synchronize()
-        g_head = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_head, stream=stream):
-            head_only()
-        g_full = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_full, stream=stream):
-            full_step()
-    us_head = _time_stream(g_head.replay, stream, 10) / len(heads)
-    us_full = _time_stream(g_full.replay, stream, 20)
+    us_head = _time_stream(_graph(head_only, stream), stream, 10) / len(heads)
+    us_full = _time_stream(_graph(full_step, stream), stream, 20)
     head_bytes = VOCAB * HID * 2
     wbytes = 36 * (weight_bytes(Q + 2 * KV, HID) + weight_bytes(HID, Q) + 2 * weight_bytes(F, HID) +
                    weight_bytes(HID, F))
     pk = peaks()
+    for t in layers:
+        for l in t:
+            l.close()
     return {"workload": "cfg4 NF4 linear stack, M=1: 36 x {qkv 2560->6144, o 4096->2560, "
-                        "gate|up+SiLU 2560->2x9728, down 9728->2560}", "launches_per_step": 144,
+                        "gate|up+SiLU 2560->2x9728, down 9728->2560}, one chained launch of 144 operations",
+            "operations_per_step": 144, "launches_per_step": 1,
             "weight_bytes_per_step": wbytes, "us_per_step": us, "weight_GBps": wbytes / us / 1e3,
             "frac_of_measured_hbm": wbytes / us / 1e3 / pk["hbm"],
+            "per_call": {"launches_per_step": 144, "us_per_step": us_calls,
+                         "frac_of_measured_hbm": wbytes / us_calls / 1e3 / pk["hbm"]},
             "small_batch": batch,
             "lm_head": {"workload": "bf16 dense GEMV 2560 -> 151936, 4 distinct weights in turn",
                         "us": us_head, "weight_GBps": head_bytes / us_head / 1e3,
                         "frac_of_measured_hbm": head_bytes / us_head / 1e3 / pk["hbm"]},
-            "with_lm_head_and_argmax": {"us_per_step": us_full,
+            "with_lm_head_and_argmax": {"launches_per_step": 3, "us_per_step": us_full,
                                         "weight_bytes_per_step": wbytes + head_bytes,
                                         "weight_GBps": (wbytes + head_bytes) / us_full / 1e3,
                                         "frac_of_measured_hbm": (wbytes + head_bytes) / us_full / 1e3 / pk["hbm"]}}
+
+
+# ------------------------------------------------------------------------------------------
+def profile_case(case: str):
+    """Small, self-terminating runs of one kernel each, for capture under ncu (a few launches, well
+    under a GB on the device except `dense`)."""
+    import torch
+
+    from aila_b200 import synth
+    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch, DecodeChain, Linear
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    scratch = Bnb4BitLinearScratch(0)
+    gate = synth.synth_linear(synth.seed_for(2, 0, "gate"), FF, H)
+    up = synth.synth_linear(synth.seed_for(2, 0, "up"), FF, H)
+    x = synth.gaussian_activation(2009, 1, H).to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    if case in ("chain", "per_call", "batch"):
+        n = 8  # 8 x 25.7 MB = 206 MB of weights: larger than L2
+        fused = [_fuse(_lin(_rolled(gate, 16 * i), 0), _lin(_rolled(up, 16 * i), 0)) for i in range(n)]
+        M = 8 if case == "batch" else 1
+        xm = synth.gaussian_activation(2109, M, H).to(dev)
+        outs = [torch.empty(M, FF, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+        chain = DecodeChain(scratch, [dict(linear=f, ff_dim=FF, x=x, y=o) for f, o in zip(fused, outs)]) \
+            if case == "chain" else None
+        for _ in range(3):
+            flush.zero_()
+            if chain is not None:
+                chain.run()
+            else:
+                for f, o in zip(fused, outs):
+                    assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, xm, o, FF, seq_len=M)
+    elif case == "prefill":
+        down = _lin(synth.synth_linear(synth.seed_for(3, 0, "down"), H, FF), 0)
+        gu = _fuse(_lin(gate, 0), _lin(up, 0))
+        scratch.ensure(PREFILL_M, FF, 2 * FF, True)
+        xm = synth.gaussian_activation(3009, PREFILL_M, H).to(dev)
+        mid = torch.empty(PREFILL_M, FF, dtype=torch.bfloat16, device=dev)
+        ym = torch.empty(PREFILL_M, H, dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            flush.zero_()
+            assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(gu, scratch, xm, mid, FF, seq_len=PREFILL_M)
+            down.forward(scratch, mid, ym, PREFILL_M)
+    elif case == "dense":
+        VOCAB = 151936
+        g = torch.Generator(device=dev).manual_seed(7)
+        head = Linear()
+        head.init((torch.randn(VOCAB, H, generator=g, device=dev) * 0.02).to(torch.bfloat16), H, VOCAB, 0)
+        logits = torch.empty(1, VOCAB, dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            flush.zero_()
+            head.forward(scratch, x, logits, 1)
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+    torch.cuda.synchronize()
+    scratch.check()
+    print(json.dumps({"profile_case": case, "status": "ok"}))
+
 
 # ------------------------------------------------------------------------------------------
 def main():
@@ -474,19 +607,22 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--no-tp", action="store_true", help="skip the sharded cfg5 MLP latency (N > 1)")
-    ap.add_argument("--tp", action="store_true", help="also time the cfg5 MLP at N = 1")
-    ap.add_argument("--stack", action="store_true", help="also time the cfg4 decode linear stack")
+    ap.add_argument("--no-tp", action="store_true", help="skip the sharded cfg5 linears")
+    ap.add_argument("--no-stack", action="store_true", help="skip the cfg4 decode linear stack")
+    ap.add_argument("--stack", action="store_true", help="time the cfg4 stack also when N > 1 (rank 0)")
+    ap.add_argument("--profile-case", default=None)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.profile_case:
+        return profile_case(args.profile_case)
 
     import numpy as np
     import torch
     import torch.distributed as dist
 
     from aila_b200 import synth
-    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch
+    from aila_b200.linear import Bnb4BitLinear, Bnb4BitLinearScratch, DecodeChain
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -504,43 +640,19 @@ def main():
     # versions of the same bytes (distinct memory, same value distribution).
     gate = synth.synth_linear(synth.seed_for(2, 0, "gate"), FF, H)
     up = synth.synth_linear(synth.seed_for(2, 0, "up"), FF, H)
-    linears = []
-    for i in range(layers):
-        def rolled(w, shift):
-            if shift == 0:
-                return w
-            import dataclasses
-            rows = np.asarray(w.packed).reshape(FF, H // 2)
-            codes = np.asarray(w.absmax_codes).reshape(FF, H // 64)
-            return dataclasses.replace(w, packed=np.roll(rows, shift, 0).reshape(-1),
-                                       absmax_codes=np.roll(codes, shift, 0).reshape(-1))
-        lg, lu, f = Bnb4BitLinear(), Bnb4BitLinear(), Bnb4BitLinear()
-        assert lg.init(rolled(gate, 16 * i), local), lg.last_error
-        assert lu.init(rolled(up, 16 * i), local), lu.last_error
-        assert f.init_fused_rows(lg, lu), f.last_error
-        lg.close()
-        lu.close()
-        linears.append(f)
+    linears = [_fuse(_lin(_rolled(gate, 16 * i), local), _lin(_rolled(up, 16 * i), local)) for i in range(layers)]
+    gates = [_lin(_rolled(gate, 16 * i + 8), local) for i in range(layers)]
     scratch = Bnb4BitLinearScratch(local)
     scratch.ensure(1, H, 2 * FF, False)
     x = synth.gaussian_activation(2009, 1, H).to(dev)
     outs = [torch.empty(1, FF, dtype=torch.bfloat16, device=dev) for _ in range(layers)]
-
     stream = torch.cuda.Stream(dev)
-
-    def one_pass():
-        for f, o in zip(linears, outs):
-            ok = Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x, o, FF)
-            assert ok
+    chain = DecodeChain(scratch, [dict(linear=f, ff_dim=FF, x=x, y=o) for f, o in zip(linears, outs)])
+    replay = _graph(chain.run, stream)
 
     with torch.cuda.stream(stream):
-        one_pass()
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            one_pass()
         for _ in range(args.warmup):
-            graph.replay()
+            replay()
         stream.synchronize()
         if world > 1:
             dist.barrier()
@@ -549,7 +661,7 @@ def main():
         with ClockSampler(local) as clocks:
             ev[0].record(stream)
             for i in range(args.steps):
-                graph.replay()
+                replay()
                 ev[i + 1].record(stream)
             stream.synchronize()
         if world > 1:
@@ -564,41 +676,66 @@ def main():
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
     value = world * layers * GATE_UP_WEIGHT_BYTES / (ms_per_step * 1e-3) / 1e9
-    launch_us = ms_per_step * 1e3 / layers
-    achieved = GATE_UP_ALGO_BYTES / (launch_us * 1e-6) / 1e9
+    op_us = ms_per_step * 1e3 / layers
+    achieved = GATE_UP_ALGO_BYTES / (op_us * 1e-6) / 1e9
 
-    # ---- end to end through the host-buffer C-ABI call
+    # ---- what was timed is right: layer 0 (and the last one) against the CPU oracle
+    parity = None
+    if rank == 0:
+        O, g0, packed, am, xb = _cpu_inputs()
+        want = O.gemv_gate_up_swiglu(packed, g0.quant_map, am, xb, FF, H, 64)
+        parity = _max_rel_err(_bits(outs[0]).reshape(-1), want)
+        assert parity <= 2e-2, f"timed output differs from the oracle: {parity}"
+
+    # ---- the same operations as separate calls (one launch each), and cfg1 chained
+    def per_call():
+        for f, o in zip(linears, outs):
+            assert Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x, o, FF)
+
+    call_us = _time_stream(_graph(per_call, stream), stream, max(5, args.steps // 2)) / layers
+    outs1 = [torch.empty(1, FF, dtype=torch.bfloat16, device=dev) for _ in range(layers)]
+    chain1 = DecodeChain(scratch, [dict(linear=f, x=x, y=o) for f, o in zip(gates, outs1)])
+    cfg1_us = _time_stream(_graph(chain1.run, stream), stream, max(5, args.steps // 2)) / layers
+    scratch.check()
+
+    # ---- end to end through the host-buffer C-ABI calls
     xh = synth.gaussian_activation(2009, 1, H).pin_memory()
     yh = torch.empty(1, FF, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
     with torch.cuda.stream(stream):
         for _ in range(2):
-            for f in linears:
-                f.gate_up_swiglu_host(scratch, xh, yh, 1, FF)
-        e2e_steps = max(3, min(args.steps, 20))
+            chain.run_host(xh, yh)
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
+            chain.run_host(xh, yh)
+        torch.cuda.synchronize()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        assert torch.equal(yh.view(torch.uint16), outs[-1].cpu().view(torch.uint16))
+        for f in linears[:2]:
+            f.gate_up_swiglu_host(scratch, xh, yh, 1, FF)
+        t0 = time.perf_counter()
+        for _ in range(3):
             for f in linears:
                 f.gate_up_swiglu_host(scratch, xh, yh, 1, FF)
         torch.cuda.synchronize()
-        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        e2e_call_s = (time.perf_counter() - t0) / 3
     if world > 1:
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_val = world * layers * GATE_UP_WEIGHT_BYTES / e2e_s / 1e9
-
-    # ---- parity spot check of what was timed (one layer against the oracle is done in tests;
-    # here only finiteness so the bench never reports numbers for garbage)
-    assert torch.isfinite(outs[0].float()).all() and torch.isfinite(yh.float()).all()
+    chain.close()
+    chain1.close()
+    for f in gates:
+        f.close()
 
     # ---- prefill GEMM pair (cfg3), rank 0 only
     prefill = None
     if not args.no_prefill and rank == 0:
         down_w = synth.synth_linear(synth.seed_for(3, 0, "down"), H, FF)
-        down = Bnb4BitLinear()
-        assert down.init(down_w, local), down.last_error
+        down = _lin(down_w, local)
         gu = linears[0]
         scratch.ensure(PREFILL_M, FF, 2 * FF, True)
         xm = synth.gaussian_activation(3009, PREFILL_M, H).to(dev)
@@ -631,29 +768,31 @@ def main():
         scratch.check()
         prefill = {"metric": "nf4_prefill_gemm_pair", "value": tf, "unit": "TFLOP/s",
                    "ms": ms, "workload": "cfg3: X[2048,2560] -> gate_up 2x9728 (+SwiGLU) -> down 2560; "
-                                         "includes NF4->bf16 dequant pass of both weights",
+                                         "includes the NF4 -> bf16 dequantisation of both weights",
                    "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["tf"], "unit": "TFLOP/s",
-                                "frac": tf / pk["tf"], "peak_source": pk["source"] + " burst"},
+                                "frac": tf / pk["tf"], "frac_of_sustained": tf / pk["tf_sus"] if pk["tf_sus"] else None,
+                                "peak_source": pk["source"] + " burst"},
                    "l2": "256 MB flush between iterations"}
+        down.close()
+        del flush, xm, mid, ym
+    for f in linears:
+        f.close()
+    linears = []
+    torch.cuda.empty_cache()
 
-    tp = None
-    if (world > 1 and not args.no_tp) or args.tp:
-        for f in linears:
-            f.close()
-        linears = []
-        try:
-            tp = tp_mlp_latency(rank, world, local, stream)
-        except Exception as e:  # keep the headline line even if the extra fails
-            tp = {"error": repr(e)}
     stack = None
-    if args.stack and rank == 0:
-        for f in linears:
-            f.close()
-        linears = []
+    if rank == 0 and not args.no_stack and (world == 1 or args.stack):
         try:
             stack = decode_stack(local, stream)
+        except Exception as e:  # keep the headline line even if an extra fails
+            stack = {"error": repr(e)[:300]}
+        torch.cuda.empty_cache()
+    tp = None
+    if not args.no_tp:
+        try:
+            tp = tp_linears(rank, world, local, stream)
         except Exception as e:
-            stack = {"error": repr(e)}
+            tp = {"error": repr(e)[:300]}
 
     if rank != 0:
         if world > 1:
@@ -663,29 +802,38 @@ def main():
 
     cpu = None
     if not args.no_cpu and world == 1:
-        cpu = cpu_gate_up_baseline()
+        cpu = cpu_baselines()
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x nf4 -> f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": "cfg2 fused gate+up+SiLU NF4 GEMV, M=1, K=2560, 2x9728 rows, bs64 double-quant",
+        "config": {"workload": WORKLOAD,
                    "layers_per_step": layers, "bytes_per_step": layers * GATE_UP_ALGO_BYTES,
                    "l2": f"inputs larger than L2: {layers} distinct weight copies = "
                          f"{layers * GATE_UP_WEIGHT_BYTES / 1e6:.0f} MB per step",
-                   "launch": "CUDA graph of the C-ABI calls", "parallelism": f"replicas x{world}"},
+                   "launch": f"one chained launch of {layers} operations per step (aila_nf4_chain_run), "
+                             "replayed from a CUDA graph", "parallelism": f"replicas x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                     "peak_source": pk["source"], "launch_us": launch_us,
-                     "algorithmic_bytes_per_launch": GATE_UP_ALGO_BYTES,
+                     "frac": achieved / pk["hbm"], "traffic": NCU_TRAFFIC_BYTES_PER_OP,
+                     "peak_source": pk["source"], "operation_us": op_us,
+                     "algorithmic_bytes_per_operation": GATE_UP_ALGO_BYTES,
                      "frac_of_nominal_8TBps": achieved / 8000.0},
-        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": layers * 2 * H,
-                "d2h_bytes_per_step": layers * 2 * FF,
-                "note": "aila_nf4_forward_gate_up_swiglu_host per layer: pinned H2D copy of x, kernel "
-                        "whose epilogue stores y straight into the pinned host buffer (the D2H "
-                        "bytes cross PCIe as the kernel's stores), stream sync"},
-        "gpu_launches": args.steps * layers,
+        "per_call": {"what": "the same operations as separate aila_nf4_forward_gate_up_swiglu calls "
+                             "(one launch each, CUDA graph)", "launch_us": call_us,
+                     "frac": GATE_UP_ALGO_BYTES / call_us / 1e3 / pk["hbm"]},
+        "cfg1": {"workload": "cfg1 NF4 GEMV 2560 -> 9728, M=1: 36 distinct weights, one chained launch",
+                 "operation_us": cfg1_us, "algorithmic_bytes_per_operation": CFG1_ALGO_BYTES,
+                 "frac": CFG1_ALGO_BYTES / cfg1_us / 1e3 / pk["hbm"]},
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": 2 * H, "d2h_bytes_per_step": 2 * FF,
+                "note": "aila_nf4_chain_run_host: pinned H2D copy of x, the chained launch, D2H copy of the "
+                        "last operation's output, one stream sync",
+                "per_call_value": layers * GATE_UP_WEIGHT_BYTES / e2e_call_s / 1e9,
+                "per_call_note": "aila_nf4_forward_gate_up_swiglu_host per layer: H2D x, kernel storing y "
+                                 "into the pinned host buffer, sync - 36 times per step"},
+        "parity_max_rel_err_layer0": parity,
+        "gpu_launches": args.steps,
         "clocks": clocks.summary(),
         "step_ms_min_max": [min(step_ms), max(step_ms)],
     }

@@ -207,12 +207,17 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu_host(
  *    streams) race on it - keep calls to this entry point on one stream per GPU;
  *  - the first call on each GPU looks up the array's device address; make that call before any
  *    stream capture begins.
- * Results are identical to aila_nf4_forward with seq_len == 1.
+ * Results are identical to aila_nf4_forward with seq_len == 1 (it always runs the streaming ring
+ * kernel, whatever aila_nf4_set_gemv_kernel says). A bounded wait that runs out inside the
+ * kernel leaves a code in a status word of the same array: aila_nf4_static_check(device, stream)
+ * reads and clears it (synchronises the stream; allocates nothing) and returns
+ * AILA_NF4_ERR_KERNEL_TIMEOUT if a wait expired since the last check.
  */
 AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_static(const AilaNf4Linear* linear,
                                                           const void* x_bf16, void* y_bf16,
                                                           const void* residual_bf16,
                                                           void* stream);
+AILA_NF4_API AilaNf4Status aila_nf4_static_check(int device, void* stream);
 
 /*
  * Row-parallel decode with the sum exchange folded into the GEMV. No reference counterpart
@@ -401,8 +406,9 @@ AILA_NF4_API AilaNf4Status aila_nf4_expand_absmax(const AilaNf4Linear* linear, v
 /*
  * Kernel selection for the seq_len == 1 route, for A/B measurement: 0 = automatic,
  * 1 = plain CUDA-core kernel (fp32 weights, exactly the reference's arithmetic up to
- * summation order), 2 = streaming tensor-core kernel with a shared-memory ring, 3 = the chained
- * kernel as a one-operation launch (what automatic picks when it takes the call). Process-wide; also settable with the
+ * summation order), 2 = streaming tensor-core kernel with a shared-memory ring (what automatic
+ * picks for a single call when it takes the shape), 3 = the chained kernel as a one-operation
+ * launch. Process-wide; also settable with the
  * environment variable AILA_NF4_GEMV_KERNEL read at first use.
  */
 AILA_NF4_API AilaNf4Status aila_nf4_set_gemv_kernel(int which);

@@ -20,6 +20,15 @@ def nf4():
     return linear
 
 
+@pytest.fixture(autouse=True)
+def chained_kernel_for_single_calls(nf4):
+    """Single forward calls in this file run the chained kernel too (as one-operation launches), so
+    that "the same linears called one by one" can be compared bit for bit."""
+    nf4.set_gemv_kernel(3)
+    yield
+    nf4.set_gemv_kernel(0)
+
+
 @pytest.fixture(scope="module")
 def scratch(nf4):
     s = nf4.Bnb4BitLinearScratch(0)

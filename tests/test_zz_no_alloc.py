@@ -35,8 +35,12 @@ def test_static_scratch_entry_matches_regular_entry(oracle, N, K):
         y_ref = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
         lin.forward(scratch, x, y_ref, 1, add_residual=res)
         y = torch.full((1, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         lin.forward_decode_static(x, y, add_residual=res)
         torch.cuda.synchronize()
+        if call == 1:  # (the first call may load the kernel's code)
+            assert torch.cuda.mem_get_info()[0] == free_before, "the entry point allocated device memory"
         assert_close_norm(bf16_bits(y).reshape(-1), bf16_bits(y_ref).reshape(-1), REL,
                           f"static vs regular, call {call}")
         assert np.array_equal(bf16_bits(y), bf16_bits(y_ref)), f"call {call}: not bit-identical"
@@ -45,6 +49,7 @@ def test_static_scratch_entry_matches_regular_entry(oracle, N, K):
                                   residual=bf16_bits(res).reshape(-1))
         assert_close_norm(bf16_bits(y).reshape(-1), want_oracle, REL, f"static vs oracle, call {call}")
     scratch.check()
+    nf4.static_check(0)  # the status word of the built-in work space: no wait ran out
 
 
 def test_static_scratch_entry_rejects_oversize():
