@@ -140,11 +140,6 @@ __device__ __forceinline__ uint2 ldg_stream_v2(const uint8_t* p) {
                  : "l"(p));
     return v;
 }
-__device__ __forceinline__ uint32_t ldg_stream_u8(const uint8_t* p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u8 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ uint32_t ldg_stream_u32(const uint8_t* p) {
     uint32_t v;
     asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
@@ -241,7 +236,12 @@ __device__ __forceinline__ void bar_arrive(int id, int count) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
+// KIND: how the absmax values are stored in the unit stream (the same for every operation of a
+// launch): it fixes the distance between units, so every weight load is base + constant.
+template <int KIND>
 __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const ChainParams p) {
+    constexpr int ST = KIND == kAbsmaxCodes ? kUnitStrideCodes : kUnitStrideF32;
+    constexpr bool codes = KIND == kAbsmaxCodes;
     const uint32_t base = smem_u32(chain_smem);
     uint8_t* gen = chain_smem - base;  // generic pointer to shared-window address 0
     const int tid = threadIdx.x;
@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         }
     // the step about to run: items [pos, pos + n) of this warp's range [.., w1), pair / first block,
     // where each half's units start (this lane's bytes), distance between units
-    int pos = 0, w1 = 0, pair = 0, kb0 = 0, n = 0, stride = kUnitStrideCodes;
+    int pos = 0, w1 = 0, pair = 0, kb0 = 0, n = 0;
     const uint8_t* ph0 = nullptr;
     const uint8_t* ph1 = nullptr;
     bool loaded = false;  // W / raw / sc already hold the first step of the operation that starts next
@@ -640,19 +640,22 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
 
     auto half_ptr = [&](const ChainOpDev& o, int h, int pr, int kb) {
         const int tile = min(pr + h * o.pair_offset, o.n_tiles - 1);
-        return o.units + ((size_t)tile * o.KB + kb) * (size_t)o.unit_stride + lane_off;
+        return o.units + ((size_t)tile * o.KB + kb) * (size_t)ST + lane_off;
     };
-    auto load_half = [&](int h, int u, const uint8_t* q, int st) {
-        W[h][u][0] = ldg_stream_v2(q + u * st);
-        W[h][u][1] = ldg_stream_v2(q + u * st + 256);
+    auto load_half = [&](int h, int u, const uint8_t* q) {
+        W[h][u][0] = ldg_stream_v2(q + u * ST);
+        W[h][u][1] = ldg_stream_v2(q + u * ST + 256);
     };
     // Scale inputs of a step, fetched one step ahead: the absmax codes (or fp32 absmax) of this
     // lane's block t, rows g and g+8 of both halves, and for codes the second-level scale
     // nabs[flat / 256] of each; rowflat / rowoff follow the step's pair.
+    // (this lane's block t of a step: its absmax entries sit scale_off bytes after the pointer the
+    // weight loads use)
+    const int scale_off = t * ST + kUnitNibbleBytes - (int)lane_off;
+    const uint32_t code_sel = 0x7604u | ((uint32_t)(g & 3) << 4);  // PRMT: byte g % 4 of a code word into bits [8,16)
     auto prepare_scales = [&](const ChainOpDev& o, int oj, int pr, int kb, int nn, const uint8_t* q0,
                               const uint8_t* q1) {
-        const bool cd = o.absmax_kind == kAbsmaxCodes;
-        if (cd && (pr != prep_pair || oj != prep_op)) {
+        if (codes && (pr != prep_pair || oj != prep_op)) {
             prep_pair = pr;
             prep_op = oj;
 #pragma unroll
@@ -667,14 +670,13 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 }
         }
         if (t < nn) {
-            const int st = o.unit_stride;
-            const uint8_t* s0 = q0 - lane_off + t * st + kUnitNibbleBytes;
-            const uint8_t* s1 = q1 - lane_off + t * st + kUnitNibbleBytes;
-            if (cd) {
-                raw[0][0] = ldg_stream_u8(s0 + g);
-                raw[0][1] = ldg_stream_u8(s0 + g + 8);
-                raw[1][0] = ldg_stream_u8(s1 + g);
-                raw[1][1] = ldg_stream_u8(s1 + g + 8);
+            if (codes) {
+                // the four-byte words that hold the codes of rows g and g + 8
+                const int w0 = (g >> 2) * 4;
+                raw[0][0] = ldg_stream_u32(q0 + scale_off + w0);
+                raw[0][1] = ldg_stream_u32(q0 + scale_off + w0 + 8);
+                raw[1][0] = ldg_stream_u32(q1 + scale_off + w0);
+                raw[1][1] = ldg_stream_u32(q1 + scale_off + w0 + 8);
                 const unsigned kbt = (unsigned)(kb + t) >> o.sp.blk_shift;
                 const float* nabs = o.sp.nabs;
                 const int nbs_shift = o.sp.nbs_shift;
@@ -683,10 +685,10 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
 #pragma unroll
                     for (int r = 0; r < 2; ++r) sc[h][r] = __ldg(nabs + ((rowflat[h][r] + kbt) >> nbs_shift));
             } else {
-                raw[0][0] = ldg_stream_u32(s0 + 4 * g);
-                raw[0][1] = ldg_stream_u32(s0 + 4 * g + 32);
-                raw[1][0] = ldg_stream_u32(s1 + 4 * g);
-                raw[1][1] = ldg_stream_u32(s1 + 4 * g + 32);
+                raw[0][0] = ldg_stream_u32(q0 + scale_off + 4 * g);
+                raw[0][1] = ldg_stream_u32(q0 + scale_off + 4 * g + 32);
+                raw[1][0] = ldg_stream_u32(q1 + scale_off + 4 * g);
+                raw[1][1] = ldg_stream_u32(q1 + scale_off + 4 * g + 32);
             }
         }
     };
@@ -717,13 +719,12 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
     auto issue_first = [&](const ChainOpDev& o, int oj) {  // this warp's first step of operation oj
         const First f = first_step(o);
         pos = f.pos; w1 = f.w1; pair = f.pair; kb0 = f.kb0; n = f.n; ph0 = f.p0; ph1 = f.p1;
-        stride = o.unit_stride;
         if (n > 0) {
 #pragma unroll
             for (int u = 0; u < kStepUnits; ++u)
                 if (u < n) {
-                    load_half(0, u, ph0, stride);
-                    load_half(1, u, ph1, stride);
+                    load_half(0, u, ph0);
+                    load_half(1, u, ph1);
                 }
             prepare_scales(o, oj, pair, kb0, n, ph0, ph1);
         }
@@ -868,7 +869,6 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         const ChainOpDev& op = desc(oi);
         const unsigned tag = tag_of(oi);
         const int KB = op.KB;
-        const bool codes = op.absmax_kind == kAbsmaxCodes;
         const bool has_next = oi + 1 < n_ops;
         // the finalizer is through with operation oi - kRing: its slots are ours
         if (oi >= kRing) bar_sync(kBarGo + (oi & (kRing - 1)), kChainThreads);
@@ -905,7 +905,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 pair_n = pair + 1;
             }
             // what the freed registers are re-loaded with
-            int ld_n = 0, ld_stride = stride, ld_pair = pair_n, ld_kb0 = kb0_n, ld_pos = pos_n, ld_w1 = w1;
+            int ld_n = 0, ld_pair = pair_n, ld_kb0 = kb0_n, ld_pos = pos_n, ld_w1 = w1;
             const uint8_t* pl0 = ph0;
             const uint8_t* pl1 = ph1;
             bool cross = false;
@@ -920,7 +920,6 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 cross = true;
                 ld_n = f.n; ld_pair = f.pair; ld_kb0 = f.kb0; ld_pos = f.pos; ld_w1 = f.w1;
                 pl0 = f.p0; pl1 = f.p1;
-                ld_stride = nx.unit_stride;
             }
             if (pair != cur_pair) {
                 cur_pair = pair;
@@ -934,7 +933,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {
                     if (codes) {
-                        const float nm = __uint_as_float(lds_u32(__byte_perm(raw[h][r], nmap_base, 0x7604)));
+                        const float nm = __uint_as_float(lds_u32(__byte_perm(raw[h][r], nmap_base, code_sel)));
                         am[h][r] = __fadd_rn(__fmul_rn(nm, sc[h][r]), rowoff[h][r]);
                     } else {
                         am[h][r] = __uint_as_float(raw[h][r]);
@@ -976,7 +975,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
 #pragma unroll
                         for (int i = 0; i < 16; ++i) a[i] = lds_u32(a[i]);
                         // the registers of this unit are free: fetch the same unit of the next step
-                        if (u < ld_n) load_half(h, u, h == 0 ? pl0 : pl1, ld_stride);
+                        if (u < ld_n) load_half(h, u, h == 0 ? pl0 : pl1);
                         float d[4];
                         mma_16816_init(d, a[0], a[1], a[2], a[3], xq0.x, xq0.y);
                         mma_16816(d, a[4], a[5], a[6], a[7], xq0.z, xq0.w);
@@ -987,8 +986,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                         acc[h][1] = fmaf((t == u) ? am[h][1] : 0.0f, d[2], acc[h][1]);
                     }
                 } else if (u < ld_n) {
-                    load_half(0, u, pl0, ld_stride);
-                    load_half(1, u, pl1, ld_stride);
+                    load_half(0, u, pl0);
+                    load_half(1, u, pl1);
                 }
             }
             if (ld_n > 0) prepare_scales(cross ? desc(oi + 1) : op, cross ? oi + 1 : oi, ld_pair, ld_kb0, ld_n, pl0, pl1);
@@ -1033,7 +1032,6 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             w1 = ld_w1;
             pair = ld_pair;
             kb0 = ld_kb0;
-            stride = ld_stride;
             ph0 = pl0;
             ph1 = pl1;
             if (cross) {
@@ -1086,8 +1084,11 @@ cudaError_t chain_prepare_kernel(int device, int smem) {
     static int have[64] = {0};
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
     if (have[device] >= smem) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(gemv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemv_chain_kernel<kAbsmaxCodes>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kChainSmemMax);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemv_chain_kernel<kAbsmaxF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kChainSmemMax);
     if (e != cudaSuccess) return e;
     have[device] = kChainSmemMax;
     return cudaSuccess;
@@ -1120,7 +1121,7 @@ bool chain_fill_op(ChainOpDev* d, const AilaNf4Linear& w, int64_t ff_pair, int g
     return true;
 }
 
-cudaError_t chain_launch(const ChainParams& p, int grid, cudaStream_t s) {
+cudaError_t chain_launch(const ChainParams& p, int kind, int grid, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kChainThreads);
@@ -1131,7 +1132,8 @@ cudaError_t chain_launch(const ChainParams& p, int grid, cudaStream_t s) {
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gemv_chain_kernel, p);
+    return kind == kAbsmaxCodes ? cudaLaunchKernelEx(&cfg, gemv_chain_kernel<kAbsmaxCodes>, p)
+                                : cudaLaunchKernelEx(&cfg, gemv_chain_kernel<kAbsmaxF32>, p);
 }
 
 void chain_params_from_scratch(ChainParams* p, const AilaNf4Scratch& sc) {
@@ -1180,7 +1182,7 @@ AilaNf4Status launch_gemv_chain_single(const AilaNf4Linear& w, AilaNf4Scratch& s
     chain_params_from_scratch(&p, sc);
     chain_plan_smem(&p, w.K, 1);
     NF4_CUDA(chain_prepare_kernel(sc.device, p.smem_bytes));
-    NF4_CUDA(chain_launch(p, sc.sm_count, s));
+    NF4_CUDA(chain_launch(p, w.absmax_kind, sc.sm_count, s));
     return AILA_NF4_OK;
 }
 
@@ -1209,6 +1211,7 @@ AilaNf4Status ensure_chain_scratch(AilaNf4Scratch* sc) {
 struct AilaNf4Chain {
     int device = 0;
     int n_ops = 0;
+    int kind = nf4::kAbsmaxCodes;  // how every linear of the chain stores its absmax
     AilaNf4Scratch* scratch = nullptr;
     nf4::ChainOpDev* d_ops = nullptr;
     nf4::ChainParams params;
@@ -1236,8 +1239,9 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const 
         const AilaNf4Linear& w = *o.linear;
         if (w.device != scratch->device)
             return fail(AILA_NF4_ERR_INVALID_ARGUMENT, at + "scratch and linear live on different devices");
-        if (w.d_qmap != first->d_qmap || w.d_nmap != first->d_nmap)
-            return fail(AILA_NF4_ERR_UNSUPPORTED, at + "all linears of a chain must share their code books");
+        if (w.d_qmap != first->d_qmap || w.d_nmap != first->d_nmap || w.absmax_kind != first->absmax_kind)
+            return fail(AILA_NF4_ERR_UNSUPPORTED,
+                        at + "all linears of a chain must share their code books and absmax storage");
         if (o.ff_dim < 0 || (o.ff_dim > 0 && (w.N != 2 * o.ff_dim || o.ff_dim % nf4::kTileRows != 0)))
             return fail(AILA_NF4_NOT_APPLICABLE, at + "out_features != 2 * ff_dim or ff_dim not a multiple of 16");
         if (o.ff_dim > 0 && o.residual_bf16)
@@ -1293,6 +1297,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const 
     };
     ch->device = scratch->device;
     ch->n_ops = n_ops;
+    ch->kind = first->absmax_kind;
     ch->scratch = scratch;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ch->d_ops), (size_t)n_ops * nf4::kDescBytes);
     if (e == cudaSuccess)
@@ -1337,7 +1342,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_run(AilaNf4Chain* chain, void* stream)
     NF4_CUDA(cudaGetDevice(&prev));
     if (prev != chain->device) NF4_CUDA(cudaSetDevice(chain->device));
     nf4::chain_params_from_scratch(&chain->params, *chain->scratch);
-    const cudaError_t e = nf4::chain_launch(chain->params, chain->scratch->sm_count,
+    const cudaError_t e = nf4::chain_launch(chain->params, chain->kind, chain->scratch->sm_count,
                                             static_cast<cudaStream_t>(stream));
     if (prev != chain->device) cudaSetDevice(prev);
     NF4_CUDA(e);
@@ -1358,7 +1363,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_run_host(AilaNf4Chain* chain, const vo
                                     cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess) {
         nf4::chain_params_from_scratch(&chain->params, *chain->scratch);
-        e = nf4::chain_launch(chain->params, chain->scratch->sm_count, s);
+        e = nf4::chain_launch(chain->params, chain->kind, chain->scratch->sm_count, s);
     }
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(y_host_bf16, chain->last_y, (size_t)chain->last_out * 2, cudaMemcpyDeviceToHost, s);
