@@ -473,20 +473,16 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 const uint32_t slots = a_slots + (uint32_t)r * (kChainWarps * 256u);
                 const uint32_t segs = a_seg + (uint32_t)r * (kChainWarps * 8u);
                 constexpr int NQ = kConsumerWarps * 2;
-                // all tags first (the same word for every lane): which slots hold sums, where pairs start
-                int tq[NQ];
-#pragma unroll
-                for (int q = 0; q < NQ; ++q) tq[q] = (int)lds_u32(segs + 4u * (uint32_t)q);
-                unsigned valid = 0u, first = 0u;
+                // lane q holds the tag of slot q: which slots hold sums, and which of them start a pair
+                // (the valid tags never decrease)
+                const int tq = lane < NQ ? (int)lds_u32(segs + 4u * (uint32_t)lane) : -1;
+                const unsigned valid = __ballot_sync(0xffffffffu, tq >= 0);
+                unsigned first;
                 {
-                    int cur = -1;
-#pragma unroll
-                    for (int q = 0; q < NQ; ++q)
-                        if (tq[q] >= 0) {
-                            valid |= 1u << q;
-                            if (tq[q] != cur) first |= 1u << q;
-                            cur = tq[q];
-                        }
+                    const unsigned before = valid & ((1u << lane) - 1u);
+                    const int prev = 31 - __clz((int)before);  // the valid slot before this one, or -1
+                    const int ptag = __shfl_sync(0xffffffffu, tq, prev & 31);
+                    first = __ballot_sync(0xffffffffu, tq >= 0 && (before == 0u || ptag != tq));
                 }
                 // what the epilogue needs, read from the descriptor once
                 const int e_swiglu = op.swiglu, e_n_out = op.n_out, e_pair_offset = op.pair_offset;
@@ -521,33 +517,39 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                                            ((unsigned long long)tag << 32) | (unsigned long long)(bits | (hi16 << 16)));
                     }
                 };
-                int checked = 0;  // 1: the exchange slots of this operation may be written
-                while (first != 0u && checked >= 0) {
-                    const int q0 = __ffs((int)first) - 1;
-                    first &= first - 1u;
-                    // the pair's slots: the valid ones from q0 up to the next pair's first slot
-                    const unsigned upto = first != 0u ? ((1u << (__ffs((int)first) - 1)) - 1u) : 0xffffffffu;
-                    unsigned run = valid & upto & ~((1u << q0) - 1u);
-                    // up to six slots with independent loads, any further ones after them, in slot order
-                    float part[6];
+                // The sums of the pair whose first slot is the lowest bit of `rest`, added in slot order
+                // (eight independent loads at a time); takes that pair out of `rest`.
+                auto gather = [&](unsigned& rest, int& pr, float& sum) {
+                    const int q0 = __ffs((int)rest) - 1;
+                    rest &= rest - 1u;
+                    const unsigned upto = rest != 0u ? ((1u << (__ffs((int)rest) - 1)) - 1u) : 0xffffffffu;
+                    unsigned run = (valid & upto) >> q0;  // bit 0 is set
+                    pr = __shfl_sync(0xffffffffu, tq, q0);
+                    uint32_t at = slots + (uint32_t)q0 * 128u + 4u * lane;
+                    sum = 0.0f;
+                    do {
+                        float part[8];
 #pragma unroll
-                    for (int k = 0; k < 6; ++k) {
-                        part[k] = 0.0f;
-                        if (run != 0u) {
-                            const int q = __ffs((int)run) - 1;
-                            run &= run - 1u;
-                            part[k] = lds_f32(slots + (uint32_t)q * 128u + 4u * lane);
+                        for (int k = 0; k < 8; ++k) {
+                            part[k] = 0.0f;
+                            if (run & (1u << k)) part[k] = lds_f32(at + 128u * k);
                         }
-                    }
-                    float sum = part[0];
 #pragma unroll
-                    for (int k = 1; k < 6; ++k) sum += part[k];  // (absent slots add +0)
-                    for (; run != 0u; run &= run - 1u)
-                        sum += lds_f32(slots + (uint32_t)(__ffs((int)run) - 1) * 128u + 4u * lane);
-                    int pr = 0;
-#pragma unroll
-                    for (int q = 0; q < NQ; ++q)
-                        if (q == q0) pr = tq[q];
+                        for (int k = 0; k < 8; ++k) sum += part[k];  // (absent slots add +0)
+                        run >>= 8;
+                        at += 1024u;
+                    } while (run != 0u);
+                };
+                int checked = 0;  // 1: the exchange slots of this operation may be written
+                int pr_next = 0;
+                float sum_next = 0.0f;
+                bool more = first != 0u;
+                if (more) gather(first, pr_next, sum_next);
+                while (more && checked >= 0) {
+                    const int pr = pr_next;
+                    float sum = sum_next;
+                    more = first != 0u;
+                    if (more) gather(first, pr_next, sum_next);  // (its loads overlap this pair's epilogue)
                     const int t0 = pr * KB, t1 = t0 + KB;
                     const int lo = max(i0, t0), hi = min(i1, t1);
                     const bool writes_ring = e_publish || hi - lo != KB;
