@@ -111,6 +111,7 @@ void free_linear(AilaNf4Linear* l) {
     release_table(l->d_nmap);
     cudaFree(l->d_nabs);
     cudaFree(l->d_cache_bf16);
+    cudaFree(l->d_row_scales);
     delete l;
 }
 
@@ -133,7 +134,17 @@ bool cache_dequant_enabled() {
     return on;
 }
 
+// Last step of every way a linear comes into being: the per-row second-level scales of the
+// chained decode kernel (when no row changes its second-level block twice), and the optional
+// bf16 copy.
 AilaNf4Status maybe_cache_dequant(AilaNf4Linear* l) {
+    if (l->absmax_kind == nf4::kAbsmaxCodes && l->KU <= l->nbs * (l->blocksize / nf4::kUnitK)) {
+        cudaError_t e = cudaMalloc(&l->d_row_scales, (size_t)l->N * 16 + 16);
+        if (e != cudaSuccess) return nf4::cuda_fail(e, "cudaMalloc(row scales)");
+        NF4_CUDA(nf4::launch_row_scales(*l, 0));
+        NF4_CUDA(cudaDeviceSynchronize());
+        l->device_bytes += (int64_t)l->N * 16;
+    }
     if (!cache_dequant_enabled()) return AILA_NF4_OK;
     const size_t bytes = (size_t)l->N * (size_t)l->K * 2;
     cudaError_t e = cudaMalloc(&l->d_cache_bf16, bytes + 256);

@@ -67,6 +67,16 @@ constexpr int kDescBytes = 256;
 constexpr int kChainMaxGrid = 256;       // CTAs a launch may have (one per SM)
 
 // One operation of a chain as the kernel sees it (kDescBytes each, copied to shared memory).
+// Second-level scales of one output row (8-bit absmax codes): the row's blocks use `lo` up to unit
+// column `cross` and `hi` from there on (a row of at most 256 blocks changes its second-level
+// block at most once); absmax = code_book[code] * scale + offset.
+struct RowScales {
+    float lo, hi;
+    int cross;
+    float offset;
+};
+static_assert(sizeof(RowScales) == 16, "one 16-byte load per row");
+
 struct ChainOpDev {
     const uint8_t* units;
     ScaleParams sp;
@@ -89,7 +99,8 @@ struct ChainOpDev {
     uint32_t div_kb_m;
     int div_kb_s;
     int publish;                  // 1: the next operation reads this output (exchange words)
-    int pad_[8];
+    const RowScales* row_scales;  // [n_rows], 8-bit absmax codes only
+    int pad_[6];
 };
 static_assert(sizeof(ChainOpDev) == kDescBytes, "descriptor size");
 
@@ -617,8 +628,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
     // ---- per-warp pipeline state; it crosses operation boundaries ----
     uint2 W[2][kStepUnits][2];   // packed weights of the step about to run (loads in flight)
     uint32_t raw[2][2];          // absmax codes (or fp32 absmax) of this lane's block of that step
-    float sc[2][2];              // their second-level scales
-    unsigned rowflat[2][2];
+    float slo[2][2], shi[2][2];  // second-level scales of those rows: before / from column scross
+    int scross[2][2];
     float rowoff[2][2];
     int prep_op = -1, prep_pair = -1;
 #pragma unroll
@@ -626,8 +637,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             raw[h][r] = 0u;
-            sc[h][r] = 0.0f;
-            rowflat[h][r] = 0u;
+            slo[h][r] = shi[h][r] = 0.0f;
+            scross[h][r] = 0;
             rowoff[h][r] = 0.0f;
 #pragma unroll
             for (int u = 0; u < kStepUnits; ++u) W[h][u][r] = make_uint2(0u, 0u);
@@ -660,15 +671,18 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         if (codes && (pr != prep_pair || oj != prep_op)) {
             prep_pair = pr;
             prep_op = oj;
+            const float4* table = reinterpret_cast<const float4*>(o.row_scales);
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {
                     const int tile = min(pr + h * o.pair_offset, o.n_tiles - 1);
                     const int row = min(tile * kTileRows + g + 8 * r, o.n_rows - 1);
-                    const SegmentRow sr = segment_row(o.sp, row);
-                    rowflat[h][r] = sr.flat;
-                    rowoff[h][r] = sr.offset;
+                    const float4 e = __ldg(table + row);
+                    slo[h][r] = e.x;
+                    shi[h][r] = e.y;
+                    scross[h][r] = __float_as_int(e.z);
+                    rowoff[h][r] = e.w;
                 }
         }
         if (t < nn) {
@@ -679,13 +693,6 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 raw[0][1] = ldg_stream_u32(q0 + scale_off + w0 + 8);
                 raw[1][0] = ldg_stream_u32(q1 + scale_off + w0);
                 raw[1][1] = ldg_stream_u32(q1 + scale_off + w0 + 8);
-                const unsigned kbt = (unsigned)(kb + t) >> o.sp.blk_shift;
-                const float* nabs = o.sp.nabs;
-                const int nbs_shift = o.sp.nbs_shift;
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int r = 0; r < 2; ++r) sc[h][r] = __ldg(nabs + ((rowflat[h][r] + kbt) >> nbs_shift));
             } else {
                 raw[0][0] = ldg_stream_u32(q0 + scale_off + 4 * g);
                 raw[0][1] = ldg_stream_u32(q0 + scale_off + 4 * g + 32);
@@ -936,7 +943,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 for (int r = 0; r < 2; ++r) {
                     if (codes) {
                         const float nm = __uint_as_float(lds_u32(__byte_perm(raw[h][r], nmap_base, code_sel)));
-                        am[h][r] = __fadd_rn(__fmul_rn(nm, sc[h][r]), rowoff[h][r]);
+                        const float second = kb0 + t >= scross[h][r] ? shi[h][r] : slo[h][r];
+                        am[h][r] = __fadd_rn(__fmul_rn(nm, second), rowoff[h][r]);
                     } else {
                         am[h][r] = __uint_as_float(raw[h][r]);
                     }
@@ -1097,11 +1105,28 @@ cudaError_t chain_prepare_kernel(int device, int smem) {
 }
 
 // Fills the part of a descriptor that depends only on the linear and the grid.
+__global__ void row_scales_kernel(ScaleParams sp, int n_rows, int KB, RowScales* out) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= n_rows) return;
+    const SegmentRow sr = segment_row(sp, n);
+    const unsigned nbs = 1u << sp.nbs_shift;
+    const unsigned first = sr.flat >> sp.nbs_shift;
+    const long long cross = (long long)(nbs - (sr.flat & (nbs - 1u))) << sp.blk_shift;
+    RowScales e;
+    e.lo = __ldg(sp.nabs + first);
+    e.hi = cross < KB ? __ldg(sp.nabs + first + 1) : e.lo;
+    e.cross = (int)(cross < 0x7fffffffll ? cross : 0x7fffffffll);
+    e.offset = sr.offset;
+    out[n] = e;
+}
+
 bool chain_fill_op(ChainOpDev* d, const AilaNf4Linear& w, int64_t ff_pair, int grid) {
     std::memset(d, 0, sizeof(*d));
     const bool paired = ff_pair > 0;
     if (paired && (ff_pair % kTileRows != 0 || w.N != 2 * ff_pair)) return false;
+    if (w.absmax_kind == kAbsmaxCodes && !w.d_row_scales) return false;
     d->units = w.d_units;
+    d->row_scales = static_cast<const RowScales*>(w.d_row_scales);
     d->sp = w.scale_params();
     d->K = (int)w.K;
     d->KB = w.KU;
@@ -1150,6 +1175,13 @@ void chain_params_from_scratch(ChainParams* p, const AilaNf4Scratch& sc) {
 }
 
 }  // namespace
+
+cudaError_t launch_row_scales(const AilaNf4Linear& l, cudaStream_t s) {
+    const int threads = 256;
+    row_scales_kernel<<<(unsigned)((l.N + threads - 1) / threads), threads, 0, s>>>(
+        l.scale_params(), (int)l.N, l.KU, static_cast<RowScales*>(l.d_row_scales));
+    return cudaGetLastError();
+}
 
 bool gemv_chain_supported(const AilaNf4Linear& w, int64_t ff_pair, const AilaNf4Scratch& sc) {
     if (!sc.d_chain_x || sc.sm_count <= 0 || sc.sm_count > kChainThreads || sc.sm_count > kChainMaxGrid)

@@ -21,6 +21,10 @@ struct AilaNf4Linear {
     float* d_nmap = nullptr;     // [256]
     float* d_nabs = nullptr;     // concatenated nested_absmax
     void* d_cache_bf16 = nullptr;  // optional bf16 [N][K] copy (AILA_BNB4_CACHE_DEQUANT=1)
+    // Per output row, for 8-bit absmax codes: the second-level scale of the row's first block, the
+    // scale after the row's (single) change of second-level block, the unit column of that change
+    // and the second-level offset (nf4::RowScales). Null when a row could change twice.
+    void* d_row_scales = nullptr;
     int64_t nabs_count = 0;
     float h_qmap[16] = {0};
     int nbs = 256;
@@ -141,6 +145,8 @@ int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);  //
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);
 AilaNf4Status check_gemv_stream_static(cudaStream_t s);
+// Fills l.d_row_scales (N entries of 16 bytes, allocated by the caller).
+cudaError_t launch_row_scales(const AilaNf4Linear& l, cudaStream_t s);
 
 // nf4_chain.cu --------------------------------------------------------------------------
 // The chained decode kernel: one cooperative launch walks a list of linears. A one-operation
