@@ -64,7 +64,8 @@ constexpr int kXBatch = 6;                 // 8-byte chunks of x one thread has 
 constexpr uint32_t kLutAddr = 65536u;      // shared-window address of the 64 KB table block
 constexpr uint32_t kXAddr = 131072u;       // x in fragment order
 constexpr int kDescBytes = 256;
-constexpr int kChainMaxGrid = 256;       // CTAs a launch may have (one per SM)
+constexpr int kChainMaxGrid = 256;         // CTAs a launch may have (one per SM)
+constexpr int kChainMaxOps = 160;          // operations of one launch (their descriptors sit in shared memory)
 
 // One operation of a chain as the kernel sees it (kDescBytes each, copied to shared memory).
 // Second-level scales of one output row (8-bit absmax codes): the row's blocks use `lo` up to unit
@@ -100,7 +101,10 @@ struct ChainOpDev {
     int div_kb_s;
     int publish;                  // 1: the next operation reads this output (exchange words)
     const RowScales* row_scales;  // [n_rows], 8-bit absmax codes only
-    int pad_[6];
+    long long half1_bytes;        // from a unit of half 0 to the same unit of half 1
+    int clamp_pair;               // pairs from here on have no half 1 of their own (it reads the last row tile)
+    int x_copy;                   // 1: x is a plain, 16-byte aligned tensor that asynchronous copies can fetch
+    int pad_[2];
 };
 static_assert(sizeof(ChainOpDev) == kDescBytes, "descriptor size");
 
@@ -154,6 +158,13 @@ __device__ __forceinline__ uint2 ldg_stream_v2(const uint8_t* p) {
 __device__ __forceinline__ uint32_t ldg_stream_u32(const uint8_t* p) {
     uint32_t v;
     asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+// the same load at a constant distance from the pointer (the distance goes into the instruction)
+template <int OFF>
+__device__ __forceinline__ uint32_t ldg_stream_u32_at(const uint8_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1+%2];" : "=r"(v) : "l"(p), "n"(OFF));
     return v;
 }
 __device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
@@ -272,7 +283,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
     const uint32_t a_seg = a_slots + kRing * kChainWarps * 2 * 32 * 4;  // [kRing][warp][2] pair whose sums the slot holds, or -1
     const uint32_t a_xbar = a_seg + kRing * kChainWarps * 2 * 4;        // [2] mbarriers: x buffer granted / filled
     const uint32_t a_rflag = a_xbar + 16;               // [8] tag of the operation that may write exchange slot tag & 7
-    const uint32_t a_desc = a_rflag + 32;
+    const uint32_t a_slice = a_rflag + 32;              // [n_ops] first work item of this CTA and of the next one
+    const uint32_t a_desc = a_slice + 8u * kChainMaxOps;
     const int n_ops = p.n_ops;
     const int xbufs = p.x_buffers;
     if (base > 2048u || a_desc + (uint32_t)n_ops * kDescBytes > kLutAddr ||
@@ -328,6 +340,11 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(row + 128u), "r"(nv) : "memory");
         }
     }
+    for (int oj = tid; oj < n_ops; oj += kChainThreads) {
+        const ChainOpDev& o = *reinterpret_cast<const ChainOpDev*>(gen + a_desc + (uint32_t)oj * kDescBytes);
+        sts_u32(a_slice + 8u * oj, (uint32_t)slice_begin(o, c));
+        sts_u32(a_slice + 8u * oj + 4u, (uint32_t)slice_begin(o, c + 1));
+    }
     const unsigned epoch0 = *(volatile unsigned*)p.ctrl;
     __syncthreads();
 
@@ -335,6 +352,13 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         return *reinterpret_cast<const ChainOpDev*>(gen + a_desc + (uint32_t)oj * kDescBytes);
     };
     auto tag_of = [&](int oj) { return epoch0 + (unsigned)oj + 1u; };
+    // work items [i0, i1) of this CTA in operation oj
+    auto my_slice = [&](int oj, int& i0, int& i1) {
+        uint32_t lo, hi;
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(a_slice + 8u * (uint32_t)oj));
+        i0 = (int)lo;
+        i1 = (int)hi;
+    };
     auto give_up = [&](int code) {
         atomicExch(p.status, code);
         atomicExch(p.ctrl + 2, 1u);
@@ -352,10 +376,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
     // An operation whose input is its own plain tensor gets it copied into the x buffer by the
     // copy engine (one bulk copy per block), with no work for the consumers (x_ext is stable:
     // operations of a chain never read through a pointer what an earlier one writes).
-    auto prestaged = [&](int oj) {
-        const ChainOpDev& o = desc(oj);
-        return o.x_ext != nullptr && o.norm_w == nullptr && (reinterpret_cast<uintptr_t>(o.x_ext) & 15) == 0;
-    };
+    auto prestaged = [&](int oj) { return desc(oj).x_copy != 0; };
     auto x_phase = [&](int oj) { return (uint32_t)((xbufs == 2 ? (oj >> 1) : oj) & 1); };
     auto x_bar = [&](int oj) { return reinterpret_cast<uint64_t*>(gen + a_xbar + 8u * (uint32_t)x_buf(oj)); };
     // The x buffer of operation oj is free (every consumer is through with its previous user):
@@ -478,7 +499,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             if (oi + xbufs < n_ops) x_grant(oi + xbufs, aborted);
             // Add up the consumers' slots pair by pair, in slot order (warp 0 slot 0, warp 0 slot 1,
             // warp 1 slot 0, ...; the pairs in them never decrease), and finish every pair.
-            const int i0 = slice_begin(op, c), i1 = slice_begin(op, c + 1);
+            int i0, i1;
+            my_slice(oi, i0, i1);
             if (!aborted && i1 > i0) {
                 const int KB = op.KB;
                 const uint32_t slots = a_slots + (uint32_t)r * (kChainWarps * 256u);
@@ -664,7 +686,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
     // nabs[flat / 256] of each; rowflat / rowoff follow the step's pair.
     // (this lane's block t of a step: its absmax entries sit scale_off bytes after the pointer the
     // weight loads use)
-    const int scale_off = t * ST + kUnitNibbleBytes - (int)lane_off;
+    const int scale_off = t * ST + kUnitNibbleBytes - (int)lane_off + (codes ? (g >> 2) * 4 : 4 * g);
     const uint32_t code_sel = 0x7604u | ((uint32_t)(g & 3) << 4);  // PRMT: byte g % 4 of a code word into bits [8,16)
     auto prepare_scales = [&](const ChainOpDev& o, int oj, int pr, int kb, int nn, const uint8_t* q0,
                               const uint8_t* q1) {
@@ -688,16 +710,15 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         if (t < nn) {
             if (codes) {
                 // the four-byte words that hold the codes of rows g and g + 8
-                const int w0 = (g >> 2) * 4;
-                raw[0][0] = ldg_stream_u32(q0 + scale_off + w0);
-                raw[0][1] = ldg_stream_u32(q0 + scale_off + w0 + 8);
-                raw[1][0] = ldg_stream_u32(q1 + scale_off + w0);
-                raw[1][1] = ldg_stream_u32(q1 + scale_off + w0 + 8);
+                raw[0][0] = ldg_stream_u32_at<0>(q0 + scale_off);
+                raw[0][1] = ldg_stream_u32_at<8>(q0 + scale_off);
+                raw[1][0] = ldg_stream_u32_at<0>(q1 + scale_off);
+                raw[1][1] = ldg_stream_u32_at<8>(q1 + scale_off);
             } else {
-                raw[0][0] = ldg_stream_u32(q0 + scale_off + 4 * g);
-                raw[0][1] = ldg_stream_u32(q0 + scale_off + 4 * g + 32);
-                raw[1][0] = ldg_stream_u32(q1 + scale_off + 4 * g);
-                raw[1][1] = ldg_stream_u32(q1 + scale_off + 4 * g + 32);
+                raw[0][0] = ldg_stream_u32_at<0>(q0 + scale_off);
+                raw[0][1] = ldg_stream_u32_at<32>(q0 + scale_off);
+                raw[1][0] = ldg_stream_u32_at<0>(q1 + scale_off);
+                raw[1][1] = ldg_stream_u32_at<32>(q1 + scale_off);
             }
         }
     };
@@ -707,9 +728,10 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         const uint8_t* p0;
         const uint8_t* p1;
     };
-    auto first_step = [&](const ChainOpDev& o) {
+    auto first_step = [&](const ChainOpDev& o, int oj) {
         First f;
-        const int i0 = slice_begin(o, c), i1 = slice_begin(o, c + 1);
+        int i0, i1;
+        my_slice(oj, i0, i1);
         f.pos = warp_begin(i0, i1 - i0, warp);
         f.w1 = warp_begin(i0, i1 - i0, warp + 1);
         f.pair = 0;
@@ -720,13 +742,14 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             f.pair = fast_div(f.pos, o.div_kb_m, o.div_kb_s);
             f.kb0 = f.pos - f.pair * o.KB;
             f.n = min(min(kStepUnits, f.w1 - f.pos), o.KB - f.kb0);
-            f.p0 = half_ptr(o, 0, f.pair, f.kb0);
-            f.p1 = half_ptr(o, 1, f.pair, f.kb0);
+            // (half 0: the unit of work item i is unit i of the stream)
+            f.p0 = o.units + (size_t)f.pos * (size_t)ST + lane_off;
+            f.p1 = f.pair < o.clamp_pair ? f.p0 + o.half1_bytes : half_ptr(o, 1, f.pair, f.kb0);
         }
         return f;
     };
     auto issue_first = [&](const ChainOpDev& o, int oj) {  // this warp's first step of operation oj
-        const First f = first_step(o);
+        const First f = first_step(o, oj);
         pos = f.pos; w1 = f.w1; pair = f.pair; kb0 = f.kb0; n = f.n; ph0 = f.p0; ph1 = f.p1;
         if (n > 0) {
 #pragma unroll
@@ -745,7 +768,9 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         const ChainOpDev& o = desc(oj);
         const unsigned tg = tag_of(oj);
         bool ok = true;
-        const int len = slice_begin(o, c + 1) - slice_begin(o, c);
+        int j0, j1;
+        my_slice(oj, j0, j1);
+        const int len = j1 - j0;
         // CTA 0 stages x even without work when it has the residual stream to write
         const bool stage = !skip && (len > 0 || (c == 0 && o.norm_w != nullptr && o.norm_hidden_out != nullptr));
         const uint32_t xa = x_addr(oj);
@@ -921,11 +946,14 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             if (pos_n < w1) {
                 n_n = min(min(kStepUnits, w1 - pos_n), KB - kb0_n);
                 ld_n = n_n;
-                pl0 = half_ptr(op, 0, pair_n, kb0_n);
-                pl1 = half_ptr(op, 1, pair_n, kb0_n);
+                // the units follow one another in memory, across pairs too; only a pair without a
+                // half 1 of its own needs its pointer worked out
+                pl0 = ph0 + n * ST;
+                pl1 = ph1 + n * ST;
+                if (kb0_n == 0 && pair_n >= op.clamp_pair) pl1 = half_ptr(op, 1, pair_n, 0);
             } else if (has_next) {
                 const ChainOpDev& nx = desc(oi + 1);
-                const First f = first_step(nx);
+                const First f = first_step(nx, oi + 1);
                 cross = true;
                 ld_n = f.n; ld_pair = f.pair; ld_kb0 = f.kb0; ld_pos = f.pos; ld_w1 = f.w1;
                 pl0 = f.p0; pl1 = f.p1;
@@ -1074,7 +1102,6 @@ int chain_window_base() {
 }
 
 constexpr int kChainSmemMax = 227 * 1024;
-constexpr int kChainMaxOps = 160;
 
 // bytes between two x buffers for a launch whose largest in_features is k_max
 int chain_x_pitch(int64_t k_max) { return (int)(k_max / kUnitK) * kXBlockPitch; }
@@ -1145,7 +1172,14 @@ bool chain_fill_op(ChainOpDev* d, const AilaNf4Linear& w, int64_t ff_pair, int g
     d->slice_r = (int)(total % grid);
     make_fast_div((uint32_t)grid, &d->div_g_m, &d->div_g_s);
     make_fast_div((uint32_t)w.KU, &d->div_kb_m, &d->div_kb_s);
+    d->half1_bytes = (long long)pairs * w.KU * w.unit_stride;
+    d->clamp_pair = w.RT - (int)pairs;
     return true;
+}
+
+// After the tensors of an operation are known.
+void chain_seal_op(ChainOpDev* d) {
+    d->x_copy = d->x_ext != nullptr && d->norm_w == nullptr && (reinterpret_cast<uintptr_t>(d->x_ext) & 15) == 0;
 }
 
 cudaError_t chain_launch(const ChainParams& p, int kind, int grid, cudaStream_t s) {
@@ -1209,6 +1243,7 @@ AilaNf4Status launch_gemv_chain_single(const AilaNf4Linear& w, AilaNf4Scratch& s
         p.inline_op.norm_hidden_out = static_cast<uint16_t*>(norm->hidden_out);
         p.inline_op.norm_eps = norm->eps;
     }
+    chain_seal_op(&p.inline_op);
     p.ops = nullptr;
     p.n_ops = 1;
     p.qmap = w.d_qmap;
@@ -1319,6 +1354,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const 
             d.norm_eps = o.norm->eps;
         }
         if (!d.y && i == n_ops - 1) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, at + "the last operation needs an output");
+        nf4::chain_seal_op(&d);
         k_max = w.K > k_max ? w.K : k_max;
     }
     int prev = -1;
