@@ -56,9 +56,8 @@ constexpr int kChainWarps = 16;            // 15 consumer warps and the finalize
 constexpr int kChainThreads = kChainWarps * 32;
 constexpr int kConsumerWarps = kChainWarps - 1;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-// x / 15 for 0 <= x < 2^31 (see fast_div)
-constexpr uint32_t kDivWarpsM = 2290649225u;  // ceil(2^35 / 15)
-constexpr int kDivWarpsS = 35;
+constexpr int kItemsPerWarp = 8;           // work items a consumer warp should get from an operation, at least
+constexpr int kMinWarps = 6;               // consumer warps an operation uses, at least
 constexpr int kStepUnits = 4;
 constexpr int kXBatch = 6;                 // 8-byte chunks of x one thread has in flight
 constexpr uint32_t kLutAddr = 65536u;      // shared-window address of the 64 KB table block
@@ -88,7 +87,9 @@ struct ChainOpDev {
     const uint16_t* norm_w;
     uint16_t* norm_hidden_out;
     float norm_eps;
-    int K, KB, unit_stride, absmax_kind;
+    int K, KB;
+    int n_warps;                  // consumer warps that share a CTA's slice of this operation
+    uint32_t div_w_m;             // x / n_warps as (x * div_w_m) >> div_w_s
     int n_rows, n_tiles;          // rows / row tiles of the linear
     int swiglu;                   // 1: halves are gate and up, output silu(gate) * up
     int pair_offset;              // row-tile distance from half 0 to half 1
@@ -104,7 +105,8 @@ struct ChainOpDev {
     long long half1_bytes;        // from a unit of half 0 to the same unit of half 1
     int clamp_pair;               // pairs from here on have no half 1 of their own (it reads the last row tile)
     int x_copy;                   // 1: x is a plain, 16-byte aligned tensor that asynchronous copies can fetch
-    int pad_[2];
+    int div_w_s;
+    int pad_[1];
 };
 static_assert(sizeof(ChainOpDev) == kDescBytes, "descriptor size");
 
@@ -155,12 +157,7 @@ __device__ __forceinline__ uint2 ldg_stream_v2(const uint8_t* p) {
                  : "l"(p));
     return v;
 }
-__device__ __forceinline__ uint32_t ldg_stream_u32(const uint8_t* p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
-// the same load at a constant distance from the pointer (the distance goes into the instruction)
+// streaming load at a constant distance from the pointer (the distance goes into the instruction)
 template <int OFF>
 __device__ __forceinline__ uint32_t ldg_stream_u32_at(const uint8_t* p) {
     uint32_t v;
@@ -331,8 +328,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         // Table rows are 256 bytes: [0,128) the pair, [128,256) the second-level entry, one word
         // per lane. One 16-byte store per lane fills a quarter of a half row.
 #pragma unroll
-        for (int i = 0; i < 64 / kChainWarps; ++i) {
-            const int b = (warp + i * kChainWarps) * 4 + (lane >> 3);
+        for (int bq = warp; bq < 64; bq += kChainWarps) {
+            const int b = bq * 4 + (lane >> 3);
             const uint32_t pv = lds_u32(a_ptab + 4u * b);
             const uint32_t nv = lds_u32(a_nmap + 4u * b);
             const uint32_t row = kLutAddr + (uint32_t)b * 256u + (uint32_t)(lane & 7) * 16u;
@@ -460,8 +457,9 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 if (!poll_word(p.tokens + lane + 32 * i, need, true, p.spin_limit, g_abort, tk[i])) fine = false;
         return __all_sync(0xffffffffu, fine) != 0;
     };
-    auto warp_begin = [&](int i0, int len, int w) {  // first item of consumer warp w: i0 + len * w / 15
-        return i0 + fast_div(len * w, kDivWarpsM, kDivWarpsS);
+    // first item of consumer warp w in a slice of len items from i0: i0 + len * w / n_warps
+    auto warp_begin = [&](const ChainOpDev& o, int i0, int len, int w) {
+        return i0 + fast_div(len * min(w, o.n_warps), o.div_w_m, o.div_w_s);
     };
 
     if (warp == kConsumerWarps) {
@@ -732,8 +730,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         First f;
         int i0, i1;
         my_slice(oj, i0, i1);
-        f.pos = warp_begin(i0, i1 - i0, warp);
-        f.w1 = warp_begin(i0, i1 - i0, warp + 1);
+        f.pos = warp_begin(o, i0, i1 - i0, warp);
+        f.w1 = warp_begin(o, i0, i1 - i0, warp + 1);
         f.pair = 0;
         f.kb0 = 0;
         f.n = 0;
@@ -1157,8 +1155,6 @@ bool chain_fill_op(ChainOpDev* d, const AilaNf4Linear& w, int64_t ff_pair, int g
     d->sp = w.scale_params();
     d->K = (int)w.K;
     d->KB = w.KU;
-    d->unit_stride = w.unit_stride;
-    d->absmax_kind = w.absmax_kind;
     d->n_rows = (int)w.N;
     d->n_tiles = w.RT;
     d->swiglu = paired ? 1 : 0;
@@ -1173,6 +1169,13 @@ bool chain_fill_op(ChainOpDev* d, const AilaNf4Linear& w, int64_t ff_pair, int g
     make_fast_div((uint32_t)grid, &d->div_g_m, &d->div_g_s);
     make_fast_div((uint32_t)w.KU, &d->div_kb_m, &d->div_kb_s);
     d->half1_bytes = (long long)pairs * w.KU * w.unit_stride;
+    // A warp pays a fixed price per operation: a small slice goes to fewer warps, about
+    // kItemsPerWarp work items each.
+    const long long per_cta = (total + grid - 1) / grid;
+    long long nw = (per_cta + kItemsPerWarp - 1) / kItemsPerWarp;
+    nw = nw < kMinWarps ? kMinWarps : nw > kConsumerWarps ? kConsumerWarps : nw;
+    d->n_warps = (int)nw;
+    make_fast_div((uint32_t)nw, &d->div_w_m, &d->div_w_s);
     d->clamp_pair = w.RT - (int)pairs;
     return true;
 }
