@@ -5,34 +5,48 @@
 // the list; an operation may take the previous operation's output as its input.
 //
 // Shape of the kernel
-//  * One CTA per SM, 16 warps, launched cooperatively (all CTAs resident: CTAs wait on one
-//    another inside the launch, every wait is bounded).
+//  * One CTA per SM, launched cooperatively (all CTAs resident: CTAs wait on one another inside
+//    the launch, every wait is bounded). 16 warps: 15 CONSUMER warps stream and decode weights,
+//    one FINALIZER warp turns their sums into outputs and feeds them x, an operation behind.
 //  * Work items are UNIT PAIRS: unit (row tile a, 64-block kb) together with unit (row tile b, kb).
 //    For a fused gate|up linear a/b are the gate tile and its up tile; for a plain linear two row
 //    tiles half the matrix apart ride together. Both halves need the same slice of x.
 //  * The item stream (pair-major, then kb) is cut into equal contiguous slices, one per CTA, and
-//    each slice into 16 contiguous warp ranges. A warp walks its range in STEPS of up to four
-//    consecutive 64-blocks of one pair.
+//    each slice into contiguous ranges for the consumer warps (all 15, or fewer when the slice is
+//    small: a warp pays a fixed price per operation). A warp walks its range in STEPS of up to
+//    four consecutive 64-blocks of one pair.
 //  * Weights go global memory -> registers directly (two 8-byte loads per lane and unit; a lane's
 //    bytes are exactly its tensor-core fragments, see nf4_common.cuh). While unit u of a step is
-//    being decoded, the registers it frees are re-loaded with unit u of the NEXT step, so a full
-//    step of loads per warp is always in flight. No shared-memory staging of weights.
+//    being decoded, the registers it frees are re-loaded with unit u of the NEXT step - of the next
+//    operation, when the range ends - so a full step of loads per warp is always in flight and
+//    the pipeline does not drain between operations. No shared-memory staging of weights.
 //  * byte -> bf16 pair through a bank-private shared-memory table: one PRMT + one LDS per two
 //    weights; the pairs are the A fragments of mma.sync m16n8k16 (bf16 x bf16 -> fp32).
 //  * The four blocks of a step put their slice of x into four different columns of the B
 //    fragment (lanes g = 0, 2, 4, 6 hold x of block 0..3), so lane (g, t) ends up with the raw
 //    sums of rows g and g+8 for block t: every lane decodes and applies exactly the absmax values
-//    of its own block, no shuffles. absmax = nmap[code] * nabs[flat / 256] + offset in two rounded
-//    fp32 operations (Bnb4BitLinear.cpp:485-487); the second-level code book sits bank-private in
-//    the unused half rows of the table.
-//  * Row sums: a warp reduces over t when it leaves a pair, writes 32 floats to its slot; after a
-//    CTA barrier the warps sum the slots in warp order. A pair whose items span several CTAs is
-//    finished by the CTA that holds its first item: the others publish their partial sums as
-//    8-byte words {value, tag}, which the owner reads (bounded wait) and adds in CTA order.
+//    of its own block, no shuffles. absmax = nmap[code] * second_level + offset in two rounded
+//    fp32 operations (Bnb4BitLinear.cpp:485-487). The second-level scale of a row changes at most
+//    once along the row; a table built with the linear gives, per row, the value before and after
+//    that column and the offset (one 16-byte load per row and pair). The second-level code book
+//    sits bank-private in the unused half rows of the byte table.
+//  * x of an operation sits in shared memory (up to two buffers, so the next operation's x is in
+//    place before the consumers get there). A plain tensor is fetched by the finalizer warp with
+//    asynchronous copies that arrive on an mbarrier; the previous operation's output, or an input
+//    with a fused RMSNorm, is staged by the consumers themselves.
+//  * Row sums: a warp reduces over t when it leaves a pair and writes 32 floats to one of its two
+//    slots (tagged with the pair). There are four sets of slots, so the consumers run up to four
+//    operations ahead of the finalizer, which adds the slots of a pair in slot order. A pair whose
+//    items span several CTAs is finished by the CTA that holds its first item: the others publish
+//    their partial sums as 8-byte words {value, tag}, which the owner reads (bounded wait) and adds
+//    in CTA order. Every sum is added in a fixed order: results do not depend on timing.
 //  * Output: bf16 to y and/or, when the next operation consumes it, as 8-byte words
 //    {two bf16, tag} that every CTA polls while it stages the next x into shared memory. A word
 //    carries its own validity (a naturally aligned 8-byte access is single-copy atomic), so there
 //    is no fence and no flag on the path from one operation to the next.
+//  * Exchange words (outputs, partial sums) live in eight slots used round-robin by operation.
+//    Every CTA leaves a token when it is through with an operation; a slot is written only when
+//    all tokens show that its words of eight operations ago have been read.
 //  * Tags are epoch + operation index; the epoch lives in device memory and is advanced by the
 //    CTA that finishes last, so launches can be captured in a CUDA graph and replayed.
 //
@@ -123,7 +137,7 @@ struct ChainParams {
     int* status;
     long long spin_limit;         // SM cycles a wait may take
     int smem_bytes;
-    int x_buffers;                // 1 or 2 buffers of x_pitch bytes for x in shared memory
+    int x_buffers;                // 1 or 2 buffers of x_pitch bytes for x in shared memory (2 when they fit)
     int x_pitch;
     ChainOpDev inline_op;         // the operation of a one-operation launch (ops == NULL)
 };

@@ -43,9 +43,10 @@ METRIC = "nf4_gemv_weight_bandwidth"
 UNIT = "GB/s"
 WORKLOAD = "cfg2 fused gate+up+SiLU NF4 GEMV, M=1, K=2560, 2x9728 rows, bs64 double-quant"
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum per operation of the dominant kernel (one
-# capture of a chained launch, divided by its operations); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_OP = None
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per operation of the dominant kernel: one
+# capture of a chained launch of 8 operations (python bench.py --profile-case chain), 208.04 MB
+# read + 3.82 MB written, divided by 8. Traffic grows in proportion to the operations.
+NCU_TRAFFIC_BYTES_PER_OP = 26_483_264
 
 
 def weight_bytes(n: int, k: int) -> int:
@@ -816,9 +817,12 @@ def main():
                    "launch": f"one chained launch of {layers} operations per step (aila_nf4_chain_run), "
                              "replayed from a CUDA graph", "parallelism": f"replicas x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm"], "traffic": NCU_TRAFFIC_BYTES_PER_OP,
+                     "frac": achieved / pk["hbm"], "traffic": NCU_TRAFFIC_BYTES_PER_OP * layers,
                      "peak_source": pk["source"], "operation_us": op_us,
+                     "algorithmic_bytes_per_launch": GATE_UP_ALGO_BYTES * layers,
+                     "operations_per_launch": layers,
                      "algorithmic_bytes_per_operation": GATE_UP_ALGO_BYTES,
+                     "traffic_per_operation": NCU_TRAFFIC_BYTES_PER_OP,
                      "frac_of_nominal_8TBps": achieved / 8000.0},
         "per_call": {"what": "the same operations as separate aila_nf4_forward_gate_up_swiglu calls "
                              "(one launch each, CUDA graph)", "launch_us": call_us,

@@ -294,7 +294,10 @@ AILA_NF4_API AilaNf4Status aila_add_rms_norm(const void* x_bf16, const void* add
  * operation with an input of its own still starts only after the previous one has finished.
  * Rules: all linears share their code books (quant_map, nested_quant_map) and the scratch's
  * device; in_features of a linked operation equals the previous output size; at most 160
- * operations; in_features <= 49,000 (x lives in shared memory). Buffers named in the list must
+ * operations; in_features <= 40,832 (x lives in shared memory), and with double-quantized
+ * absmax in_features <= 256 * blocksize (a row then changes its second-level block at most
+ * once; 16,384 at blocksize 64); an operation with a fused RMSNorm takes in_features <= 11,520.
+ * Buffers named in the list must
  * stay valid for the life of the chain; an operation must not read, through a pointer of its own,
  * memory that an earlier operation of the same chain writes (use the link instead).
  * The launch is cooperative (one thread block per SM, all resident) and every device-side wait is
