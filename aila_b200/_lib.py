@@ -99,6 +99,7 @@ _SIGNATURES = {
                                                ctypes.c_int64, ctypes.POINTER(_VP)]),
     "aila_nf4_peerbuf_export": (ctypes.c_int, [_VP, _VP]),
     "aila_nf4_peerbuf_import": (ctypes.c_int, [_VP, ctypes.c_int, _VP]),
+    "aila_nf4_peerbuf_import_local": (ctypes.c_int, [_VP, ctypes.c_int, _VP]),
     "aila_nf4_peerbuf_destroy": (None, [_VP]),
     "aila_nf4_forward_decode_allreduce": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "aila_nf4_forward_rmsnorm": (ctypes.c_int, [_VP, _VP, _VP, ctypes.POINTER(RmsNorm), _VP, _VP, _VP]),

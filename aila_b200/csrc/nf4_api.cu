@@ -408,8 +408,12 @@ AilaNf4Status ensure_counters(AilaNf4Scratch* sc, size_t tiles) {
     if (sc->d_counters) NF4_CUDA(cudaFree(sc->d_counters));
     sc->d_counters = nullptr;
     sc->counters_ints = 0;
+    // Growing inside a forward call (more than 262,144 output rows without an
+    // aila_nf4_scratch_reserve before) allocates: not capturable, and it waits for the device so
+    // that the zeros are in place whatever stream the kernel runs on.
     NF4_CUDA(cudaMalloc(reinterpret_cast<void**>(&sc->d_counters), tiles * sizeof(int)));
     NF4_CUDA(cudaMemset(sc->d_counters, 0, tiles * sizeof(int)));
+    NF4_CUDA(cudaDeviceSynchronize());
     sc->counters_ints = tiles;
     return AILA_NF4_OK;
 }

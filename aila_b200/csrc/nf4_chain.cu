@@ -227,6 +227,8 @@ __device__ __forceinline__ int slice_begin(const ChainOpDev& op, int c) {
     return op.slice_q * c + fast_div(op.slice_r * c, op.div_g_m, op.div_g_s);
 }
 
+constexpr long long kTightLimit = 4096;  // wait limits below this are checked on every polling round
+
 // Waits until the word carries `tag` (exact match) or, with at_least, a tag not older than it.
 // Gives up after `limit` SM cycles or when another thread of the grid has given up.
 __device__ __forceinline__ bool poll_word(const unsigned long long* w, unsigned tag, bool at_least,
@@ -249,7 +251,8 @@ __device__ __forceinline__ bool poll_word(const unsigned long long* w, unsigned 
             out = q;
             return true;
         }
-        if ((++it & 15u) == 0u) {
+        // (the clock is read every 16th round; a limit below kTightLimit is looked at every round)
+        if ((++it & 15u) == 0u || limit < kTightLimit) {
             if (clock64() - t0 > limit || *(volatile const unsigned*)g_abort != 0u) return false;
             __nanosleep(64);
         }
@@ -416,7 +419,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         const long long t0 = clock64();
         for (unsigned it = 0;; ++it) {
             if (mbar_try_wait(bar, ph)) return true;
-            if ((it & 63u) == 63u && (clock64() - t0 > p.spin_limit || is_aborted())) return false;
+            if (((it & 63u) == 63u || p.spin_limit < kTightLimit) && (clock64() - t0 > p.spin_limit || is_aborted()))
+                return false;
             __nanosleep(32);
         }
     };
@@ -821,7 +825,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                             all = all && (unsigned)(wq[b][0] >> 32) == want && (unsigned)(wq[b][1] >> 32) == want;
                         if (all) break;
                         if (round == 0) t_start = clock64();
-                        if ((round & 7u) == 7u &&
+                        if (((round & 7u) == 7u || p.spin_limit < kTightLimit) &&
                             (clock64() - t_start > p.spin_limit || *(volatile const unsigned*)g_abort != 0u)) {
                             ok = false;
                             break;

@@ -257,9 +257,12 @@ using nf4::fail;
 
 namespace {
 
+// Element count of a tensor from an untrusted header; -1 when a dimension is negative or the
+// product does not fit 63 bits.
 int64_t numel_of(const StTensor& t) {
     int64_t n = 1;
-    for (int64_t d : t.shape) n *= d;
+    for (int64_t d : t.shape)
+        if (d < 0 || __builtin_mul_overflow(n, d, &n)) return -1;
     return n;
 }
 
@@ -331,7 +334,9 @@ AILA_NF4_API AilaNf4Status aila_st_open(const char* path, AilaStFile** out) {
         t.begin = (size_t)off->arr[0].i;
         t.end = (size_t)off->arr[1].i;
         const int es = dtype_size(t.dtype);
-        if (es > 0 && (uint64_t)numel_of(t) * (uint64_t)es != (uint64_t)(t.end - t.begin))
+        const int64_t count = numel_of(t);
+        if (count < 0) return bail("entry '" + kv.first + "': shape overflows");
+        if (es > 0 && ((uint64_t)count > f->data_bytes || (uint64_t)count * (uint64_t)es != (uint64_t)(t.end - t.begin)))
             return bail("entry '" + kv.first + "': shape and dtype do not match its byte range");
         if (f->tensors.count(kv.first)) return bail("duplicate entry '" + kv.first + "'");
         f->names.push_back(kv.first);
@@ -440,8 +445,9 @@ AILA_NF4_API AilaNf4Status aila_st_load_bnb4_weight(const AilaStFile* f, const c
         return fail(AILA_NF4_ERR_UNSUPPORTED, "Only NF4 bitsandbytes weights are supported: " + w);
     if (blocksize->i <= 0)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "bitsandbytes blocksize must be positive: " + w);
-    const int64_t logical = dims[0] * dims[1];
-    if (dims[0] <= 0 || dims[1] <= 0 || logical <= 0)
+    int64_t logical = 0;
+    if (dims[0] <= 0 || dims[1] <= 0 || dims[0] >= (int64_t(1) << 27) || dims[1] >= (int64_t(1) << 27) ||
+        __builtin_mul_overflow(dims[0], dims[1], &logical) || logical <= 0)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "bitsandbytes logical weight shape is invalid: " + w);
     if (numel_of(*packed) * 2 != logical)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT,

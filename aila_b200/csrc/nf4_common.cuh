@@ -107,7 +107,8 @@ __device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Bounded waits. Every spin in this library gives up after kSpinLimitCycles SM cycles
+// Bounded waits. Every spin in this library gives up after a limit of SM cycles (this default,
+// or the scratch's setting: aila_nf4_scratch_set_wait_limit)
 // (about a second), records a code in a global status word and lets the kernel drain.
 // ---------------------------------------------------------------------------------------
 constexpr long long kSpinLimitCycles = 2000000000LL;
@@ -158,7 +159,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Returns false after the cycle limit; the caller records a status and stops using the pipe.
 // A waiting thread backs off with nanosleep so that it does not take issue slots from the warps
 // of its scheduler that have work.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  long long limit = kSpinLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
@@ -167,7 +169,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
             if (mbar_try_wait(bar, parity)) return true;
             __nanosleep(100);
         }
-        if (clock64() - t0 > kSpinLimitCycles) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 

@@ -119,6 +119,7 @@ struct StreamParams {
     float* partials;
     int* counters;
     int* status;
+    long long spin_limit;   // SM cycles a wait may take
     int total_items;        // work items (units, or gate/up unit pairs), < 2^31
     int slice_q, slice_r;   // total_items = slice_q * grid + slice_r
     uint32_t div_g_m, div_ku_m;  // multiply-shift division by the grid size and by KU
@@ -348,7 +349,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     do {
                         __nanosleep(40);
                         asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(q) : "l"(word) : "memory");
-                        if (*(volatile int*)abort_flag || clock64() - t0 > kSpinLimitCycles) {
+                        if (*(volatile int*)abort_flag || clock64() - t0 > p.spin_limit) {
                             atomicExch(p.status, kStatusTimeoutPeer);
                             ok = false;
                             break;
@@ -587,10 +588,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 // Only the first stages are requested before x has arrived: the load of x slows
                 // down under the copies' traffic (measured), and it is the one load every
                 // consumer waits for once the previous kernel has finished.
-                if (g == early_stages && !mbar_wait_bounded(x_ready, 0)) break;
+                if (g == early_stages && !mbar_wait_bounded(x_ready, 0, p.spin_limit)) break;
                 if (g >= p.stages) {
                     if (*(volatile int*)abort_flag) break;
-                    if (!mbar_wait_bounded(&empty[s], ph ^ 1u)) {
+                    if (!mbar_wait_bounded(&empty[s], ph ^ 1u, p.spin_limit)) {
                         atomicExch(p.status, kStatusTimeoutEmpty);
                         *(volatile int*)abort_flag = 1;
                         break;
@@ -632,7 +633,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     s = p.stages - 1;
                     ph ^= 1u;
                 }
-                mbar_wait_bounded(&full[s], ph);
+                mbar_wait_bounded(&full[s], ph, p.spin_limit);
             }
         }
         return;
@@ -657,7 +658,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     }
                     if (ok) break;
                     if (*(volatile int*)abort_flag) break;
-                    if (clock64() - t0 > kSpinLimitCycles) {
+                    if (clock64() - t0 > p.spin_limit) {
                         atomicExch(p.status, kStatusTimeoutFull);
                         break;
                     }
@@ -960,7 +961,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     int s = 0;
     uint32_t ph = 0;  // (g / stages) & 1
     for (int g = 0; g < n_groups; ++g) {
-        if (!mbar_wait_bounded(&full[s], ph)) {
+        if (!mbar_wait_bounded(&full[s], ph, p.spin_limit)) {
             atomicExch(p.status, kStatusTimeoutFull);
             *(volatile int*)abort_flag = 1;
             failed = true;
@@ -1295,6 +1296,7 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.partials = scratch.d_partials;
     p.counters = scratch.d_counters;
     p.status = scratch.d_status;
+    p.spin_limit = scratch.wait_limit_cycles;
     const int rt_work = paired ? (int)(ff_pair / kTileRows) : w.RT;
     p.total_items = rt_work * w.KU;
     p.slice_q = p.total_items / pl.grid;

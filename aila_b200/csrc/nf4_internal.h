@@ -67,7 +67,7 @@ struct AilaNf4Scratch {
     unsigned long long* d_chain_p = nullptr;
     unsigned long long* d_chain_x = nullptr;
     long long chain_xwords = 0;
-    long long wait_limit_cycles = 2000000000LL;  // bound of every device-side wait of the chained kernel
+    long long wait_limit_cycles = 2000000000LL;  // bound of every device-side wait of the decode kernels
 };
 
 namespace nf4 {
@@ -163,7 +163,7 @@ AilaNf4Status ensure_chain_scratch(AilaNf4Scratch* sc);
 // advances the epoch.
 cudaError_t launch_peer_reduce(const unsigned long long* part_base, unsigned* ctrl, int world,
                                int64_t max_rows, int64_t n, const void* residual, void* y,
-                               int* d_status, cudaStream_t s);
+                               int* d_status, long long spin_limit, cudaStream_t s);
 AilaNf4Status ensure_counters(AilaNf4Scratch* sc, size_t tiles);
 
 // nf4_gemm.cu ---------------------------------------------------------------------------

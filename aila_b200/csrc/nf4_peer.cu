@@ -37,6 +37,7 @@ struct AilaNf4PeerBuf {
     void* local = nullptr;      // this rank's buffer (cudaMalloc)
     void* base[8] = {nullptr};  // every rank's buffer as mapped here (base[rank] == local)
     bool imported[8] = {false};
+    bool by_ipc[8] = {false};   // mapped with cudaIpcOpenMemHandle (closed on destroy)
     size_t bytes = 0;
 };
 
@@ -55,7 +56,7 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
 __global__ void __launch_bounds__(256)
 peer_reduce_kernel(const unsigned long long* __restrict__ part_base, unsigned* ctrl, int world,
                    long long max_rows, long long n, const uint16_t* __restrict__ residual,
-                   uint16_t* __restrict__ y, int* status) {
+                   uint16_t* __restrict__ y, int* status, long long spin_limit) {
     const unsigned epoch = *(volatile unsigned*)ctrl;
     const unsigned parity = epoch & 1u;
     const unsigned tag = epoch + 1u;
@@ -72,7 +73,7 @@ peer_reduce_kernel(const unsigned long long* __restrict__ part_base, unsigned* c
                 do {
                     __nanosleep(40);
                     q = ld_relaxed_sys_u64(word);
-                    if (clock64() - t0 > kSpinLimitCycles) {
+                    if (clock64() - t0 > spin_limit) {
                         atomicExch(status, kStatusTimeoutPeer);
                         ok = false;
                         break;
@@ -112,12 +113,12 @@ unsigned* ctrl_of(void* base, int world, int64_t max_rows) {
 
 cudaError_t launch_peer_reduce(const unsigned long long* part_base, unsigned* ctrl, int world,
                                int64_t max_rows, int64_t n, const void* residual, void* y,
-                               int* d_status, cudaStream_t s) {
+                               int* d_status, long long spin_limit, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     peer_reduce_kernel<<<blocks, 256, 0, s>>>(part_base, ctrl, world, (long long)max_rows,
                                               (long long)n, static_cast<const uint16_t*>(residual),
-                                              static_cast<uint16_t*>(y), d_status);
+                                              static_cast<uint16_t*>(y), d_status, spin_limit);
     return cudaGetLastError();
 }
 
@@ -195,6 +196,31 @@ AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_import(AilaNf4PeerBuf* b, int peer_r
     NF4_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
     b->base[peer_rank] = p;
     b->imported[peer_rank] = true;
+    b->by_ipc[peer_rank] = true;
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_import_local(AilaNf4PeerBuf* b, int peer_rank,
+                                                         const AilaNf4PeerBuf* peer) {
+    if (!b || !peer) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    if (peer_rank < 0 || peer_rank >= b->world || peer_rank == b->rank)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "peer_rank must name another rank of the group");
+    if (peer->rank != peer_rank || peer->world != b->world || peer->max_rows != b->max_rows)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "the peer's buffer belongs to another rank, group size or row count");
+    if (b->imported[peer_rank])
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "this peer's buffer is already mapped");
+    if (peer->device != b->device) {
+        DevGuard guard(b->device);
+        int can = 0;
+        NF4_CUDA(cudaDeviceCanAccessPeer(&can, b->device, peer->device));
+        if (!can) return fail(AILA_NF4_ERR_UNSUPPORTED, "no peer access between the two devices");
+        const cudaError_t e = cudaDeviceEnablePeerAccess(peer->device, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return nf4::cuda_fail(e, "cudaDeviceEnablePeerAccess");
+        (void)cudaGetLastError();
+    }
+    b->base[peer_rank] = peer->local;
+    b->imported[peer_rank] = true;
+    b->by_ipc[peer_rank] = false;
     return AILA_NF4_OK;
 }
 
@@ -203,7 +229,7 @@ AILA_NF4_API void aila_nf4_peerbuf_destroy(AilaNf4PeerBuf* b) {
     DevGuard guard(b->device);
     cudaDeviceSynchronize();
     for (int r = 0; r < b->world; ++r)
-        if (r != b->rank && b->imported[r] && b->base[r]) cudaIpcCloseMemHandle(b->base[r]);
+        if (r != b->rank && b->imported[r] && b->by_ipc[r] && b->base[r]) cudaIpcCloseMemHandle(b->base[r]);
     cudaFree(b->local);
     delete b;
 }
@@ -253,7 +279,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear
     }
     NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, nullptr, nullptr, 0, s, &pt));
     NF4_CUDA(nf4::launch_peer_reduce(nf4::part_base_of(b->local), pt.ctrl, b->world, b->max_rows,
-                                     l->N, residual, y, sc->d_status, s));
+                                     l->N, residual, y, sc->d_status, sc->wait_limit_cycles, s));
     return AILA_NF4_OK;
 }
 

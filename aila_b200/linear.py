@@ -389,6 +389,11 @@ class PeerBuffer:
         buf = ctypes.create_string_buffer(handle, _lib.IPC_HANDLE_BYTES)
         _lib.check(_lib.load().aila_nf4_peerbuf_import(self._h, peer_rank, buf))
 
+    def import_local(self, peer_rank: int, peer: "PeerBuffer") -> None:
+        """Maps a peer's buffer that this same process created (no IPC handle)."""
+        _lib.check(_lib.load().aila_nf4_peerbuf_import_local(self._h, peer_rank, peer._h))
+        self._peers = getattr(self, "_peers", []) + [peer]  # keeps the peer's buffer alive
+
     def close(self) -> None:
         if self._h:
             _lib.load().aila_nf4_peerbuf_destroy(self._h)

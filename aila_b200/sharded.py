@@ -53,6 +53,19 @@ def shard_bounds(w: Nf4Tensors, mode: int, rank: int, world: int) -> tuple[int, 
     return 0, w.out_features, rank * cols, cols
 
 
+def exchange_handles(group, mine: bytes, device: torch.device | None = None) -> list[bytes]:
+    """Every rank's fixed-size handle, in rank order (one all-gather through the process group;
+    ``device`` is where the group's backend wants its tensors: None = host memory). A rank that
+    never arrives makes the collective raise after the group's timeout, on every other rank."""
+    world = dist.get_world_size(group)
+    t = torch.frombuffer(bytearray(mine), dtype=torch.uint8)
+    if device is not None:
+        t = t.to(device)
+    got = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(got, t, group=group)
+    return [bytes(h.cpu().numpy().tobytes()) for h in got]
+
+
 class CudaBackend:
     """Compute through libaila_nf4.so on this rank's GPU."""
 
@@ -92,13 +105,10 @@ class CudaBackend:
         from .linear import PeerBuffer
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         buf = PeerBuffer(self.device, rank, world, max_rows)
-        mine = torch.frombuffer(bytearray(buf.export_handle()), dtype=torch.uint8)
-        mine = mine.to(torch.device("cuda", self.device))
-        handles = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(handles, mine, group=group)
+        handles = exchange_handles(group, buf.export_handle(), torch.device("cuda", self.device))
         for r, h in enumerate(handles):
             if r != rank:
-                buf.import_handle(r, bytes(h.cpu().numpy().tobytes()))
+                buf.import_handle(r, h)
         dist.barrier(group=group)
         return buf
 

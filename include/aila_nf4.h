@@ -137,6 +137,8 @@ AILA_NF4_API void aila_nf4_scratch_destroy(AilaNf4Scratch* scratch);
  * Pre-size the work space so later forward calls never allocate (call before capturing a
  * CUDA graph). Mirrors Bnb4BitLinearScratch::ensure (src/ops/Bnb4BitLinear.cpp:414-451);
  * need_weight != 0 reserves the [out,in] bf16 weight buffer the seq_len > 1 route uses.
+ * A decode call for more than 262,144 output rows that was not reserved for grows the work space
+ * inside the call: it allocates and waits for the device, so it cannot be captured.
  */
 AILA_NF4_API AilaNf4Status aila_nf4_scratch_reserve(AilaNf4Scratch* scratch, int seq_len,
                                                     int64_t in_features, int64_t out_features,
@@ -234,9 +236,10 @@ AILA_NF4_API AilaNf4Status aila_nf4_static_check(int device, void* stream);
  * 64-byte handle, hands it to the other ranks by any host channel, and imports theirs.
  * Rules: all ranks issue the same aila_nf4_forward_decode_allreduce calls in the same order;
  * the calls of one buffer go to one stream per GPU; the sequence may be captured in a CUDA
- * graph (all exchange state lives on the device). A rank that waits more than about a second
- * for another rank records AILA_NF4_ERR_KERNEL_TIMEOUT for aila_nf4_scratch_check; after that
- * the buffers of the group must be recreated.
+ * graph (all exchange state lives on the device). A rank that waits longer for another rank than
+ * the scratch's wait limit (about a second unless aila_nf4_scratch_set_wait_limit changed it)
+ * records AILA_NF4_ERR_KERNEL_TIMEOUT for aila_nf4_scratch_check; y is then not written, and the
+ * buffers of the group must be recreated.
  */
 typedef struct AilaNf4PeerBuf AilaNf4PeerBuf;
 #define AILA_NF4_IPC_HANDLE_BYTES 64
@@ -245,6 +248,11 @@ AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_create(int device, int rank, int wor
 AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_export(const AilaNf4PeerBuf* buf, void* handle_out);
 AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_import(AilaNf4PeerBuf* buf, int peer_rank,
                                                    const void* handle);
+/* The same for a peer whose buffer was created by THIS process (one process that drives several
+ * GPUs, or two ranks of a test on one GPU): no handle, the buffer itself. The peer's buffer must
+ * outlive this one's use. */
+AILA_NF4_API AilaNf4Status aila_nf4_peerbuf_import_local(AilaNf4PeerBuf* buf, int peer_rank,
+                                                         const AilaNf4PeerBuf* peer);
 AILA_NF4_API void aila_nf4_peerbuf_destroy(AilaNf4PeerBuf* buf);
 /* seq_len == 1 only; x is this rank's column slice [in_features / world] (bf16, 16-byte
  * aligned), y receives all out_features rows. */
@@ -325,8 +333,10 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_run(AilaNf4Chain* chain, void* stream)
  * waits for it. One copy in, one launch, one copy out, one synchronisation for the whole chain. */
 AILA_NF4_API AilaNf4Status aila_nf4_chain_run_host(AilaNf4Chain* chain, const void* x_host_bf16,
                                                    void* y_host_bf16, void* stream);
-/* Bound, in SM clock cycles, of every device-side wait of the chained decode kernel (default
- * 2e9, about a second). Takes effect at the next launch. No reference counterpart. */
+/* Bound, in SM clock cycles, of every device-side wait of the decode kernels launched with this
+ * scratch: the chained kernel, the single-call kernel and the row-parallel exchange (default
+ * 2e9, about a second). Takes effect at the next launch. Chains copy it when they are created.
+ * No reference counterpart. */
 AILA_NF4_API AilaNf4Status aila_nf4_scratch_set_wait_limit(AilaNf4Scratch* scratch,
                                                            int64_t sm_cycles);
 

@@ -134,6 +134,10 @@ def test_malformed_files_are_rejected(tmp_path):
     expect(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16, "do not match")
     hdr = json.dumps({"t": {"dtype": "F32", "shape": [4]}}).encode()
     expect(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16, "lacks dtype, shape or data_offsets")
+    # a shape whose product wraps around 2^64 to the byte range's size must not pass
+    hdr = json.dumps({"t": {"dtype": "F32", "shape": [1 << 62, 4, 1 << 60, 16],
+                            "data_offsets": [0, 16]}}).encode()
+    expect(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16, "shape overflows")
 
 
 def test_header_escapes_and_empty_tensors(tmp_path):

@@ -141,3 +141,64 @@ def test_shard_rules():
         sharded.shard_bounds(w, sharded.ROWS, 0, 5)
     with pytest.raises(ValueError):
         sharded.shard_bounds(w, sharded.ROWS, 2, 2)
+
+
+def _handle_worker(rank, world, port, absent, q):
+    """Rank `absent` (if any) leaves before the exchange, as a rank that died during set-up."""
+    import datetime
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+        if rank == absent:
+            q.put((rank, "left"))
+            return  # never joins the collective (no destroy: the others must not be helped out)
+        mine = bytes([rank]) * 64
+        try:
+            got = sharded.exchange_handles(None, mine)
+            q.put((rank, "ok", got))
+        except Exception as e:
+            q.put((rank, "raised", type(e).__name__))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "err", repr(e)))
+
+
+@pytest.mark.parametrize("absent", [None, 1])
+def test_handle_exchange_and_a_rank_that_never_arrives(absent):
+    """The host side of make_peer_buffer: every rank gets every rank's 64-byte handle in rank
+    order; when one rank never arrives, the others get an exception after the group's timeout
+    instead of waiting for ever."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_handle_worker, args=(r, world, port, absent, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        item = q.get(timeout=120)
+        res[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=60)
+        if p.is_alive():  # pragma: no cover
+            p.terminate()
+    if absent is None:
+        for r in range(world):
+            assert res[r][0] == "ok", res
+            assert res[r][1] == [bytes([i]) * 64 for i in range(world)]
+    else:
+        assert res[absent][0] == "left"
+        assert res[0][0] == "raised", res
+
+
+def test_mis_sized_shards_are_refused_on_the_host():
+    w = make_weight(10, 100, 192)
+    with pytest.raises(ValueError):
+        sharded.check_shardable(w, sharded.ROWS, 3)   # 100 rows over 3 ranks
+    with pytest.raises(ValueError):
+        sharded.check_shardable(w, sharded.COLS, 2)   # 96 columns per rank: not a multiple of 64
+    with pytest.raises(ValueError):
+        sharded.shard_bounds(w, sharded.ROWS, 2, 2)   # rank outside the group
+    be = OracleBackend()
+    with pytest.raises(ValueError):
+        be.make_shard(w, sharded.COLS, 0, 2)

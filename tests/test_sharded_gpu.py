@@ -135,3 +135,74 @@ def test_sharded_mlp_nccl(oracle, world):
             assert err <= 2e-2 * np.abs(want).max(), ("fused", err)
             # (not bit-equal to the library route, which rounds every rank's partial sum to bf16
             # before the all-reduce; the fused route adds the fp32 partial sums and rounds once)
+
+
+def _skip_worker(rank, world, port, q):
+    """Step 1: both ranks call. Step 2: rank 1 leaves the call out (between steps, nothing of it in
+    flight); rank 0's wait runs out after a few milliseconds and the launch reports it. Step 3:
+    fresh exchange buffers, both ranks call, the numbers are those of step 1."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from aila_b200 import _lib, sharded
+        be = sharded.CudaBackend(rank)
+        w = make_weight(21, 512, 256 * world)
+        x = synth.gaussian_activation(22, 1, 256 * world).cuda()
+        xl = x[:, rank * 256:(rank + 1) * 256].contiguous()
+        peers = be.make_peer_buffer(None, 512)
+        rp = sharded.RowParallelNf4Linear(w, be, peers=peers)
+        y1 = rp.forward(xl).clone()
+        torch.cuda.synchronize()
+        be.scratch.check()
+        dist.barrier()
+        torch.cuda.synchronize()
+        status = None
+        if rank == 0:
+            be.scratch.set_wait_limit(20_000_000)  # about 10 ms
+            rp.forward(xl)
+            torch.cuda.synchronize()
+            try:
+                be.scratch.check()
+            except _lib.Nf4Error as e:
+                status = e.status
+            be.scratch.set_wait_limit(2_000_000_000)
+        dist.barrier()  # rank 1 learns on the host that the step is over
+        torch.cuda.synchronize()
+        peers.close()
+        peers = be.make_peer_buffer(None, 512)
+        rp = sharded.RowParallelNf4Linear(w, be, peers=peers)
+        y3 = rp.forward(xl)
+        torch.cuda.synchronize()
+        be.scratch.check()
+        same = torch.equal(y1, y3)
+        peers.close()
+        if rank == 0:
+            q.put(("ok", status, bool(same)))
+        dist.barrier()
+    except Exception as e:  # pragma: no cover
+        if rank == 0:
+            q.put(("err", repr(e)))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_that_skips_a_call_times_the_other_out():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from aila_b200 import _lib
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_skip_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+    assert res[0] == "ok", res
+    assert res[1] == _lib.ERR_KERNEL_TIMEOUT, res
+    assert res[2], "after new exchange buffers the result must be that of the first step"
