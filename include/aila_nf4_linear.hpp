@@ -27,6 +27,14 @@ namespace nf4 {
 struct Context {
     int device = 0;
     void* stream = nullptr;  // cudaStream_t
+    // Work space of the calls that take no scratch argument in the reference
+    // (try_forward_decode_gate_up_swiglu(ctx, fused, in, out, ff)): one per context, made on first use.
+    AilaNf4Scratch* decode_scratch = nullptr;
+
+    Context() = default;
+    Context(const Context&) = delete;
+    Context& operator=(const Context&) = delete;
+    ~Context() { aila_nf4_scratch_destroy(decode_scratch); }
 };
 
 struct TensorView {
@@ -194,6 +202,21 @@ public:
         const AilaNf4Status st = aila_nf4_forward_gate_up_swiglu(
             fused_gate_up.handle_, scratch.handle, input.data(), output.data(), seq_len, ff_dim,
             ctx.stream);
+        if (st == AILA_NF4_NOT_APPLICABLE) return false;
+        if (st != AILA_NF4_OK) throw std::runtime_error(aila_nf4_last_error());
+        return true;
+    }
+
+    // The reference's own signature (src/ops/Bnb4BitLinear.hpp:52-56; called at
+    // src/models/Qwen35HybridBnb4Backend.cpp:2172-2173): the work space is the context's.
+    static bool try_forward_decode_gate_up_swiglu(Context& ctx, Bnb4BitLinear& fused_gate_up,
+                                                  TensorView& input, TensorView& output, int ff_dim) {
+        if (!input.is_bf16() || !output.is_bf16()) return false;
+        if (input.ndim() != 2 || input.rows != 1) return false;
+        if (!ctx.decode_scratch && aila_nf4_scratch_create(ctx.device, &ctx.decode_scratch) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+        const AilaNf4Status st = aila_nf4_forward_gate_up_swiglu(
+            fused_gate_up.handle_, ctx.decode_scratch, input.data(), output.data(), 1, ff_dim, ctx.stream);
         if (st == AILA_NF4_NOT_APPLICABLE) return false;
         if (st != AILA_NF4_OK) throw std::runtime_error(aila_nf4_last_error());
         return true;

@@ -75,6 +75,22 @@ int main() {
     if (!k.init(ctx, d, &err)) return 4;
     if (!fused.init_fused_rows(ctx, q, k, &err)) return 5;
     if (fused.out_features() != 2 * N || fused.in_features() != K) return 6;
+    {
+        // the reference's own call shape (Qwen35HybridBnb4Backend.cpp:2172-2173): no scratch argument.
+        // Null tensors: the call must get as far as the library's argument check and throw.
+        TensorView x, y;
+        x.rows = 1;
+        x.cols = K;
+        y.rows = 1;
+        y.cols = N;
+        bool threw = false;
+        try {
+            (void)Bnb4BitLinear::try_forward_decode_gate_up_swiglu(ctx, fused, x, y, N);
+        } catch (const std::runtime_error&) {
+            threw = true;
+        }
+        if (!threw || ctx.decode_scratch == nullptr) return 10;
+    }
     std::printf("adapter ok on a GPU: fused %d x %d\n", fused.out_features(), fused.in_features());
     return 0;
 }

@@ -1,7 +1,7 @@
 """Parity of the CUDA library with the CPU oracle, through the C ABI (ctypes), on a B200.
 
 Bars: dequantised weights and absmax bit-exact; GEMV / fused gate+up+SiLU / prefill GEMM
-outputs within max|err| <= 2e-2 * ||y||_inf at bf16 output (the bound BASELINE.json states).
+outputs within max|err| <= 2e-2 * ||y||_inf at bf16 output (the bound this hot path is held to).
 """
 import numpy as np
 import pytest
@@ -104,6 +104,53 @@ def test_gemv(nf4, oracle, scratch, kernel, N, K):
     scratch.check()
     want = oracle.gemv(w.packed, w.quant_map, am, bf16_bits(x).reshape(-1), N, K, 64)
     assert_close_norm(bf16_bits(y).reshape(-1), want, REL, f"gemv k{kernel} {N}x{K}")
+
+
+@pytest.mark.parametrize("N,K", [(8192, 5120), (5120, 8192), (5120, 25600)])
+def test_gemv_large_model_shapes(nf4, oracle, scratch, N, K):
+    """The attention and MLP-down linears of the 32B-class configuration, unsharded on one GPU
+    (the default kernel choice; 25600 input columns are beyond the chained kernel's reach)."""
+    w = make_weight(1500 + N + K, N, K)
+    l = _lin(nf4, w)
+    x = _act(1509 + N, 1, K)
+    y = torch.full((1, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    l.forward(scratch, x.cuda(), y, 1)
+    torch.cuda.synchronize()
+    scratch.check()
+    want = oracle.gemv(w.packed, w.quant_map, oracle_absmax(oracle, w), bf16_bits(x).reshape(-1), N, K, 64)
+    assert_close_norm(bf16_bits(y).reshape(-1), want, REL, f"gemv {N}x{K}")
+    if K <= 16384:
+        y3 = torch.full((1, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        nf4.set_gemv_kernel(3)
+        try:
+            l.forward(scratch, x.cuda(), y3, 1)
+            torch.cuda.synchronize()
+        finally:
+            nf4.set_gemv_kernel(0)
+        scratch.check()
+        assert_close_norm(bf16_bits(y3).reshape(-1), want, REL, f"chained gemv {N}x{K}")
+    l.close()
+
+
+def test_gate_up_swiglu_large_model_shape(nf4, oracle, scratch):
+    ff, K = 25600, 5120
+    ws = [make_weight(1600, ff, K), make_weight(1601, ff, K)]
+    f, _ = _fused(nf4, ws)
+    packed = np.concatenate([w.packed for w in ws])
+    am = np.concatenate([oracle_absmax(oracle, w) for w in ws])
+    x = _act(1609, 1, K)
+    want = oracle.gemv_gate_up_swiglu(packed, ws[0].quant_map, am, bf16_bits(x).reshape(-1), ff, K, 64)
+    for kernel in (0, 3):
+        out = torch.full((1, ff), float("nan"), dtype=torch.bfloat16, device="cuda")
+        nf4.set_gemv_kernel(kernel)
+        try:
+            assert nf4.Bnb4BitLinear.try_forward_decode_gate_up_swiglu(f, scratch, x.cuda(), out, ff)
+            torch.cuda.synchronize()
+        finally:
+            nf4.set_gemv_kernel(0)
+        scratch.check()
+        assert_close_norm(bf16_bits(out).reshape(-1), want, REL, f"gate_up 2x{ff}x{K} kernel {kernel}")
+    f.close()
 
 
 def test_gemv_repeatable_and_residual(nf4, oracle, scratch):
@@ -475,6 +522,24 @@ def test_dense_linear_decode(nf4, oracle, scratch, N, K):
     lin.forward(scratch, x.cuda(), y, 1, add_residual=res.cuda())
     want_r = bits_to_f32(want) + bits_to_f32(bf16_bits(res))
     assert np.abs(bits_to_f32(bf16_bits(y.cpu())) - want_r).max() <= 2e-2 * np.abs(want_r).max()
+
+
+def test_dense_lm_head_full_size(nf4, oracle, scratch):
+    """The whole 151936 x 2560 bf16 output head at seq_len == 1, and its argmax, against the CPU
+    oracle."""
+    N, K = 151936, 2560
+    g = torch.Generator().manual_seed(7300)
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    lin = nf4.Linear()
+    lin.init(w, K, N, 0)
+    x = _act(7301, 1, K)
+    y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+    lin.forward(scratch, x.cuda(), y, 1)
+    torch.cuda.synchronize()
+    want = oracle.gemm_bf16w(bf16_bits(w), bf16_bits(x), 1, N, K)
+    got = bf16_bits(y.cpu())
+    assert np.abs(bits_to_f32(got) - bits_to_f32(want)).max() <= 4e-3 * np.abs(bits_to_f32(want)).max() + 1e-6
+    assert int(np.argmax(bits_to_f32(got))) == int(np.argmax(bits_to_f32(want)))
 
 
 def test_dense_linear_prefill(nf4, oracle, scratch):
