@@ -127,6 +127,8 @@ _SIGNATURES = {
     "aila_nf4_set_gemv_kernel": (ctypes.c_int, [ctypes.c_int]),
     "aila_nf4_chain_create": (ctypes.c_int, [_VP, ctypes.POINTER(ChainOp), ctypes.c_int,
                                              ctypes.POINTER(_VP)]),
+    "aila_nf4_chain_create_allreduce": (ctypes.c_int, [_VP, ctypes.POINTER(ChainOp), ctypes.c_int, _VP,
+                                                        ctypes.POINTER(_VP)]),
     "aila_nf4_chain_destroy": (None, [_VP]),
     "aila_nf4_chain_length": (ctypes.c_int, [_VP]),
     "aila_nf4_chain_run": (ctypes.c_int, [_VP, _VP]),

@@ -120,7 +120,7 @@ struct ChainOpDev {
     int clamp_pair;               // pairs from here on have no half 1 of their own (it reads the last row tile)
     int x_copy;                   // 1: x is a plain, 16-byte aligned tensor that asynchronous copies can fetch
     int div_w_s;
-    int pad_[1];
+    int peer;                     // 1: the sums go to the row-parallel exchange instead of y
 };
 static_assert(sizeof(ChainOpDev) == kDescBytes, "descriptor size");
 
@@ -139,6 +139,15 @@ struct ChainParams {
     int smem_bytes;
     int x_buffers;                // 1 or 2 buffers of x_pitch bytes for x in shared memory (2 when they fit)
     int x_pitch;
+    // Row-parallel exchange after the LAST operation (peer_world > 0): its fp32 row sums go, as
+    // 8-byte words {value, tag = peer epoch + 1}, into every rank's exchange buffer (plain stores
+    // to peer memory); then every CTA adds up a share of the rows over the ranks, in rank order.
+    int peer_world, peer_rank;
+    long long peer_max_rows;
+    unsigned long long* peer_part[8];  // rank d's row area (both parities, all source ranks)
+    unsigned* peer_ctrl;               // this rank's {epoch, ...}
+    uint16_t* peer_y;                  // bf16 [n_out of the last operation]
+    const uint16_t* peer_residual;     // added to the sum, or NULL
     ChainOpDev inline_op;         // the operation of a one-operation launch (ops == NULL)
 };
 
@@ -425,6 +434,17 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
         }
     };
 
+    // row-parallel exchange: this launch's tag and half of the buffers
+    const unsigned peer_epoch = p.peer_world > 0 ? *(volatile unsigned*)p.peer_ctrl : 0u;
+    auto peer_store = [&](int n, bool valid, float sum) {
+        const size_t at = ((size_t)(peer_epoch & 1u) * p.peer_world + p.peer_rank) * (size_t)p.peer_max_rows + n;
+        const unsigned long long word =
+            ((unsigned long long)(peer_epoch + 1u) << 32) | (unsigned long long)__float_as_uint(sum);
+        if (valid)
+            for (int d = 0; d < p.peer_world; ++d)
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.peer_part[d] + at), "l"(word) : "memory");
+    };
+
     // ---- the output of one pair of operation o: lane = half * 16 + row holds the finished sum ----
     auto epilogue = [&](const ChainOpDev& o, unsigned tg, int pr, float v) {
         const int row = lane & 15;
@@ -443,6 +463,10 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             valid = tile < o.n_tiles && n < o.n_out;
             out = v;
             if (valid && o.residual) out += bf16_bits_to_f32(__ldcg(o.residual + n));
+        }
+        if (o.peer) {
+            peer_store(n, valid, out);
+            return;
         }
         const uint32_t bits = f32_to_bf16_bits(out);
         if (valid && o.y) o.y[n] = (uint16_t)bits;
@@ -535,7 +559,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 }
                 // what the epilogue needs, read from the descriptor once
                 const int e_swiglu = op.swiglu, e_n_out = op.n_out, e_pair_offset = op.pair_offset;
-                const int e_n_tiles = op.n_tiles, e_publish = op.publish;
+                const int e_n_tiles = op.n_tiles, e_publish = op.publish, e_peer = op.peer;
                 uint16_t* const e_y = op.y;
                 const uint16_t* const e_res = op.residual;
                 unsigned long long* const e_xw = p.xbuf + (size_t)(tag & 7u) * (size_t)p.xwords;
@@ -556,6 +580,10 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                         ok_row = tile < e_n_tiles && n < e_n_out;
                         out = val;
                         if (ok_row && e_res) out += bf16_bits_to_f32(__ldcg(e_res + n));
+                    }
+                    if (e_peer) {
+                        peer_store(n, ok_row, out);
+                        return;
                     }
                     const uint32_t bits = f32_to_bf16_bits(out);
                     if (ok_row && e_y) e_y[n] = (uint16_t)bits;
@@ -637,7 +665,45 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
             // the slots of this ring position are free for operation oi + kRing
             if (oi + kRing < n_ops) bar_arrive(kBarGo + r, kChainThreads);
         }
+        // ---- row-parallel exchange: this CTA's share of the rows, summed over the ranks ----
+        if (p.peer_world > 0 && !is_aborted()) {
+            const int n_out = desc(n_ops - 1).n_out;
+            const int per = (n_out + G - 1) / G;
+            const int r0 = c * per, r1 = min(n_out, r0 + per);
+            const unsigned long long* part =
+                p.peer_part[p.peer_rank] + (size_t)(peer_epoch & 1u) * p.peer_world * (size_t)p.peer_max_rows;
+            bool ok = true;
+            for (int row = r0 + lane; row < r1 && ok; row += 32) {
+                float acc = 0.0f;
+                for (int src = 0; src < p.peer_world && ok; ++src) {
+                    const unsigned long long* word = part + (size_t)src * (size_t)p.peer_max_rows + row;
+                    unsigned long long q;
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(q) : "l"(word) : "memory");
+                    if ((unsigned)(q >> 32) != peer_epoch + 1u) {
+                        const long long t0 = clock64();
+                        do {
+                            __nanosleep(40);
+                            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(q) : "l"(word) : "memory");
+                            if (clock64() - t0 > p.spin_limit || *(volatile const unsigned*)g_abort != 0u) {
+                                ok = false;
+                                break;
+                            }
+                        } while ((unsigned)(q >> 32) != peer_epoch + 1u);
+                    }
+                    acc += __uint_as_float((unsigned)q);
+                }
+                if (ok) {
+                    if (p.peer_residual) acc += bf16_bits_to_f32(p.peer_residual[row]);
+                    p.peer_y[row] = f32_to_bf16_bits(acc);
+                }
+            }
+            if (!ok) {
+                atomicExch(p.status, kStatusTimeoutPeer);
+                atomicExch(p.ctrl + 2, 1u);
+            }
+        }
         // ---- the CTA that finishes last advances the epoch (every CTA has read it by then) ----
+        __syncwarp();
         if (lane == 0) {
             __threadfence();
             const unsigned done = atomicAdd(p.ctrl + 1, 1u);
@@ -645,6 +711,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                 p.ctrl[1] = 0u;
                 __threadfence();
                 *(volatile unsigned*)p.ctrl = epoch0 + (unsigned)n_ops;
+                if (p.peer_world > 0) *(volatile unsigned*)p.peer_ctrl = peer_epoch + 1u;
             }
         }
         return;
@@ -1310,8 +1377,26 @@ struct AilaNf4Chain {
     void* last_y = nullptr;        // where the last operation writes y (device)
 };
 
+namespace {
+AilaNf4Status chain_create(AilaNf4Scratch* scratch, const AilaNf4ChainOp* ops, int n_ops,
+                           const AilaNf4PeerBuf* peers, AilaNf4Chain** out);
+}
+
 AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const AilaNf4ChainOp* ops,
                                                  int n_ops, AilaNf4Chain** out) {
+    return chain_create(scratch, ops, n_ops, nullptr, out);
+}
+
+AILA_NF4_API AilaNf4Status aila_nf4_chain_create_allreduce(AilaNf4Scratch* scratch,
+                                                           const AilaNf4ChainOp* ops, int n_ops,
+                                                           AilaNf4PeerBuf* peers, AilaNf4Chain** out) {
+    if (!peers) return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "peer buffer is NULL");
+    return chain_create(scratch, ops, n_ops, peers, out);
+}
+
+namespace {
+AilaNf4Status chain_create(AilaNf4Scratch* scratch, const AilaNf4ChainOp* ops, int n_ops,
+                           const AilaNf4PeerBuf* peers, AilaNf4Chain** out) {
     using nf4::fail;
     if (!out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "output handle pointer is NULL");
     *out = nullptr;
@@ -1378,6 +1463,23 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const 
         nf4::chain_seal_op(&d);
         k_max = w.K > k_max ? w.K : k_max;
     }
+    // row-parallel exchange after the last operation: its sums go to the ranks, y is written from
+    // the sum over the ranks
+    nf4::PeerTargets pt;
+    uint16_t* peer_y = nullptr;
+    const uint16_t* peer_residual = nullptr;
+    if (peers) {
+        nf4::ChainOpDev& last = h.back();
+        if (ops[n_ops - 1].ff_dim > 0)
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "the row-parallel operation cannot be a gate|up operation");
+        const AilaNf4Status st = nf4::peer_targets_of(peers, scratch->device, last.n_out, &pt);
+        if (st != AILA_NF4_OK) return st;
+        peer_y = last.y;
+        peer_residual = last.residual;
+        last.y = nullptr;
+        last.residual = nullptr;
+        last.peer = 1;
+    }
     int prev = -1;
     NF4_CUDA(cudaGetDevice(&prev));
     if (prev != scratch->device) NF4_CUDA(cudaSetDevice(scratch->device));
@@ -1406,6 +1508,15 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const 
     ch->params.qmap = first->d_qmap;
     ch->params.nmap = first->d_nmap;
     nf4::chain_plan_smem(&ch->params, k_max, n_ops);
+    if (peers) {
+        ch->params.peer_world = pt.world;
+        ch->params.peer_rank = pt.rank;
+        ch->params.peer_max_rows = pt.max_rows;
+        for (int d = 0; d < 8; ++d) ch->params.peer_part[d] = pt.part_base[d];
+        ch->params.peer_ctrl = pt.ctrl;
+        ch->params.peer_y = peer_y;
+        ch->params.peer_residual = peer_residual;
+    }
     ch->first_in = ops[0].linear->K;
     ch->last_out = h[(size_t)n_ops - 1].n_out;
     ch->first_x = const_cast<void*>(ops[0].x_bf16);
@@ -1414,6 +1525,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const 
     *out = ch;
     return AILA_NF4_OK;
 }
+}  // namespace
 
 AILA_NF4_API void aila_nf4_chain_destroy(AilaNf4Chain* chain) {
     if (!chain) return;

@@ -70,6 +70,8 @@ struct AilaNf4Scratch {
     long long wait_limit_cycles = 2000000000LL;  // bound of every device-side wait of the decode kernels
 };
 
+struct AilaNf4PeerBuf;
+
 namespace nf4 {
 
 // error plumbing (nf4_api.cu)
@@ -165,6 +167,8 @@ cudaError_t launch_peer_reduce(const unsigned long long* part_base, unsigned* ct
                                int64_t max_rows, int64_t n, const void* residual, void* y,
                                int* d_status, long long spin_limit, cudaStream_t s);
 AilaNf4Status ensure_counters(AilaNf4Scratch* sc, size_t tiles);
+// The exchange addresses of a peer buffer whose peers have all been imported, for `rows` rows.
+AilaNf4Status peer_targets_of(const ::AilaNf4PeerBuf* b, int device, int64_t rows, PeerTargets* out);
 
 // nf4_gemm.cu ---------------------------------------------------------------------------
 // y[M][N_out] = x[M][K] * w_nk[N][K]^T on tcgen05. swiglu_ff > 0: N == 2*ff and the output

@@ -126,6 +126,29 @@ cudaError_t launch_peer_reduce(const unsigned long long* part_base, unsigned* ct
 
 using nf4::fail;
 
+namespace nf4 {
+AilaNf4Status peer_targets_of(const AilaNf4PeerBuf* b, int device, int64_t rows, PeerTargets* pt) {
+    if (!b) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "peer buffer is NULL");
+    if (device != b->device)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "linear, scratch and peer buffer must share a device");
+    if (rows > b->max_rows)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "out_features " + std::to_string(rows) +
+                                                       " exceeds the peer buffer's " + std::to_string(b->max_rows) + " rows");
+    for (int r = 0; r < b->world; ++r)
+        if (!b->imported[r])
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT,
+                        "peer buffer of rank " + std::to_string(r) + " has not been imported");
+    pt->world = b->world;
+    pt->rank = b->rank;
+    pt->max_rows = b->max_rows;
+    pt->ctrl = ctrl_of(b->local, b->world, b->max_rows);
+    for (int d = 0; d < 8; ++d) pt->part_base[d] = nullptr;
+    for (int d = 0; d < b->world; ++d) pt->part_base[d] = part_base_of(b->base[d]);
+    pt->inline_reduce = false;
+    return AILA_NF4_OK;
+}
+}  // namespace nf4
+
 namespace {
 struct DevGuard {
     int prev = -1;
@@ -259,20 +282,12 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_decode_allreduce(const AilaNf4Linear
     AilaNf4Status st = nf4::ensure_counters(sc, (size_t)l->RT);
     if (st != AILA_NF4_OK) return st;
     nf4::PeerTargets pt;
-    pt.world = b->world;
-    pt.rank = b->rank;
-    pt.max_rows = b->max_rows;
-    pt.ctrl = nf4::ctrl_of(b->local, b->world, b->max_rows);
-    for (int d = 0; d < 8; ++d) pt.part_base[d] = nullptr;
-    for (int d = 0; d < b->world; ++d) pt.part_base[d] = nf4::part_base_of(b->base[d]);
+    st = nf4::peer_targets_of(b, l->device, l->N, &pt);
+    if (st != AILA_NF4_OK) return st;
     // One launch when all CTAs of the grid are resident together (they wait for each other's
     // rows through the arrival counters); otherwise the GEMV publishes and a second kernel sums.
-    static const bool allow_inline = [] {
-        const char* e = std::getenv("AILA_NF4_PEER_INLINE");
-        return !(e && e[0] == '0');
-    }();
     const int grid = nf4::gemv_stream_grid(*l, 0, sc->sm_count);
-    pt.inline_reduce = allow_inline && grid > 0 && grid <= sc->sm_count;
+    pt.inline_reduce = grid > 0 && grid <= sc->sm_count;
     if (pt.inline_reduce) {
         NF4_CUDA(nf4::launch_gemv_stream(*l, *sc, x, y, residual, 0, s, &pt));
         return AILA_NF4_OK;

@@ -411,9 +411,11 @@ class DecodeChain:
     reference's decode step makes back to back (Qwen3Bnb4Backend.cpp:400-418). ``ops`` is a list
     of dicts with keys ``linear`` (Bnb4BitLinear), and optionally ``ff_dim`` (> 0: fused gate|up
     + SwiGLU), ``x`` (input tensor; omitted = the previous operation's output), ``y`` (output
-    tensor), ``residual`` and ``norm`` = dict(weight=, eps=, add=None, hidden_out=None)."""
+    tensor), ``residual`` and ``norm`` = dict(weight=, eps=, add=None, hidden_out=None). With
+    ``peers`` (a PeerBuffer whose peers are all imported) the last operation is row-parallel: the
+    launch exchanges its row sums with the other ranks and writes the sum (+ residual) to ``y``."""
 
-    def __init__(self, scratch: Bnb4BitLinearScratch, ops: list[dict]):
+    def __init__(self, scratch: Bnb4BitLinearScratch, ops: list[dict], peers: "PeerBuffer | None" = None):
         lib = _lib.load()
         self.scratch = scratch
         self.device = scratch.device
@@ -437,7 +439,11 @@ class DecodeChain:
                 arr[i].norm = ctypes.pointer(n)
             self._keep.append(o["linear"])
         h = ctypes.c_void_p()
-        _lib.check(lib.aila_nf4_chain_create(scratch._h, arr, len(ops), ctypes.byref(h)))
+        if peers is None:
+            _lib.check(lib.aila_nf4_chain_create(scratch._h, arr, len(ops), ctypes.byref(h)))
+        else:  # the last operation is row-parallel: its y is the sum over the ranks
+            _lib.check(lib.aila_nf4_chain_create_allreduce(scratch._h, arr, len(ops), peers._h, ctypes.byref(h)))
+            self._keep.append(peers)
         self._h = h
 
     def run(self) -> None:

@@ -112,6 +112,10 @@ class CudaBackend:
         dist.barrier(group=group)
         return buf
 
+    def make_chain(self, ops: list[dict], peers=None):
+        from .linear import DecodeChain
+        return DecodeChain(self.scratch, ops, peers)
+
     def forward_allreduce(self, handle, peers, x: torch.Tensor, out: torch.Tensor,
                           residual: torch.Tensor | None = None) -> None:
         handle.forward_decode_allreduce(self.scratch, peers, x, out, residual)
@@ -202,6 +206,24 @@ class ShardedNf4Mlp:
         u = backend.make_shard(up, ROWS, self.rank, self.world)
         self.gate_up = backend.fuse(g, u)  # gate_r rows then up_r rows: SwiGLU stays local
         self.down = backend.make_shard(down, COLS, self.rank, self.world)
+        self._chains = {}
+
+    def forward_chained(self, x: torch.Tensor) -> torch.Tensor:
+        """Single-row input, exchange buffer given: gate|up + SwiGLU -> down -> sum over the ranks as
+        ONE launch per rank (aila_nf4_chain_create_allreduce). The chain is built once per input
+        tensor and writes into a buffer of its own, which is returned (overwritten by the next
+        call with the same input tensor)."""
+        if x.shape[0] != 1 or self.peers is None:
+            raise ValueError("forward_chained takes one row and needs the exchange buffer")
+        key = x.data_ptr()
+        hit = self._chains.get(key)
+        if hit is None:
+            out = self.backend.empty(1, self.hidden)
+            chain = self.backend.make_chain([dict(linear=self.gate_up, ff_dim=self.local_ff, x=x),
+                                             dict(linear=self.down, y=out)], self.peers)
+            hit = self._chains[key] = (chain, out, x)
+        hit[0].run()
+        return hit[1]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         m = x.shape[0]

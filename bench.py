@@ -320,7 +320,11 @@ def tp_linears(rank, world, local, stream):
 
     out = {"workload": "cfg5 linears: MLP 5120 -> 2x25600 -> 5120 (gate|up row-sharded + local SwiGLU, down "
                        "column-sharded, one sum exchange), q 5120->8192 row-sharded, o 8192->5120 column-sharded",
-           "world": world, "scaling": "strong"}
+           "world": world, "scaling": "strong",
+           "fields": "M1_mlp_chained_us: gate|up -> down -> exchange as ONE launch per rank; "
+                     "M1_mlp_fused_exchange_us: two launches, exchange folded into the second; "
+                     "*_with_exchange_us: library all-reduce; *_with_reduce_scatter_us: library reduce-scatter, "
+                     "result sharded by batch rows; *_efficiency = t(unsharded on one GPU) / (world x best sharded time)"}
     parity = 0.0
 
     def allmax(v):
@@ -331,6 +335,11 @@ def tp_linears(rank, world, local, stream):
         return float(t[0])
 
     peers = be.make_peer_buffer(None, H5) if world > 1 else None
+    peers_chain = be.make_peer_buffer(None, H5) if world > 1 else None
+    # the unsharded linears on this GPU: t(1) of the strong-scaling efficiencies below
+    if world > 1:
+        gu_full = be.fuse(be.make_shard(gate, sharded.ROWS, 0, 1), be.make_shard(up, sharded.ROWS, 0, 1))
+        dn_full = be.make_shard(down, sharded.COLS, 0, 1)
     for M, reps in ((1, 100), (2048, 10)):
         x = synth.gaussian_activation(5009 + M, M, H5).to(dev)
         xo = synth.gaussian_activation(5019 + M, M, Q5).to(dev)
@@ -363,6 +372,21 @@ def tp_linears(rank, world, local, stream):
             assert be.gate_up_swiglu(gate_up, x, mid, 1, local_ff)
             be.forward_allreduce(dn, peers, mid, y_fused)
 
+        y_chain = be.empty(1, H5)
+        chain = None
+        if M == 1:
+            try:  # gate|up -> down (-> exchange) as ONE launch per rank
+                chain = be.make_chain([dict(linear=gate_up, ff_dim=local_ff, x=x), dict(linear=dn, y=y_chain)],
+                                      peers_chain)
+            except Exception as e:  # (unsharded, the 25600 input columns of down are beyond the chained kernel)
+                out["M1_mlp_chained_note"] = f"not applicable at world {world}: {e}"
+
+        rs_out = be.empty(max(1, M // world), H5)
+
+        def mlp_reduce_scatter():  # the sum arrives sharded by rows of the batch: half the NVLink bytes
+            mlp_compute()
+            dist.reduce_scatter_tensor(rs_out, part)
+
         def q_proj():
             be.forward(q_r, x, yq, M)
 
@@ -391,13 +415,34 @@ def tp_linears(rank, world, local, stream):
         out[f"M{M}_o_compute_us"], out[f"M{M}_o_with_exchange_us"] = t_oc, t_of
         if M == 1 and world > 1:
             out["M1_mlp_fused_exchange_us"] = timed(mlp_fused)
+        if chain is not None:
+            out["M1_mlp_chained_us"] = timed(chain.run)
+        if M > 1 and world > 1 and M % world == 0:
+            out[f"M{M}_mlp_with_reduce_scatter_us"] = timed(mlp_reduce_scatter)
+        if world > 1:
+            mid_f, y_f = be.empty(M, FF5), be.empty(M, H5)
+
+            def mlp_unsharded():
+                assert be.gate_up_swiglu(gu_full, x, mid_f, M, FF5)
+                be.forward(dn_full, mid_f, y_f, M)
+
+            t1 = timed(mlp_unsharded)
+            out[f"M{M}_mlp_unsharded_one_gpu_us"] = t1
+            best = min(v for k, v in out.items() if k.startswith(f"M{M}_mlp_") and k.endswith("_us")
+                       and "compute" not in k and "collective" not in k and "unsharded" not in k)
+            out[f"M{M}_mlp_efficiency"] = t1 / (world * best)
+            del mid_f, y_f
         # ---- parity against the oracle on the unsharded weights
         with torch.cuda.stream(stream):
+            if M > 1 and world > 1 and M % world == 0:
+                mlp_reduce_scatter()  # (before mlp_full: both leave their input in `part`)
             mlp_full()
             o_full()
             q_proj()
             if M == 1 and world > 1:
                 mlp_fused()
+            if chain is not None:
+                chain.run()
             stream.synchronize()
         be.scratch.check()
         rows = [0] if M == 1 else [0, 1029, 2047]
@@ -424,11 +469,20 @@ def tp_linears(rank, world, local, stream):
                          _max_rel_err(_bits(yq)[r], q_w[i][rank * local_q:(rank + 1) * local_q]))
             if M == 1 and world > 1:
                 parity = max(parity, _max_rel_err(_bits(y_fused)[0], y_w[i]))
+            if chain is not None:
+                parity = max(parity, _max_rel_err(_bits(y_chain)[0], y_w[i]))
+            if M > 1 and world > 1 and M % world == 0:
+                per = M // world
+                if rank * per <= r < (rank + 1) * per:
+                    parity = max(parity, _max_rel_err(_bits(rs_out)[r - rank * per], y_w[i]))
+        if chain is not None:
+            chain.close()
     out["parity_max_rel_err"] = allmax(parity)
     out["parity_bound"] = 2e-2
     if peers is not None:
         dist.barrier()
         peers.close()
+        peers_chain.close()
     return out
 
 

@@ -327,6 +327,17 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_create(AilaNf4Scratch* scratch, const 
                                                  int n_ops, AilaNf4Chain** out);
 AILA_NF4_API void aila_nf4_chain_destroy(AilaNf4Chain* chain);
 AILA_NF4_API int aila_nf4_chain_length(const AilaNf4Chain* chain);
+/* A chain whose LAST operation is row-parallel (its linear holds a column shard of the weight,
+ * aila_nf4_linear_create_shard with AILA_NF4_SHARD_COLS): the launch stores that operation's fp32
+ * row sums into every rank's exchange buffer and writes y_bf16 of the last operation as
+ * bf16(sum over the ranks (+ residual_bf16)), bit-identical on all ranks - the exchange of
+ * aila_nf4_forward_decode_allreduce inside the chained launch (for example gate|up -> down of
+ * a tensor-parallel MLP in one launch per rank). The rules of both apply: every rank runs the
+ * same chains in the same order on one stream per GPU; the buffer must outlive the chain. No
+ * reference counterpart. */
+AILA_NF4_API AilaNf4Status aila_nf4_chain_create_allreduce(AilaNf4Scratch* scratch,
+                                                           const AilaNf4ChainOp* ops, int n_ops,
+                                                           AilaNf4PeerBuf* peers, AilaNf4Chain** out);
 AILA_NF4_API AilaNf4Status aila_nf4_chain_run(AilaNf4Chain* chain, void* stream);
 /* Same with HOST buffers at both ends: copies x of the first operation (in_features bf16) to
  * the device buffer named in the list, runs the chain, copies the last operation's y back and
@@ -335,8 +346,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_chain_run_host(AilaNf4Chain* chain, const vo
                                                    void* y_host_bf16, void* stream);
 /* Bound, in SM clock cycles, of every device-side wait of the decode kernels launched with this
  * scratch: the chained kernel, the single-call kernel and the row-parallel exchange (default
- * 2e9, about a second). Takes effect at the next launch. Chains copy it when they are created.
- * No reference counterpart. */
+ * 2e9, about a second). Takes effect at the next launch. No reference counterpart. */
 AILA_NF4_API AilaNf4Status aila_nf4_scratch_set_wait_limit(AilaNf4Scratch* scratch,
                                                            int64_t sm_cycles);
 

@@ -245,3 +245,46 @@ def test_chain_rejects_bad_lists(nf4, scratch):
         nf4.DecodeChain(scratch, [dict(linear=a, x=x)])
     with pytest.raises(_lib.Nf4Error):
         nf4.DecodeChain(scratch, [])
+
+
+def test_chain_with_exchange_on_one_rank(nf4, oracle, scratch):
+    """gate|up -> down as one launch whose last operation goes through the row-parallel exchange,
+    in a group of ONE rank: the sum over the ranks is this rank's sum, so the result must equal the
+    plain chain bit for bit - eagerly (both halves of the exchange buffer) and replayed from a CUDA
+    graph. The multi-rank case runs with the sharded tests."""
+    H, FF = 1024, 2048
+    g, u, d = make_weight(7600, FF, H), make_weight(7601, FF, H), make_weight(7602, H, FF)
+    gu, dn = _fused(nf4, [g, u]), _lin(nf4, d)
+    x, res = _act(7603, 1, H).cuda(), _act(7604, 1, H).cuda()
+    y_plain, y_peer = _empty(H), _empty(H)
+    plain = nf4.DecodeChain(scratch, [dict(linear=gu, ff_dim=FF, x=x), dict(linear=dn, y=y_plain, residual=res)])
+    peers = nf4.PeerBuffer(0, 0, 1, H)
+    shared = nf4.DecodeChain(scratch, [dict(linear=gu, ff_dim=FF, x=x), dict(linear=dn, y=y_peer, residual=res)],
+                             peers=peers)
+    plain.run()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        y_peer.fill_(float("nan"))
+        shared.run()
+        torch.cuda.synchronize()
+        scratch.check()
+        assert torch.equal(y_peer.view(torch.uint16), y_plain.view(torch.uint16))
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            shared.run()
+        y_peer.fill_(float("nan"))
+        for _ in range(3):
+            graph.replay()
+        st.synchronize()
+    scratch.check()
+    assert torch.equal(y_peer.view(torch.uint16), y_plain.view(torch.uint16))
+    mid = _gate_up_want(oracle, g, u, bf16_bits(x))
+    want = _gemv_want(oracle, d, mid, residual=bf16_bits(res).reshape(-1))
+    assert_close_norm(bf16_bits(y_peer).reshape(-1), want, REL, "exchange chain on one rank")
+    with pytest.raises(_lib.Nf4Error):  # a gate|up operation cannot be the row-parallel one
+        nf4.DecodeChain(scratch, [dict(linear=gu, ff_dim=FF, x=x, y=_empty(FF))], peers=peers)
+    shared.close()
+    plain.close()
+    peers.close()

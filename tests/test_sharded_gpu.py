@@ -71,6 +71,16 @@ def _worker(rank, world, port, q):
         everyone = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(everyone, mine)
         same = same and all(torch.equal(mine, t) for t in everyone)
+        # the same MLP as ONE launch per rank (gate|up -> down -> exchange inside the chained kernel)
+        yc = [fused.forward_chained(x1).clone() for _ in range(4)]
+        torch.cuda.synchronize()
+        be.scratch.check()
+        same = same and all(torch.equal(yc[0], t) for t in yc[1:])
+        dist.all_gather(everyone, yc[0])
+        same = same and all(torch.equal(yc[0], t) for t in everyone)
+        chained_err = float((yc[0].float() - ys[0].float()).abs().max() / ys[0].float().abs().max())
+        same = same and chained_err < 1e-2
+        outs["chained"] = yc[0].cpu().view(torch.uint16).numpy()
         # a tall, narrow row-parallel linear: its grid exceeds the SM count, so the exchange takes
         # the two-kernel form (publish, then a reducer kernel) instead of the single launch
         tall = make_weight(4, 20000, 128 * world)
@@ -120,6 +130,7 @@ def test_sharded_mlp_nccl(oracle, world):
     am = np.concatenate([oracle_absmax(oracle, gate), oracle_absmax(oracle, up)])
     assert res[1].pop("fused_consistent"), "fused exchange: results differ between calls or ranks"
     fused_bits = res[1].pop("fused")
+    chained_bits = res[1].pop("chained")
     for M, got in res[1].items():
         x = synth.gaussian_activation(10 + M, M, H).view(torch.uint16).numpy()
         if M == 1:
@@ -133,6 +144,8 @@ def test_sharded_mlp_nccl(oracle, world):
         if M == 1:
             err = np.abs(bits_to_f32(fused_bits) - want).max()
             assert err <= 2e-2 * np.abs(want).max(), ("fused", err)
+            err = np.abs(bits_to_f32(chained_bits) - want).max()
+            assert err <= 2e-2 * np.abs(want).max(), ("chained", err)
             # (not bit-equal to the library route, which rounds every rank's partial sum to bf16
             # before the all-reduce; the fused route adds the fp32 partial sums and rounds once)
 
