@@ -575,6 +575,30 @@ def decode_stack(local, stream, batches=(4, 8, 16, 32)):
     wbytes = 36 * (weight_bytes(Q + 2 * KV, HID) + weight_bytes(HID, Q) + 2 * weight_bytes(F, HID) +
                    weight_bytes(HID, F))
     pk = peaks()
+    # the whole decode step of the same model through the backend skeleton (embedding, per-head
+    # norm + RoPE + cache append, attention, the linears, lm_head, argmax), host-driven, greedy
+    from aila_b200.backend import Qwen3Bnb4Backend, Qwen3Config
+    cfgm = Qwen3Config(hidden_size=HID, intermediate_size=F, num_hidden_layers=36, num_attention_heads=32,
+                       num_key_value_heads=8, head_dim=128, vocab_size=VOCAB)
+    ones = torch.ones(HID, dtype=torch.bfloat16)
+    model = Qwen3Bnb4Backend(cfgm, local, max_seq_len=256)
+    model.load((torch.randn(VOCAB, HID, generator=g, device=dev) * 0.02).to(torch.bfloat16),
+               [dict(qkv=t[0], o=t[1], gate_up=t[2], down=t[3], input_ln=ones, post_attn_ln=ones,
+                     q_norm=torch.ones(128, dtype=torch.bfloat16), k_norm=torch.ones(128, dtype=torch.bfloat16))
+                for t in layers], ones, heads[0])
+    n_prompt, n_gen = 16, 48
+    with torch.cuda.stream(stream):
+        model.forward(torch.arange(1, n_prompt + 1, dtype=torch.int32))
+        tok = model.greedy_token()
+        stream.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n_gen):
+            model.forward(tok)
+            tok = model.greedy_token()
+        stream.synchronize()
+        tok_s = n_gen / (time.perf_counter() - t0)
+    model.scratch.check()
+    model.close()
     for t in layers:
         for l in t:
             l.close()
@@ -586,6 +610,9 @@ def decode_stack(local, stream, batches=(4, 8, 16, 32)):
             "per_call": {"launches_per_step": 144, "us_per_step": us_calls,
                          "frac_of_measured_hbm": wbytes / us_calls / 1e3 / pk["hbm"]},
             "small_batch": batch,
+            "backend_decode": {"what": "whole decode steps of the 36-layer model through "
+                                       "aila_b200.backend.Qwen3Bnb4Backend (4 launches per layer, driven from "
+                                       "Python, greedy), context 16..64, wall clock", "tokens_per_s": tok_s},
             "lm_head": {"workload": "bf16 dense GEMV 2560 -> 151936, 4 distinct weights in turn",
                         "us": us_head, "weight_GBps": head_bytes / us_head / 1e3,
                         "frac_of_measured_hbm": head_bytes / us_head / 1e3 / pk["hbm"]},

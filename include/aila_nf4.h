@@ -377,6 +377,35 @@ AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, 
                                             int device, void* stream);
 
 /*
+ * The operators of a decode step between the linears (the reference's callers of this path,
+ * src/models/Qwen3Bnb4Backend.cpp:298-439): simple kernels with the reference's arithmetic and
+ * roundings, so that a backend built on this library runs end to end.
+ *   aila_embedding_lookup      ops::embedding_lookup   (src/ops/ElementwiseOps.cpp:14-27)
+ *   aila_decode_prepare_qkv    ops::decode_prepare_qkv (src/ops/ElementwiseOps.cpp:105-215): per
+ *       head RMSNorm of q and k (weights [head_dim]), rotation by start_pos * rope_freq[d]
+ *       (rope_freq[d] = theta^(-2d/head_dim), d < head_dim/2; halves d and d + head_dim/2 pair
+ *       up), in place; k and v of the new token are appended to the caches
+ *       [kv_head][max_seq_len][head_dim] at start_pos.
+ *   aila_attention_decode      ops::attention_decode, baseline form (src/ops/AttentionOps.cpp:
+ *       73-166): one query token against cached_len cached positions, grouped-query heads,
+ *       scale 1/sqrt(head_dim), fp32 softmax; at most about 51,000 cached positions.
+ */
+AILA_NF4_API AilaNf4Status aila_embedding_lookup(const void* table_bf16, int64_t vocab_size,
+                                                 const int32_t* token_ids_device, int seq_len,
+                                                 int hidden_size, void* out_bf16, int device,
+                                                 void* stream);
+AILA_NF4_API AilaNf4Status aila_decode_prepare_qkv(void* q_bf16, void* k_bf16, const void* v_bf16,
+                                                   const float* rope_freq, const void* q_norm_weight_bf16,
+                                                   const void* k_norm_weight_bf16, void* k_cache_bf16,
+                                                   void* v_cache_bf16, int max_seq_len, int start_pos,
+                                                   int num_heads_q, int num_kv_heads, int head_dim,
+                                                   float eps, int device, void* stream);
+AILA_NF4_API AilaNf4Status aila_attention_decode(const void* q_bf16, const void* k_cache_bf16,
+                                                 const void* v_cache_bf16, void* out_bf16, int num_heads,
+                                                 int num_kv_heads, int head_dim, int cached_len,
+                                                 int max_seq_len, int device, void* stream);
+
+/*
  * Checkpoint front-end (host side, no GPU work): a memory-mapped safetensors file and the
  * assembly of one bitsandbytes 4-bit weight into an AilaNf4WeightDesc whose pointers lie
  * inside the mapping, ready for aila_nf4_linear_create (keep the file open until the create

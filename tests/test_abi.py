@@ -22,7 +22,7 @@ def lib():
 
 def test_header_and_binding_agree(lib):
     text = open(os.path.join(ROOT, "include", "aila_nf4.h")).read()
-    declared = set(re.findall(r"\b(aila_(?:nf4|st|dense|argmax|add)_[a-z0-9_]+)\s*\(", text))
+    declared = set(re.findall(r"\b(aila_(?:nf4|st|dense|argmax|add|embedding|decode|attention)_[a-z0-9_]+)\s*\(", text))
     assert declared == set(_lib.EXPORTED_SYMBOLS), declared ^ set(_lib.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
