@@ -100,11 +100,11 @@ _SIGNATURES = {
     "aila_nf4_peerbuf_export": (ctypes.c_int, [_VP, _VP]),
     "aila_nf4_peerbuf_import": (ctypes.c_int, [_VP, ctypes.c_int, _VP]),
     "aila_embedding_lookup": (ctypes.c_int, [_VP, ctypes.c_int64, _VP, ctypes.c_int, ctypes.c_int, _VP, ctypes.c_int, _VP]),
-    "aila_decode_prepare_qkv": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, ctypes.c_int, ctypes.c_int,
+    "aila_decode_prepare_qkv": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, ctypes.c_int, ctypes.c_int, _VP,
                                                 ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int,
                                                 _VP]),
     "aila_attention_decode": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                              ctypes.c_int, ctypes.c_int, _VP]),
+                                              _VP, ctypes.c_int, ctypes.c_int, _VP]),
     "aila_nf4_peerbuf_import_local": (ctypes.c_int, [_VP, ctypes.c_int, _VP]),
     "aila_nf4_peerbuf_destroy": (None, [_VP]),
     "aila_nf4_forward_decode_allreduce": (ctypes.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),

@@ -57,21 +57,25 @@ def embedding_lookup(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Te
 
 
 def decode_prepare_qkv(q, k, v, rope_freq, q_norm_w, k_norm_w, k_cache, v_cache, start_pos, num_heads,
-                       num_kv_heads, head_dim, eps) -> None:
+                       num_kv_heads, head_dim, eps, position: torch.Tensor | None = None) -> None:
     """ops::decode_prepare_qkv (src/ops/ElementwiseOps.cpp:105-215); q, k, v may be views into one
-    qkv buffer."""
+    qkv buffer. ``position`` (int32 device tensor of one element) overrides start_pos on the device."""
     _lib.check(_lib.load().aila_decode_prepare_qkv(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), rope_freq.data_ptr(), q_norm_w.data_ptr(), k_norm_w.data_ptr(),
-        k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[1], int(start_pos), num_heads, num_kv_heads,
+        k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[1], int(start_pos),
+        position.data_ptr() if position is not None else None, num_heads, num_kv_heads,
         head_dim, float(eps), q.device.index, _stream_ptr(q.device)))
 
 
-def attention_decode(q, k_cache, v_cache, out, num_heads, num_kv_heads, head_dim, cached_len) -> None:
-    """ops::attention_decode (src/ops/AttentionOps.cpp:73-166, whole window)."""
+def attention_decode(q, k_cache, v_cache, out, num_heads, num_kv_heads, head_dim, cached_len,
+                     position: torch.Tensor | None = None) -> None:
+    """ops::attention_decode (src/ops/AttentionOps.cpp:73-166, whole window). With ``position`` the
+    kernel attends to position + 1 cached tokens (read on the device); cached_len is then the most
+    the launch can hold."""
     _lib.check(_lib.load().aila_attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                                                  out.data_ptr(), num_heads, num_kv_heads, head_dim,
-                                                 int(cached_len), k_cache.shape[1], q.device.index,
-                                                 _stream_ptr(q.device)))
+                                                 int(cached_len), position.data_ptr() if position is not None else None,
+                                                 k_cache.shape[1], q.device.index, _stream_ptr(q.device)))
 
 
 class Qwen3Bnb4Backend:
@@ -109,6 +113,8 @@ class Qwen3Bnb4Backend:
         self.logits = torch.zeros(1, c.vocab_size, **bf)
         self.token = torch.zeros(1, dtype=torch.int32, device=dev)
         self.next_token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.position = torch.zeros(1, dtype=torch.int32, device=dev)   # device copy of current_length
+        self._graph = None
         self.rope_freq = (1.0 / torch.pow(torch.tensor(float(c.rope_theta)),
                                           2.0 * torch.arange(c.head_dim // 2, dtype=torch.float32) / c.head_dim)
                           ).to(dev)
@@ -155,12 +161,16 @@ class Qwen3Bnb4Backend:
                 dict(linear=L["down"], y=self.down_out)]))
 
     # -- one token ------------------------------------------------------------------------------
-    def _decode_one(self) -> None:
+    def _decode_one(self, on_device: bool = False) -> None:
+        """One token through the model. on_device: the position comes from self.position (for a
+        captured step that is replayed), and the attention launch is sized for the whole window."""
         c = self.cfg
         pos = self.current_length
         if pos + 1 > self.max_seq_len:
             raise RuntimeError(f"Qwen3Bnb4Backend::forward: context window exceeded (cached_len={pos + 1}, "
                                f"max_seq_len={self.max_seq_len})")
+        where = self.position if on_device else None
+        length = self.max_seq_len if on_device else pos + 1
         embedding_lookup(self.embed, self.token, self.hidden)
         add_rms_norm(self.hidden, None, self.norms[0]["input_ln"], c.rms_norm_eps, None, self.normed)
         self.lin[0]["qkv"].forward(self.scratch, self.normed, self.qkv, 1)
@@ -171,9 +181,9 @@ class Qwen3Bnb4Backend:
         for i in range(n):
             decode_prepare_qkv(q, k, v, self.rope_freq, self.norms[i]["q_norm"], self.norms[i]["k_norm"],
                                self.k_cache[i], self.v_cache[i], pos, c.num_attention_heads,
-                               c.num_key_value_heads, c.head_dim, c.rms_norm_eps)
+                               c.num_key_value_heads, c.head_dim, c.rms_norm_eps, where)
             attention_decode(q, self.k_cache[i], self.v_cache[i], self.attn_out, c.num_attention_heads,
-                             c.num_key_value_heads, c.head_dim, pos + 1)
+                             c.num_key_value_heads, c.head_dim, length, where)
             self.chains[i].run()  # hidden2 = hidden + o_proj(attn); down_out = MLP(norm(hidden2))
             if i + 1 < n:
                 # hidden = hidden2 + down_out; qkv of the next layer from its input norm, one launch
@@ -186,7 +196,8 @@ class Qwen3Bnb4Backend:
         # after the last layer: hidden2 holds hidden + o, down_out the MLP output
         add_rms_norm(self.hidden2, self.down_out, self.final_norm, c.rms_norm_eps, None, self.normed)
         self.lm_head.forward(self.scratch, self.normed, self.logits, 1)
-        self.current_length = pos + 1
+        if not on_device:
+            self.current_length = pos + 1
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         """token_ids: int32 device tensor [seq_len]; appends them to the context and returns the
@@ -203,6 +214,38 @@ class Qwen3Bnb4Backend:
         """ops::argmax over the current logits (device int32 tensor of one element)."""
         argmax(self.logits, self.cfg.vocab_size, self.next_token)
         return self.next_token
+
+    def generate(self, n_tokens: int) -> torch.Tensor:
+        """Greedy decoding of n_tokens after the context so far, starting from the token that the
+        last forward() chose. One whole step (embedding ... lm_head, argmax, feeding the choice back
+        and advancing the position) is captured in a CUDA graph once and replayed per token: the
+        host issues one launch per token and never waits. Returns the int32 tokens [n_tokens]."""
+        if self.current_length == 0:
+            raise RuntimeError("generate() continues a context: call forward() with a prompt first")
+        if self.current_length + n_tokens > self.max_seq_len:
+            raise RuntimeError(f"Qwen3Bnb4Backend::generate: context window exceeded (cached_len="
+                               f"{self.current_length + n_tokens}, max_seq_len={self.max_seq_len})")
+        out = torch.empty(n_tokens, dtype=torch.int32, device=self.dev)
+        stream = torch.cuda.current_stream(self.dev)
+        self.position.fill_(self.current_length)
+        argmax(self.logits, self.cfg.vocab_size, self.token)    # the choice after the context so far
+        if self._graph is None:
+            side = torch.cuda.Stream(self.dev)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                self._decode_one(on_device=True)               # warm-up outside the capture (same state)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    self._decode_one(on_device=True)
+                    argmax(self.logits, self.cfg.vocab_size, self.token)
+                    self.position.add_(1)
+            stream.wait_stream(side)
+            self._graph = graph
+        for i in range(n_tokens):
+            out[i:i + 1].copy_(self.token)
+            self._graph.replay()
+        self.current_length += n_tokens
+        return out
 
     def reset(self) -> None:
         self.current_length = 0

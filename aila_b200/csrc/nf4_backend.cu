@@ -44,9 +44,11 @@ __global__ void __launch_bounds__(128)
 prepare_qkv_kernel(uint16_t* __restrict__ q, uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
                    const float* __restrict__ rope_freq, const uint16_t* __restrict__ q_norm_w,
                    const uint16_t* __restrict__ k_norm_w, uint16_t* __restrict__ k_cache,
-                   uint16_t* __restrict__ v_cache, int max_seq_len, int pos, int n_kv, int head_dim,
-                   float eps) {
+                   uint16_t* __restrict__ v_cache, int max_seq_len, int pos, const int* __restrict__ pos_dev,
+                   int n_kv, int head_dim, float eps) {
     __shared__ float scratch[128];
+    if (pos_dev) pos = *pos_dev;
+    if (pos < 0 || pos >= max_seq_len) return;  // (the host refuses such a step; nothing is written)
     const int head = blockIdx.x;
     const int half = head_dim / 2;
     auto norm_and_rotate = [&](uint16_t* x, const uint16_t* w) {
@@ -83,10 +85,13 @@ prepare_qkv_kernel(uint16_t* __restrict__ q, uint16_t* __restrict__ k, const uin
 __global__ void __launch_bounds__(256)
 attention_decode_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k_cache,
                         const uint16_t* __restrict__ v_cache, uint16_t* __restrict__ out,
-                        int heads_per_kv, int head_dim, int cached_len, int max_seq_len) {
+                        int heads_per_kv, int head_dim, int cached_len, const int* __restrict__ pos_dev,
+                        int max_seq_len) {
     extern __shared__ float att_smem[];
-    float* score = att_smem;               // [cached_len]
-    float* qf = att_smem + cached_len;     // [head_dim]
+    if (pos_dev) cached_len = min(*pos_dev + 1, cached_len);  // (the launch holds `cached_len` scores at most)
+    if (cached_len <= 0) return;
+    float* qf = att_smem;                  // [head_dim]
+    float* score = att_smem + head_dim;    // [cached_len]
     __shared__ float red[8];
     const int head = blockIdx.x, kv_head = head / heads_per_kv;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -170,8 +175,9 @@ AILA_NF4_API AilaNf4Status aila_decode_prepare_qkv(void* q_bf16, void* k_bf16, c
                                                    const float* rope_freq, const void* q_norm_weight_bf16,
                                                    const void* k_norm_weight_bf16, void* k_cache_bf16,
                                                    void* v_cache_bf16, int max_seq_len, int start_pos,
-                                                   int num_heads_q, int num_kv_heads, int head_dim,
-                                                   float eps, int device, void* stream) {
+                                                   const int32_t* position_device, int num_heads_q,
+                                                   int num_kv_heads, int head_dim, float eps, int device,
+                                                   void* stream) {
     if (!q_bf16 || !k_bf16 || !v_bf16 || !rope_freq || !q_norm_weight_bf16 || !k_norm_weight_bf16 ||
         !k_cache_bf16 || !v_cache_bf16)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
@@ -187,7 +193,7 @@ AILA_NF4_API AilaNf4Status aila_decode_prepare_qkv(void* q_bf16, void* k_bf16, c
         static_cast<uint16_t*>(q_bf16), static_cast<uint16_t*>(k_bf16), static_cast<const uint16_t*>(v_bf16),
         rope_freq, static_cast<const uint16_t*>(q_norm_weight_bf16),
         static_cast<const uint16_t*>(k_norm_weight_bf16), static_cast<uint16_t*>(k_cache_bf16),
-        static_cast<uint16_t*>(v_cache_bf16), max_seq_len, start_pos, num_kv_heads, head_dim, eps);
+        static_cast<uint16_t*>(v_cache_bf16), max_seq_len, start_pos, position_device, num_kv_heads, head_dim, eps);
     NF4_CUDA(cudaGetLastError());
     return AILA_NF4_OK;
 }
@@ -195,7 +201,8 @@ AILA_NF4_API AilaNf4Status aila_decode_prepare_qkv(void* q_bf16, void* k_bf16, c
 AILA_NF4_API AilaNf4Status aila_attention_decode(const void* q_bf16, const void* k_cache_bf16,
                                                  const void* v_cache_bf16, void* out_bf16, int num_heads,
                                                  int num_kv_heads, int head_dim, int cached_len,
-                                                 int max_seq_len, int device, void* stream) {
+                                                 const int32_t* position_device, int max_seq_len, int device,
+                                                 void* stream) {
     if (!q_bf16 || !k_cache_bf16 || !v_cache_bf16 || !out_bf16) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || head_dim <= 0)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "query heads must be a positive multiple of the key/value heads");
@@ -216,7 +223,7 @@ AILA_NF4_API AilaNf4Status aila_attention_decode(const void* q_bf16, const void*
     nf4::attention_decode_kernel<<<(unsigned)num_heads, 256, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(q_bf16), static_cast<const uint16_t*>(k_cache_bf16),
         static_cast<const uint16_t*>(v_cache_bf16), static_cast<uint16_t*>(out_bf16), num_heads / num_kv_heads,
-        head_dim, cached_len, max_seq_len);
+        head_dim, cached_len, position_device, max_seq_len);
     NF4_CUDA(cudaGetLastError());
     return AILA_NF4_OK;
 }

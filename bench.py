@@ -597,6 +597,12 @@ def decode_stack(local, stream, batches=(4, 8, 16, 32)):
             tok = model.greedy_token()
         stream.synchronize()
         tok_s = n_gen / (time.perf_counter() - t0)
+        model.generate(4)  # captures the step
+        stream.synchronize()
+        t0 = time.perf_counter()
+        model.generate(n_gen)
+        stream.synchronize()
+        tok_s_graph = n_gen / (time.perf_counter() - t0)
     model.scratch.check()
     model.close()
     for t in layers:
@@ -612,7 +618,10 @@ def decode_stack(local, stream, batches=(4, 8, 16, 32)):
             "small_batch": batch,
             "backend_decode": {"what": "whole decode steps of the 36-layer model through "
                                        "aila_b200.backend.Qwen3Bnb4Backend (4 launches per layer, driven from "
-                                       "Python, greedy), context 16..64, wall clock", "tokens_per_s": tok_s},
+                                       "Python, greedy), context 16..64, wall clock", "tokens_per_s": tok_s,
+                               "tokens_per_s_graph": tok_s_graph,
+                               "graph": "generate(): one captured step (position and token stay on the device) "
+                                        "replayed per token, context 68..116"},
             "lm_head": {"workload": "bf16 dense GEMV 2560 -> 151936, 4 distinct weights in turn",
                         "us": us_head, "weight_GBps": head_bytes / us_head / 1e3,
                         "frac_of_measured_hbm": head_bytes / us_head / 1e3 / pk["hbm"]},

@@ -389,6 +389,10 @@ AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, 
  *   aila_attention_decode      ops::attention_decode, baseline form (src/ops/AttentionOps.cpp:
  *       73-166): one query token against cached_len cached positions, grouped-query heads,
  *       scale 1/sqrt(head_dim), fp32 softmax; at most about 51,000 cached positions.
+ * position_device (may be NULL) lets the position live on the device, so that a whole decode step
+ * can be one CUDA graph replayed per token: when given, aila_decode_prepare_qkv uses
+ * *position_device instead of start_pos, and aila_attention_decode uses *position_device + 1
+ * cached positions, of which the launch can hold `cached_len` (pass the window's size).
  */
 AILA_NF4_API AilaNf4Status aila_embedding_lookup(const void* table_bf16, int64_t vocab_size,
                                                  const int32_t* token_ids_device, int seq_len,
@@ -398,12 +402,14 @@ AILA_NF4_API AilaNf4Status aila_decode_prepare_qkv(void* q_bf16, void* k_bf16, c
                                                    const float* rope_freq, const void* q_norm_weight_bf16,
                                                    const void* k_norm_weight_bf16, void* k_cache_bf16,
                                                    void* v_cache_bf16, int max_seq_len, int start_pos,
-                                                   int num_heads_q, int num_kv_heads, int head_dim,
-                                                   float eps, int device, void* stream);
+                                                   const int32_t* position_device, int num_heads_q,
+                                                   int num_kv_heads, int head_dim, float eps, int device,
+                                                   void* stream);
 AILA_NF4_API AilaNf4Status aila_attention_decode(const void* q_bf16, const void* k_cache_bf16,
                                                  const void* v_cache_bf16, void* out_bf16, int num_heads,
                                                  int num_kv_heads, int head_dim, int cached_len,
-                                                 int max_seq_len, int device, void* stream);
+                                                 const int32_t* position_device, int max_seq_len, int device,
+                                                 void* stream);
 
 /*
  * Checkpoint front-end (host side, no GPU work): a memory-mapped safetensors file and the

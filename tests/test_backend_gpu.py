@@ -139,4 +139,24 @@ def test_qwen3_backend_decodes_like_the_oracle(be, oracle):
     assert model.current_length == 6
     with pytest.raises(RuntimeError, match="context window exceeded"):
         model.forward(torch.tensor([1, 2, 3], dtype=torch.int32))
+    # greedy generation replayed from one captured step must choose what step-by-step calls choose
+    prompt = torch.tensor(tokens[:3], dtype=torch.int32)
+    model.reset()
+    model.forward(prompt)
+    by_hand = []
+    for _ in range(4):
+        tok = model.greedy_token().clone()
+        by_hand.append(int(tok.cpu()[0]))
+        model.forward(tok)
+    last_by_hand = bf16_bits(model.logits).copy()
+    model.reset()
+    model.forward(prompt)
+    replayed = model.generate(2).cpu().tolist() + model.generate(2).cpu().tolist()
+    torch.cuda.synchronize()
+    model.scratch.check()
+    assert replayed == by_hand
+    assert np.array_equal(bf16_bits(model.logits), last_by_hand)
+    assert model.current_length == 7
+    with pytest.raises(RuntimeError, match="context window exceeded"):
+        model.generate(2)
     model.close()
