@@ -125,6 +125,13 @@ _SIGNATURES = {
     "aila_st_tensor_count": (ctypes.c_int64, [_VP]),
     "aila_st_tensor_name": (ctypes.c_char_p, [_VP, ctypes.c_int64]),
     "aila_st_find": (ctypes.c_int, [_VP, ctypes.c_char_p, ctypes.POINTER(StTensorView)]),
+    "aila_st_dir_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_VP)]),
+    "aila_st_dir_close": (None, [_VP]),
+    "aila_st_dir_shard_count": (ctypes.c_int64, [_VP]),
+    "aila_st_dir_shard": (_VP, [_VP, ctypes.c_int64]),
+    "aila_st_dir_find": (ctypes.c_int, [_VP, ctypes.c_char_p, ctypes.POINTER(StTensorView)]),
+    "aila_st_dir_load_bnb4_weight": (ctypes.c_int, [_VP, ctypes.c_char_p, ctypes.c_int,
+                                                     ctypes.POINTER(WeightDesc)]),
     "aila_st_load_bnb4_weight": (ctypes.c_int, [_VP, ctypes.c_char_p, ctypes.c_int,
                                                 ctypes.POINTER(WeightDesc)]),
     "aila_nf4_dequantize": (ctypes.c_int, [_VP, _VP, _VP]),

@@ -82,6 +82,68 @@ class SafetensorsFile:
         return desc
 
 
+class ModelDir:
+    """A model directory: ``model.safetensors``, or the shards that
+    ``model.safetensors.index.json`` names (reference LoadModelWeightsFromDir,
+    src/utils/SafeTensors.cpp:491-535). Tensor data stays valid until ``close``."""
+
+    def __init__(self, path: str):
+        self._h = ctypes.c_void_p()
+        self.path = str(path)
+        _lib.check(_lib.load().aila_st_dir_open(self.path.encode(), ctypes.byref(self._h)))
+
+    def close(self) -> None:
+        if self._h:
+            _lib.load().aila_st_dir_close(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def shard_count(self) -> int:
+        return int(_lib.load().aila_st_dir_shard_count(self._h))
+
+    def names(self) -> list[str]:
+        lib = _lib.load()
+        seen: dict[str, None] = {}
+        for i in range(self.shard_count()):
+            f = lib.aila_st_dir_shard(self._h, i)
+            for j in range(lib.aila_st_tensor_count(f)):
+                seen[lib.aila_st_tensor_name(f, j).decode()] = None
+        return list(seen)
+
+    def has(self, name: str) -> bool:
+        view = _lib.StTensorView()
+        st = _lib.load().aila_st_dir_find(self._h, name.encode(), ctypes.byref(view))
+        if st == _lib.NOT_APPLICABLE:
+            return False
+        _lib.check(st)
+        return True
+
+    def get(self, name: str) -> np.ndarray:
+        view = _lib.StTensorView()
+        _lib.check(_lib.load().aila_st_dir_find(self._h, name.encode(), ctypes.byref(view)))
+        dt = _ST_TO_NP[_lib.ST_DTYPES[view.dtype]]
+        shape = tuple(view.shape[i] for i in range(view.rank))
+        raw = ctypes.string_at(view.data, view.nbytes) if view.nbytes else b""
+        return np.frombuffer(raw, dtype=dt).reshape(shape).copy()
+
+    def load_bnb4_weight_ref(self, name: str, device: int = 0) -> _lib.WeightDesc:
+        desc = _lib.WeightDesc()
+        _lib.check(_lib.load().aila_st_dir_load_bnb4_weight(self._h, name.encode(), int(device),
+                                                            ctypes.byref(desc)))
+        return desc
+
+
 def write_safetensors(path: str, tensors: dict[str, np.ndarray],
                       metadata: dict[str, str] | None = None) -> None:
     """Writes ``tensors`` in safetensors layout: u64 header length, JSON header, tensor bytes."""

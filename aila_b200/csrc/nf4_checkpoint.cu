@@ -18,11 +18,13 @@
 
 #include <cerrno>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
 #include <new>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -378,21 +380,36 @@ AILA_NF4_API AilaNf4Status aila_st_find(const AilaStFile* f, const char* name,
     return AILA_NF4_OK;
 }
 
+}  // extern "C"
+
+namespace {
+
+// A tensor and the data section of the file that holds it.
+struct Found {
+    const StTensor* t = nullptr;
+    const uint8_t* data = nullptr;
+    const StTensor* operator->() const { return t; }
+    const StTensor& operator*() const { return *t; }
+    explicit operator bool() const { return t != nullptr; }
+    bool operator!() const { return t == nullptr; }
+    const uint8_t* bytes() const { return data + t->begin; }
+};
+
 // Same tensor names, dtype rules and size invariants as LoadBnb4BitWeightRef
-// (src/utils/SafeTensors.cpp:370-489).
-AILA_NF4_API AilaNf4Status aila_st_load_bnb4_weight(const AilaStFile* f, const char* name,
-                                                    int device, AilaNf4WeightDesc* out) {
-    if (!f || !name || !out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+// (src/utils/SafeTensors.cpp:370-489). `lookup` finds a tensor by name in one file or in the
+// shards of a directory.
+template <typename Lookup>
+AilaNf4Status load_bnb4_weight(Lookup&& lookup, const char* name, int device, AilaNf4WeightDesc* out) {
     std::memset(out, 0, sizeof(*out));
     const std::string w = name;
-    const StTensor* packed = find_tensor(f, w);
+    const Found packed = lookup(w);
     if (!packed)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Missing bitsandbytes packed weight tensor: " + w);
-    const StTensor* absmax = find_tensor(f, w + ".absmax");
-    const StTensor* qmap = find_tensor(f, w + ".quant_map");
-    const StTensor* state = find_tensor(f, w + ".quant_state.bitsandbytes__nf4");
-    const StTensor* nabs = find_tensor(f, w + ".nested_absmax");
-    const StTensor* nmap = find_tensor(f, w + ".nested_quant_map");
+    const Found absmax = lookup(w + ".absmax");
+    const Found qmap = lookup(w + ".quant_map");
+    const Found state = lookup(w + ".quant_state.bitsandbytes__nf4");
+    const Found nabs = lookup(w + ".nested_absmax");
+    const Found nmap = lookup(w + ".nested_quant_map");
     if (!absmax || !qmap || !state)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT,
                     "Missing required bitsandbytes side tensors for weight: " + w);
@@ -409,7 +426,7 @@ AILA_NF4_API AilaNf4Status aila_st_load_bnb4_weight(const AilaStFile* f, const c
     // nested_blocksize, nested_dtype, nested_offset (any of the three marks the state nested)
     Json qs;
     std::string jerr;
-    if (!parse_json(reinterpret_cast<const char*>(f->data + state->begin), state->end - state->begin, qs, jerr) ||
+    if (!parse_json(reinterpret_cast<const char*>(state.bytes()), state->end - state->begin, qs, jerr) ||
         qs.kind != Json::Object)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "parse bitsandbytes quant_state failed: " + jerr);
     const Json* quant_type = qs.find("quant_type");
@@ -486,15 +503,137 @@ AILA_NF4_API AilaNf4Status aila_st_load_bnb4_weight(const AilaStFile* f, const c
     out->nested = nested ? 1 : 0;
     out->nested_blocksize = (int32_t)nested_blocksize;
     out->nested_offset = nested_offset;
-    out->packed_weight = f->data + packed->begin;
-    out->absmax = f->data + absmax->begin;
-    out->quant_map = reinterpret_cast<const float*>(f->data + qmap->begin);
-    out->nested_absmax = nested ? reinterpret_cast<const float*>(f->data + nabs->begin) : nullptr;
-    out->nested_quant_map = nested ? reinterpret_cast<const float*>(f->data + nmap->begin) : nullptr;
+    out->packed_weight = packed.bytes();
+    out->absmax = absmax.bytes();
+    out->quant_map = reinterpret_cast<const float*>(qmap.bytes());
+    out->nested_absmax = nested ? reinterpret_cast<const float*>(nabs.bytes()) : nullptr;
+    out->nested_quant_map = nested ? reinterpret_cast<const float*>(nmap.bytes()) : nullptr;
     out->nested_absmax_count = nested ? numel_of(*nabs) : 0;
     out->pointers_on_device = 0;
     out->device = device;
     return AILA_NF4_OK;
+}
+
+Found find_in(const AilaStFile* f, const std::string& name) {
+    Found r;
+    r.t = find_tensor(f, name);
+    r.data = f->data;
+    return r;
+}
+
+bool file_exists(const std::string& path) {
+    struct stat st;
+    return ::stat(path.c_str(), &st) == 0 && S_ISREG(st.st_mode);
+}
+
+}  // namespace
+
+// A model directory: model.safetensors, or the shards named by model.safetensors.index.json
+// (LoadModelWeightsFromDir, src/utils/SafeTensors.cpp:491-535; parse_sharded_safetensors_index,
+// :336-366). Shards are opened in sorted name order; a tensor present in several shards is taken
+// from the last one, as the reference's merge does.
+struct AilaStDir {
+    std::vector<AilaStFile*> files;
+};
+
+extern "C" {
+
+AILA_NF4_API AilaNf4Status aila_st_load_bnb4_weight(const AilaStFile* f, const char* name,
+                                                    int device, AilaNf4WeightDesc* out) {
+    if (!f || !name || !out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    return load_bnb4_weight([f](const std::string& n) { return find_in(f, n); }, name, device, out);
+}
+
+AILA_NF4_API void aila_st_dir_close(AilaStDir* d) {
+    if (!d) return;
+    for (AilaStFile* f : d->files) aila_st_close(f);
+    delete d;
+}
+
+AILA_NF4_API AilaNf4Status aila_st_dir_open(const char* model_dir, AilaStDir** out) {
+    if (!model_dir || !out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    const std::string dir = model_dir;
+    std::vector<std::string> shards;
+    if (file_exists(dir + "/model.safetensors")) {
+        shards.push_back("model.safetensors");
+    } else {
+        const std::string index = dir + "/model.safetensors.index.json";
+        if (!file_exists(index))
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT,
+                        "No model.safetensors or model.safetensors.index.json found in: " + dir);
+        std::string text;
+        {
+            FILE* fp = std::fopen(index.c_str(), "rb");
+            if (fp) {
+                char buf[65536];
+                size_t n;
+                while ((n = std::fread(buf, 1, sizeof(buf), fp)) > 0) text.append(buf, n);
+                std::fclose(fp);
+            }
+        }
+        if (text.empty())
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Empty or unreadable safetensors index: " + index);
+        Json root;
+        std::string jerr;
+        if (!parse_json(text.data(), text.size(), root, jerr) || root.kind != Json::Object)
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Invalid safetensors index: " + (jerr.empty() ? "not a JSON object" : jerr));
+        const Json* wm = root.find("weight_map");
+        if (!wm) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Invalid safetensors index: missing weight_map");
+        if (wm->kind != Json::Object)
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Invalid safetensors index: weight_map is not an object");
+        std::set<std::string> unique;
+        for (const auto& kv : wm->obj)
+            if (kv.second.kind == Json::String) unique.insert(kv.second.str);
+        shards.assign(unique.begin(), unique.end());  // (a set iterates in sorted order)
+        if (shards.empty()) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "No shard entries found in: " + index);
+    }
+    AilaStDir* d = new (std::nothrow) AilaStDir();
+    if (!d) return fail(AILA_NF4_ERR_OUT_OF_MEMORY, "host allocation failed");
+    for (const std::string& name : shards) {
+        const std::string path = dir + "/" + name;
+        if (name.find("..") != std::string::npos || name.find('/') != std::string::npos || !file_exists(path)) {
+            aila_st_dir_close(d);
+            return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "Missing safetensors shard: " + path);
+        }
+        AilaStFile* f = nullptr;
+        const AilaNf4Status st = aila_st_open(path.c_str(), &f);
+        if (st != AILA_NF4_OK) {
+            aila_st_dir_close(d);
+            return st;
+        }
+        d->files.push_back(f);
+    }
+    *out = d;
+    return AILA_NF4_OK;
+}
+
+AILA_NF4_API int64_t aila_st_dir_shard_count(const AilaStDir* d) { return d ? (int64_t)d->files.size() : 0; }
+
+AILA_NF4_API const AilaStFile* aila_st_dir_shard(const AilaStDir* d, int64_t index) {
+    if (!d || index < 0 || index >= (int64_t)d->files.size()) return nullptr;
+    return d->files[(size_t)index];
+}
+
+AILA_NF4_API AilaNf4Status aila_st_dir_find(const AilaStDir* d, const char* name, AilaStTensorView* out) {
+    if (!d || !name || !out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    for (size_t i = d->files.size(); i-- > 0;)
+        if (find_tensor(d->files[i], name)) return aila_st_find(d->files[i], name, out);
+    return fail(AILA_NF4_NOT_APPLICABLE, std::string("no tensor named ") + name);
+}
+
+AILA_NF4_API AilaNf4Status aila_st_dir_load_bnb4_weight(const AilaStDir* d, const char* name, int device,
+                                                        AilaNf4WeightDesc* out) {
+    if (!d || !name || !out) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
+    return load_bnb4_weight(
+        [d](const std::string& n) {
+            for (size_t i = d->files.size(); i-- > 0;) {
+                const Found r = find_in(d->files[i], n);
+                if (r) return r;
+            }
+            return Found();
+        },
+        name, device, out);
 }
 
 }  // extern "C"

@@ -445,6 +445,22 @@ AILA_NF4_API AilaNf4Status aila_st_find(const AilaStFile* file, const char* name
                                         AilaStTensorView* out);
 AILA_NF4_API AilaNf4Status aila_st_load_bnb4_weight(const AilaStFile* file, const char* name,
                                                     int device, AilaNf4WeightDesc* out);
+/* A model directory (reference LoadModelWeightsFromDir, src/utils/SafeTensors.cpp:491-535, and
+ * parse_sharded_safetensors_index, :336-366): `model.safetensors` if it exists, otherwise the
+ * shards that `model.safetensors.index.json` names in its weight_map, opened in sorted order.
+ * A tensor that several shards hold is taken from the last of them (the reference's merge
+ * replaces earlier entries). aila_st_dir_find / aila_st_dir_load_bnb4_weight look through all
+ * shards, so the side tensors of a weight may sit in another shard than its packed bytes. The
+ * reference's messages are kept ("No model.safetensors or model.safetensors.index.json found
+ * in: ...", "Invalid safetensors index: missing weight_map", "Missing safetensors shard: ..."). */
+typedef struct AilaStDir AilaStDir;
+AILA_NF4_API AilaNf4Status aila_st_dir_open(const char* model_dir, AilaStDir** out);
+AILA_NF4_API void aila_st_dir_close(AilaStDir* dir);
+AILA_NF4_API int64_t aila_st_dir_shard_count(const AilaStDir* dir);
+AILA_NF4_API const AilaStFile* aila_st_dir_shard(const AilaStDir* dir, int64_t index);
+AILA_NF4_API AilaNf4Status aila_st_dir_find(const AilaStDir* dir, const char* name, AilaStTensorView* out);
+AILA_NF4_API AilaNf4Status aila_st_dir_load_bnb4_weight(const AilaStDir* dir, const char* name, int device,
+                                                        AilaNf4WeightDesc* out);
 
 /*
  * Whole-weight dequantisation into the TRANSPOSED bf16 matrix Wt[in][out], bit-equal to

@@ -146,6 +146,35 @@ inline bool LoadBnb4BitWeightRef(Context& ctx, SafetensorsFile& weights, const s
     return false;
 }
 
+// A model directory: model.safetensors or the shards of model.safetensors.index.json
+// (reference LoadModelWeightsFromDir, src/utils/SafeTensors.cpp:491-535). Throws
+// std::runtime_error with the reference's messages, as that function does.
+struct ModelWeightsDir {
+    AilaStDir* handle = nullptr;
+
+    ModelWeightsDir() = default;
+    explicit ModelWeightsDir(const std::string& model_dir) {
+        if (aila_st_dir_open(model_dir.c_str(), &handle) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+    }
+    ModelWeightsDir(const ModelWeightsDir&) = delete;
+    ModelWeightsDir& operator=(const ModelWeightsDir&) = delete;
+    ~ModelWeightsDir() { aila_st_dir_close(handle); }
+
+    bool has(const std::string& name) const {
+        AilaStTensorView v;
+        return aila_st_dir_find(handle, name.c_str(), &v) == AILA_NF4_OK;
+    }
+};
+
+inline bool LoadBnb4BitWeightRef(Context& ctx, ModelWeightsDir& weights, const std::string& name,
+                                 AilaNf4WeightDesc& out, std::string* error_message = nullptr) {
+    if (aila_st_dir_load_bnb4_weight(weights.handle, name.c_str(), ctx.device, &out) == AILA_NF4_OK)
+        return true;
+    if (error_message) *error_message = aila_nf4_last_error();
+    return false;
+}
+
 class Bnb4BitLinear {
 public:
     Bnb4BitLinear() = default;

@@ -41,6 +41,13 @@ int main() {
             threw = true;
         }
         if (!threw) return 7;
+        threw = false;
+        try {
+            aila::nf4::ModelWeightsDir nodir("/nonexistent/model_dir");
+        } catch (const std::runtime_error& e) {
+            threw = std::strstr(e.what(), "No model.safetensors or model.safetensors.index.json found in") != nullptr;
+        }
+        if (!threw) return 11;
         aila::nf4::SafetensorsFile empty;
         AilaNf4WeightDesc view;
         if (aila::nf4::LoadBnb4BitWeightRef(ctx, empty, "w", view, &err) || err.empty()) return 8;

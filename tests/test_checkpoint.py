@@ -147,3 +147,72 @@ def test_header_escapes_and_empty_tensors(tmp_path):
         assert f.names() == list(tensors)
         assert f.get('odd "name"\\with\tescapes \u00e9').shape == (0, 4)
         assert np.array_equal(f.get("b"), tensors["b"])
+
+
+def _index(tmp_path, weight_map, **extra):
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map, **extra}))
+
+
+def test_model_directory_single_file_and_shards(tmp_path):
+    """LoadModelWeightsFromDir (SafeTensors.cpp:491-535): model.safetensors wins; otherwise the
+    shards of the index, sorted; a weight's side tensors may sit in another shard than its bytes; a
+    tensor held by two shards comes from the last one."""
+    wa, wb = make_weight(11, 32, 128), make_weight(12, 48, 64, nested=False)
+    ta, tb = checkpoint.bnb4_checkpoint_tensors("a.weight", wa), checkpoint.bnb4_checkpoint_tensors("b.weight", wb)
+    single = tmp_path / "single"
+    single.mkdir()
+    checkpoint.write_safetensors(str(single / "model.safetensors"), {**ta, **tb})
+    with checkpoint.ModelDir(str(single)) as d:
+        assert d.shard_count() == 1 and d.has("a.weight") and not d.has("c.weight")
+        assert d.load_bnb4_weight_ref("b.weight").out_features == 48
+    sharded = tmp_path / "sharded"
+    sharded.mkdir()
+    # shard 1: a's packed bytes and b; shard 2: a's side tensors and a second copy of "dup"
+    first = {"a.weight": ta["a.weight"], **tb, "dup": np.full(4, 1.0, np.float32)}
+    second = {k: v for k, v in ta.items() if k != "a.weight"}
+    second["dup"] = np.full(4, 2.0, np.float32)
+    checkpoint.write_safetensors(str(sharded / "model-00001-of-00002.safetensors"), first)
+    checkpoint.write_safetensors(str(sharded / "model-00002-of-00002.safetensors"), second)
+    wm = {k: "model-00001-of-00002.safetensors" for k in first}
+    wm.update({k: "model-00002-of-00002.safetensors" for k in second})
+    _index(sharded, wm)
+    with checkpoint.ModelDir(str(sharded)) as d:
+        assert d.shard_count() == 2
+        assert set(d.names()) == set(first) | set(second)
+        desc = d.load_bnb4_weight_ref("a.weight")
+        assert (desc.out_features, desc.in_features, desc.nested) == (32, 128, 1)
+        assert np.array_equal(_array_at(desc.packed_weight, np.uint8, 32 * 128 // 2), np.asarray(wa.packed))
+        assert np.array_equal(_array_at(desc.absmax, np.uint8, 32 * 2), np.asarray(wa.absmax_codes))
+        assert np.array_equal(_array_at(desc.nested_absmax, np.float32, desc.nested_absmax_count),
+                              np.asarray(wa.nested_absmax))
+        assert d.load_bnb4_weight_ref("b.weight").nested == 0
+        assert np.array_equal(d.get("dup"), np.full(4, 2.0, np.float32))
+        with pytest.raises(_lib.Nf4Error, match="Missing bitsandbytes packed weight tensor"):
+            d.load_bnb4_weight_ref("c.weight")
+
+
+def test_model_directory_errors(tmp_path):
+    def expect(text):
+        with pytest.raises(_lib.Nf4Error) as e:
+            checkpoint.ModelDir(str(tmp_path))
+        assert text in str(e.value)
+
+    expect("No model.safetensors or model.safetensors.index.json found in")
+    (tmp_path / "model.safetensors.index.json").write_text("")
+    expect("Empty or unreadable safetensors index")
+    (tmp_path / "model.safetensors.index.json").write_text("[1, 2]")
+    expect("Invalid safetensors index")
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}}))
+    expect("missing weight_map")
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": [1]}))
+    expect("weight_map is not an object")
+    _index(tmp_path, {})
+    expect("No shard entries found in")
+    _index(tmp_path, {"t": "model-00001-of-00001.safetensors"})
+    expect("Missing safetensors shard")
+    _index(tmp_path, {"t": "../elsewhere.safetensors"})
+    expect("Missing safetensors shard")
+    checkpoint.write_safetensors(str(tmp_path / "model-00001-of-00001.safetensors"), {"t": np.zeros(3, np.float32)})
+    _index(tmp_path, {"t": "model-00001-of-00001.safetensors"})
+    with checkpoint.ModelDir(str(tmp_path)) as d:
+        assert d.names() == ["t"]
