@@ -112,6 +112,19 @@ class CudaBackend:
         dist.barrier(group=group)
         return buf
 
+    def make_dense(self, weight: torch.Tensor):
+        from .linear import Linear
+        lin = Linear()
+        lin.init(weight.to(torch.bfloat16), weight.shape[1], weight.shape[0], self.device)
+        return lin
+
+    def dense_forward(self, handle, x: torch.Tensor, out: torch.Tensor, seq_len: int) -> None:
+        handle.forward(self.scratch, x, out, seq_len)
+
+    def argmax(self, logits: torch.Tensor, n: int, result: torch.Tensor) -> None:
+        from .linear import argmax
+        argmax(logits, n, result)
+
     def make_chain(self, ops: list[dict], peers=None):
         from .linear import DecodeChain
         return DecodeChain(self.scratch, ops, peers)
@@ -184,6 +197,45 @@ def reduce_partials(part: torch.Tensor, group, fp32: bool) -> torch.Tensor:
         return acc.to(torch.bfloat16)
     dist.all_reduce(part, group=group)
     return part
+
+
+class VocabParallelHead:
+    """The bf16 output head with its vocabulary rows split over the ranks, and the greedy token
+    choice on top (reference: lm_head_.forward + ops::argmax, src/models/Qwen3Bnb4Backend.cpp:432-439,
+    src/ops/SamplingOps.cpp:321-365; sharding is net-new). Each rank runs the dense GEMV on its row
+    slice and the argmax over its slice of the logits; the ranks exchange one (value, index) pair
+    each instead of the logits, and every rank picks the same winner: the largest value, the
+    smallest index among equal values."""
+
+    def __init__(self, weight: torch.Tensor, backend, group=None):
+        self.rank, self.world = _group_info(group)
+        self.group, self.backend = group, backend
+        self.vocab, self.hidden = weight.shape
+        if self.vocab % self.world:
+            raise ValueError(f"vocabulary {self.vocab} is not divisible by {self.world} shards")
+        if self.vocab >= 1 << 24:
+            raise ValueError("vocabulary too large for the packed (value, index) exchange")
+        self.local = self.vocab // self.world
+        self.handle = backend.make_dense(weight[self.rank * self.local:(self.rank + 1) * self.local].contiguous())
+        self.logits = backend.empty(1, self.local)
+        self._idx = backend.empty(1, dtype=torch.int32)
+
+    def greedy(self, x: torch.Tensor) -> torch.Tensor:
+        """x: [1, hidden] bf16 (replicated). Returns the chosen token as an int64 tensor of one
+        element, the same on every rank."""
+        self.backend.dense_forward(self.handle, x, self.logits, 1)
+        self.backend.argmax(self.logits, self.local, self._idx)
+        idx = self._idx.to(torch.int64)
+        val = self.logits.reshape(-1)[idx].float()
+        if self.world == 1:
+            return idx
+        # (a token index below 2^24 is exact in fp32, so the pair travels as one tensor)
+        pair = torch.stack([val.reshape(()), (idx.reshape(()) + self.rank * self.local).float()])
+        got = [torch.empty_like(pair) for _ in range(self.world)]
+        dist.all_gather(got, pair, group=self.group)
+        allp = torch.stack(got)                      # [world, 2], ranks own ascending index ranges
+        best = torch.argmax(allp[:, 0])              # first maximum = smallest rank = smallest index
+        return allp[best, 1].to(torch.int64).reshape(1)
 
 
 class ShardedNf4Mlp:

@@ -57,6 +57,18 @@ class OracleBackend:
         return True
 
 
+    def make_dense(self, weight):
+        return weight.contiguous()
+
+    def dense_forward(self, h, x, out, seq_len):
+        y = self.O.gemm_bf16w(h.view(torch.uint16).numpy(), x.contiguous().view(torch.uint16).numpy(), seq_len,
+                              h.shape[0], h.shape[1])
+        out.copy_(torch.from_numpy(y.reshape(seq_len, h.shape[0])).view(torch.bfloat16))
+
+    def argmax(self, logits, n, result):
+        result.copy_(torch.argmax(logits.reshape(-1)[:n].float()).to(torch.int32).reshape(1))
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -202,3 +214,50 @@ def test_mis_sized_shards_are_refused_on_the_host():
     be = OracleBackend()
     with pytest.raises(ValueError):
         be.make_shard(w, sharded.COLS, 0, 2)
+
+
+def _head_worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        g = torch.Generator().manual_seed(77)
+        w = (torch.randn(512, 128, generator=g) * 0.05).to(torch.bfloat16)
+        w[300] = w[40]                      # two equal rows in different shards: the smaller index must win
+        x = synth.gaussian_activation(78, 1, 128)
+        head = sharded.VocabParallelHead(w, OracleBackend())
+        toks = [int(head.greedy(x)[0])]
+        x2 = (w[40].float() * 8).to(torch.bfloat16).reshape(1, -1)   # aligned with rows 40 and 300
+        toks.append(int(head.greedy(x2)[0]))
+        if rank == 0:
+            q.put(("ok", toks))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # pragma: no cover
+        if rank == 0:
+            q.put(("err", repr(e)))
+        raise
+
+
+def test_vocab_parallel_head_two_gloo_ranks(oracle):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_head_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+    assert res[0] == "ok", res
+    g = torch.Generator().manual_seed(77)
+    w = (torch.randn(512, 128, generator=g) * 0.05).to(torch.bfloat16)
+    w[300] = w[40]
+    x = synth.gaussian_activation(78, 1, 128)
+    x2 = (w[40].float() * 8).to(torch.bfloat16).reshape(1, -1)
+    for xi, tok in zip((x, x2), res[1]):
+        logits = bits_to_f32(oracle.gemm_bf16w(w.view(torch.uint16).numpy(), xi.view(torch.uint16).numpy(), 1, 512, 128))
+        assert tok == int(np.argmax(logits))     # numpy: first maximum = smallest index
+    assert res[1][1] == 40
+    with pytest.raises(ValueError):
+        sharded.check_shardable(make_weight(1, 96, 64), sharded.ROWS, 5)

@@ -96,6 +96,17 @@ def _worker(rank, world, port, q):
         tall_err = float((yt[0].float() - yt_ref.float()).abs().max() / yt_ref.float().abs().max())
         same = same and all(torch.equal(yt[0], t) for t in yt[1:]) and tall_err < 1e-2
         peers_tall.close()
+        # the output head with its vocabulary split over the ranks: the exchanged (value, index)
+        # pairs must pick the token that the whole head picks on one GPU
+        gen = torch.Generator().manual_seed(31)
+        wh = (torch.randn(4096, H, generator=gen) * 0.05).to(torch.bfloat16)
+        xh = synth.gaussian_activation(32, 1, H).cuda()
+        head = sharded.VocabParallelHead(wh, be)
+        tok = int(head.greedy(xh)[0])
+        whole = be.make_dense(wh)
+        full_logits = be.empty(1, 4096)
+        be.dense_forward(whole, xh, full_logits, 1)
+        same = same and tok == int(torch.argmax(full_logits.float().reshape(-1)))
         outs["fused"] = ys[0].cpu().view(torch.uint16).numpy()
         outs["fused_consistent"] = bool(same)
         peers.close()
