@@ -18,6 +18,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "aila_nf4.h"
 
@@ -269,6 +270,76 @@ private:
     }
     AilaNf4Linear* handle_ = nullptr;
     AilaNf4Linear* fresh_ = nullptr;
+};
+
+// A run of seq_len == 1 linears as ONE launch (aila_nf4_chain_*): what the decode step issues
+// back to back (reference src/models/Qwen3Bnb4Backend.cpp:339-418), listed once after load() and
+// run per token. add() returns *this so the list reads like the call sites it replaces:
+//
+//   chain.add(layer.o_proj, attn_out.data(), nullptr)                          // x given, y linked on
+//        .add_gate_up(layer.gate_up_proj, ff_dim, nullptr, nullptr, &post_attn_norm)
+//        .add(layer.down_proj, nullptr, mlp_out.data());
+//   chain.build(ctx, scratch_);   ...   chain.run(ctx);
+class DecodeChain {
+public:
+    DecodeChain() = default;
+    DecodeChain(const DecodeChain&) = delete;
+    DecodeChain& operator=(const DecodeChain&) = delete;
+    ~DecodeChain() { aila_nf4_chain_destroy(handle_); }
+
+    // x == nullptr: the previous operation's output; y == nullptr: only the next operation reads it.
+    DecodeChain& add(const Bnb4BitLinear& linear, const void* x, void* y, const void* residual = nullptr,
+                     const AilaNf4RmsNorm* norm = nullptr) {
+        return push(linear, 0, x, y, residual, norm);
+    }
+    DecodeChain& add_gate_up(const Bnb4BitLinear& fused_gate_up, int ff_dim, const void* x, void* y,
+                             const AilaNf4RmsNorm* norm = nullptr) {
+        return push(fused_gate_up, ff_dim, x, y, nullptr, norm);
+    }
+
+    bool build(Context& ctx, Bnb4BitLinearScratch& scratch, std::string* error_message = nullptr) {
+        scratch.open(ctx);
+        for (size_t i = 0; i < ops_.size(); ++i)
+            if (has_norm_[i]) ops_[i].norm = &norms_[i];
+        AilaNf4Chain* fresh = nullptr;
+        if (aila_nf4_chain_create(scratch.handle, ops_.data(), (int)ops_.size(), &fresh) != AILA_NF4_OK) {
+            if (error_message) *error_message = aila_nf4_last_error();
+            return false;
+        }
+        aila_nf4_chain_destroy(handle_);
+        handle_ = fresh;
+        return true;
+    }
+
+    void run(Context& ctx) {
+        if (aila_nf4_chain_run(handle_, ctx.stream) != AILA_NF4_OK) throw std::runtime_error(aila_nf4_last_error());
+    }
+    // host x in, host y out, one synchronisation
+    void run_host(Context& ctx, const void* x_host_bf16, void* y_host_bf16) {
+        if (aila_nf4_chain_run_host(handle_, x_host_bf16, y_host_bf16, ctx.stream) != AILA_NF4_OK)
+            throw std::runtime_error(aila_nf4_last_error());
+    }
+    int length() const { return aila_nf4_chain_length(handle_); }
+
+private:
+    DecodeChain& push(const Bnb4BitLinear& l, int ff, const void* x, void* y, const void* res,
+                      const AilaNf4RmsNorm* norm) {
+        AilaNf4ChainOp op{};
+        op.linear = l.handle();
+        op.ff_dim = ff;
+        op.x_bf16 = x;
+        op.y_bf16 = y;
+        op.residual_bf16 = res;
+        op.norm = nullptr;
+        ops_.push_back(op);
+        norms_.push_back(norm ? *norm : AilaNf4RmsNorm{});
+        has_norm_.push_back(norm != nullptr);
+        return *this;
+    }
+    std::vector<AilaNf4ChainOp> ops_;
+    std::vector<AilaNf4RmsNorm> norms_;   // copies: the caller's structs need not outlive add()
+    std::vector<bool> has_norm_;
+    AilaNf4Chain* handle_ = nullptr;
 };
 
 }  // namespace nf4

@@ -98,6 +98,15 @@ int main() {
         }
         if (!threw || ctx.decode_scratch == nullptr) return 10;
     }
+    {
+        // a chain of two operations that do not fit together (fused output 2N feeds a linear of K
+        // inputs): build() must report it through the bool + message, like init
+        aila::nf4::DecodeChain chain;
+        Bnb4BitLinearScratch s;
+        std::string cerr2;
+        chain.add(fused, reinterpret_cast<const void*>(0x1000), nullptr).add(q, nullptr, reinterpret_cast<void*>(0x2000));
+        if (chain.build(ctx, s, &cerr2) || cerr2.empty() || chain.length() != 0) return 12;
+    }
     std::printf("adapter ok on a GPU: fused %d x %d\n", fused.out_features(), fused.in_features());
     return 0;
 }
