@@ -6,10 +6,19 @@
  * operator src/ops/Bnb4BitLinear.cpp (Blackwood416/Aila v0.1.2). Every function cites the
  * reference lines it follows.
  *
- * PARITY UNPINNED: the reference holds no golden vectors, known-answer tests or numeric
- * fixtures for this path, and its SYCL/oneDNN sources cannot be compiled in a CUDA-only
- * image. This restatement is therefore pinned only by reading, by a second independent
- * numpy restatement (oracle/nf4_numpy.py) and by hand-computed tiny cases in tests/.
+ * PARITY PINNED AGAINST THE REFERENCE'S SOURCE: the reference holds no golden vectors,
+ * known-answer tests or numeric fixtures for this path, and no SYCL compiler or oneDNN exists
+ * in a CUDA-only image; instead src/ops/Bnb4BitLinear.cpp itself is compiled unmodified with
+ * g++ against a serial host stand-in for the SYCL / oneDNN headers (oracle/ref_shim/,
+ * oracle/ref_harness.cpp -> oracle/_ref/libaila_ref.so) and tests/test_reference_pin.py holds
+ * this restatement bit-exact against it: absmax expansion, dequantisation, both GEMV branches,
+ * fused rows, gate+up+SiLU, the seq_len > 1 route. Two things stay the stand-in's choice, not
+ * the reference's: the order of sub-group / work-group reductions (unspecified in SYCL; a
+ * balanced tree on both sides) and the bf16 matmul after dequantisation (oneDNN in the
+ * reference; k-ascending fp32 accumulation on both sides). The quantiser and the code books
+ * of third-party bitsandbytes are absent, so the ENCODE side stays unpinned; they are runtime
+ * inputs here as in the reference. Also pinned by a second independent numpy restatement
+ * (oracle/nf4_numpy.py) and hand-computed tiny cases in tests/.
  *
  * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (see oracle/Makefile).
  * -ffp-contract=off matters: the reference source writes the double-quant expansion as a

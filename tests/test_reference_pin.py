@@ -1,0 +1,155 @@
+"""The CPU oracle against the reference's own operator source, compiled for the host
+(oracle/ref_harness.cpp around src/ops/Bnb4BitLinear.cpp on the stand-in runtime of oracle/ref_shim/).
+
+Bit-exact everywhere: both sides reduce partial sums in the same balanced-tree order, and the stand-in
+matmul of the seq_len > 1 route accumulates k in ascending order in fp32 like the oracle's. Skipped
+where the library was not built (the reference's sources were absent at build time). No GPU.
+"""
+import numpy as np
+import pytest
+import torch
+
+from aila_b200 import synth
+from oracle import ref_cpu as R
+from tests.helpers import make_weight, oracle_absmax
+
+pytestmark = pytest.mark.skipif(not R.available(), reason="oracle/_ref/libaila_ref.so was not built")
+
+
+def _x(seed, M, K):
+    return synth.gaussian_activation(seed, M, K).view(torch.uint16).numpy()
+
+
+# K/2 < 256 takes the small-K branch of packed_nf4_gemv_bf16, K/2 >= 256 the sub-group-of-16 branch;
+# 448 and 2560 are not multiples of 512 (ragged last chunk); 33 rows leave a ragged work-group
+SHAPES = [(16, 64, True), (48, 448, True), (33, 512, False), (33, 512, True), (128, 2560, True), (40, 4096, True),
+          (8, 8192, False), (24, 128, False), (1, 1024, True)]
+
+
+@pytest.mark.parametrize("N,K,nested", SHAPES)
+def test_init_and_dequantize(oracle, N, K, nested):
+    w = make_weight(11 + N + K, N, K, 64, nested)
+    am = oracle_absmax(oracle, w)
+    assert np.array_equal(R.expand_absmax(w), am)
+    assert np.array_equal(R.dequantize_kn(w), oracle.dequantize_kn(w.packed, w.quant_map, am, N, K, 64))
+
+
+@pytest.mark.parametrize("N,K,nested", SHAPES)
+def test_decode_gemv(oracle, N, K, nested):
+    w = make_weight(21 + N + K, N, K, 64, nested)
+    am = oracle_absmax(oracle, w)
+    x = _x(31 + K, 1, K)
+    assert np.array_equal(R.forward(w, x, 1).reshape(-1), oracle.gemv(w.packed, w.quant_map, am, x, N, K, 64))
+    # add_residual: the small-K branch adds it before the rounding (:323); the sub-group branch
+    # stores bf16(sum) and never reads it (:404-407). The oracle (and the library) honour it in both,
+    # which is the documented difference; here the reference's behaviour itself is pinned.
+    res = _x(41 + N, 1, N)
+    with_res = R.forward(w, x, 1, residual=res).reshape(-1)
+    if K // 2 < 256:
+        assert np.array_equal(with_res, oracle.gemv(w.packed, w.quant_map, am, x, N, K, 64, residual=res))
+    else:
+        assert np.array_equal(with_res, oracle.gemv(w.packed, w.quant_map, am, x, N, K, 64))
+
+
+@pytest.mark.parametrize("blocksize", [128, 256])
+def test_other_blocksizes(oracle, blocksize):
+    N, K = 32, 1024
+    w = make_weight(77 + blocksize, N, K, blocksize, True)
+    am = oracle_absmax(oracle, w)
+    assert np.array_equal(R.expand_absmax(w), am)
+    assert np.array_equal(R.dequantize_kn(w), oracle.dequantize_kn(w.packed, w.quant_map, am, N, K, blocksize))
+    x = _x(5, 1, K)
+    assert np.array_equal(R.forward(w, x, 1).reshape(-1), oracle.gemv(w.packed, w.quant_map, am, x, N, K, blocksize))
+
+
+@pytest.mark.parametrize("rows,K", [((64, 32, 32), 1024), ((48, 16), 448), ((32, 32, 16, 16), 2560)])
+def test_fused_rows(oracle, rows, K):
+    """init_fused_rows: absmax of the parts expanded separately and concatenated (each part's flat
+    block index restarts at 0), then one GEMV over the concatenation."""
+    ws = [make_weight(300 + i + n + K, n, K) for i, n in enumerate(rows)]
+    packed = np.concatenate([np.asarray(w.packed).reshape(-1) for w in ws])
+    am = np.concatenate([oracle_absmax(oracle, w) for w in ws])
+    x = _x(7 + K, 1, K)
+    want = oracle.gemv(packed, ws[0].quant_map, am, x, sum(rows), K, 64)
+    assert np.array_equal(R.forward(ws, x, 1).reshape(-1), want)
+
+
+@pytest.mark.parametrize("ff,K", [(64, 1024), (48, 512), (33, 2560), (16, 5120), (32, 256), (17, 64)])
+def test_gate_up_swiglu(oracle, ff, K):
+    gate, up = make_weight(500 + ff, ff, K), make_weight(501 + ff, ff, K)
+    packed = np.concatenate([np.asarray(gate.packed).reshape(-1), np.asarray(up.packed).reshape(-1)])
+    am = np.concatenate([oracle_absmax(oracle, gate), oracle_absmax(oracle, up)])
+    x = _x(9 + ff, 1, K)
+    got = R.gate_up_swiglu(gate, up, x, ff)
+    assert got is not None
+    assert np.array_equal(got, oracle.gemv_gate_up_swiglu(packed, gate.quant_map, am, x, ff, K, 64))
+
+
+def test_gate_up_swiglu_declines_other_ff():
+    """out_features != 2 * ff_dim is the one shape condition under which the reference returns false
+    (:772); the caller then runs forward and a separate activation."""
+    gate, up = make_weight(601, 32, 256), make_weight(602, 32, 256)
+    assert R.gate_up_swiglu(gate, up, _x(3, 1, 256), 16) is None
+
+
+@pytest.mark.parametrize("M,N,K", [(2, 48, 448), (5, 33, 512), (16, 64, 1024)])
+def test_prefill_route(oracle, M, N, K):
+    """seq_len > 1: bf16-rounded dequantised weights, then a bf16 matmul with fp32 accumulation."""
+    w = make_weight(700 + M + N, N, K)
+    am = oracle_absmax(oracle, w)
+    x = _x(13 + M, M, K)
+    assert np.array_equal(R.forward(w, x, M), oracle.forward(w.packed, w.quant_map, am, x, M, N, K, 64))
+
+
+def _staged_prefill_128(w, am, x, M, N, K):
+    """The arithmetic of packed_nf4_gemm_bf16 (:18-136) as written: per 128-wide k tile the NF4 bytes of
+    128 rows are staged row-major ([n][k/2], :78-87) and read back as [k/2][n] (:104-110); one absmax
+    per row and tile; fp32 multiply then add, k ascending; bf16 store."""
+    from tests.helpers import bits_to_f32
+    BN = BK = 128
+    packed = np.asarray(w.packed, np.uint8).reshape(N, K // 2)
+    xf = bits_to_f32(x).reshape(M, K)
+    amr = am.reshape(N, K // 128)
+    qmap = np.asarray(w.quant_map, np.float32)
+    out = np.zeros((M, N), np.float32)
+    for n0 in range(0, N, BN):
+        rows = min(BN, N - n0)
+        acc = np.zeros((M, BN), np.float32)
+        for kb in range(0, K, BK):
+            tile = np.full((BN, BK // 2), 0x77, np.uint8)
+            tile[:rows] = packed[n0:n0 + rows, kb // 2:kb // 2 + BK // 2]
+            flat = tile.reshape(-1)
+            scale = np.zeros(BN, np.float32)
+            scale[:rows] = amr[n0:n0 + rows, kb // 128]
+            for k in range(BK):
+                b = flat[(k // 2) * BN:(k // 2) * BN + BN]
+                nib = (b >> 4) if k % 2 == 0 else (b & 0x0F)
+                wk = qmap[nib] * scale
+                acc = acc + xf[:, kb + k:kb + k + 1] * wk[None, :]
+        out[:, n0:n0 + rows] = acc[:, :rows]
+    return out
+
+
+@pytest.mark.parametrize("M,N,K", [(2, 48, 512), (5, 160, 256)])
+def test_blocksize128_prefill_route_of_the_reference(oracle, M, N, K):
+    """With blocksize 128 and seq_len > 1 the reference takes its fused prefill kernel (:820-837), whose
+    staging and read-back of the NF4 tile disagree, so its result is not x W^T. The library and the
+    oracle compute x W^T for every blocksize. Pinned here: the reference's output equals the kernel's
+    arithmetic as written, and differs from the oracle's."""
+    w = make_weight(900 + M + N, N, K, 128, True)
+    am = oracle_absmax(oracle, w)
+    x = _x(17 + M, M, K)
+    got = R.forward(w, x, M)
+    assert np.array_equal(got, oracle.f32_to_bf16(_staged_prefill_128(w, am, x, M, N, K)))
+    assert not np.array_equal(got, oracle.forward(w.packed, w.quant_map, am, x, M, N, K, 128))
+
+
+def test_reference_error_behaviour():
+    """What the adapter mirrors: init reports a bad logical shape through its bool + message, forward
+    throws on seq_len <= 0."""
+    w = make_weight(800, 16, 128)
+    bad = synth.Nf4Tensors(**{**w.__dict__, "out_features": 0})
+    with pytest.raises(R.RefError, match="invalid logical shape"):
+        R.forward(bad, _x(1, 1, 128), 1)
+    with pytest.raises(R.RefError, match="seq_len must be positive"):
+        R.forward(w, np.zeros((0, 128), np.uint16), 0)
