@@ -949,6 +949,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
 #pragma unroll
                 for (int w = 0; w < kConsumerWarps; ++w) total += lds_f32(a_ctl + 64u + 4u * w);
                 const float inv_rms = rsqrtf(total / (float)o.K + o.norm_eps);
+                const bool renorm_from_stored = ag != nullptr && o.K != 1024;
 #pragma unroll
                 for (int b = 0; b < kXBatch; ++b) {
                     const int q4 = ctid + b * kConsumerThreads;
@@ -956,18 +957,22 @@ __global__ void __launch_bounds__(kChainThreads, 1) gemv_chain_kernel(const Chai
                         const uint2 wq = __ldg(wg + q4);
                         const float w0f = __uint_as_float(wq.x << 16), w1f = __uint_as_float(wq.x & 0xffff0000u);
                         const float w2f = __uint_as_float(wq.y << 16), w3f = __uint_as_float(wq.y & 0xffff0000u);
+                        uint2 hq;  // the updated residual stream bf16(v)
+                        hq.x = (uint32_t)f32_to_bf16_bits(vv[b][0]) | ((uint32_t)f32_to_bf16_bits(vv[b][1]) << 16);
+                        hq.y = (uint32_t)f32_to_bf16_bits(vv[b][2]) | ((uint32_t)f32_to_bf16_bits(vv[b][3]) << 16);
+                        // the reference's single-row add+RMSNorm normalises what it stored (bf16) unless
+                        // H == 1024 (src/ops/NormOps.cpp:189-240 against :152-187)
+                        const float n0 = renorm_from_stored ? __uint_as_float(hq.x << 16) : vv[b][0];
+                        const float n1 = renorm_from_stored ? __uint_as_float(hq.x & 0xffff0000u) : vv[b][1];
+                        const float n2 = renorm_from_stored ? __uint_as_float(hq.y << 16) : vv[b][2];
+                        const float n3 = renorm_from_stored ? __uint_as_float(hq.y & 0xffff0000u) : vv[b][3];
                         uint2 ov;
-                        ov.x = (uint32_t)f32_to_bf16_bits(vv[b][0] * inv_rms * w0f) |
-                               ((uint32_t)f32_to_bf16_bits(vv[b][1] * inv_rms * w1f) << 16);
-                        ov.y = (uint32_t)f32_to_bf16_bits(vv[b][2] * inv_rms * w2f) |
-                               ((uint32_t)f32_to_bf16_bits(vv[b][3] * inv_rms * w3f) << 16);
+                        ov.x = (uint32_t)f32_to_bf16_bits(n0 * inv_rms * w0f) |
+                               ((uint32_t)f32_to_bf16_bits(n1 * inv_rms * w1f) << 16);
+                        ov.y = (uint32_t)f32_to_bf16_bits(n2 * inv_rms * w2f) |
+                               ((uint32_t)f32_to_bf16_bits(n3 * inv_rms * w3f) << 16);
                         sts_v2(xa + chunk_off(q4), ov);
-                        if (c == 0 && o.norm_hidden_out) {
-                            uint2 hq;
-                            hq.x = (uint32_t)f32_to_bf16_bits(vv[b][0]) | ((uint32_t)f32_to_bf16_bits(vv[b][1]) << 16);
-                            hq.y = (uint32_t)f32_to_bf16_bits(vv[b][2]) | ((uint32_t)f32_to_bf16_bits(vv[b][3]) << 16);
-                            reinterpret_cast<uint2*>(o.norm_hidden_out)[q4] = hq;
-                        }
+                        if (c == 0 && o.norm_hidden_out) reinterpret_cast<uint2*>(o.norm_hidden_out)[q4] = hq;
                     }
                 }
             }

@@ -166,13 +166,15 @@ argmax_bf16_kernel(const uint16_t* __restrict__ logits, long long n, int* __rest
 }
 
 // Residual add + RMSNorm, one block per row (ops::fused_add_rms_norm / rms_norm,
-// src/ops/NormOps.cpp:141-260): v = x + add in fp32, hidden_out = bf16(v),
-// normed = bf16(v * rsqrt(mean(v^2) + eps) * w). hidden_out may alias x (each element is read and
+// src/ops/NormOps.cpp:141-275): v = x + add in fp32, hidden_out = bf16(v),
+// normed = bf16(vn * rsqrt(mean(v^2) + eps) * w). vn = v, except on the reference's single-row route
+// for H != 1024 (:189-240), whose second pass re-reads the sum it has just stored as bf16:
+// there (`renorm_from_stored`) vn = float(bf16(v)). hidden_out may alias x (each element is read and
 // written by the same thread).
 __global__ void __launch_bounds__(256)
 add_rms_norm_kernel(const uint16_t* x, const uint16_t* __restrict__ add,
                     const uint16_t* __restrict__ w, float eps, int H, uint16_t* hidden_out,
-                    uint16_t* __restrict__ normed) {
+                    uint16_t* __restrict__ normed, int renorm_from_stored) {
     __shared__ float warp_sum[8];
     const size_t row = (size_t)blockIdx.x * H;
     float ss = 0.0f;
@@ -190,8 +192,10 @@ add_rms_norm_kernel(const uint16_t* x, const uint16_t* __restrict__ add,
     const float inv_rms = rsqrtf(total / (float)H + eps);
     for (int k = threadIdx.x; k < H; k += blockDim.x) {
         const float v = bf16_bits_to_f32(__ldcg(x + row + k)) + (add ? bf16_bits_to_f32(__ldcg(add + row + k)) : 0.0f);
-        if (hidden_out) hidden_out[row + k] = f32_to_bf16_bits(v);
-        normed[row + k] = f32_to_bf16_bits(v * inv_rms * bf16_bits_to_f32(w[k]));
+        const uint16_t stored = f32_to_bf16_bits(v);
+        if (hidden_out) hidden_out[row + k] = stored;
+        const float vn = renorm_from_stored ? bf16_bits_to_f32(stored) : v;
+        normed[row + k] = f32_to_bf16_bits(vn * inv_rms * bf16_bits_to_f32(w[k]));
     }
 }
 
@@ -327,7 +331,8 @@ AILA_NF4_API AilaNf4Status aila_add_rms_norm(const void* x_bf16, const void* add
     nf4::add_rms_norm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(x_bf16), static_cast<const uint16_t*>(add_bf16),
         static_cast<const uint16_t*>(weight_bf16), eps, hidden_size,
-        static_cast<uint16_t*>(hidden_out_bf16), static_cast<uint16_t*>(normed_out_bf16));
+        static_cast<uint16_t*>(hidden_out_bf16), static_cast<uint16_t*>(normed_out_bf16),
+        (add_bf16 != nullptr && rows == 1 && hidden_size != 1024) ? 1 : 0);
     NF4_CUDA(cudaGetLastError());
     return AILA_NF4_OK;
 }

@@ -877,20 +877,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
 #pragma unroll
         for (int w = 0; w < W; ++w) total += lds_f32(a_red + 4u * w);
         const float inv_rms = rsqrtf(total / (float)p.K + p.norm_eps);
+        const bool renorm_from_stored = p.norm_add != nullptr && p.K != 1024;
         auto emit = [&](int q4, const float (&vv)[4]) {
             const uint2 wq = __ldg(wg + q4);
             const float w0 = __uint_as_float(wq.x << 16), w1 = __uint_as_float(wq.x & 0xffff0000u);
             const float w2 = __uint_as_float(wq.y << 16), w3 = __uint_as_float(wq.y & 0xffff0000u);
+            uint2 hq;  // the updated residual stream bf16(v)
+            hq.x = (uint32_t)f32_to_bf16_bits(vv[0]) | ((uint32_t)f32_to_bf16_bits(vv[1]) << 16);
+            hq.y = (uint32_t)f32_to_bf16_bits(vv[2]) | ((uint32_t)f32_to_bf16_bits(vv[3]) << 16);
+            // the reference's single-row add+RMSNorm normalises what it stored (bf16) unless H == 1024
+            // (src/ops/NormOps.cpp:189-240 against :152-187); without an added tensor v is bf16 already
+            const float n0 = renorm_from_stored ? __uint_as_float(hq.x << 16) : vv[0];
+            const float n1 = renorm_from_stored ? __uint_as_float(hq.x & 0xffff0000u) : vv[1];
+            const float n2 = renorm_from_stored ? __uint_as_float(hq.y << 16) : vv[2];
+            const float n3 = renorm_from_stored ? __uint_as_float(hq.y & 0xffff0000u) : vv[3];
             uint2 o;
-            o.x = (uint32_t)f32_to_bf16_bits(vv[0] * inv_rms * w0) | ((uint32_t)f32_to_bf16_bits(vv[1] * inv_rms * w1) << 16);
-            o.y = (uint32_t)f32_to_bf16_bits(vv[2] * inv_rms * w2) | ((uint32_t)f32_to_bf16_bits(vv[3] * inv_rms * w3) << 16);
+            o.x = (uint32_t)f32_to_bf16_bits(n0 * inv_rms * w0) | ((uint32_t)f32_to_bf16_bits(n1 * inv_rms * w1) << 16);
+            o.y = (uint32_t)f32_to_bf16_bits(n2 * inv_rms * w2) | ((uint32_t)f32_to_bf16_bits(n3 * inv_rms * w3) << 16);
             sts_x(q4, o);
-            if (c == 0 && p.norm_hidden_out) {
-                uint2 hq;
-                hq.x = (uint32_t)f32_to_bf16_bits(vv[0]) | ((uint32_t)f32_to_bf16_bits(vv[1]) << 16);
-                hq.y = (uint32_t)f32_to_bf16_bits(vv[2]) | ((uint32_t)f32_to_bf16_bits(vv[3]) << 16);
-                reinterpret_cast<uint2*>(p.norm_hidden_out)[q4] = hq;
-            }
+            if (c == 0 && p.norm_hidden_out) reinterpret_cast<uint2*>(p.norm_hidden_out)[q4] = hq;
         };
         if (tid < n8) emit(tid, v0);
         if (tid + W * 32 < n8) emit(tid + W * 32, v1);

@@ -1,6 +1,8 @@
 """TEST INFRASTRUCTURE ONLY: numpy restatement of the reference operators that sit between the NF4
-linears in a Qwen3 decode step, and of the decode step itself. Parity unpinned (the reference has
-no golden vectors for them and cannot be built here); every function cites the lines it follows.
+linears in a Qwen3 decode step, and of the decode step itself. Every function cites the lines it
+follows; embedding_lookup and decode_prepare_qkv are held against the reference's own source compiled
+for the host (tests/test_reference_pin.py); attention_decode and the decode step are pinned by
+reading only (the reference has no golden vectors for them).
 
   embedding_lookup     src/ops/ElementwiseOps.cpp:14-27
   decode_prepare_qkv   src/ops/ElementwiseOps.cpp:105-215

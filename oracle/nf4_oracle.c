@@ -313,25 +313,69 @@ void nf4o_swiglu_rows(const bf16_t* gate_up, int64_t M, int64_t ff, bf16_t* out)
     }
 }
 
-/* Residual add + RMSNorm in front of a linear. NormOps.cpp:141-260 (ops::fused_add_rms_norm):
- * v = float(in) + float(residual) in fp32 (not rounded), sum of v^2 over the row,
- * inv_rms = 1/sqrt(sum / H + eps), hidden_out = bf16(v), normed = bf16(v * inv_rms * float(w)).
- * residual may be NULL (plain RMSNorm, NormOps.cpp rms_norm). The summation here is sequential in
- * double so that it is a tight reference for any fp32 reduction order. */
+/* Balanced tree over n = 2^k partial sums, t[i] += t[i + w] for w = n/2 .. 1: what a work-group
+ * reduction does on the hardware the reference targets (SYCL leaves the order open). */
+static float tree_sum_n(float* t, int n) {
+    for (int w = n / 2; w >= 1; w >>= 1)
+        for (int i = 0; i < w; ++i) t[i] = t[i] + t[i + w];
+    return t[0];
+}
+
+/* Residual add + RMSNorm in front of a linear. NormOps.cpp:141-275 (ops::fused_add_rms_norm) and,
+ * with residual == NULL, NormOps.cpp:14-75 (ops::rms_norm). v = float(in) + float(residual) in fp32,
+ * hidden_out = bf16(v), inv_rms = 1/sqrt(sum(v^2) / H + eps). The reference has three routes and this
+ * follows each one's order of additions and its choice of what is normalised:
+ *   one row, H == 1024 (:152-187): 128 work-items of 8 consecutive elements, the eight squares added
+ *     left to right; normed = bf16(v * inv_rms * w) from the UNROUNDED v;
+ *   one row, other H (:189-240): 256 work-items, item l takes the 8-element chunks l, l+256, ... and
+ *     then the tail elements; normed = bf16(float(bf16(v)) * inv_rms * w): the second pass re-reads
+ *     the residual stream it has just stored as bf16;
+ *   several rows (:243-274), and rms_norm in both of its forms: 256 work-items, item l takes elements
+ *     l, l+256, ...; normed from the unrounded v.
+ * The work-group sum is a balanced tree over the items' partial sums. */
 void nf4o_add_rms_norm(const bf16_t* in, const bf16_t* residual, const bf16_t* weight, float eps,
                        int64_t M, int64_t H, bf16_t* hidden_out, bf16_t* normed_out) {
+    const int decode_1024 = residual && M == 1 && H == 1024;
+    const int decode_chunks = residual && M == 1 && H != 1024;
     for (int64_t m = 0; m < M; ++m) {
-        double sum = 0.0;
-        for (int64_t k = 0; k < H; ++k) {
-            const float v = bf16_to_f32(in[m * H + k]) + (residual ? bf16_to_f32(residual[m * H + k]) : 0.0f);
-            sum += (double)v * (double)v;
+        const bf16_t* x = in + m * H;
+        const bf16_t* r = residual ? residual + m * H : NULL;
+        float part[256];
+        int lanes = 256;
+#define NF4O_V(k) (bf16_to_f32(x[k]) + (r ? bf16_to_f32(r[k]) : 0.0f))
+        if (decode_1024) {
+            lanes = 128;
+            for (int l = 0; l < 128; ++l) {
+                float acc = NF4O_V(l * 8) * NF4O_V(l * 8);
+                for (int k = 1; k < 8; ++k) acc = acc + NF4O_V(l * 8 + k) * NF4O_V(l * 8 + k);
+                part[l] = acc;
+            }
+        } else if (decode_chunks) {
+            const int64_t chunks = H / 8, tail = chunks * 8;
+            for (int l = 0; l < 256; ++l) {
+                float acc = 0.0f;
+                for (int64_t c = l; c < chunks; c += 256)
+                    for (int k = 0; k < 8; ++k) acc = acc + NF4O_V(c * 8 + k) * NF4O_V(c * 8 + k);
+                for (int64_t k = tail + l; k < H; k += 256) acc = acc + NF4O_V(k) * NF4O_V(k);
+                part[l] = acc;
+            }
+        } else {
+            for (int l = 0; l < 256; ++l) {
+                float acc = 0.0f;
+                for (int64_t k = l; k < H; k += 256) acc = acc + NF4O_V(k) * NF4O_V(k);
+                part[l] = acc;
+            }
         }
-        const float inv_rms = 1.0f / sqrtf((float)(sum / (double)H) + eps);
+        const float sum = tree_sum_n(part, lanes);
+        const float inv_rms = 1.0f / sqrtf(sum / (float)H + eps);
         for (int64_t k = 0; k < H; ++k) {
-            const float v = bf16_to_f32(in[m * H + k]) + (residual ? bf16_to_f32(residual[m * H + k]) : 0.0f);
-            if (hidden_out) hidden_out[m * H + k] = f32_to_bf16(v);
-            normed_out[m * H + k] = f32_to_bf16(v * inv_rms * bf16_to_f32(weight[k]));
+            const float v = NF4O_V(k);
+            const bf16_t stored = f32_to_bf16(v);
+            if (hidden_out) hidden_out[m * H + k] = stored;
+            const float vn = decode_chunks ? bf16_to_f32(stored) : v;
+            normed_out[m * H + k] = f32_to_bf16(vn * inv_rms * bf16_to_f32(weight[k]));
         }
+#undef NF4O_V
     }
 }
 

@@ -128,3 +128,72 @@ def dequantize_kn(w) -> np.ndarray:
     _check(lib().aila_ref_dequantize(ctypes.byref(d), out.ctypes.data_as(ctypes.c_void_p), err, ctypes.c_int(512)),
            err)
     return out
+
+
+# ---------------------------------------------------------------- operators around the linears
+def _u16(a):
+    return np.ascontiguousarray(a, np.uint16)
+
+
+def _vp(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _run(name, *args):
+    err = ctypes.create_string_buffer(512)
+    fn = getattr(lib(), name)
+    fn.restype = ctypes.c_int
+    _check(fn(*args, err, ctypes.c_int(512)), err)
+
+
+def rms_norm(x_bf16, weight_bf16, eps, M, H) -> np.ndarray:
+    x, w = _u16(x_bf16).reshape(M, H).copy(), _u16(weight_bf16).reshape(H).copy()
+    out = np.zeros((M, H), np.uint16)
+    _run("aila_ref_rms_norm", _vp(x), _vp(w), ctypes.c_float(eps), _vp(out), ctypes.c_int(M), ctypes.c_int(H))
+    return out
+
+
+def fused_add_rms_norm(x_bf16, residual_bf16, weight_bf16, eps, M, H):
+    """(hidden, normed): the reference updates its input in place; here the input is copied first."""
+    x, r = _u16(x_bf16).reshape(M, H).copy(), _u16(residual_bf16).reshape(M, H).copy()
+    w = _u16(weight_bf16).reshape(H).copy()
+    out = np.zeros((M, H), np.uint16)
+    _run("aila_ref_fused_add_rms_norm", _vp(x), _vp(r), _vp(w), ctypes.c_float(eps), _vp(out), ctypes.c_int(M),
+         ctypes.c_int(H))
+    return x, out
+
+
+def embedding_lookup(table_bf16, token_ids) -> np.ndarray:
+    t = _u16(table_bf16).copy()
+    ids = np.ascontiguousarray(token_ids, np.int32)
+    out = np.zeros((ids.size, t.shape[1]), np.uint16)
+    _run("aila_ref_embedding_lookup", _vp(t), ctypes.c_int(t.shape[0]), _vp(ids), ctypes.c_int(ids.size), _vp(out),
+         ctypes.c_int(t.shape[1]))
+    return out
+
+
+def decode_prepare_qkv(q_bf16, k_bf16, v_bf16, freq, q_norm_w, k_norm_w, k_cache, v_cache, pos, n_heads, n_kv,
+                       head_dim, eps, theta=1e6) -> np.ndarray:
+    """Returns the rotated q; k_cache / v_cache ([n_kv, max_len, head_dim] uint16) are updated in place."""
+    q, k, v = _u16(q_bf16).reshape(-1).copy(), _u16(k_bf16).reshape(-1).copy(), _u16(v_bf16).reshape(-1).copy()
+    f = np.ascontiguousarray(freq, np.float32).copy()
+    qn, kn = _u16(q_norm_w).copy(), _u16(k_norm_w).copy()
+    assert k_cache.dtype == np.uint16 and k_cache.flags.c_contiguous and v_cache.flags.c_contiguous
+    _run("aila_ref_decode_prepare_qkv", _vp(q), _vp(k), _vp(v), _vp(f), _vp(qn), _vp(kn), _vp(k_cache), _vp(v_cache),
+         ctypes.c_int(k_cache.shape[1]), ctypes.c_int(pos), ctypes.c_int(n_heads), ctypes.c_int(n_kv),
+         ctypes.c_int(head_dim), ctypes.c_float(eps), ctypes.c_float(theta))
+    return q
+
+
+def swiglu(gate_bf16, up_bf16) -> np.ndarray:
+    g, u = _u16(gate_bf16).reshape(-1).copy(), _u16(up_bf16).reshape(-1).copy()
+    out = np.zeros(g.size, np.uint16)
+    _run("aila_ref_swiglu", _vp(g), _vp(u), _vp(out), ctypes.c_int(g.size))
+    return out
+
+
+def fused_gate_up_swiglu(gate_up_bf16, ff) -> np.ndarray:
+    gu = _u16(gate_up_bf16).reshape(-1).copy()
+    out = np.zeros(ff, np.uint16)
+    _run("aila_ref_fused_gate_up_swiglu", _vp(gu), _vp(out), ctypes.c_int(ff))
+    return out

@@ -153,3 +153,68 @@ def test_reference_error_behaviour():
         R.forward(bad, _x(1, 1, 128), 1)
     with pytest.raises(R.RefError, match="seq_len must be positive"):
         R.forward(w, np.zeros((0, 128), np.uint16), 0)
+
+
+# ---------------------------------------------------------------- the operators around the linears
+@pytest.mark.parametrize("M,H", [(1, 1024), (1, 2560), (1, 5120), (1, 100), (1, 4100), (3, 2560), (2, 1024)])
+def test_add_rms_norm_routes(oracle, M, H):
+    """ops::fused_add_rms_norm (single row with H == 1024, single row otherwise, several rows) and
+    ops::rms_norm: residual stream and normalised output bit-exact."""
+    x, r, w = _x(1, M, H), _x(2, M, H), _x(3, 1, H).reshape(-1)
+    hidden, normed = oracle.add_rms_norm(x, r, w, 1e-6, M, H)
+    ref_hidden, ref_normed = R.fused_add_rms_norm(x, r, w, 1e-6, M, H)
+    assert np.array_equal(hidden, ref_hidden)
+    assert np.array_equal(normed, ref_normed)
+    _, plain = oracle.add_rms_norm(x, None, w, 1e-6, M, H)
+    assert np.array_equal(plain, R.rms_norm(x, w, 1e-6, M, H))
+
+
+def test_single_row_route_normalises_the_stored_sum(oracle):
+    """For H != 1024 the single-row route re-reads bf16(x + r) for its second pass; with the unrounded
+    sum some outputs would differ by a bf16 ulp. The oracle keeps the reference's choice."""
+    H = 2560
+    x, r, w = _x(4, 1, H), _x(5, 1, H), _x(6, 1, H).reshape(-1)
+    _, one_row = oracle.add_rms_norm(x, r, w, 1e-6, 1, H)
+    _, as_rows = oracle.add_rms_norm(np.concatenate([x, x]), np.concatenate([r, r]), w, 1e-6, 2, H)
+    assert np.array_equal(one_row, R.fused_add_rms_norm(x, r, w, 1e-6, 1, H)[1])
+    assert not np.array_equal(one_row.reshape(-1), as_rows[0])
+
+
+@pytest.mark.parametrize("ff", [3584, 512, 40])
+def test_swiglu(oracle, ff):
+    gu = _x(20 + ff, 1, 2 * ff).reshape(-1)
+    want = oracle.swiglu_rows(gu, 1, ff).reshape(-1)
+    assert np.array_equal(R.fused_gate_up_swiglu(gu, ff), want)
+    assert np.array_equal(R.swiglu(gu[:ff], gu[ff:]), want)
+
+
+def test_embedding_lookup():
+    from oracle import backend_numpy as B
+    table = _x(30, 50, 64)
+    ids = [0, 49, 3, 3, 17]
+    assert np.array_equal(R.embedding_lookup(table, ids), B.embedding_lookup(table, ids))
+
+
+@pytest.mark.parametrize("heads,kv,hd,pos", [(4, 2, 64, 0), (32, 8, 128, 37), (16, 16, 128, 1000), (8, 1, 256, 5)])
+def test_decode_prepare_qkv(heads, kv, hd, pos):
+    """Per-head RMSNorm + RoPE of q and k and the cache append. cos/sin come from two libraries
+    (libm in the stand-in, numpy in the oracle): a last-bit difference there may move a rotated value
+    by one bf16 ulp, so q and the new k row are held to that; v and the untouched cache are exact."""
+    from oracle import backend_numpy as B
+    q, k, v = _x(40, 1, heads * hd), _x(41, 1, kv * hd), _x(42, 1, kv * hd)
+    qw, kw = _x(43, 1, hd).reshape(-1), _x(44, 1, hd).reshape(-1)
+    freq = B.rope_freq(hd, 1e6)
+    kc_r = np.zeros((kv, 1024, hd), np.uint16)
+    vc_r, kc_o, vc_o = np.zeros_like(kc_r), np.zeros_like(kc_r), np.zeros_like(kc_r)
+    q_r = R.decode_prepare_qkv(q, k, v, freq, qw, kw, kc_r, vc_r, pos, heads, kv, hd, 1e-6)
+    q_o = B.decode_prepare_qkv(q, k, v, freq, qw, kw, kc_o, vc_o, pos, heads, kv, hd, 1e-6)
+
+    def within_one_ulp(a, b):
+        a, b = a.astype(np.int32), b.astype(np.int32)
+        return np.abs(a - b).max() <= 1 and (a != b).mean() < 0.01
+
+    assert within_one_ulp(q_r, q_o)
+    assert within_one_ulp(kc_r[:, pos], kc_o[:, pos])
+    assert np.array_equal(vc_r, vc_o)
+    kc_r[:, pos] = kc_o[:, pos] = 0
+    assert not kc_r.any() and not kc_o.any()
