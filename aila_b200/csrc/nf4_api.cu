@@ -340,9 +340,9 @@ AilaNf4Status ensure_io(void** buf, size_t* have, size_t need) {
 }
 
 // Small batches (2 .. AILA_NF4_DECODE_ROWS_MAX rows; 0 or 1 turns it off): batched decode
-// launches of up to eight rows each instead of the dequantise + GEMM route, when the streaming
-// kernel takes the shape and no bf16 weight cache exists (with a cache the GEMM has nothing to
-// dequantise).
+// launches of up to 32 rows each (one pass over the weights) instead of the dequantise + GEMM
+// route, when the streaming kernel takes the shape and no bf16 weight cache exists (with a cache
+// the GEMM has nothing to dequantise).
 int decode_rows_max() {
     static const int v = [] {
         const char* e = std::getenv("AILA_NF4_DECODE_ROWS_MAX");
@@ -359,6 +359,12 @@ bool use_batched_decode(const AilaNf4Linear* l, const AilaNf4Scratch* sc, const 
     if (gemv_kernel_choice() == 1) return false;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (l->K * 2) % 16) return false;
     return nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
+}
+
+// Rows one batched launch carries: 32 (four row blocks) where the kernel's shared-memory plan has
+// room for the larger accumulation tiles, else 8.
+int batched_rows_per_launch(const AilaNf4Linear* l, const AilaNf4Scratch* sc) {
+    return nf4::gemv_stream_supported(*l, 0, sc->sm_count, 4) ? 32 : 8;
 }
 
 // seq_len == 1: decode kernels. ff_pair > 0 selects the gate/up pair kernel.
@@ -721,14 +727,16 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward(const AilaNf4Linear* l, AilaNf4Scrat
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, y, residual, 0, s);
     if (use_batched_decode(l, sc, x, seq_len, 0)) {
-        // a few rows: the batched decode kernel carries up to eight rows through the tensor-core
-        // tile's batch columns and reads 0.52 B per weight per launch; the dequantise + GEMM
-        // route moves 4.5 B per weight whatever the row count
+        // a few rows: the batched decode kernel carries up to 32 rows through the tensor-core
+        // tile's batch columns (every decoded weight fragment feeds one operation per block of
+        // eight rows) and reads 0.52 B per weight per launch; the dequantise + GEMM route moves
+        // 4.5 B per weight whatever the row count
         const char* xb = static_cast<const char*>(x);
         char* yb = static_cast<char*>(y);
         const char* rb = static_cast<const char*>(residual);
-        for (int m = 0; m < seq_len; m += 8) {
-            const int rows = seq_len - m < 8 ? seq_len - m : 8;
+        const int step = batched_rows_per_launch(l, sc);
+        for (int m = 0; m < seq_len; m += step) {
+            const int rows = seq_len - m < step ? seq_len - m : step;
             st = run_decode(l, sc, xb + (size_t)m * l->K * 2, yb + (size_t)m * l->N * 2,
                             rb ? rb + (size_t)m * l->N * 2 : nullptr, 0, s, rows);
             if (st != AILA_NF4_OK) return st;
@@ -760,6 +768,22 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, out, nullptr, ff_dim, s);
+    if (seq_len > 8 && use_batched_decode(l, sc, x, seq_len, 0) && batched_rows_per_launch(l, sc) > 8) {
+        // more than eight rows: the unpaired batched kernel over the fused rows (one pass over the
+        // weights for up to 32 rows) into a bf16 gate|up buffer, then the row-wise activation -
+        // the arithmetic of the reference's seq_len > 1 route (bf16 gate_up, then ops::swiglu)
+        st = ensure_weight(sc, (size_t)seq_len * (size_t)l->N * 2);
+        if (st != AILA_NF4_OK) return st;
+        const char* xb = static_cast<const char*>(x);
+        char* gu = static_cast<char*>(sc->d_weight);
+        for (int m = 0; m < seq_len; m += 32) {
+            const int rows = seq_len - m < 32 ? seq_len - m : 32;
+            st = run_decode(l, sc, xb + (size_t)m * l->K * 2, gu + (size_t)m * l->N * 2, nullptr, 0, s, rows);
+            if (st != AILA_NF4_OK) return st;
+        }
+        NF4_CUDA(nf4::launch_swiglu_rows(sc->d_weight, out, seq_len, ff_dim, s));
+        return AILA_NF4_OK;
+    }
     if (use_batched_decode(l, sc, x, seq_len, ff_dim)) {
         const char* xb = static_cast<const char*>(x);
         char* ob = static_cast<char*>(out);

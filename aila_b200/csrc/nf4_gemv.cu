@@ -230,15 +230,27 @@ __device__ __forceinline__ int slice_begin(const StreamParams& p, int c) {
 }
 
 
-// BATCH: up to eight rows of x ride in the eight batch columns of the tensor-core tile, so the
-// weights are read and dequantised once for all of them. Differences from the single-row kernel:
-// x fragments come straight from global memory (L2) per work item, every lane keeps 2x2
-// accumulators per half, warps add their tile sums into one shared fp32 tile with shared-memory
-// atomics (the order of these additions is not fixed: last-bit differences between runs), and
-// the epilogue writes [rows][out] outputs.
-template <int KIND, bool PAIRED, bool BATCH>
+// Bytes of the per-(row tile, half) accumulation slot: one 16-float row per consumer warp in the
+// single-row kernel, `row_blocks` tiles of 16 rows x 8 batch columns in the batched one.
+__host__ __device__ constexpr int stream_slot_bytes(int row_blocks) {
+    return kConsumerWarps * 64 > row_blocks * 512 ? kConsumerWarps * 64 : row_blocks * 512;
+}
+
+// BATCH = number of 8-row blocks of x (0: the single-row kernel; 1, 2 or 4: up to 8, 16 or 32 rows).
+// The rows of a block ride in the eight batch columns of the tensor-core tile, and every decoded
+// weight fragment feeds one tensor-core operation per block, so the weights are read and
+// dequantised once for all rows. Differences from the single-row kernel: x fragments come straight
+// from global memory (L2) per work item, every lane keeps 2x2 accumulators per half and block,
+// warps add their tile sums into shared fp32 tiles with shared-memory atomics (the order of these
+// additions is not fixed: last-bit differences between runs), and the epilogue writes [rows][out]
+// outputs. More than one block only without the gate/up pairing (register budget).
+template <int KIND, bool PAIRED, int BATCH>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const StreamParams p) {
     constexpr int NP = PAIRED ? 2 : 1;
+    constexpr int RB = BATCH > 0 ? BATCH : 1;  // 8-row blocks of x
+    static_assert(BATCH == 0 || BATCH == 1 || BATCH == 2 || BATCH == 4, "row blocks");
+    static_assert(!(PAIRED && RB > 1), "the paired kernel takes one row block");
+    constexpr int kSlotBytes = stream_slot_bytes(RB);
     constexpr int W = kConsumerWarps;
     constexpr int IPW = kItemsPerWarp;
     constexpr int unit_stride = (KIND == kAbsmaxCodes) ? kUnitStrideCodes : kUnitStrideF32;
@@ -263,7 +275,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const uint32_t a_ptab = a_nabsw + 2 * kNabsWindow * 4;       // [256] byte value -> bf16 pair
     const uint32_t a_tinfo = a_ptab + 1024;                      // [tile][lane] absmax row base, offset
     const uint32_t a_slots = a_tinfo + kMaxLocalTiles * 32 * 8;  // [tile][pair][warp][16] floats
-    const uint32_t a_xs_small = a_slots + kMaxLocalTiles * NP * W * 64;
+    const uint32_t a_xs_small = a_slots + kMaxLocalTiles * NP * kSlotBytes;
     const uint32_t a_lut = 65536u;
     const uint32_t a_xs = p.x_in_b ? 131072u : a_xs_small;
     const uint32_t a_ring_b = 131072u + (p.x_in_b ? (uint32_t)p.x_bytes : 0u);
@@ -443,10 +455,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     };
     // ---- batched variants: a tile is 16 rows x 8 batch columns, lane l holds the four entries
     // 4l .. 4l+3 of its row-major order ----
-    auto write_rows_b = [&](int rtile, const float (&v)[NP][4]) {
+    auto write_rows_b = [&](int rtile, const float (&v)[NP][4], int rb) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int idx = lane * 4 + e, r = idx >> 3, m = idx & 7;
+            const int idx = lane * 4 + e, r = idx >> 3, m = (idx & 7) + 8 * rb;
             const int n = rtile * kTileRows + r;
             if (m < p.m_rows && n < p.n_out) {
                 float o;
@@ -472,46 +484,53 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         int c_lo = c, c_hi = c;
         while (c_lo > 0 && slice_begin(p, c_lo) > t0) --c_lo;
         while (c_hi + 1 < G && slice_begin(p, c_hi + 1) < t1) ++c_hi;
-        float v[NP][4];
+#pragma unroll 1
+        for (int rb = 0; rb < RB; ++rb) {
+            float v[NP][4];
 #pragma unroll
-        for (int h = 0; h < NP; ++h)
+            for (int h = 0; h < NP; ++h)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) v[h][e] = 0.0f;
-        for (int cc = c_lo; cc <= c_hi; ++cc) {
-            const int cc_first = fast_div(slice_begin(p, cc), p.div_ku_m, p.div_ku_s);
-            const int hs = (rtile == cc_first) ? 0 : 1;
+                for (int e = 0; e < 4; ++e) v[h][e] = 0.0f;
+            for (int cc = c_lo; cc <= c_hi; ++cc) {
+                const int cc_first = fast_div(slice_begin(p, cc), p.div_ku_m, p.div_ku_s);
+                const int hs = (rtile == cc_first) ? 0 : 1;
 #pragma unroll
-            for (int h = 0; h < NP; ++h) {
-                const float4 q = __ldcg(reinterpret_cast<const float4*>(
-                    p.partials + (((size_t)cc * 2 + hs) * NP + h) * 128) + lane);
-                v[h][0] += q.x; v[h][1] += q.y; v[h][2] += q.z; v[h][3] += q.w;
+                for (int h = 0; h < NP; ++h) {
+                    const float4 q = __ldcg(reinterpret_cast<const float4*>(
+                        p.partials + ((((size_t)cc * 2 + hs) * NP + h) * RB + rb) * 128) + lane);
+                    v[h][0] += q.x; v[h][1] += q.y; v[h][2] += q.z; v[h][3] += q.w;
+                }
             }
+            write_rows_b(rtile, v, rb);
         }
         if (lane == 0) p.counters[rtile] = 0;
-        write_rows_b(rtile, v);
     };
     auto finalize_tile_b = [&](int li) {
         const int rtile = rt_first + li;
-        float v[NP][4];
-#pragma unroll
-        for (int h = 0; h < NP; ++h) {
-            uint4 q;
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                         : "r"(a_slots + (uint32_t)((li * NP + h) * 128 + lane * 4) * 4u));
-            v[h][0] = __uint_as_float(q.x); v[h][1] = __uint_as_float(q.y);
-            v[h][2] = __uint_as_float(q.z); v[h][3] = __uint_as_float(q.w);
-        }
         const int items = tile_items(li);
-        if (items == p.KU) {
-            write_rows_b(rtile, v);
-            return;
-        }
         const int hslot = (li == 0) ? 0 : 1;
+#pragma unroll 1
+        for (int rb = 0; rb < RB; ++rb) {
+            float v[NP][4];
 #pragma unroll
-        for (int h = 0; h < NP; ++h)
-            reinterpret_cast<float4*>(p.partials + (((size_t)c * 2 + hslot) * NP + h) * 128)[lane] =
-                make_float4(v[h][0], v[h][1], v[h][2], v[h][3]);
+            for (int h = 0; h < NP; ++h) {
+                uint4 q;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                             : "r"(a_slots + (uint32_t)((li * NP + h) * kSlotBytes + rb * 512 + lane * 16)));
+                v[h][0] = __uint_as_float(q.x); v[h][1] = __uint_as_float(q.y);
+                v[h][2] = __uint_as_float(q.z); v[h][3] = __uint_as_float(q.w);
+            }
+            if (items == p.KU) {
+                write_rows_b(rtile, v, rb);
+                continue;
+            }
+#pragma unroll
+            for (int h = 0; h < NP; ++h)
+                reinterpret_cast<float4*>(p.partials + ((((size_t)c * 2 + hslot) * NP + h) * RB + rb) * 128)[lane] =
+                    make_float4(v[h][0], v[h][1], v[h][2], v[h][3]);
+        }
+        if (items == p.KU) return;
         __syncwarp();
         int old = 0;
         if (lane == 0)
@@ -714,7 +733,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
         }
     }
     auto zero_slots = [&]() {
-        constexpr int kSlotVecs = kMaxLocalTiles * NP * W * 16 / 4;
+        constexpr int kSlotVecs = kMaxLocalTiles * NP * kSlotBytes / 16;
 #pragma unroll
         for (int i = 0; i < (kSlotVecs + W * 32 - 1) / (W * 32); ++i) {
             const int q = tid + i * W * 32;
@@ -736,7 +755,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     const uint32_t my_win = a_nabsw + (uint32_t)(dhalf * kNabsWindow) * 4u;
 
     // single row: [h][row gq / gq + 8] in lanes t = 0; batched: [h][2 * (row) + (column 2t / 2t+1)]
-    constexpr int NACC = BATCH ? 4 : 2;
+    constexpr int NACC = BATCH ? 4 * RB : 2;  // batched: [4 * block + e]
     float acc[NP][NACC];
 #pragma unroll
     for (int h = 0; h < NP; ++h)
@@ -933,15 +952,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     };
     auto flush_current = [&]() {
         if (cur_li >= 0) {
-            if constexpr (BATCH) {
-                // every warp adds its share of the tile into one fp32 tile [16 rows][8 columns]
+            if constexpr (BATCH != 0) {
+                // every warp adds its share of the tile into one fp32 tile [16 rows][8 columns] per block
 #pragma unroll
                 for (int h = 0; h < NP; ++h) {
-                    const uint32_t tb = a_slots + (uint32_t)((cur_li * NP + h) * 128) * 4u;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t idx = (uint32_t)((gq + 8 * (e >> 1)) * 8 + 2 * t + (e & 1));
-                        asm volatile("red.shared.add.f32 [%0], %1;" ::"r"(tb + 4u * idx), "f"(acc[h][e]) : "memory");
+                    for (int rb = 0; rb < RB; ++rb) {
+                        const uint32_t tb = a_slots + (uint32_t)((cur_li * NP + h) * kSlotBytes + rb * 512);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t idx = (uint32_t)((gq + 8 * (e >> 1)) * 8 + 2 * t + (e & 1));
+                            asm volatile("red.shared.add.f32 [%0], %1;" ::"r"(tb + 4u * idx), "f"(acc[h][4 * rb + e])
+                                         : "memory");
+                        }
                     }
                 }
             } else if (t == 0) {
@@ -982,19 +1005,27 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 // that hold batch column 0 of the tile; the other columns stay zero and are never
                 // read back. A 16-byte load is served a quarter warp at a time, so the
                 // predicated pair costs two shared-memory wavefronts instead of eight.
+                uint4 xr0[RB > 1 ? RB - 1 : 1], xr1[RB > 1 ? RB - 1 : 1];  // blocks 1 .. RB-1
                 if (BATCH) {
-                    // batch row gq of x, straight from L2 (coherent loads: x may be the previous
-                    // kernel's output): tile j wants k = 64 kb + 16 j + 4 t + {0..3}
-                    const uint2* xr = reinterpret_cast<const uint2*>(p.x + (size_t)gq * p.K + (size_t)kb * 64 + 4 * t);
-                    uint2 xb0 = make_uint2(0u, 0u), xb1 = xb0, xb2 = xb0, xb3 = xb0;
-                    if (gq < p.m_rows) {
-                        xb0 = __ldcg(xr);
-                        xb1 = __ldcg(xr + 4);
-                        xb2 = __ldcg(xr + 8);
-                        xb3 = __ldcg(xr + 12);
-                    }
-                    xq0 = make_uint4(xb0.x, xb0.y, xb1.x, xb1.y);
-                    xq1 = make_uint4(xb2.x, xb2.y, xb3.x, xb3.y);
+                    // batch row gq (+ 8 per block) of x, straight from L2 (coherent loads: x may be
+                    // the previous kernel's output): tile j wants k = 64 kb + 16 j + 4 t + {0..3}
+                    auto load_block = [&](int rb, uint4& q0, uint4& q1) {
+                        const int row = gq + 8 * rb;
+                        const uint2* xr =
+                            reinterpret_cast<const uint2*>(p.x + (size_t)row * p.K + (size_t)kb * 64 + 4 * t);
+                        uint2 xb0 = make_uint2(0u, 0u), xb1 = xb0, xb2 = xb0, xb3 = xb0;
+                        if (row < p.m_rows) {
+                            xb0 = __ldcg(xr);
+                            xb1 = __ldcg(xr + 4);
+                            xb2 = __ldcg(xr + 8);
+                            xb3 = __ldcg(xr + 12);
+                        }
+                        q0 = make_uint4(xb0.x, xb0.y, xb1.x, xb1.y);
+                        q1 = make_uint4(xb2.x, xb2.y, xb3.x, xb3.y);
+                    };
+                    load_block(0, xq0, xq1);
+#pragma unroll
+                    for (int rb = 1; rb < RB; ++rb) load_block(rb, xr0[rb - 1], xr1[rb - 1]);
                 } else {
                 const uint32_t xa = a_xs + (uint32_t)kb * 128u + 16u * t;
                     asm volatile(
@@ -1080,7 +1111,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                 }
 #pragma unroll
                 for (int h = 0; h < NP; ++h) {
-                    if constexpr (BATCH) {
+                    if constexpr (BATCH != 0) {
                         acc[h][0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][0]);
                         acc[h][1] = fmaf(am0[h], c0[h][1] + c1[h][1], acc[h][1]);
                         acc[h][2] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][2]);
@@ -1088,6 +1119,24 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
                     } else {
                         acc[h][0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][0]);
                         acc[h][1] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][1]);
+                    }
+                }
+                if constexpr (RB > 1) {
+                    // the other row blocks against the same decoded fragments
+#pragma unroll
+                    for (int rb = 1; rb < RB; ++rb) {
+                        const uint4 q0 = xr0[rb - 1], q1 = xr1[rb - 1];
+#pragma unroll
+                        for (int h = 0; h < NP; ++h) {
+                            mma_bf16_16816_init(c0[h], a[h][0], a[h][1], a[h][2], a[h][3], q0.x, q0.y);
+                            mma_bf16_16816_init(c1[h], a[h][4], a[h][5], a[h][6], a[h][7], q0.z, q0.w);
+                            mma_bf16_16816(c0[h], a[h][8], a[h][9], a[h][10], a[h][11], q1.x, q1.y);
+                            mma_bf16_16816(c1[h], a[h][12], a[h][13], a[h][14], a[h][15], q1.z, q1.w);
+                            acc[h][4 * rb + 0] = fmaf(am0[h], c0[h][0] + c1[h][0], acc[h][4 * rb + 0]);
+                            acc[h][4 * rb + 1] = fmaf(am0[h], c0[h][1] + c1[h][1], acc[h][4 * rb + 1]);
+                            acc[h][4 * rb + 2] = fmaf(am1[h], c0[h][2] + c1[h][2], acc[h][4 * rb + 2]);
+                            acc[h][4 * rb + 3] = fmaf(am1[h], c0[h][3] + c1[h][3], acc[h][4 * rb + 3]);
+                        }
                     }
                 }
                 // ---- this warp's next item: W positions further along the traversal ----
@@ -1154,7 +1203,7 @@ int smem_window_base() {
 
 constexpr int kStreamSmemBytes = 227 * 1024;  // every launch asks for the whole budget
 
-StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int sm_count) {
+StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int sm_count, int row_blocks = 1) {
     StreamPlan pl;
     const int np = paired ? 2 : 1;
     const int stage_bytes = kStageItems * w.unit_stride * np + (paired ? kPairSkewBytes : 0);
@@ -1164,7 +1213,7 @@ StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int
     // base + budget): x otherwise, then ring stages.
     const int base = (smem_window_base() + 15) / 16 * 16;
     const int a_fixed = base + 400 + 64 + 16 + 64 + 1024 + 2 * kNabsWindow * 4 + 1024 +
-                        kMaxLocalTiles * 32 * 8 + kMaxLocalTiles * np * kConsumerWarps * 64;
+                        kMaxLocalTiles * 32 * 8 + kMaxLocalTiles * np * stream_slot_bytes(row_blocks);
     pl.x_in_b = (a_fixed + x_bytes > 65536) ? 1 : 0;
     const int ring_a = (a_fixed + (pl.x_in_b ? 0 : x_bytes) + 127) / 128 * 128;
     const int stages_a = ring_a < 65536 ? (65536 - ring_a) / stage_bytes : 0;
@@ -1194,7 +1243,7 @@ StreamPlan stream_plan(const AilaNf4Linear& w, bool paired, int64_t ff_pair, int
     return pl;
 }
 
-template <int KIND, bool PAIRED, bool BATCH>
+template <int KIND, bool PAIRED, int BATCH>
 cudaError_t launch_stream_t(const StreamParams& p, int grid, int smem, cudaStream_t s) {
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -1271,8 +1320,9 @@ cudaError_t launch_gemv_simple(const AilaNf4Linear& w, const void* x, void* y,
 }
 
 size_t gemv_stream_partials_floats(int sm_count) {
-    // per CTA: two shared tiles x two halves x (16 rows x up to 8 batch columns)
-    return (size_t)sm_count * kMaxGridMult * 2 * 2 * 128;
+    // per CTA: two shared tiles x (two halves of one row block, or one half of up to four row blocks)
+    // x (16 rows x 8 batch columns)
+    return (size_t)sm_count * kMaxGridMult * 2 * 4 * 128;
 }
 
 int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count) {
@@ -1280,16 +1330,19 @@ int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count) {
     return pl.ok ? pl.grid : 0;
 }
 
-bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count) {
+bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count, int row_blocks) {
     if (w.K > 65535 * 4) return false;
-    return stream_plan(w, ff_pair > 0, ff_pair, sm_count).ok;
+    if (ff_pair > 0 && row_blocks > 1) return false;
+    return stream_plan(w, ff_pair > 0, ff_pair, sm_count, row_blocks).ok;
 }
 
 cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x,
                                void* y, const void* residual, int64_t ff_pair, cudaStream_t s,
                                const PeerTargets* peers, int m_rows, const NormInput* norm) {
     const bool paired = ff_pair > 0;
-    const StreamPlan pl = stream_plan(w, paired, ff_pair, scratch.sm_count);
+    if (m_rows < 1 || m_rows > (paired ? 8 : 32) || (m_rows > 1 && (peers || norm))) return cudaErrorInvalidValue;
+    const int row_blocks = m_rows <= 8 ? 1 : (m_rows <= 16 ? 2 : 4);
+    const StreamPlan pl = stream_plan(w, paired, ff_pair, scratch.sm_count, row_blocks);
     if (!pl.ok) return cudaErrorInvalidConfiguration;
     StreamParams p;
     p.units = w.d_units;
@@ -1321,7 +1374,6 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     p.x_in_b = pl.x_in_b;
     p.smem_bytes = pl.smem;
     p.n_rows = (int)w.N;
-    if (m_rows < 1 || m_rows > 8 || (m_rows > 1 && (peers || norm))) return cudaErrorInvalidValue;
     p.m_rows = m_rows;
     p.norm_add = norm ? static_cast<const uint16_t*>(norm->add) : nullptr;
     p.norm_w = norm ? static_cast<const uint16_t*>(norm->weight) : nullptr;
@@ -1349,17 +1401,21 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     }
     const bool batch = m_rows > 1;
     if (w.absmax_kind == kAbsmaxCodes) {
+        if (batch && row_blocks == 4) return launch_stream_t<kAbsmaxCodes, false, 4>(p, pl.grid, pl.smem, s);
+        if (batch && row_blocks == 2) return launch_stream_t<kAbsmaxCodes, false, 2>(p, pl.grid, pl.smem, s);
         if (batch)
-            return paired ? launch_stream_t<kAbsmaxCodes, true, true>(p, pl.grid, pl.smem, s)
-                          : launch_stream_t<kAbsmaxCodes, false, true>(p, pl.grid, pl.smem, s);
-        return paired ? launch_stream_t<kAbsmaxCodes, true, false>(p, pl.grid, pl.smem, s)
-                      : launch_stream_t<kAbsmaxCodes, false, false>(p, pl.grid, pl.smem, s);
+            return paired ? launch_stream_t<kAbsmaxCodes, true, 1>(p, pl.grid, pl.smem, s)
+                          : launch_stream_t<kAbsmaxCodes, false, 1>(p, pl.grid, pl.smem, s);
+        return paired ? launch_stream_t<kAbsmaxCodes, true, 0>(p, pl.grid, pl.smem, s)
+                      : launch_stream_t<kAbsmaxCodes, false, 0>(p, pl.grid, pl.smem, s);
     }
+    if (batch && row_blocks == 4) return launch_stream_t<kAbsmaxF32, false, 4>(p, pl.grid, pl.smem, s);
+    if (batch && row_blocks == 2) return launch_stream_t<kAbsmaxF32, false, 2>(p, pl.grid, pl.smem, s);
     if (batch)
-        return paired ? launch_stream_t<kAbsmaxF32, true, true>(p, pl.grid, pl.smem, s)
-                      : launch_stream_t<kAbsmaxF32, false, true>(p, pl.grid, pl.smem, s);
-    return paired ? launch_stream_t<kAbsmaxF32, true, false>(p, pl.grid, pl.smem, s)
-                  : launch_stream_t<kAbsmaxF32, false, false>(p, pl.grid, pl.smem, s);
+        return paired ? launch_stream_t<kAbsmaxF32, true, 1>(p, pl.grid, pl.smem, s)
+                      : launch_stream_t<kAbsmaxF32, false, 1>(p, pl.grid, pl.smem, s);
+    return paired ? launch_stream_t<kAbsmaxF32, true, 0>(p, pl.grid, pl.smem, s)
+                  : launch_stream_t<kAbsmaxF32, false, 0>(p, pl.grid, pl.smem, s);
 }
 
 // Decode GEMV on the static work space: no allocation of any kind. The first call on a device

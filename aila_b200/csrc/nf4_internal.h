@@ -142,7 +142,8 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
                                void* y, const void* residual, int64_t ff_pair, cudaStream_t s,
                                const PeerTargets* peers = nullptr, int m_rows = 1,
                                const NormInput* norm = nullptr);
-bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);
+// row_blocks: 8-row blocks of x one launch carries (1 for a single row; 2 or 4 only unpaired)
+bool gemv_stream_supported(const AilaNf4Linear& w, int64_t ff_pair, int sm_count, int row_blocks = 1);
 int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);  // 0: shape not taken
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);

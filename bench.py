@@ -530,7 +530,7 @@ def decode_stack(local, stream, batches=(4, 8, 16, 32)):
     us = _time_stream(_graph(chain.run, stream), stream, 20)
     us_calls = _time_stream(_graph(per_call, stream), stream, 10)
     scratch.check()
-    # small batches (batched decode kernel, eight rows per launch)
+    # small batches (batched decode kernel: up to 32 rows per launch, one pass over the weights)
     batch = {}
     for M in batches:
         xb_h = synth.gaussian_activation(4100 + M, M, HID).to(dev)

@@ -584,8 +584,8 @@ def test_argmax_bf16(nf4):
 
 @pytest.mark.parametrize("M", [2, 5, 8, 9, 17, 32, 33])
 def test_small_batch_routes_agree(nf4, oracle, scratch, M):
-    """2..32 rows take the batched decode kernel (eight rows per launch), more rows the
-    dequantise + GEMM route: both must meet the bound against the oracle's forward."""
+    """2..32 rows take the batched decode kernel (one launch of 8, 16 or 32 row slots), more rows
+    the dequantise + GEMM route: both must meet the bound against the oracle's forward."""
     N, K = 272, 512
     w = make_weight(8100 + M, N, K)
     lin = _lin(nf4, w)
@@ -600,7 +600,11 @@ def test_small_batch_routes_agree(nf4, oracle, scratch, M):
 
 
 @pytest.mark.parametrize("N,K,nested,M", [(16, 64, True, 2), (100, 448, False, 3), (2560, 9728, True, 8),
-                                          (6144, 2560, True, 5), (33, 128, True, 7)])
+                                          (6144, 2560, True, 5), (33, 128, True, 7),
+                                          # two and four row blocks in one launch; ragged row counts;
+                                          # outputs long enough that row tiles are shared between CTAs
+                                          (2560, 9728, True, 16), (6144, 2560, True, 32), (100, 448, False, 13),
+                                          (5120, 5120, False, 27), (33, 128, True, 32), (19456, 2560, True, 24)])
 def test_batched_decode_rows_match_single_rows(nf4, scratch, N, K, nested, M):
     """Every row of a batched decode launch against the single-row kernel on the same row: the
     same dequantised operands and fp32 accumulation, different summation order across warps."""
@@ -617,7 +621,7 @@ def test_batched_decode_rows_match_single_rows(nf4, scratch, N, K, nested, M):
     assert np.abs(a - b).max() <= 1e-2 * np.abs(b).max() + 1e-6
 
 
-@pytest.mark.parametrize("M", [2, 8, 11])
+@pytest.mark.parametrize("M", [2, 8, 11, 16, 32])
 def test_batched_gate_up_swiglu(nf4, oracle, scratch, M):
     H, FF = 512, 1040
     g, u = make_weight(8601, FF, H), make_weight(8602, FF, H)
