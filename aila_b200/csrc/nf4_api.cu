@@ -329,6 +329,20 @@ AilaNf4Status ensure_weight(AilaNf4Scratch* sc, size_t bytes) {
 
 using nf4::ensure_counters;
 
+// Accumulation tiles of the K-sliced small-batch kernel: zero when allocated, and every launch
+// leaves them zero. Growing allocates and waits for the device (not capturable).
+AilaNf4Status ensure_rows_acc(AilaNf4Scratch* sc, size_t bytes) {
+    if (sc->rows_acc_bytes >= bytes) return AILA_NF4_OK;
+    if (sc->d_rows_acc) NF4_CUDA(cudaFree(sc->d_rows_acc));
+    sc->d_rows_acc = nullptr;
+    sc->rows_acc_bytes = 0;
+    NF4_CUDA(cudaMalloc(reinterpret_cast<void**>(&sc->d_rows_acc), bytes));
+    NF4_CUDA(cudaMemset(sc->d_rows_acc, 0, bytes));
+    NF4_CUDA(cudaDeviceSynchronize());
+    sc->rows_acc_bytes = bytes;
+    return AILA_NF4_OK;
+}
+
 AilaNf4Status ensure_io(void** buf, size_t* have, size_t need) {
     if (*have >= need) return AILA_NF4_OK;
     if (*buf) NF4_CUDA(cudaFree(*buf));
@@ -353,17 +367,32 @@ int decode_rows_max() {
     return v;
 }
 
+// The K-sliced kernel (x slice of all rows in shared memory) serves 9 .. 32 rows where it takes the
+// linear: up to eight rows the streaming kernel's batched form is faster (its x fragments from L2
+// cost less than the K-sliced kernel's accumulation in global memory).
+// AILA_NF4_ROWS_KERNEL=0 turns it off, =1 uses it from two rows on.
+bool use_rows_kernel(const AilaNf4Linear* l, int64_t ff_pair, int rows) {
+    static const int mode = [] {
+        const char* e = std::getenv("AILA_NF4_ROWS_KERNEL");
+        return (e && e[0] == '0') ? 0 : ((e && e[0] == '1') ? 1 : 2);
+    }();
+    if (mode == 0 || rows < 2 || (mode == 2 && rows <= 8)) return false;
+    return nf4::gemv_rows_supported(*l, ff_pair);
+}
+
 bool use_batched_decode(const AilaNf4Linear* l, const AilaNf4Scratch* sc, const void* x, int seq_len,
                   int64_t ff_pair) {
     if (seq_len < 2 || seq_len > decode_rows_max() || l->d_cache_bf16) return false;
     if (gemv_kernel_choice() == 1) return false;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (l->K * 2) % 16) return false;
-    return nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
+    return use_rows_kernel(l, ff_pair, seq_len) || nf4::gemv_stream_supported(*l, ff_pair, sc->sm_count);
 }
 
 // Rows one batched launch carries: 32 (four row blocks) where the kernel's shared-memory plan has
 // room for the larger accumulation tiles, else 8.
-int batched_rows_per_launch(const AilaNf4Linear* l, const AilaNf4Scratch* sc) {
+int batched_rows_per_launch(const AilaNf4Linear* l, const AilaNf4Scratch* sc, int64_t ff_pair, int seq_len) {
+    if (use_rows_kernel(l, ff_pair, seq_len)) return 32;
+    if (ff_pair > 0) return 8;
     return nf4::gemv_stream_supported(*l, 0, sc->sm_count, 4) ? 32 : 8;
 }
 
@@ -371,6 +400,14 @@ int batched_rows_per_launch(const AilaNf4Linear* l, const AilaNf4Scratch* sc) {
 AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void* x, void* y,
                          const void* residual, int64_t ff_pair, cudaStream_t s, int m_rows = 1,
                          const nf4::NormInput* norm = nullptr) {
+    if (m_rows > 1 && !norm && use_rows_kernel(l, ff_pair, m_rows) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        AilaNf4Status st = ensure_counters(sc, (size_t)l->RT);
+        if (st != AILA_NF4_OK) return st;
+        st = ensure_rows_acc(sc, nf4::gemv_rows_acc_bytes(*l));
+        if (st != AILA_NF4_OK) return st;
+        NF4_CUDA(nf4::launch_gemv_rows(*l, *sc, x, y, residual, ff_pair, s, m_rows));
+        return AILA_NF4_OK;
+    }
     const int choice = gemv_kernel_choice();
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     // One operation per launch: the ring kernel starts faster than the chained kernel (which pays
@@ -670,6 +707,7 @@ AILA_NF4_API void aila_nf4_scratch_destroy(AilaNf4Scratch* sc) {
     if (!sc) return;
     DeviceGuard guard(sc->device);
     cudaFree(sc->d_partials);
+    cudaFree(sc->d_rows_acc);
     cudaFree(sc->d_counters);
     cudaFree(sc->d_status);
     cudaFree(sc->d_weight);
@@ -734,7 +772,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward(const AilaNf4Linear* l, AilaNf4Scrat
         const char* xb = static_cast<const char*>(x);
         char* yb = static_cast<char*>(y);
         const char* rb = static_cast<const char*>(residual);
-        const int step = batched_rows_per_launch(l, sc);
+        const int step = batched_rows_per_launch(l, sc, 0, seq_len);
         for (int m = 0; m < seq_len; m += step) {
             const int rows = seq_len - m < step ? seq_len - m : step;
             st = run_decode(l, sc, xb + (size_t)m * l->K * 2, yb + (size_t)m * l->N * 2,
@@ -768,7 +806,8 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (seq_len == 1) return run_decode(l, sc, x, out, nullptr, ff_dim, s);
-    if (seq_len > 8 && use_batched_decode(l, sc, x, seq_len, 0) && batched_rows_per_launch(l, sc) > 8) {
+    if (seq_len > 8 && !use_rows_kernel(l, ff_dim, seq_len) && use_batched_decode(l, sc, x, seq_len, 0) &&
+        batched_rows_per_launch(l, sc, 0, seq_len) > 8) {
         // more than eight rows: the unpaired batched kernel over the fused rows (one pass over the
         // weights for up to 32 rows) into a bf16 gate|up buffer, then the row-wise activation -
         // the arithmetic of the reference's seq_len > 1 route (bf16 gate_up, then ops::swiglu)
@@ -787,8 +826,9 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
     if (use_batched_decode(l, sc, x, seq_len, ff_dim)) {
         const char* xb = static_cast<const char*>(x);
         char* ob = static_cast<char*>(out);
-        for (int m = 0; m < seq_len; m += 8) {
-            const int rows = seq_len - m < 8 ? seq_len - m : 8;
+        const int step = batched_rows_per_launch(l, sc, ff_dim, seq_len);
+        for (int m = 0; m < seq_len; m += step) {
+            const int rows = seq_len - m < step ? seq_len - m : step;
             st = run_decode(l, sc, xb + (size_t)m * l->K * 2, ob + (size_t)m * ff_dim * 2, nullptr,
                             ff_dim, s, rows);
             if (st != AILA_NF4_OK) return st;

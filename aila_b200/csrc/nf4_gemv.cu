@@ -1297,6 +1297,430 @@ struct StaticScratchHost {
 StaticScratchHost g_static_host[64];
 std::mutex g_static_mutex;
 
+
+// ------------------------------------------------------------------------------------------
+// Small batches (2 .. 32 rows of x) with the x slice in shared memory: gemv_rows_kernel.
+//
+// The streaming kernel's batched form fetches the x fragments of every work item from L2, 8 bytes
+// of L2 traffic per weight byte at 32 rows. Here the work is cut along K instead: a work item is
+// (K slice s of 512 columns, row tile rt), the items are ordered slice-major, every CTA takes a
+// contiguous range of them and keeps the x slice of ALL rows (8 * RB rows x 1 KB) in shared memory
+// while its warps run through the row tiles of that slice. Each warp owns its items (round-robin
+// inside the CTA's part of a slice), fetches their units itself with bulk-async copies into a
+// private ring of three 4-unit chunks, and adds the finished 16 x (8 RB) partial tile into an fp32
+// accumulation tile in global memory with vector reductions. A counter per row tile (per gate/up
+// pair) counts the finished items; the warp that completes the count reads the tile back,
+// applies the epilogue (residual, or SiLU(gate) * up on the bf16-rounded halves as the reference's
+// seq_len > 1 route does), writes y and leaves tile and counter zero for the next launch. Nothing
+// waits on another CTA. Column order of the accumulation tile: batch row m sits in column m; the
+// x row fed to tensor-core column g of block rb is m = (g/2) * 2RB + 2 rb + g%2, so that a lane's
+// 2 RB results are adjacent in memory.
+// ------------------------------------------------------------------------------------------
+constexpr int kRowsWarps = 16;
+constexpr int kRowsThreads = kRowsWarps * 32;
+constexpr int kRowsSliceUnits = 8;   // 512 columns of K per slice
+constexpr int kRowsChunkUnits = 4;   // units per bulk copy
+constexpr int kRowsSlots = 3;        // chunks in flight per warp
+constexpr int kRowsSmemBytes = 227 * 1024;
+
+struct RowsParams {
+    const uint8_t* units;
+    const float* qmap;
+    const float* nmap;         // [256] second-level code book (8-bit absmax codes)
+    const float4* row_scales;  // [n_rows] {lo, hi, cross, offset} (8-bit absmax codes)
+    const uint16_t* x;         // [m_rows][K]
+    uint16_t* y;               // [m_rows][n_out]
+    const uint16_t* residual;  // [m_rows][n_out] or null (unpaired only)
+    float* acc;                // [n_tiles * 16][8 * RB], zero on entry and on exit
+    int* counters;             // [n_tiles], zero on entry and on exit
+    int* status;
+    long long spin_limit;
+    int K, KU, n_slices, n_tiles, n_rows, n_out, m_rows;
+    int pair_offset;           // row tiles between a gate tile and its up tile; 0 = unpaired
+    int total_items, slice_q, slice_r;
+    uint32_t div_g_m;
+    int div_g_s;
+    int smem_bytes;
+};
+
+__device__ __forceinline__ int rows_slice_begin(const RowsParams& p, int c) {
+    return p.slice_q * c + fast_div(p.slice_r * c, p.div_g_m, p.div_g_s);
+}
+
+template <int N>
+__device__ __forceinline__ void red_add_f32(float* dst, const float* v);
+template <>
+__device__ __forceinline__ void red_add_f32<2>(float* dst, const float* v) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1,%2};" ::"l"(dst), "f"(v[0]), "f"(v[1]) : "memory");
+}
+template <>
+__device__ __forceinline__ void red_add_f32<4>(float* dst, const float* v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
+                 : "memory");
+}
+template <>
+__device__ __forceinline__ void red_add_f32<8>(float* dst, const float* v) {
+    red_add_f32<4>(dst, v);
+    red_add_f32<4>(dst + 4, v + 4);
+}
+
+template <int KIND, int RB>
+__global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const RowsParams p) {
+    constexpr int W = kRowsWarps;
+    constexpr int ST = (KIND == kAbsmaxCodes) ? kUnitStrideCodes : kUnitStrideF32;
+    constexpr int CH = kRowsChunkUnits * ST;
+    constexpr int COLS = 8 * RB;          // batch columns of the accumulation tile
+    constexpr int XS_BYTES = COLS * 1024; // x slice: COLS rows of 512 bf16
+
+    // ---- shared-memory map (absolute shared-window addresses) ----
+    // [base, 64 KB): barriers, code books, x slice, ring chunks; [64 KB, 128 KB): lookup table;
+    // [128 KB, ...): ring chunks
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t a_bar = (base + 15u) & ~15u;  // full[W * kRowsSlots]
+    static_assert(W * kRowsSlots * 8 <= 400, "barrier block");
+    const uint32_t a_nmap = a_bar + 400;
+    const uint32_t a_ptab = a_nmap + 1024;
+    const uint32_t a_xs = (a_ptab + 1024 + 1023u) & ~1023u;
+    const uint32_t a_ring_a = a_xs + XS_BYTES;
+    const uint32_t a_lut = 65536u;
+    const uint32_t a_ring_b = 131072u;
+    const int n_b = (int)((base + (uint32_t)p.smem_bytes - a_ring_b) / CH);  // chunks behind the table
+    auto chunk_addr = [&](int j) {
+        return j < n_b ? a_ring_b + (uint32_t)j * CH : a_ring_a + (uint32_t)(j - n_b) * CH;
+    };
+    uint8_t* gen = smem_raw - base;  // generic pointer to shared-window address 0
+    uint64_t* full = reinterpret_cast<uint64_t*>(gen + a_bar);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int gq = lane >> 2;
+    const int t = lane & 3;
+    const int G = gridDim.x;
+    const int c = blockIdx.x;
+    const int RT = p.n_tiles;
+    const int I0 = rows_slice_begin(p, c);
+    const int I1 = rows_slice_begin(p, c + 1);
+
+    {
+        const int need_a = W * kRowsSlots - n_b;  // chunks that must fit below the table
+        if (base > 2048u || p.smem_bytes < 131072 || (need_a > 0 && a_ring_a + (uint32_t)need_a * CH > 65536u) ||
+            a_ring_a > 65536u || I1 <= I0 || G <= 0) {
+            if (tid == 0 && I1 > I0) atomicExch(p.status, kStatusBadArgument);
+            return;
+        }
+    }
+
+    // let a dependent launch begin its own set-up; it waits for our completion before it reads x
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // ---- tables: byte value -> bf16 pair, second-level code book; barriers ----
+    if (tid < 256) {
+        const float q_hi = __ldg(p.qmap + (tid >> 4)), q_lo = __ldg(p.qmap + (tid & 15));
+        const uint32_t pr = (uint32_t)f32_to_bf16_bits(q_hi) | ((uint32_t)f32_to_bf16_bits(q_lo) << 16);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(a_ptab + 4u * tid), "r"(pr) : "memory");
+        if (KIND == kAbsmaxCodes) sts_f32(a_nmap + 4u * tid, __ldg(p.nmap + tid));
+    }
+    if (tid < W * kRowsSlots) mbar_init(&full[tid], 1);
+    mbar_fence_init();
+    __syncthreads();
+    {
+        // the bank-private table: rows of 128 bytes (one word per lane) on a 256-byte pitch
+        static_assert(64 % W == 0, "table rows per warp");
+#pragma unroll
+        for (int i = 0; i < 64 / W; ++i) {
+            const int b = (warp + i * W) * 4 + (lane >> 3);
+            const uint32_t pv = lds_u32(a_ptab + 4u * (uint32_t)b);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(a_lut + (uint32_t)b * 256u +
+                                                                         (uint32_t)(lane & 7) * 16u),
+                         "r"(pv)
+                         : "memory");
+        }
+    }
+    // (the table is first read after the CTA-wide barrier that follows the first x slice)
+
+    // ---- this warp's sequence of chunks: its items slice by slice, two chunks per item ----
+    const int s_first = I0 / RT;  // (host guarantees the quotient is small: plain division)
+    const int s_last = (I1 - 1) / RT;
+    struct It {
+        int s, I, h;
+    };
+    auto seg_lo = [&](int s) { return max(I0, s * RT); };
+    auto seg_hi = [&](int s) { return min(I1, (s + 1) * RT); };
+    auto normalize = [&](It& it) {
+        while (it.s <= s_last && it.I >= seg_hi(it.s)) {
+            ++it.s;
+            if (it.s <= s_last) it.I = seg_lo(it.s) + warp;
+        }
+    };
+    auto slice_units = [&](int s) { return min(kRowsSliceUnits, p.KU - s * kRowsSliceUnits); };
+    auto advance = [&](It& it) {
+        if (it.h == 0 && slice_units(it.s) > kRowsChunkUnits) {
+            it.h = 1;
+        } else {
+            it.h = 0;
+            it.I += W;
+            normalize(it);
+        }
+    };
+    auto chunk_units = [&](const It& it) { return min(kRowsChunkUnits, slice_units(it.s) - it.h * kRowsChunkUnits); };
+    auto issue = [&](const It& it, int k) {  // one lane
+        const int rt = it.I - it.s * RT;
+        const size_t unit0 = (size_t)rt * p.KU + (size_t)(it.s * kRowsSliceUnits + it.h * kRowsChunkUnits);
+        const uint32_t bytes = (uint32_t)chunk_units(it) * ST;
+        const int j = warp * kRowsSlots + (k % kRowsSlots);
+        mbar_expect_tx(&full[j], bytes);
+        bulk_g2s(gen + chunk_addr(j), p.units + unit0 * ST, bytes, &full[j]);
+    };
+    It prod, cons;
+    prod.s = s_first;
+    prod.I = seg_lo(s_first) + warp;
+    prod.h = 0;
+    normalize(prod);
+    cons = prod;
+    int kp = 0, kc = 0;
+    for (; kp < kRowsSlots && prod.s <= s_last; ++kp) {
+        if (lane == 0) issue(prod, kp);
+        advance(prod);
+    }
+
+    const uint32_t lane_base = a_lut + ((uint32_t)lane << 2);
+    const uint32_t w_off = (uint32_t)(gq * 32 + 8 * t);
+    const int drow = gq + 8 * (t & 1);  // the row whose absmax this lane decodes (8-bit codes)
+    // x rows of this lane's tensor-core column in every block, and the swizzle of their 32-byte chunks
+    const uint32_t x_swz = (uint32_t)(gq >> 1);
+    const uint32_t x_row0 = a_xs + (uint32_t)((gq >> 1) * 2 * RB + (gq & 1)) * 1024u + 8u * (uint32_t)t;
+
+    float acc[RB][4];
+    float4 rs = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    bool failed = false;
+
+    // ---- epilogue of one row tile (or gate/up pair of tiles) by the warp that completed it ----
+    auto finalize = [&](int ctr) {
+        __threadfence();
+        constexpr int GR = 32 / COLS;  // lane groups: 1, 2, 4
+        constexpr int R = 16 / GR;     // rows of the tile per lane: 16, 8, 4
+        const int m = lane % COLS, grp = lane / COLS;
+        const int n0 = ctr * kTileRows + grp * R;
+        float* tg = p.acc + ((size_t)ctr * kTileRows + grp * R) * COLS + m;
+        float* tu = tg + (size_t)p.pair_offset * kTileRows * COLS;
+        float vg[R], vu[R];
+#pragma unroll
+        for (int i = 0; i < R; ++i) vg[i] = __ldcg(tg + i * COLS);
+        if (p.pair_offset > 0) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) vu[i] = __ldcg(tu + i * COLS);
+        }
+#pragma unroll
+        for (int i = 0; i < R; ++i) __stcg(tg + i * COLS, 0.0f);
+        if (p.pair_offset > 0) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) __stcg(tu + i * COLS, 0.0f);
+        }
+        if (lane == 0) p.counters[ctr] = 0;
+        if (m >= p.m_rows) return;
+        uint16_t o[R];
+        const bool whole = (p.n_out % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);  // tile inside the output and rows aligned for vector access
+        const size_t yo = (size_t)m * p.n_out + n0;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            float v = vg[i];
+            if (p.pair_offset > 0) {
+                const float gt = bf16_bits_to_f32(f32_to_bf16_bits(vg[i]));
+                const float up = bf16_bits_to_f32(f32_to_bf16_bits(vu[i]));
+                v = __fdividef(gt, 1.0f + __expf(-gt)) * up;
+            } else if (p.residual && n0 + i < p.n_out) {
+                v += bf16_bits_to_f32(__ldcg(p.residual + yo + i));
+            }
+            o[i] = f32_to_bf16_bits(v);
+        }
+        if (whole) {
+            if constexpr (R == 4) {
+                *reinterpret_cast<uint2*>(p.y + yo) =
+                    make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
+            } else {
+#pragma unroll
+                for (int q = 0; q < R / 8; ++q)
+                    *reinterpret_cast<uint4*>(p.y + yo + 8 * q) =
+                        make_uint4((uint32_t)o[8 * q] | ((uint32_t)o[8 * q + 1] << 16),
+                                   (uint32_t)o[8 * q + 2] | ((uint32_t)o[8 * q + 3] << 16),
+                                   (uint32_t)o[8 * q + 4] | ((uint32_t)o[8 * q + 5] << 16),
+                                   (uint32_t)o[8 * q + 6] | ((uint32_t)o[8 * q + 7] << 16));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+                if (n0 + i < p.n_out) p.y[yo + i] = o[i];
+        }
+    };
+
+    // Everything above touched only this launch's shared memory and data that no kernel writes
+    // (weights, code books, row scales). x, the accumulation tiles and the counters belong to the
+    // stream's order: wait for the kernels before this one.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    for (int s = s_first; s <= s_last; ++s) {
+        // ---- the x slice of every row: 16-byte pieces, 32-byte chunks swizzled by the row group ----
+        if (s != s_first) __syncthreads();  // every warp is done with the previous slice
+        {
+            const int k0 = s * kRowsSliceUnits * kUnitK;
+#pragma unroll
+            for (int i = 0; i < COLS * 64 / kRowsThreads; ++i) {
+                const int piece = tid + i * kRowsThreads;
+                const int m = piece >> 6, q = piece & 63;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (m < p.m_rows && k0 + q * 8 < p.K)
+                    v = __ldcg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + k0 + q * 8));
+                const uint32_t swz = (uint32_t)(m / (2 * RB)) & 3u;
+                const uint32_t dst = a_xs + (uint32_t)m * 1024u + ((((uint32_t)q >> 1) ^ swz) << 5) + (((uint32_t)q & 1u) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                             : "memory");
+            }
+        }
+        __syncthreads();
+
+        while (cons.s == s) {
+            const int rt = cons.I - s * RT;
+            if (cons.h == 0) {
+#pragma unroll
+                for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[rb][e] = 0.0f;
+                if (KIND == kAbsmaxCodes) rs = __ldg(p.row_scales + min(rt * kTileRows + drow, p.n_rows - 1));
+            }
+            const int j = warp * kRowsSlots + (kc % kRowsSlots);
+            if (!mbar_wait_bounded(&full[j], (uint32_t)((kc / kRowsSlots) & 1), failed ? 1000000LL : p.spin_limit)) {
+                if (!failed) atomicExch(p.status, kStatusTimeoutFull);
+                failed = true;
+            }
+            const int nu = chunk_units(cons);
+            const uint32_t ca = chunk_addr(j);
+            if (!failed) {
+#pragma unroll 1
+                for (int u = 0; u < nu; ++u) {
+                    const uint32_t ua = ca + (uint32_t)u * ST;
+                    const int ul = cons.h * kRowsChunkUnits + u;  // unit inside the slice
+                    const int kb = s * kRowsSliceUnits + ul;
+                    // x fragments of every block: k = 64 kb + 16 i + 4 t + {0..3}, i = 0..3
+                    uint2 xb[RB][4];
+#pragma unroll
+                    for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            xb[rb][i] = lds_v2(x_row0 + (uint32_t)rb * 2048u + ((((uint32_t)(ul * 4 + i)) ^ x_swz) << 5));
+                    float am0, am1;
+                    if (KIND == kAbsmaxCodes) {
+                        const unsigned code = lds_u8(ua + kUnitNibbleBytes + drow);
+                        const float scale = kb >= __float_as_int(rs.z) ? rs.y : rs.x;
+                        const float am = __fadd_rn(__fmul_rn(lds_f32(a_nmap + 4u * code), scale), rs.w);
+                        am0 = __shfl_sync(0xffffffffu, am, lane & ~3);
+                        am1 = __shfl_sync(0xffffffffu, am, (lane & ~3) | 1);
+                    } else {
+                        am0 = lds_f32(ua + kUnitNibbleBytes + 4u * gq);
+                        am1 = lds_f32(ua + kUnitNibbleBytes + 4u * (gq + 8));
+                    }
+                    const uint2 l = lds_v2(ua + w_off), uu = lds_v2(ua + w_off + 256u);
+                    uint32_t a[16];
+                    a[0] = lut_pair<0>(l.x, lane_base);  a[1] = lut_pair<0>(uu.x, lane_base);
+                    a[2] = lut_pair<1>(l.x, lane_base);  a[3] = lut_pair<1>(uu.x, lane_base);
+                    a[4] = lut_pair<2>(l.x, lane_base);  a[5] = lut_pair<2>(uu.x, lane_base);
+                    a[6] = lut_pair<3>(l.x, lane_base);  a[7] = lut_pair<3>(uu.x, lane_base);
+                    a[8] = lut_pair<0>(l.y, lane_base);  a[9] = lut_pair<0>(uu.y, lane_base);
+                    a[10] = lut_pair<1>(l.y, lane_base); a[11] = lut_pair<1>(uu.y, lane_base);
+                    a[12] = lut_pair<2>(l.y, lane_base); a[13] = lut_pair<2>(uu.y, lane_base);
+                    a[14] = lut_pair<3>(l.y, lane_base); a[15] = lut_pair<3>(uu.y, lane_base);
+#pragma unroll
+                    for (int rb = 0; rb < RB; ++rb) {
+                        float c0[4], c1[4];
+                        mma_bf16_16816_init(c0, a[0], a[1], a[2], a[3], xb[rb][0].x, xb[rb][0].y);
+                        mma_bf16_16816_init(c1, a[4], a[5], a[6], a[7], xb[rb][1].x, xb[rb][1].y);
+                        mma_bf16_16816(c0, a[8], a[9], a[10], a[11], xb[rb][2].x, xb[rb][2].y);
+                        mma_bf16_16816(c1, a[12], a[13], a[14], a[15], xb[rb][3].x, xb[rb][3].y);
+                        acc[rb][0] = fmaf(am0, c0[0] + c1[0], acc[rb][0]);
+                        acc[rb][1] = fmaf(am0, c0[1] + c1[1], acc[rb][1]);
+                        acc[rb][2] = fmaf(am1, c0[2] + c1[2], acc[rb][2]);
+                        acc[rb][3] = fmaf(am1, c0[3] + c1[3], acc[rb][3]);
+                    }
+                }
+            }
+            // the chunk's shared memory is free (every lane's loads have fed the arithmetic above):
+            // refill the slot with this warp's next chunk
+            __syncwarp();
+            if (prod.s <= s_last) {
+                if (lane == 0 && !failed) issue(prod, kp);
+                if (failed) prod.s = s_last + 1;  // stop issuing
+                else {
+                    ++kp;
+                    advance(prod);
+                }
+            }
+            ++kc;
+            const bool last_chunk = !(cons.h == 0 && slice_units(s) > kRowsChunkUnits);
+            if (last_chunk && !failed) {
+                // ---- the item's partial tile into the accumulation tile, then the count ----
+                float lo[2 * RB], hi[2 * RB];
+#pragma unroll
+                for (int rb = 0; rb < RB; ++rb) {
+                    lo[2 * rb] = acc[rb][0];
+                    lo[2 * rb + 1] = acc[rb][1];
+                    hi[2 * rb] = acc[rb][2];
+                    hi[2 * rb + 1] = acc[rb][3];
+                }
+                float* dst = p.acc + ((size_t)rt * kTileRows + gq) * COLS + t * 2 * RB;
+                red_add_f32<2 * RB>(dst, lo);
+                red_add_f32<2 * RB>(dst + 8 * COLS, hi);
+                __threadfence();
+                __syncwarp();
+                const int ctr = (p.pair_offset > 0 && rt >= p.pair_offset) ? rt - p.pair_offset : rt;
+                const int target = p.n_slices * (p.pair_offset > 0 ? 2 : 1);
+                int old = 0;
+                if (lane == 0)
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;"
+                                 : "=r"(old) : "l"(p.counters + ctr), "r"(1) : "memory");
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == target - 1) finalize(ctr);
+            }
+            advance(cons);
+        }
+    }
+    // never leave with copies still landing in this CTA's shared memory (only after a failure can
+    // issued chunks be unconsumed here)
+    if (failed) {
+        for (; kc < kp; ++kc)
+            mbar_wait_bounded(&full[warp * kRowsSlots + (kc % kRowsSlots)], (uint32_t)((kc / kRowsSlots) & 1), 1000000LL);
+    }
+}
+
+template <int KIND, int RB>
+cudaError_t launch_rows_t(const RowsParams& p, int grid, cudaStream_t s) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_rows_kernel<KIND, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kRowsSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    // Programmatic dependent launch, as for the streaming kernel: table build, barrier set-up and the
+    // first weight copies overlap the previous kernel's tail. Disabled with AILA_NF4_PDL=0.
+    static const bool use_pdl = [] {
+        const char* e = std::getenv("AILA_NF4_PDL");
+        return !(e && e[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kRowsThreads);
+    cfg.dynamicSmemBytes = (size_t)kRowsSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemv_rows_kernel<KIND, RB>, p);
+}
+
 }  // namespace
 
 cudaError_t launch_gemv_simple(const AilaNf4Linear& w, const void* x, void* y,
@@ -1417,6 +1841,61 @@ cudaError_t launch_gemv_stream(const AilaNf4Linear& w, AilaNf4Scratch& scratch, 
     return paired ? launch_stream_t<kAbsmaxF32, true, 0>(p, pl.grid, pl.smem, s)
                   : launch_stream_t<kAbsmaxF32, false, 0>(p, pl.grid, pl.smem, s);
 }
+
+bool gemv_rows_supported(const AilaNf4Linear& w, int64_t ff_pair) {
+    if (w.absmax_kind == kAbsmaxCodes && !w.d_row_scales) return false;
+    if (ff_pair > 0 && (ff_pair % kTileRows != 0 || w.N != 2 * ff_pair)) return false;
+    const long long total = (long long)((w.KU + kRowsSliceUnits - 1) / kRowsSliceUnits) * w.RT;
+    return total > 0 && total < (1ll << 30);
+}
+
+size_t gemv_rows_acc_bytes(const AilaNf4Linear& w) { return (size_t)w.RT * kTileRows * 32 * sizeof(float); }
+
+// 2 .. 32 rows of x through the K-sliced kernel. scratch.d_rows_acc (gemv_rows_acc_bytes, zero) and
+// scratch.d_counters (one per row tile, zero) must be in place; both are zero again afterwards.
+cudaError_t launch_gemv_rows(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x, void* y,
+                             const void* residual, int64_t ff_pair, cudaStream_t s, int m_rows) {
+    if (m_rows < 1 || m_rows > 32 || !gemv_rows_supported(w, ff_pair) || (ff_pair > 0 && residual))
+        return cudaErrorInvalidValue;
+    if (reinterpret_cast<uintptr_t>(x) & 15) return cudaErrorInvalidValue;
+    RowsParams p;
+    p.units = w.d_units;
+    p.qmap = w.d_qmap;
+    const ScaleParams sp = w.scale_params();
+    p.nmap = sp.nmap;
+    p.row_scales = static_cast<const float4*>(w.d_row_scales);
+    p.x = static_cast<const uint16_t*>(x);
+    p.y = static_cast<uint16_t*>(y);
+    p.residual = static_cast<const uint16_t*>(residual);
+    p.acc = scratch.d_rows_acc;
+    p.counters = scratch.d_counters;
+    p.status = scratch.d_status;
+    p.spin_limit = scratch.wait_limit_cycles;
+    p.K = (int)w.K;
+    p.KU = w.KU;
+    p.n_slices = (w.KU + kRowsSliceUnits - 1) / kRowsSliceUnits;
+    p.n_tiles = w.RT;
+    p.n_rows = (int)w.N;
+    p.n_out = ff_pair > 0 ? (int)ff_pair : (int)w.N;
+    p.m_rows = m_rows;
+    p.pair_offset = ff_pair > 0 ? (int)(ff_pair / kTileRows) : 0;
+    p.total_items = p.n_slices * p.n_tiles;
+    const int grid = p.total_items < scratch.sm_count ? p.total_items : scratch.sm_count;
+    p.slice_q = p.total_items / grid;
+    p.slice_r = p.total_items % grid;
+    make_fast_div((uint32_t)grid, &p.div_g_m, &p.div_g_s);
+    p.smem_bytes = kRowsSmemBytes;
+    const int rb = m_rows <= 8 ? 1 : (m_rows <= 16 ? 2 : 4);
+    if (w.absmax_kind == kAbsmaxCodes) {
+        if (rb == 1) return launch_rows_t<kAbsmaxCodes, 1>(p, grid, s);
+        if (rb == 2) return launch_rows_t<kAbsmaxCodes, 2>(p, grid, s);
+        return launch_rows_t<kAbsmaxCodes, 4>(p, grid, s);
+    }
+    if (rb == 1) return launch_rows_t<kAbsmaxF32, 1>(p, grid, s);
+    if (rb == 2) return launch_rows_t<kAbsmaxF32, 2>(p, grid, s);
+    return launch_rows_t<kAbsmaxF32, 4>(p, grid, s);
+}
+
 
 // Decode GEMV on the static work space: no allocation of any kind. The first call on a device
 // resolves the device address of the array (the array's name is only a host-side stand-in for

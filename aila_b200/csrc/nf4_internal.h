@@ -48,6 +48,8 @@ struct AilaNf4Scratch {
     // arrival counters (counters are zero between launches; the last arriver resets them).
     float* d_partials = nullptr;
     size_t partials_floats = 0;
+    float* d_rows_acc = nullptr;  // accumulation tiles of the K-sliced small-batch kernel (kept zero)
+    size_t rows_acc_bytes = 0;
     int* d_counters = nullptr;
     size_t counters_ints = 0;
     int* d_status = nullptr;  // device status word written by bounded waits
@@ -148,6 +150,12 @@ int gemv_stream_grid(const AilaNf4Linear& w, int64_t ff_pair, int sm_count);  //
 AilaNf4Status launch_gemv_stream_static(const AilaNf4Linear& w, const void* x, void* y,
                                         const void* residual, cudaStream_t s);
 AilaNf4Status check_gemv_stream_static(cudaStream_t s);
+// K-sliced small-batch decode kernel (2 .. 32 rows, x slice in shared memory)
+bool gemv_rows_supported(const AilaNf4Linear& w, int64_t ff_pair);
+size_t gemv_rows_acc_bytes(const AilaNf4Linear& w);
+cudaError_t launch_gemv_rows(const AilaNf4Linear& w, AilaNf4Scratch& scratch, const void* x, void* y,
+                             const void* residual, int64_t ff_pair, cudaStream_t s, int m_rows);
+
 // Fills l.d_row_scales (N entries of 16 bytes, allocated by the caller).
 cudaError_t launch_row_scales(const AilaNf4Linear& l, cudaStream_t s);
 
