@@ -1488,12 +1488,15 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const RowsPa
     const uint32_t w_off = (uint32_t)(gq * 32 + 8 * t);
     const int drow = gq + 8 * (t & 1);  // the row whose absmax this lane decodes (8-bit codes)
     // x rows of this lane's tensor-core column in every block, and the swizzle of their 32-byte chunks
-    const uint32_t x_swz = (uint32_t)(gq >> 1);
+    // (a 64-bit shared load is served half a warp at a time: the four rows a half-warp touches must
+    // fall into four different 32-byte bank groups, hence the swizzle by gq % 4)
+    const uint32_t x_swz = (uint32_t)(gq & 3);
     const uint32_t x_row0 = a_xs + (uint32_t)((gq >> 1) * 2 * RB + (gq & 1)) * 1024u + 8u * (uint32_t)t;
 
     float acc[RB][4];
     float4 rs = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     bool failed = false;
+    int pending_ctr = -1;  // row tile whose count this warp still owes (its additions are in flight)
 
     // ---- epilogue of one row tile (or gate/up pair of tiles) by the warp that completed it ----
     auto finalize = [&](int ctr) {
@@ -1559,6 +1562,23 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const RowsPa
     // stream's order: wait for the kernels before this one.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    // Publishes the owed count: every lane's additions are ordered before it (fence, then the warp
+    // barrier, then one release/acquire increment); the warp that completes a tile finishes it.
+    auto count_pending = [&]() {
+        if (pending_ctr < 0) return;
+        const int ctr = pending_ctr;
+        pending_ctr = -1;
+        __threadfence();
+        __syncwarp();
+        const int target = p.n_slices * (p.pair_offset > 0 ? 2 : 1);
+        int old = 0;
+        if (lane == 0)
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;"
+                         : "=r"(old) : "l"(p.counters + ctr), "r"(1) : "memory");
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == target - 1) finalize(ctr);
+    };
+
     for (int s = s_first; s <= s_last; ++s) {
         // ---- the x slice of every row: 16-byte pieces, 32-byte chunks swizzled by the row group ----
         if (s != s_first) __syncthreads();  // every warp is done with the previous slice
@@ -1571,7 +1591,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const RowsPa
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
                 if (m < p.m_rows && k0 + q * 8 < p.K)
                     v = __ldcg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + k0 + q * 8));
-                const uint32_t swz = (uint32_t)(m / (2 * RB)) & 3u;
+                const uint32_t swz = ((((uint32_t)(m / (2 * RB))) & 1u) << 1) | ((uint32_t)m & 1u);
                 const uint32_t dst = a_xs + (uint32_t)m * 1024u + ((((uint32_t)q >> 1) ^ swz) << 5) + (((uint32_t)q & 1u) << 4);
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                              : "memory");
@@ -1666,23 +1686,18 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const RowsPa
                     hi[2 * rb] = acc[rb][2];
                     hi[2 * rb + 1] = acc[rb][3];
                 }
+                // The count of an item is published one item late: by then its additions have long
+                // been acknowledged, so the fence in front of the count does not wait for them.
+                count_pending();
                 float* dst = p.acc + ((size_t)rt * kTileRows + gq) * COLS + t * 2 * RB;
                 red_add_f32<2 * RB>(dst, lo);
                 red_add_f32<2 * RB>(dst + 8 * COLS, hi);
-                __threadfence();
-                __syncwarp();
-                const int ctr = (p.pair_offset > 0 && rt >= p.pair_offset) ? rt - p.pair_offset : rt;
-                const int target = p.n_slices * (p.pair_offset > 0 ? 2 : 1);
-                int old = 0;
-                if (lane == 0)
-                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;"
-                                 : "=r"(old) : "l"(p.counters + ctr), "r"(1) : "memory");
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == target - 1) finalize(ctr);
+                pending_ctr = (p.pair_offset > 0 && rt >= p.pair_offset) ? rt - p.pair_offset : rt;
             }
             advance(cons);
         }
     }
+    count_pending();
     // never leave with copies still landing in this CTA's shared memory (only after a failure can
     // issued chunks be unconsumed here)
     if (failed) {

@@ -19,7 +19,7 @@ streams from HBM), run as ONE chained launch (aila_nf4_chain_run) replayed from 
   cpu_baseline / --impl reference: the CPU restatement of the reference kernels on host cores
 
 Usage: python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-       python bench.py --profile-case chain|per_call|batch|dense|prefill   (small runs for ncu)
+       python bench.py --profile-case chain|per_call|batch|batch32|dense|prefill   (small runs for ncu)
 """
 from __future__ import annotations
 
@@ -646,10 +646,10 @@ def profile_case(case: str):
     up = synth.synth_linear(synth.seed_for(2, 0, "up"), FF, H)
     x = synth.gaussian_activation(2009, 1, H).to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    if case in ("chain", "per_call", "batch"):
+    if case in ("chain", "per_call", "batch", "batch32"):
         n = 8  # 8 x 25.7 MB = 206 MB of weights: larger than L2
         fused = [_fuse(_lin(_rolled(gate, 16 * i), 0), _lin(_rolled(up, 16 * i), 0)) for i in range(n)]
-        M = 8 if case == "batch" else 1
+        M = {"batch": 8, "batch32": 32}.get(case, 1)
         xm = synth.gaussian_activation(2109, M, H).to(dev)
         outs = [torch.empty(M, FF, dtype=torch.bfloat16, device=dev) for _ in range(n)]
         chain = DecodeChain(scratch, [dict(linear=f, ff_dim=FF, x=x, y=o) for f, o in zip(fused, outs)]) \
