@@ -747,6 +747,10 @@ AILA_NF4_API AilaNf4Status aila_nf4_scratch_check(AilaNf4Scratch* sc, void* stre
         NF4_CUDA(cudaMemsetAsync(sc->d_status, 0, sizeof(int), s));
         // the chained kernel's "somebody gave up" word: later launches start clean
         if (sc->d_chain_ctrl) NF4_CUDA(cudaMemsetAsync(sc->d_chain_ctrl + 2, 0, sizeof(unsigned), s));
+        // a launch that gave up may have left row-tile counters and accumulation tiles of the decode
+        // kernels half-way; every kernel expects to find them zero
+        if (sc->d_counters) NF4_CUDA(cudaMemsetAsync(sc->d_counters, 0, sc->counters_ints * sizeof(int), s));
+        if (sc->d_rows_acc) NF4_CUDA(cudaMemsetAsync(sc->d_rows_acc, 0, sc->rows_acc_bytes, s));
         NF4_CUDA(cudaStreamSynchronize(s));
         return nf4::fail(AILA_NF4_ERR_KERNEL_TIMEOUT,
                          "a bounded device-side wait expired (code " + std::to_string(host) + ")");
