@@ -1616,7 +1616,8 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_rows_kernel(const RowsPa
             const int nu = chunk_units(cons);
             const uint32_t ca = chunk_addr(j);
             if (!failed) {
-#pragma unroll 1
+                // (two units in flight per warp where the registers allow it)
+#pragma unroll(RB <= 2 ? 2 : 1)
                 for (int u = 0; u < nu; ++u) {
                     const uint32_t ua = ca + (uint32_t)u * ST;
                     const int ul = cons.h * kRowsChunkUnits + u;  // unit inside the slice
