@@ -85,6 +85,17 @@ def test_gate_up_swiglu(oracle, ff, K):
     assert np.array_equal(got, oracle.gemv_gate_up_swiglu(packed, gate.quant_map, am, x, ff, K, 64))
 
 
+def test_gate_up_swiglu_at_the_headline_size(oracle):
+    """cfg2 itself: 2 x [9728, 2560], the workload of the bench line."""
+    ff, K = 9728, 2560
+    gate, up = make_weight(1, ff, K), make_weight(2, ff, K)
+    packed = np.concatenate([np.asarray(gate.packed).reshape(-1), np.asarray(up.packed).reshape(-1)])
+    am = np.concatenate([oracle_absmax(oracle, gate), oracle_absmax(oracle, up)])
+    x = _x(3, 1, K)
+    assert np.array_equal(R.gate_up_swiglu(gate, up, x, ff),
+                          oracle.gemv_gate_up_swiglu(packed, gate.quant_map, am, x, ff, K, 64))
+
+
 def test_gate_up_swiglu_declines_other_ff():
     """out_features != 2 * ff_dim is the one shape condition under which the reference returns false
     (:772); the caller then runs forward and a separate activation."""
