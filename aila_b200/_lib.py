@@ -120,6 +120,7 @@ _SIGNATURES = {
     "aila_dense_linear_out_features": (ctypes.c_int64, [_VP]),
     "aila_dense_linear_forward": (ctypes.c_int, [_VP, _VP, _VP, _VP, ctypes.c_int, _VP, _VP]),
     "aila_argmax_bf16": (ctypes.c_int, [_VP, ctypes.c_int64, _VP, ctypes.c_int, _VP]),
+    "aila_argmax_bf16_shard": (ctypes.c_int, [_VP, ctypes.c_int64, ctypes.c_int64, _VP, ctypes.c_int, _VP]),
     "aila_st_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(_VP)]),
     "aila_st_close": (None, [_VP]),
     "aila_st_tensor_count": (ctypes.c_int64, [_VP]),

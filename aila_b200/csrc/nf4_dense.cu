@@ -117,51 +117,63 @@ dense_gemv_generic_kernel(const uint16_t* __restrict__ w, const uint16_t* __rest
     }
 }
 
-// Greedy token choice over bf16 logits: the largest value, the smallest index among equals
-// (NaN never wins). One block, like the reference's single work-group.
+// Greedy token choice over bf16 logits with the reference's result on ties (ops::argmax,
+// src/ops/SamplingOps.cpp:321-358): a work-group of 256 items, item l scans l, l + 256, ... and keeps
+// the first strict maximum above its start value -1e30, then a tree over the items keeps the LEFT
+// candidate when two are equal. Two equal candidates meet at the level of the lowest bit in which
+// their item numbers differ, and the one with a 0 there is on the left: among equal values the
+// winner has the smallest bit-reversed (index % 256), then the smallest index. `offset` is the
+// global index of logits[0] (a vocabulary shard orders by global indices and returns a local one).
+// NaN and values <= -1e30 never win; if nothing wins the result is 0.
+__device__ __forceinline__ unsigned long long argmax_tie_key(long long global_index) {
+    return ((unsigned long long)(__brev((unsigned)(global_index & 255)) >> 24) << 32) |
+           (unsigned long long)global_index;
+}
+constexpr unsigned long long kNoCandidate = ~0ull;
+
+__device__ __forceinline__ void argmax_merge(float& best, unsigned long long& best_k, float v,
+                                             unsigned long long k) {
+    if (k == kNoCandidate) return;
+    if (v > best || (v == best && k < best_k)) {
+        best = v;
+        best_k = k;
+    }
+}
+
 __global__ void __launch_bounds__(1024)
-argmax_bf16_kernel(const uint16_t* __restrict__ logits, long long n, int* __restrict__ out) {
+argmax_bf16_kernel(const uint16_t* __restrict__ logits, long long n, long long offset, int* __restrict__ out) {
     __shared__ float s_val[32];
-    __shared__ long long s_idx[32];
-    float best = -INFINITY;
-    long long best_i = 0x7fffffffffffffffll;
+    __shared__ unsigned long long s_key[32];
+    float best = -1e30f;
+    unsigned long long best_k = kNoCandidate;
     for (long long i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = bf16_bits_to_f32(__ldcg(logits + i));
-        if (v > best || (v == best && i < best_i)) {
-            best = v;
-            best_i = i;
-        }
+        if (v > -1e30f) argmax_merge(best, best_k, v, argmax_tie_key(offset + i));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const long long oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-        if (ov > best || (ov == best && oi < best_i)) {
-            best = ov;
-            best_i = oi;
-        }
+        const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best_k, o);
+        argmax_merge(best, best_k, ov, ok);
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) {
         s_val[warp] = best;
-        s_idx[warp] = best_i;
+        s_key[warp] = best_k;
     }
     __syncthreads();
     if (warp == 0) {
         const int nw = blockDim.x >> 5;
-        best = lane < nw ? s_val[lane] : -INFINITY;
-        best_i = lane < nw ? s_idx[lane] : 0x7fffffffffffffffll;
+        best = lane < nw ? s_val[lane] : -1e30f;
+        best_k = lane < nw ? s_key[lane] : kNoCandidate;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const long long oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best || (ov == best && oi < best_i)) {
-                best = ov;
-                best_i = oi;
-            }
+            const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best_k, o);
+            argmax_merge(best, best_k, ov, ok);
         }
-        // all values NaN or -inf: index 0, as a plain "first element wins" scan would give
-        if (lane == 0) *out = (int)(best_i == 0x7fffffffffffffffll ? 0 : best_i);
+        if (lane == 0)
+            *out = best_k == kNoCandidate ? 0 : (int)((long long)(best_k & 0xffffffffull) - offset);
     }
 }
 
@@ -305,16 +317,22 @@ AILA_NF4_API AilaNf4Status aila_dense_linear_forward(const AilaDenseLinear* l, A
     return AILA_NF4_OK;
 }
 
-AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, int32_t* d_result,
-                                            int device, void* stream) {
+AILA_NF4_API AilaNf4Status aila_argmax_bf16_shard(const void* logits_bf16, int64_t n, int64_t index_offset,
+                                                  int32_t* d_result, int device, void* stream) {
     if (!logits_bf16 || !d_result) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "NULL argument");
-    if (n <= 0 || n > 0x7fffffffll) return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "argmax: vocab size out of range");
+    if (n <= 0 || index_offset < 0 || n + index_offset > 0x7fffffffll)
+        return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "argmax: vocab size out of range");
     DenseDevGuard guard(device);
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
     nf4::argmax_bf16_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t*>(logits_bf16), (long long)n, d_result);
+        static_cast<const uint16_t*>(logits_bf16), (long long)n, (long long)index_offset, d_result);
     NF4_CUDA(cudaGetLastError());
     return AILA_NF4_OK;
+}
+
+AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, int32_t* d_result,
+                                            int device, void* stream) {
+    return aila_argmax_bf16_shard(logits_bf16, n, 0, d_result, device, stream);
 }
 
 AILA_NF4_API AilaNf4Status aila_add_rms_norm(const void* x_bf16, const void* add_bf16,

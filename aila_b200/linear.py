@@ -362,12 +362,15 @@ def add_rms_norm(x: torch.Tensor, add: torch.Tensor | None, weight: torch.Tensor
         normed_out.data_ptr(), x.device.index, _stream_ptr(x.device)))
 
 
-def argmax(logits: torch.Tensor, vocab_size: int, result: torch.Tensor) -> None:
+def argmax(logits: torch.Tensor, vocab_size: int, result: torch.Tensor, index_offset: int = 0) -> None:
     """ops::argmax (src/ops/SamplingOps.cpp:321-365): greedy token over bf16 logits, written to
-    the int32 device tensor ``result``."""
+    the int32 device tensor ``result``; equal values resolve as in the reference's reduction (the
+    smallest bit-reversed index % 256, then the smallest index). With ``index_offset`` the logits
+    are a vocabulary shard starting at that global index: ties are resolved on global indices and
+    the result is the local index."""
     assert logits.dtype == torch.bfloat16 and logits.is_cuda and result.dtype == torch.int32
-    _lib.check(_lib.load().aila_argmax_bf16(logits.data_ptr(), vocab_size, result.data_ptr(),
-                                            logits.device.index, _stream_ptr(logits.device)))
+    _lib.check(_lib.load().aila_argmax_bf16_shard(logits.data_ptr(), vocab_size, index_offset, result.data_ptr(),
+                                                  logits.device.index, _stream_ptr(logits.device)))
 
 
 class PeerBuffer:

@@ -121,9 +121,9 @@ class CudaBackend:
     def dense_forward(self, handle, x: torch.Tensor, out: torch.Tensor, seq_len: int) -> None:
         handle.forward(self.scratch, x, out, seq_len)
 
-    def argmax(self, logits: torch.Tensor, n: int, result: torch.Tensor) -> None:
+    def argmax(self, logits: torch.Tensor, n: int, result: torch.Tensor, index_offset: int = 0) -> None:
         from .linear import argmax
-        argmax(logits, n, result)
+        argmax(logits, n, result, index_offset)
 
     def make_chain(self, ops: list[dict], peers=None):
         from .linear import DecodeChain
@@ -199,13 +199,25 @@ def reduce_partials(part: torch.Tensor, group, fp32: bool) -> torch.Tensor:
     return part
 
 
+def reference_tie_key(index: torch.Tensor) -> torch.Tensor:
+    """Order in which ops::argmax (src/ops/SamplingOps.cpp:321-358) prefers equal logits: its tree over
+    256 work-items keeps the left candidate at every level, so the smallest bit-reversed
+    (index % 256) wins, then the smallest index. Smaller key = preferred. int64 in, int64 out."""
+    low = index & 255
+    rev = torch.zeros_like(low)
+    for bit in range(8):
+        rev = rev | (((low >> bit) & 1) << (7 - bit))
+    return (rev << 32) | index
+
+
 class VocabParallelHead:
     """The bf16 output head with its vocabulary rows split over the ranks, and the greedy token
     choice on top (reference: lm_head_.forward + ops::argmax, src/models/Qwen3Bnb4Backend.cpp:432-439,
     src/ops/SamplingOps.cpp:321-365; sharding is net-new). Each rank runs the dense GEMV on its row
     slice and the argmax over its slice of the logits; the ranks exchange one (value, index) pair
-    each instead of the logits, and every rank picks the same winner: the largest value, the
-    smallest index among equal values."""
+    each instead of the logits, and every rank picks the same winner: the largest value and, among
+    equal values, the index the reference's single reduction over the whole vocabulary would keep
+    (``reference_tie_key``)."""
 
     def __init__(self, weight: torch.Tensor, backend, group=None):
         self.rank, self.world = _group_info(group)
@@ -224,7 +236,7 @@ class VocabParallelHead:
         """x: [1, hidden] bf16 (replicated). Returns the chosen token as an int64 tensor of one
         element, the same on every rank."""
         self.backend.dense_forward(self.handle, x, self.logits, 1)
-        self.backend.argmax(self.logits, self.local, self._idx)
+        self.backend.argmax(self.logits, self.local, self._idx, self.rank * self.local)
         idx = self._idx.to(torch.int64)
         val = self.logits.reshape(-1)[idx].float()
         if self.world == 1:
@@ -233,9 +245,10 @@ class VocabParallelHead:
         pair = torch.stack([val.reshape(()), (idx.reshape(()) + self.rank * self.local).float()])
         got = [torch.empty_like(pair) for _ in range(self.world)]
         dist.all_gather(got, pair, group=self.group)
-        allp = torch.stack(got)                      # [world, 2], ranks own ascending index ranges
-        best = torch.argmax(allp[:, 0])              # first maximum = smallest rank = smallest index
-        return allp[best, 1].to(torch.int64).reshape(1)
+        allp = torch.stack(got)                      # [world, 2]: each rank's (value, global index)
+        keys = reference_tie_key(allp[:, 1].to(torch.int64))
+        keys = torch.where(allp[:, 0] == allp[:, 0].max(), keys, torch.full_like(keys, 1 << 62))
+        return allp[torch.argmin(keys), 1].to(torch.int64).reshape(1)
 
 
 class ShardedNf4Mlp:

@@ -371,10 +371,16 @@ AILA_NF4_API AilaNf4Status aila_dense_linear_forward(const AilaDenseLinear* line
                                                      void* y_bf16, int seq_len,
                                                      const void* residual_bf16, void* stream);
 /* Greedy token choice over n bf16 logits on the device (reference ops::argmax,
- * src/ops/SamplingOps.cpp:321-365): index of the largest value, the smallest index among equal
- * values, written to *d_result (device memory). */
+ * src/ops/SamplingOps.cpp:321-365): index of the largest value, written to *d_result (device
+ * memory). Equal values resolve as in the reference's 256-item reduction, which keeps the left
+ * candidate at every level: the smallest bit-reversed (index % 256) wins, then the smallest index.
+ * NaN and values <= -1e30 never win; if nothing wins the result is 0. */
 AILA_NF4_API AilaNf4Status aila_argmax_bf16(const void* logits_bf16, int64_t n, int32_t* d_result,
                                             int device, void* stream);
+/* The same over one shard of a vocabulary (no reference counterpart): logits[0] has the global
+ * index index_offset, ties are resolved on global indices, *d_result is the LOCAL index. */
+AILA_NF4_API AilaNf4Status aila_argmax_bf16_shard(const void* logits_bf16, int64_t n, int64_t index_offset,
+                                                  int32_t* d_result, int device, void* stream);
 
 /*
  * The operators of a decode step between the linears (the reference's callers of this path,

@@ -7,6 +7,7 @@ reading only (the reference has no golden vectors for them).
   embedding_lookup     src/ops/ElementwiseOps.cpp:14-27
   decode_prepare_qkv   src/ops/ElementwiseOps.cpp:105-215
   attention_decode     src/ops/AttentionOps.cpp:73-166 (baseline, whole window)
+  argmax               src/ops/SamplingOps.cpp:321-358
   decode_step          src/models/Qwen3Bnb4Backend.cpp:298-439 (seq_len == 1)
 
 bf16 tensors travel as uint16 bit patterns; arithmetic is fp32 with the reference's roundings.
@@ -77,6 +78,32 @@ def attention_decode(q_bits, k_cache, v_cache, n_heads, n_kv, head_dim, cached_l
         p = e / e.sum(dtype=np.float32)
         out[h] = to_bf16((p[:, None] * vv).sum(axis=0, dtype=np.float32))
     return out.reshape(-1)
+
+
+def argmax(logits_bits, index_offset: int = 0) -> int:
+    """ops::argmax as the reference's one work-group of 256 items computes it: item l scans
+    l, l + 256, ... and keeps the first strict maximum above -1e30 (index 0 if none), then a tree with
+    strides 128 .. 1 in which position l takes position l + stride only if that value is strictly
+    greater. With ``index_offset`` the logits are a shard starting at that global index; the scan
+    is over global indices and the local index is returned."""
+    v = to_f32(np.asarray(logits_bits, np.uint16).reshape(-1)).astype(np.float32)
+    n = v.size
+    vals = np.full(256, np.float32(-1e30), np.float32)
+    idx = np.zeros(256, np.int64)
+    g = np.arange(n, dtype=np.int64) + index_offset
+    for lid in range(256):
+        sel = np.nonzero((g & 255) == lid)[0]
+        for i in sel:                       # strict '>' keeps the first maximum; NaN never wins
+            if v[i] > vals[lid]:
+                vals[lid], idx[lid] = v[i], g[i]
+    stride = 128
+    while stride > 0:
+        for lid in range(stride):
+            if vals[lid + stride] > vals[lid]:
+                vals[lid], idx[lid] = vals[lid + stride], idx[lid + stride]
+        stride >>= 1
+    won = vals[0] > np.float32(-1e30)
+    return int(idx[0] - index_offset) if won else 0
 
 
 class Qwen3Reference:

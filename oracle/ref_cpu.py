@@ -197,3 +197,10 @@ def fused_gate_up_swiglu(gate_up_bf16, ff) -> np.ndarray:
     out = np.zeros(ff, np.uint16)
     _run("aila_ref_fused_gate_up_swiglu", _vp(gu), _vp(out), ctypes.c_int(ff))
     return out
+
+
+def argmax(logits_bf16) -> int:
+    l = _u16(logits_bf16).reshape(-1).copy()
+    out = np.zeros(1, np.int32)
+    _run("aila_ref_argmax", _vp(l), ctypes.c_int(l.size), _vp(out))
+    return int(out[0])

@@ -1,12 +1,13 @@
 // TEST INFRASTRUCTURE ONLY. C entry points around the REFERENCE's own operators that sit between
-// the NF4 linears of a decode step (src/ops/NormOps.cpp, src/ops/ElementwiseOps.cpp, compiled
+// the NF4 linears of a decode step (src/ops/NormOps.cpp, src/ops/ElementwiseOps.cpp, src/ops/SamplingOps.cpp, compiled
 // unmodified from where they lie against the stand-in headers in ref_shim/): host arrays in, host
 // arrays out. Used by the tests to check the CPU oracle's restatement; never by the product.
 //
 // Pinned through here: ops::rms_norm (NormOps.cpp:14-75), ops::fused_add_rms_norm (:141-275),
 // ops::embedding_lookup (ElementwiseOps.cpp:14-27), ops::decode_prepare_qkv (:105-215), ops::swiglu
-// (:223-245), ops::fused_gate_up_swiglu (:247-294). The stand-in fixes what SYCL leaves open:
-// reduce_over_group adds in a balanced tree, native::exp/cos/sin are libm's.
+// (:223-245), ops::fused_gate_up_swiglu (:247-294), ops::argmax (src/ops/SamplingOps.cpp:321-358).
+// The stand-in fixes what SYCL leaves open: reduce_over_group adds in a balanced tree,
+// native::exp/cos/sin are libm's.
 #include <cstdint>
 #include <cstdio>
 #include <stdexcept>
@@ -83,6 +84,16 @@ int aila_ref_decode_prepare_qkv(uint16_t* q, uint16_t* k, uint16_t* v, float* ro
         Tensor kc = bf16_view(k_cache, {kv_heads, max_seq_len, head_dim}),
                vc = bf16_view(v_cache, {kv_heads, max_seq_len, head_dim});
         ops::decode_prepare_qkv(ctx, tq, tk, tv, tf, qn, kn, kc, vc, start_pos, heads, kv_heads, head_dim, eps, theta);
+    });
+}
+
+// the token ops::argmax chooses over n bf16 logits
+int aila_ref_argmax(uint16_t* logits, int n, int32_t* out, char* err, int cap) {
+    return guarded(err, cap, [&]() {
+        Tensor l = bf16_view(logits, {n});
+        int result = -1;
+        ops::argmax(context(), l, n, &result);
+        *out = result;
     });
 }
 

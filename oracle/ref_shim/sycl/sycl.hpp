@@ -124,6 +124,8 @@ inline float rsqrt(float a) { return 1.0f / std::sqrt(a); }
 inline float fmax(float a, float b) { return std::fmax(a, b); }
 inline float fmin(float a, float b) { return std::fmin(a, b); }
 inline float fabs(float a) { return std::fabs(a); }
+inline bool isfinite(float a) { return std::isfinite(a); }
+inline bool isnan(float a) { return std::isnan(a); }
 inline float exp(float a) { return std::exp(a); }
 inline float log(float a) { return std::log(a); }
 inline float pow(float a, float b) { return std::pow(a, b); }
@@ -424,7 +426,10 @@ struct event {
     void wait() {}
 };
 struct device {};
-struct context {};
+struct context {
+    bool operator==(const context&) const { return true; }
+    bool operator!=(const context&) const { return false; }
+};
 struct default_selector_t {};
 inline constexpr default_selector_t default_selector_v{};
 namespace property {
@@ -468,5 +473,12 @@ inline void* malloc_device(size_t bytes, const queue&) { return std::calloc(byte
 inline void* malloc_host(size_t bytes, const queue&) { return std::calloc(bytes ? bytes : 1, 1); }
 inline void* malloc_shared(size_t bytes, const queue&) { return std::calloc(bytes ? bytes : 1, 1); }
 inline void free(void* p, const queue&) { std::free(p); }
+inline void free(void* p, const context&) { std::free(p); }
+template <typename T>
+inline T* malloc_device(size_t count, const queue& q) { return static_cast<T*>(malloc_device(count * sizeof(T), q)); }
+template <typename T>
+inline T* malloc_host(size_t count, const queue& q) { return static_cast<T*>(malloc_host(count * sizeof(T), q)); }
+template <typename T>
+inline T* malloc_shared(size_t count, const queue& q) { return static_cast<T*>(malloc_shared(count * sizeof(T), q)); }
 
 }  // namespace sycl

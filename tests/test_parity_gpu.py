@@ -569,17 +569,42 @@ def test_dense_linear_errors(nf4, scratch):
 
 
 def test_argmax_bf16(nf4):
+    """The greedy choice against the oracle's restatement of ops::argmax (itself held against the
+    reference's kernel): random logits, crafted ties (the reference's tree keeps the left candidate,
+    so equal maxima resolve by bit-reversed index % 256, not by index), nothing above the start value,
+    and vocabulary shards whose local result must be the global one."""
+    from oracle import backend_numpy as B
     g = torch.Generator().manual_seed(5)
+    out = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+
+    def run(logits, offset=0):
+        nf4.argmax(logits.cuda(), logits.numel(), out, offset)
+        return int(out.item())
+
     for n in (1, 7, 1024, 151936):
         logits = torch.randn(n, generator=g).to(torch.bfloat16)
         if n > 100:
             logits[n // 3] = 9.0
-            logits[n // 2] = 9.0  # a tie: the smaller index wins
-        out = torch.full((1,), -1, dtype=torch.int32, device="cuda")
-        nf4.argmax(logits.cuda(), n, out)
-        f = logits.float()
-        want = int(torch.nonzero(f == f.max())[0])
-        assert int(out.item()) == want
+            logits[n // 2] = 9.0
+        assert run(logits) == B.argmax(bf16_bits(logits))
+    for tied in ([2, 257], [1, 2], [128, 1], [255, 510], [3, 5, 9, 17], [700, 701, 702, 703], [40, 300]):
+        logits = (torch.randn(1024, generator=g) * 0.1).to(torch.bfloat16)
+        logits[tied] = 9.0
+        want = B.argmax(bf16_bits(logits))
+        assert run(logits) == want and want in tied
+    logits = (torch.randn(1024, generator=g) * 0.1).to(torch.bfloat16)
+    logits[[1, 2]] = 9.0
+    assert run(logits) == 2                      # not the smallest index
+    assert run(torch.full((300,), -3e38).to(torch.bfloat16)) == 0
+    assert run(torch.full((300,), float("nan")).to(torch.bfloat16)) == 0
+    # shards of 18992 entries (151936 / 8): offsets that are no multiple of 256
+    logits = torch.randn(4 * 18992, generator=g).to(torch.bfloat16)
+    logits[[18992 + 5, 18992 + 6, 18992 + 700]] = 9.0
+    for r in range(4):
+        part = logits[r * 18992:(r + 1) * 18992].contiguous()
+        assert run(part, r * 18992) == B.argmax(bf16_bits(part), r * 18992)
+    whole = B.argmax(bf16_bits(logits))
+    assert whole == run(logits) and whole == 18992 + run(logits[18992:2 * 18992].contiguous(), 18992)
 
 
 @pytest.mark.parametrize("M", [2, 5, 8, 9, 17, 32, 33])

@@ -229,3 +229,35 @@ def test_decode_prepare_qkv(heads, kv, hd, pos):
     assert np.array_equal(vc_r, vc_o)
     kc_r[:, pos] = kc_o[:, pos] = 0
     assert not kc_r.any() and not kc_o.any()
+
+
+def test_argmax_ties_resolve_like_the_reference():
+    """ops::argmax keeps the left candidate at every level of its 256-item tree, so equal maxima
+    resolve by bit-reversed (index % 256), not by index: the oracle's restatement against the
+    reference's kernel on crafted ties, random logits, and a vocabulary that is not a multiple of 256."""
+    from oracle import backend_numpy as B
+    rng = np.random.default_rng(7)
+    for n in (1, 7, 300, 1024, 5000):
+        logits = B.to_bf16(rng.standard_normal(n).astype(np.float32))
+        assert R.argmax(logits) == B.argmax(logits)
+    # ties: index 2 (item 2) against 257 (item 1): item 1 and item 2 differ first in bit 0, item 2 has
+    # the 0 there, so index 2 wins; 1 against 2: they differ in bit 0 too, item 2 wins again
+    for tied in ([2, 257], [1, 2], [128, 1], [255, 256 + 254], [3, 5, 9, 17], [700, 701, 702, 703]):
+        logits = B.to_bf16(rng.standard_normal(1024).astype(np.float32) * 0.1)
+        logits[tied] = B.to_bf16(np.float32([9.0]))[0]
+        got = R.argmax(logits)
+        assert got == B.argmax(logits) and got in tied
+    logits = B.to_bf16(rng.standard_normal(1024).astype(np.float32) * 0.1)
+    logits[[2, 257]] = B.to_bf16(np.float32([9.0]))[0]
+    assert R.argmax(logits) == 2
+    logits[[1, 2]] = B.to_bf16(np.float32([9.5]))[0]
+    assert R.argmax(logits) == 2      # not the smallest index
+    # nothing above the start value: index 0
+    assert R.argmax(B.to_bf16(np.full(300, -3e38, np.float32))) == 0 == B.argmax(B.to_bf16(np.full(300, -3e38, np.float32)))
+    # a shard's local result equals the global one
+    logits = B.to_bf16(rng.standard_normal(2000).astype(np.float32))
+    logits[[900, 1203]] = B.to_bf16(np.float32([8.0]))[0]
+    whole = B.argmax(logits)
+    parts = [(off, B.argmax(logits[off:off + 500], off) + off) for off in range(0, 2000, 500)]
+    vals = [B.to_f32(logits[i:i + 1])[0] for _, i in parts]
+    assert whole in [i for _, i in parts] and max(vals) == B.to_f32(logits[whole:whole + 1])[0]

@@ -106,7 +106,9 @@ def _worker(rank, world, port, q):
         whole = be.make_dense(wh)
         full_logits = be.empty(1, 4096)
         be.dense_forward(whole, xh, full_logits, 1)
-        same = same and tok == int(torch.argmax(full_logits.float().reshape(-1)))
+        whole_tok = be.empty(1, dtype=torch.int32)
+        be.argmax(full_logits, 4096, whole_tok)
+        same = same and tok == int(whole_tok.cpu()[0])
         outs["fused"] = ys[0].cpu().view(torch.uint16).numpy()
         outs["fused_consistent"] = bool(same)
         peers.close()
