@@ -1,8 +1,8 @@
 """TEST INFRASTRUCTURE ONLY: numpy restatement of the reference operators that sit between the NF4
 linears in a Qwen3 decode step, and of the decode step itself. Every function cites the lines it
-follows; embedding_lookup and decode_prepare_qkv are held against the reference's own source compiled
-for the host (tests/test_reference_pin.py); attention_decode and the decode step are pinned by
-reading only (the reference has no golden vectors for them).
+follows; embedding_lookup, decode_prepare_qkv, attention_decode and argmax are held against the
+reference's own sources compiled for the host (tests/test_reference_pin.py); how the decode step
+strings them together is restated from reading (the reference has no golden vectors for it).
 
   embedding_lookup     src/ops/ElementwiseOps.cpp:14-27
   decode_prepare_qkv   src/ops/ElementwiseOps.cpp:105-215
@@ -64,19 +64,50 @@ def decode_prepare_qkv(q_bits, k_bits, v_bits, freq, q_norm_w, k_norm_w, k_cache
     return q_out.reshape(-1)
 
 
-def attention_decode(q_bits, k_cache, v_cache, n_heads, n_kv, head_dim, cached_len) -> np.ndarray:
+def _tree_reduce(part: np.ndarray, op) -> np.float32:
+    """Balanced tree t[i] = op(t[i], t[i + w]), w = n/2 .. 1: the work-group reduction order the C
+    oracle assumes as well (SYCL leaves it open)."""
+    t = part.astype(np.float32).copy()
+    w = t.size // 2
+    while w >= 1:
+        t[:w] = op(t[:w], t[w:2 * w])
+        w //= 2
+    return t[0]
+
+
+def attention_decode(q_bits, k_cache, v_cache, n_heads, n_kv, head_dim, cached_len, wg_size: int = 512) -> np.ndarray:
+    """ops::attention_decode on its baseline route (AttentionOps.cpp:73-166, the whole window, the
+    default work-group of 512): per head, score[t] = (sum over d in order of q[d] * k[t][d]) * scale
+    with every product and sum rounded to fp32; the maximum; e[t] = exp(score[t] - max); their sum
+    as work-item partial sums (item l adds t = l, l + 512, ...) reduced by a balanced tree;
+    p[t] = e[t] / sum; out[d] = the sum over t in order of p[t] * v[t][d], rounded to bf16."""
     q = to_f32(np.asarray(q_bits, np.uint16).reshape(n_heads, head_dim))
     per = n_heads // n_kv
     scale = np.float32(1.0) / np.sqrt(np.float32(head_dim))
     out = np.empty((n_heads, head_dim), np.uint16)
+    T = cached_len
+    J = (T + wg_size - 1) // wg_size
     for h in range(n_heads):
         kv = h // per
-        kk = to_f32(k_cache[kv, :cached_len])
-        vv = to_f32(v_cache[kv, :cached_len])
-        s = (kk @ q[h]).astype(np.float32) * scale
-        e = np.exp(s - s.max()).astype(np.float32)
-        p = e / e.sum(dtype=np.float32)
-        out[h] = to_bf16((p[:, None] * vv).sum(axis=0, dtype=np.float32))
+        kk = to_f32(k_cache[kv, :T])
+        vv = to_f32(v_cache[kv, :T])
+        s = np.zeros(T, np.float32)
+        for d in range(head_dim):
+            s = s + q[h, d] * kk[:, d]
+        s = (s * scale).astype(np.float32)
+        mx = np.float32(max(np.float32(-1e30), s.max()))
+        e = np.exp((s - mx).astype(np.float32)).astype(np.float32)
+        lanes = np.zeros((J, wg_size), np.float32)
+        lanes.reshape(-1)[:T] = e
+        part = np.zeros(wg_size, np.float32)
+        for j in range(J):
+            part = part + lanes[j]
+        total = _tree_reduce(part, np.add)
+        p = (e / total).astype(np.float32)
+        acc = np.zeros(head_dim, np.float32)
+        for t in range(T):
+            acc = acc + p[t] * vv[t]
+        out[h] = to_bf16(acc)
     return out.reshape(-1)
 
 

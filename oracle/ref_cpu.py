@@ -204,3 +204,12 @@ def argmax(logits_bf16) -> int:
     out = np.zeros(1, np.int32)
     _run("aila_ref_argmax", _vp(l), ctypes.c_int(l.size), _vp(out))
     return int(out[0])
+
+
+def attention_decode(q_bf16, k_cache, v_cache, n_heads, n_kv, head_dim, cached_len) -> np.ndarray:
+    q = _u16(q_bf16).reshape(-1).copy()
+    kc, vc = _u16(k_cache).copy(), _u16(v_cache).copy()
+    out = np.zeros(n_heads * head_dim, np.uint16)
+    _run("aila_ref_attention_decode", _vp(q), _vp(kc), _vp(vc), _vp(out), ctypes.c_int(kc.shape[1]),
+         ctypes.c_int(n_heads), ctypes.c_int(n_kv), ctypes.c_int(head_dim), ctypes.c_int(cached_len))
+    return out

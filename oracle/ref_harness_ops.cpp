@@ -1,11 +1,12 @@
 // TEST INFRASTRUCTURE ONLY. C entry points around the REFERENCE's own operators that sit between
-// the NF4 linears of a decode step (src/ops/NormOps.cpp, src/ops/ElementwiseOps.cpp, src/ops/SamplingOps.cpp, compiled
+// the NF4 linears of a decode step (src/ops/NormOps.cpp, src/ops/ElementwiseOps.cpp, src/ops/SamplingOps.cpp, src/ops/AttentionOps.cpp, compiled
 // unmodified from where they lie against the stand-in headers in ref_shim/): host arrays in, host
 // arrays out. Used by the tests to check the CPU oracle's restatement; never by the product.
 //
 // Pinned through here: ops::rms_norm (NormOps.cpp:14-75), ops::fused_add_rms_norm (:141-275),
 // ops::embedding_lookup (ElementwiseOps.cpp:14-27), ops::decode_prepare_qkv (:105-215), ops::swiglu
-// (:223-245), ops::fused_gate_up_swiglu (:247-294), ops::argmax (src/ops/SamplingOps.cpp:321-358).
+// (:223-245), ops::fused_gate_up_swiglu (:247-294), ops::argmax (src/ops/SamplingOps.cpp:321-358),
+// ops::attention_decode (src/ops/AttentionOps.cpp:499-647 -> attention_decode_baseline :73-166).
 // The stand-in fixes what SYCL leaves open: reduce_over_group adds in a balanced tree,
 // native::exp/cos/sin are libm's.
 #include <cstdint>
@@ -14,6 +15,12 @@
 #include <string>
 
 #include "ops/Ops.hpp"
+#include "profile/Profiling.hpp"
+
+// the reference's logger (its own definition lives in a source file that is not part of this build)
+namespace aila {
+void log(LogLevel, const char*, ...) {}
+}  // namespace aila
 
 namespace {
 
@@ -84,6 +91,19 @@ int aila_ref_decode_prepare_qkv(uint16_t* q, uint16_t* k, uint16_t* v, float* ro
         Tensor kc = bf16_view(k_cache, {kv_heads, max_seq_len, head_dim}),
                vc = bf16_view(v_cache, {kv_heads, max_seq_len, head_dim});
         ops::decode_prepare_qkv(ctx, tq, tk, tv, tf, qn, kn, kc, vc, start_pos, heads, kv_heads, head_dim, eps, theta);
+    });
+}
+
+// single-token attention over the first cached_len cache rows; caches are [kv][max_seq_len][hd]
+int aila_ref_attention_decode(uint16_t* q, uint16_t* k_cache, uint16_t* v_cache, uint16_t* out, int max_seq_len,
+                              int heads, int kv_heads, int head_dim, int cached_len, char* err, int cap) {
+    return guarded(err, cap, [&]() {
+        Context& ctx = context();
+        Tensor tq = bf16_view(q, {1, (int64_t)heads * head_dim}), to = bf16_view(out, {1, (int64_t)heads * head_dim});
+        Tensor kc = bf16_view(k_cache, {kv_heads, max_seq_len, head_dim}),
+               vc = bf16_view(v_cache, {kv_heads, max_seq_len, head_dim});
+        Tensor scores = Tensor::allocate(ctx, {(int64_t)heads, (int64_t)max_seq_len}, dt::f32);
+        ops::attention_decode(ctx, tq, kc, vc, to, scores, heads, kv_heads, head_dim, cached_len, nullptr);
     });
 }
 

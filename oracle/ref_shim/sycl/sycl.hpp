@@ -81,7 +81,12 @@ struct nd_range {
 
 namespace access {
 enum class fence_space { local_space, global_space, global_and_local };
+enum class decorated { no, yes, legacy };
+enum class address_space { global_space, local_space, private_space, generic_space };
 }
+enum class aspect { ext_intel_matrix, fp16, fp64, gpu, cpu };
+template <access::address_space S, access::decorated D, typename T>
+inline T* address_space_cast(T* p) { return p; }
 
 // ---------------------------------------------------------------- bfloat16
 namespace ext {
@@ -107,14 +112,63 @@ private:
     }
     uint16_t bits_ = 0;
 };
+// Declarations only for the matrix extension: the stand-in device reports no matrix hardware, so
+// the kernels that use it are compiled but never chosen; calling one throws.
+namespace experimental {
+namespace matrix {
+enum class use { a, b, accumulator };
+enum class layout { row_major, col_major, dynamic };
+enum class matrix_type { bf16, fp16, tf32, fp32, fp64, sint8, uint8, sint32 };
+struct combination {
+    size_t max_msize = 0, max_nsize = 0, max_ksize = 0, msize = 0, nsize = 0, ksize = 0;
+    matrix_type atype = matrix_type::fp32, btype = matrix_type::fp32, ctype = matrix_type::fp32,
+                dtype = matrix_type::fp32;
+};
+template <typename Group, typename T, use U, size_t R, size_t C, layout L = layout::dynamic>
+struct joint_matrix {};
+template <typename... A>
+inline void joint_matrix_fill(A&&...) { throw std::runtime_error("sycl shim: no matrix extension"); }
+template <typename... A>
+inline void joint_matrix_load(A&&...) { throw std::runtime_error("sycl shim: no matrix extension"); }
+template <typename... A>
+inline void joint_matrix_mad(A&&...) { throw std::runtime_error("sycl shim: no matrix extension"); }
+template <typename... A>
+inline void joint_matrix_store(A&&...) { throw std::runtime_error("sycl shim: no matrix extension"); }
+}  // namespace matrix
+namespace info {
+namespace device {
+struct matrix_combinations {
+    using return_type = std::vector<matrix::combination>;
+};
+}  // namespace device
+}  // namespace info
+}  // namespace experimental
 }  // namespace oneapi
 }  // namespace ext
 
 template <typename T, int N>
 struct vec {
     T data[N];
+    vec() = default;
+    explicit vec(T v) {
+        for (int i = 0; i < N; ++i) data[i] = v;
+    }
     const T& operator[](int i) const { return data[i]; }
     T& operator[](int i) { return data[i]; }
+    friend vec operator*(const vec& a, const vec& b) {
+        vec r;
+        for (int i = 0; i < N; ++i) r.data[i] = a.data[i] * b.data[i];
+        return r;
+    }
+    friend vec operator+(const vec& a, const vec& b) {
+        vec r;
+        for (int i = 0; i < N; ++i) r.data[i] = a.data[i] + b.data[i];
+        return r;
+    }
+    vec& operator+=(const vec& b) {
+        for (int i = 0; i < N; ++i) data[i] += b.data[i];
+        return *this;
+    }
 };
 
 // ---------------------------------------------------------------- math
@@ -354,6 +408,8 @@ public:
     local_accessor(range<D> r, handler& h);
     T& operator[](size_t i) const { return ptr_[i]; }
     T* get_pointer() const { return ptr_; }
+    template <access::decorated Dec = access::decorated::no>
+    T* get_multi_ptr() const { return ptr_; }
 
 private:
     T* ptr_ = nullptr;
@@ -425,7 +481,11 @@ local_accessor<T, D>::local_accessor(range<D> r, handler& h) {
 struct event {
     void wait() {}
 };
-struct device {};
+struct device {
+    bool has(aspect) const { return false; }   // no matrix hardware: the plain kernels are chosen
+    template <typename Info>
+    typename Info::return_type get_info() const { return typename Info::return_type(); }
+};
 struct context {
     bool operator==(const context&) const { return true; }
     bool operator!=(const context&) const { return false; }

@@ -261,3 +261,16 @@ def test_argmax_ties_resolve_like_the_reference():
     parts = [(off, B.argmax(logits[off:off + 500], off) + off) for off in range(0, 2000, 500)]
     vals = [B.to_f32(logits[i:i + 1])[0] for _, i in parts]
     assert whole in [i for _, i in parts] and max(vals) == B.to_f32(logits[whole:whole + 1])[0]
+
+
+@pytest.mark.parametrize("heads,kv,hd,length", [(4, 2, 64, 1), (32, 8, 128, 300), (16, 16, 128, 2047), (8, 1, 256, 33)])
+def test_attention_decode(heads, kv, hd, length):
+    """ops::attention_decode on its baseline route (no matrix hardware reported, whole window). exp
+    comes from two libraries (libm in the stand-in, numpy in the oracle): outputs within one bf16 ulp,
+    all but a handful equal."""
+    from oracle import backend_numpy as B
+    q, kc, vc = _x(50, 1, heads * hd).reshape(-1), _x(51, kv * 2048, hd).reshape(kv, 2048, hd), \
+        _x(52, kv * 2048, hd).reshape(kv, 2048, hd)
+    a = R.attention_decode(q, kc, vc, heads, kv, hd, length).astype(np.int32)
+    b = B.attention_decode(q, kc, vc, heads, kv, hd, length).astype(np.int32)
+    assert np.abs(a - b).max() <= 1 and (a != b).mean() < 0.01
