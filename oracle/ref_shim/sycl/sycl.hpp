@@ -1,7 +1,7 @@
 // TEST INFRASTRUCTURE ONLY. A serial CPU stand-in for the part of SYCL 2020 that the reference's
-// NF4 operator (src/ops/Bnb4BitLinear.cpp and the headers it includes) uses, so that the
-// reference's own kernel source can be compiled with g++ and run on the host as a second opinion
-// on the CPU oracle. Not a SYCL implementation: one device (the host), in-order queues that run
+// operators of the NF4 decode path use (src/ops/Bnb4BitLinear.cpp, NormOps.cpp, ElementwiseOps.cpp,
+// SamplingOps.cpp, AttentionOps.cpp and the headers they include), so that the reference's own
+// kernel source can be compiled with g++ and run on the host as a second opinion on the CPU oracle. Not a SYCL implementation: one device (the host), in-order queues that run
 // every command at submission, USM = malloc.
 //
 // Work-items of a work-group run as cooperatively scheduled fibers (ucontext), so barriers and
