@@ -396,6 +396,21 @@ int batched_rows_per_launch(const AilaNf4Linear* l, const AilaNf4Scratch* sc, in
     return nf4::gemv_stream_supported(*l, 0, sc->sm_count, 4) ? 32 : 8;
 }
 
+// Prefill with the weight dequantised inside the GEMM instead of a bf16 copy of W written to and read
+// back from HBM: AILA_NF4_FUSED_PREFILL=1 takes the fused kernel wherever it takes the linear. It is
+// bit-identical to the two-phase route and slower at every measured size (each 256-row tile of x pays
+// the dequantisation arithmetic again, and the w tile is produced in step with the tensor core instead
+// of arriving by TMA), so the default is the two-phase route.
+bool use_fused_prefill(const AilaNf4Linear* l, int64_t ff_dim, int seq_len) {
+    static const bool on = [] {
+        const char* e = std::getenv("AILA_NF4_FUSED_PREFILL");
+        return e && e[0] == '1';
+    }();
+    (void)seq_len;
+    if (!on || l->d_cache_bf16) return false;
+    return nf4::gemm_nf4_fused_supported(*l, ff_dim);
+}
+
 // seq_len == 1: decode kernels. ff_pair > 0 selects the gate/up pair kernel.
 AilaNf4Status run_decode(const AilaNf4Linear* l, AilaNf4Scratch* sc, const void* x, void* y,
                          const void* residual, int64_t ff_pair, cudaStream_t s, int m_rows = 1,
@@ -785,6 +800,8 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward(const AilaNf4Linear* l, AilaNf4Scrat
         }
         return AILA_NF4_OK;
     }
+    if (use_fused_prefill(l, 0, seq_len))
+        return nf4::launch_gemm_nf4_fused(*l, x, y, residual, seq_len, 0, sc->sm_count, sc->d_status, s);
     const void* wsrc = l->d_cache_bf16;
     if (!wsrc) {
         st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);
@@ -839,6 +856,8 @@ AILA_NF4_API AilaNf4Status aila_nf4_forward_gate_up_swiglu(const AilaNf4Linear* 
         }
         return AILA_NF4_OK;
     }
+    if (use_fused_prefill(l, ff_dim, seq_len))
+        return nf4::launch_gemm_nf4_fused(*l, x, out, nullptr, seq_len, ff_dim, sc->sm_count, sc->d_status, s);
     const void* wsrc = l->d_cache_bf16;
     if (!wsrc) {
         st = ensure_weight(sc, (size_t)l->N * (size_t)l->K * 2);

@@ -19,6 +19,11 @@
 // worth + the matching up columns), rounding gate and up to bf16 first as the reference's
 // forward + ops::fused_gate_up_swiglu pair does (src/ops/ElementwiseOps.cpp:247-294).
 //
+// A second form of the kernel (FUSED) takes the weight as NF4 units and rebuilds every w tile in
+// shared memory itself (sixteen more warps), so no bf16 copy of W goes through HBM. Its output is
+// bit-identical to the two-phase route; it is the slower of the two at every measured size and is
+// therefore only used on request (AILA_NF4_FUSED_PREFILL=1).
+//
 // Roofline: tensor pipe. Algorithmic flops 2*M*N*K.
 #include <cuda.h>
 
@@ -39,9 +44,25 @@ constexpr int kABytes = BM * BK * 2;         // 16 KB per 128 rows of x
 constexpr int kBBytes = kMaxBN * BK * 2;     // 32 KB
 constexpr int kRingBytes = 4 * (kABytes + kBBytes);  // = 3 * (2 * kABytes + kBBytes) = 192 KB
 constexpr int kGemmThreads = 320;            // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+constexpr int kDequantWarps = 16;            // fused form: warps 10-25 write the w tiles from NF4 (one unit each)
+constexpr int kFusedThreads = kGemmThreads + kDequantWarps * 32;
+constexpr int kFusedTableBytes = 64 + 1024;  // fused form: code book (16 floats), second-level code book (256)
+constexpr int kNfSlots = 3;                  // fused form: NF4 units in flight per dequantisation warp
+constexpr int kNfSlotBytes = kUnitStrideF32; // one unit (528 or 576 bytes)
+constexpr int kFusedExtraBytes = kFusedTableBytes + kDequantWarps * kNfSlots * (kNfSlotBytes + 8);
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
 constexpr int kGemmSmem = kRingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+
+// The NF4 weight of the fused form (the w tiles are produced in shared memory from the unit stream
+// instead of being copied from a bf16 matrix).
+struct FusedWeight {
+    const uint8_t* units;      // unit stream: unit (rt, kb) at (rt * KU + kb) * unit_stride
+    const float* qmap;         // [16]
+    const float* nmap;         // [256] second-level code book (8-bit absmax codes)
+    const float4* row_scales;  // [n_rows] {lo, hi, cross, offset} (8-bit absmax codes)
+    int KU, RT, n_rows, unit_stride, kind;
+};
 
 struct GemmParams {
     uint16_t* y;
@@ -113,9 +134,16 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 extern __shared__ __align__(1024) uint8_t gemm_smem[];
 
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// FUSED: the B operand is not a bf16 matrix in global memory. Eight more warps read the NF4 units of
+// the tile's rows (the same 512-byte-per-unit pattern as the decode kernels), rebuild
+// bf16(code_book[nibble] * absmax) - bit-equal to dequantize_weight - and store it into the stage's
+// w tile in the K-major 128-byte-swizzle layout the tensor core expects; a proxy fence and one
+// arrival per warp on the stage's `full` barrier stand where the TMA completion stood.
+template <bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kFusedThreads : kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
-                         const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+                         const __grid_constant__ CUtensorMap map_w, const GemmParams p,
+                         const FusedWeight fw) {
     // 1024-byte aligned ring (the swizzle pattern is a function of the absolute address)
     uint8_t* base = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~(uintptr_t)1023);
@@ -126,6 +154,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     uint64_t* acc_empty = acc_full + kAccStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccStages);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* s_qmap = reinterpret_cast<float*>(base + kRingBytes + 256);  // fused form only
+    float* s_nmap = s_qmap + 16;
+    uint64_t* nf_full = reinterpret_cast<uint64_t*>(base + kRingBytes + 256 + kFusedTableBytes);  // [warp][slot]
+    uint8_t* nf_ring = reinterpret_cast<uint8_t*>(nf_full + kDequantWarps * kNfSlots);           // [warp][slot][unit]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -138,7 +170,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], FUSED ? 1 + kDequantWarps : 1);
             mbar_init(&empty[s], 1);
         }
         for (int a = 0; a < kAccStages; ++a) {
@@ -146,7 +178,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             mbar_init(&acc_empty[a], 4 * p.mtile);
         }
         *abort_flag = 0;
+        if (FUSED)
+            for (int i = 0; i < kDequantWarps * kNfSlots; ++i) mbar_init(&nf_full[i], 1);
         mbar_fence_init();
+    }
+    if (FUSED) {
+        if (threadIdx.x >= 64 && threadIdx.x < 80) s_qmap[threadIdx.x - 64] = __ldg(fw.qmap + (threadIdx.x - 64));
+        if (fw.kind == kAbsmaxCodes && threadIdx.x >= 320 && threadIdx.x < 576)
+            s_nmap[threadIdx.x - 320] = __ldg(fw.nmap + (threadIdx.x - 320));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -183,9 +222,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                     }
                     uint8_t* sa = base + s * kStageBytes;
                     uint8_t* sb = sa + a_bytes;
-                    mbar_expect_tx(&full[s], a_bytes + b_bytes);
+                    mbar_expect_tx(&full[s], FUSED ? (uint32_t)a_bytes : a_bytes + b_bytes);
                     tma_load_2d(sa, &map_x, kb * BK, m0, &full[s]);
-                    if (p.swiglu_ff == 0) {
+                    if (FUSED) {
+                        // the dequantisation warps fill the w tile
+                    } else if (p.swiglu_ff == 0) {
                         tma_load_2d(sb, &map_w, kb * BK, nt * p.BN, &full[s]);
                     } else {
                         const int half = p.BN / 2;
@@ -242,6 +283,147 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                 }
                 if (ok) umma_commit(&acc_full[as]);
             }
+        }
+    } else if (FUSED && warp >= kGemmThreads / 32) {
+        // ------------------------------ w tiles from NF4 (warps 10..25) ------------------------------
+        // Unit iu of a tile = its rows 16 iu .. 16 iu + 15 (gate rows first, then the matching up
+        // rows, with SwiGLU); warp dw takes unit dw. Lane (gq, t) holds, as in the decode kernels,
+        // 8 bytes of row gq and 8 bytes of row gq + 8: byte 2j + e covers k = 16 j + 4 t + 2 e (high
+        // nibble) and + 1 (low nibble).
+        const int dw = warp - kGemmThreads / 32;
+        const int gq = lane >> 2, t = lane & 3;
+        const int n_units = p.BN / 16;
+        const int half_units = p.swiglu_ff > 0 ? n_units / 2 : n_units;
+        const int ST = fw.unit_stride;
+        const uint32_t w_off = (uint32_t)(gq * 32 + 8 * t);
+        const uint32_t a_q = smem_u32(s_qmap);
+        // The warp's units arrive through a private ring of kNfSlots bulk-async copies, issued
+        // kNfSlots steps ahead, so that memory latency never meets the arithmetic. A step whose unit
+        // does not exist (rows past the weight, or this warp has no unit in the tile) copies nothing
+        // and writes zeros; the j-th copy that IS issued uses slot j % kNfSlots on both sides.
+        uint64_t* my_full = nf_full + dw * kNfSlots;
+        uint8_t* my_ring = nf_ring + (size_t)dw * kNfSlots * kNfSlotBytes;
+        // row tile of unit iu of n-tile nt (>= fw.RT: rows past the weight)
+        auto unit_rt = [&](int nt, int iu) {
+            if (p.swiglu_ff > 0)
+                return iu < half_units ? nt * half_units + iu : p.swiglu_ff / 16 + nt * half_units + (iu - half_units);
+            return nt * n_units + iu;
+        };
+        auto step_rt = [&](int tile) {  // this warp's row tile in `tile`, or -1
+            if (dw >= n_units) return -1;
+            const int rt = unit_rt(tile / p.m_tiles, dw);
+            return rt < fw.RT ? rt : -1;
+        };
+        int p_tile = blockIdx.x, p_kb = 0, p_j = 0;  // the next step to issue; copies issued so far
+        int c_j = 0;                                 // copies consumed so far
+        auto issue_next = [&]() {  // one lane
+            if (p_tile >= total_tiles) return;
+            const int rt = step_rt(p_tile);
+            if (rt >= 0) {
+                const int slot = p_j % kNfSlots;
+                mbar_expect_tx(&my_full[slot], (uint32_t)ST);
+                bulk_g2s(my_ring + slot * kNfSlotBytes, fw.units + ((size_t)rt * fw.KU + p_kb) * (size_t)ST,
+                         (uint32_t)ST, &my_full[slot]);
+                ++p_j;
+            }
+            if (++p_kb == k_blocks) {
+                p_kb = 0;
+                p_tile += gridDim.x;
+            }
+        };
+        if (lane == 0)
+            for (int i = 0; i < kNfSlots; ++i) issue_next();
+        // code book value of nibble `k` (0 = lowest) of `word`; the table never changes after set-up,
+        // so the load is free to move (not volatile, no memory clobber)
+        auto qv = [&](uint32_t word, int k) {
+            const uint32_t off = k == 0 ? (word << 2) & 0x3cu : (word >> (4 * k - 2)) & 0x3cu;
+            float v;
+            asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a_q + off));
+            return v;
+        };
+        // one row's 8 bytes -> eight packed pairs (k ascending), then four 8-byte stores
+        auto emit_row = [&](uint32_t row_base, uint2 w, float am) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t word = h == 0 ? w.x : w.y;
+#pragma unroll
+                for (int b = 0; b < 4; ++b)  // byte b: high nibble first
+                    pk[4 * h + b] = pack2(__fmul_rn(qv(word, 2 * b + 1), am), __fmul_rn(qv(word, 2 * b), am));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t a = row_base + ((((uint32_t)(2 * j + (t >> 1))) ^ (uint32_t)gq) << 4) + ((uint32_t)(t & 1) << 3);
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(a), "r"(pk[2 * j]), "r"(pk[2 * j + 1]));
+            }
+        };
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int rt = step_rt(tile);
+            float4 e0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), e1 = e0;
+            if (rt >= 0 && fw.kind == kAbsmaxCodes) {
+                e0 = __ldg(fw.row_scales + min(rt * 16 + gq, fw.n_rows - 1));
+                e1 = __ldg(fw.row_scales + min(rt * 16 + gq + 8, fw.n_rows - 1));
+            }
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % kStages;
+                bool good = true;
+                if (lane == 0) {
+                    if (it >= kStages &&
+                        (*abort_flag || !mbar_wait_bounded(&empty[s], ((it / kStages) - 1) & 1))) {
+                        if (!*abort_flag) atomicExch(p.status, kStatusTimeoutEmpty);
+                        *abort_flag = 1;
+                        good = false;
+                    }
+                    if (good && rt >= 0 &&
+                        (*abort_flag || !mbar_wait_bounded(&my_full[c_j % kNfSlots], (c_j / kNfSlots) & 1))) {
+                        if (!*abort_flag) atomicExch(p.status, kStatusTimeoutFull);
+                        *abort_flag = 1;
+                        good = false;
+                    }
+                }
+                good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;
+                if (!good) {
+                    ok = false;
+                    break;
+                }
+                if (dw < n_units) {
+                    uint2 l = make_uint2(0x77777777u, 0x77777777u), u = l;
+                    float am0 = 0.0f, am1 = 0.0f;
+                    if (rt >= 0) {
+                        const uint32_t ua = smem_u32(my_ring + (c_j % kNfSlots) * kNfSlotBytes);
+                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(l.x), "=r"(l.y) : "r"(ua + w_off));
+                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(u.x), "=r"(u.y) : "r"(ua + w_off + 256u));
+                        if (fw.kind == kAbsmaxCodes) {
+                            uint32_t c0, c1;
+                            asm volatile("ld.shared.u8 %0, [%1];" : "=r"(c0) : "r"(ua + kUnitNibbleBytes + gq));
+                            asm volatile("ld.shared.u8 %0, [%1];" : "=r"(c1) : "r"(ua + kUnitNibbleBytes + gq + 8));
+                            // absmax = second-level code book value * the row's second-level scale + offset
+                            am0 = __fadd_rn(__fmul_rn(s_nmap[c0], kb >= __float_as_int(e0.z) ? e0.y : e0.x), e0.w);
+                            am1 = __fadd_rn(__fmul_rn(s_nmap[c1], kb >= __float_as_int(e1.z) ? e1.y : e1.x), e1.w);
+                        } else {
+                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(am0) : "r"(ua + kUnitNibbleBytes + 4u * gq));
+                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(am1) : "r"(ua + kUnitNibbleBytes + 4u * (gq + 8)));
+                        }
+                    }
+                    const uint32_t rb = smem_u32(base + s * kStageBytes + a_bytes) + (uint32_t)dw * 2048u + (uint32_t)gq * 128u;
+                    emit_row(rb, l, am0);
+                    emit_row(rb + 1024u, u, am1);
+                }
+                // generic-proxy stores -> visible to the tensor core's (async proxy) reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&full[s]);
+                    issue_next();  // the unit's slot is free: every lane's loads fed the stores above
+                }
+                if (rt >= 0) ++c_j;
+            }
+        }
+        // copies issued for steps that were never reached (after a failure) must land before exit
+        if (!ok && lane == 0) {
+            for (int j = c_j; j < p_j; ++j) mbar_wait_bounded(&my_full[j % kNfSlots], (j / kNfSlots) & 1, 2000000LL);
         }
     } else {
         // ------------------------------ epilogue (warps 2..9) ------------------------------
@@ -435,10 +617,11 @@ TileChoice choose_tile(int M, int64_t n_cols, int step, int max_bn, int width_sc
 
 }  // namespace
 
-AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const void* residual,
-                               int M, int64_t N, int64_t K, int64_t swiglu_ff, int device,
-                               int sm_count, int* d_status, cudaStream_t s) {
-    (void)device;
+namespace {
+// w_nk: the bf16 weight [N][K], or nullptr with `fw` describing the NF4 weight (fused form)
+AilaNf4Status launch_gemm_common(const void* w_nk, const FusedWeight* fw, const void* x, void* y,
+                                 const void* residual, int M, int64_t N, int64_t K, int64_t swiglu_ff,
+                                 int sm_count, int* d_status, cudaStream_t s) {
     if (K % BK != 0) return fail(AILA_NF4_ERR_UNSUPPORTED, "prefill GEMM needs in_features % 64 == 0");
     if ((reinterpret_cast<uintptr_t>(w_nk) | reinterpret_cast<uintptr_t>(x)) & 15)
         return fail(AILA_NF4_ERR_INVALID_ARGUMENT, "prefill GEMM operands must be 16-byte aligned");
@@ -474,16 +657,23 @@ AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const v
     if (!encode_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)(BM * p.mtile)))
         return fail(AILA_NF4_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation tensor");
     const uint32_t w_box = (uint32_t)(swiglu_ff > 0 ? p.BN / 2 : p.BN);
-    if (!encode_map(&map_w, w_nk, (uint64_t)N, (uint64_t)K, w_box))
+    if (fw) {
+        map_w = map_x;  // unused by the fused form
+    } else if (!encode_map(&map_w, w_nk, (uint64_t)N, (uint64_t)K, w_box)) {
         return fail(AILA_NF4_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
+    }
 
     static std::once_flag attr_once[64];
     int dev = 0;
     cudaGetDevice(&dev);
     cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel,
+        attr_err = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<false>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kGemmSmem + kFusedExtraBytes);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(gemm)");
     const int total_tiles = p.m_tiles * p.n_tiles;
@@ -491,17 +681,53 @@ AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const v
     if (grid <= 0) return AILA_NF4_OK;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = kGemmSmem;
+    cfg.blockDim = dim3(fw ? kFusedThreads : kGemmThreads);
+    cfg.dynamicSmemBytes = fw ? kGemmSmem + kFusedExtraBytes : kGemmSmem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel, map_x, map_w, p);
+    const FusedWeight none = {};
+    cudaError_t e = fw ? cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<true>, map_x, map_w, p, *fw)
+                       : cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_kernel<false>, map_x, map_w, p, none);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_bf16_tcgen05_kernel launch");
     return AILA_NF4_OK;
+}
+}  // namespace
+
+AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const void* residual,
+                               int M, int64_t N, int64_t K, int64_t swiglu_ff, int device,
+                               int sm_count, int* d_status, cudaStream_t s) {
+    (void)device;
+    return launch_gemm_common(w_nk, nullptr, x, y, residual, M, N, K, swiglu_ff, sm_count, d_status, s);
+}
+
+// The fused form takes the weight as it is stored (NF4 units): no bf16 copy of W goes through HBM.
+bool gemm_nf4_fused_supported(const AilaNf4Linear& w, int64_t swiglu_ff) {
+    if (w.K % BK != 0 || w.N % kTileRows != 0) return false;
+    if (w.absmax_kind == kAbsmaxCodes && !w.d_row_scales) return false;
+    if (swiglu_ff > 0 && (swiglu_ff % kTileRows != 0 || w.N != 2 * swiglu_ff)) return false;
+    return true;
+}
+
+AilaNf4Status launch_gemm_nf4_fused(const AilaNf4Linear& w, const void* x, void* y, const void* residual,
+                                    int M, int64_t swiglu_ff, int sm_count, int* d_status, cudaStream_t s) {
+    if (!gemm_nf4_fused_supported(w, swiglu_ff))
+        return fail(AILA_NF4_ERR_UNSUPPORTED, "fused prefill does not take this linear");
+    FusedWeight fw;
+    fw.units = w.d_units;
+    fw.qmap = w.d_qmap;
+    const ScaleParams sp = w.scale_params();
+    fw.nmap = sp.nmap;
+    fw.row_scales = static_cast<const float4*>(w.d_row_scales);
+    fw.KU = w.KU;
+    fw.RT = w.RT;
+    fw.n_rows = (int)w.N;
+    fw.unit_stride = w.unit_stride;
+    fw.kind = w.absmax_kind;
+    return launch_gemm_common(nullptr, &fw, x, y, residual, M, w.N, w.K, swiglu_ff, sm_count, d_status, s);
 }
 
 }  // namespace nf4

@@ -182,6 +182,10 @@ AilaNf4Status peer_targets_of(const ::AilaNf4PeerBuf* b, int device, int64_t row
 // nf4_gemm.cu ---------------------------------------------------------------------------
 // y[M][N_out] = x[M][K] * w_nk[N][K]^T on tcgen05. swiglu_ff > 0: N == 2*ff and the output
 // is [M][ff] = silu(bf16(gate)) * bf16(up).
+// Prefill with the weight dequantised inside the GEMM (no bf16 copy of W through HBM).
+bool gemm_nf4_fused_supported(const AilaNf4Linear& w, int64_t swiglu_ff);
+AilaNf4Status launch_gemm_nf4_fused(const AilaNf4Linear& w, const void* x, void* y, const void* residual,
+                                    int M, int64_t swiglu_ff, int sm_count, int* d_status, cudaStream_t s);
 AilaNf4Status launch_gemm_bf16(const void* w_nk, const void* x, void* y, const void* residual,
                                int M, int64_t N, int64_t K, int64_t swiglu_ff, int device,
                                int sm_count, int* d_status, cudaStream_t s);
