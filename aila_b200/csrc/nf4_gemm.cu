@@ -590,16 +590,29 @@ struct TileChoice {
     int bn;  // accumulator columns per 128-row half
 };
 
+// Measurement overrides, read once: AILA_NF4_GEMM_MTILE=1|2 (rows of x per CTA tile / 128) and
+// AILA_NF4_GEMM_BN=<multiple of 16> (UMMA N; with SwiGLU gate + up columns together).
+int env_tile_override(const char* name) {
+    const char* e = std::getenv(name);
+    return (e && *e) ? std::atoi(e) : 0;
+}
+
 TileChoice choose_tile(int M, int64_t n_cols, int step, int max_bn, int width_scale, int k_blocks,
                        int sm_count) {
+    static const int force_mtile = env_tile_override("AILA_NF4_GEMM_MTILE");
+    static const int force_bn = env_tile_override("AILA_NF4_GEMM_BN");
     constexpr double kL2BytesPerClk = 70.0;  // sustained L2 -> SM operand rate per SM (measured)
     TileChoice best = {1, step};
     double best_cost = 1e300;
     for (int mtile = 1; mtile <= 2; ++mtile) {
         if (mtile == 2 && M <= BM) continue;
+        if ((force_mtile == 1 || force_mtile == 2) && mtile != force_mtile && !(force_mtile == 2 && M <= BM)) continue;
         const int m_tiles = (M + BM * mtile - 1) / (BM * mtile);
         for (int bn = step; bn <= max_bn; bn += step) {
             const int umma_n = bn * width_scale;
+            if (force_bn > 0 && force_bn % 16 == 0 && umma_n != force_bn && force_bn <= max_bn * width_scale &&
+                force_bn % (step * width_scale) == 0)
+                continue;
             const int64_t n_tiles = (n_cols + bn - 1) / bn;
             const int64_t waves = (n_tiles * m_tiles + sm_count - 1) / sm_count;
             const double mma = 2.0 * umma_n * mtile;                       // cycles per K step
