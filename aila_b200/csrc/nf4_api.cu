@@ -741,8 +741,14 @@ AILA_NF4_API AilaNf4Status aila_nf4_scratch_reserve(AilaNf4Scratch* sc, int seq_
         return nf4::fail(AILA_NF4_ERR_INVALID_ARGUMENT, "scratch_reserve: sizes must be positive");
     DeviceGuard guard(sc->device);
     if (guard.err != cudaSuccess) return nf4::cuda_fail(guard.err, "cudaSetDevice");
-    AilaNf4Status st = ensure_counters(sc, (size_t)((out_features + nf4::kTileRows - 1) / nf4::kTileRows));
+    const size_t tiles = (size_t)((out_features + nf4::kTileRows - 1) / nf4::kTileRows);
+    AilaNf4Status st = ensure_counters(sc, tiles);
     if (st != AILA_NF4_OK) return st;
+    if (seq_len > 1) {
+        // accumulation tiles of the small-batch kernel (16 rows x 32 batch columns of fp32 per row tile)
+        st = ensure_rows_acc(sc, tiles * nf4::kTileRows * 32 * sizeof(float));
+        if (st != AILA_NF4_OK) return st;
+    }
     if (need_weight) {
         st = ensure_weight(sc, (size_t)in_features * (size_t)out_features * 2);
         if (st != AILA_NF4_OK) return st;

@@ -136,7 +136,8 @@ AILA_NF4_API void aila_nf4_scratch_destroy(AilaNf4Scratch* scratch);
 /*
  * Pre-size the work space so later forward calls never allocate (call before capturing a
  * CUDA graph). Mirrors Bnb4BitLinearScratch::ensure (src/ops/Bnb4BitLinear.cpp:414-451);
- * need_weight != 0 reserves the [out,in] bf16 weight buffer the seq_len > 1 route uses.
+ * need_weight != 0 reserves the [out,in] bf16 weight buffer the seq_len > 1 route uses; seq_len > 1
+ * also reserves the fp32 accumulation tiles of the small-batch decode kernel (128 bytes per output row).
  * A decode call for more than 262,144 output rows that was not reserved for grows the work space
  * inside the call: it allocates and waits for the device, so it cannot be captured.
  */
