@@ -274,3 +274,23 @@ def test_attention_decode(heads, kv, hd, length):
     a = R.attention_decode(q, kc, vc, heads, kv, hd, length).astype(np.int32)
     b = B.attention_decode(q, kc, vc, heads, kv, hd, length).astype(np.int32)
     assert np.abs(a - b).max() <= 1 and (a != b).mean() < 0.01
+
+
+def test_random_shapes_sweep(oracle):
+    """Forty seeded random linears (rows 1..200, K a multiple of the blocksize up to 3072, blocksize
+    64/128/256, nested or plain absmax): expanded absmax, dequantised weights and the decode GEMV of
+    the oracle equal the reference's bit for bit."""
+    rng = np.random.default_rng(20240607)
+    for case in range(40):
+        blocksize = int(rng.choice([64, 64, 64, 128, 256]))
+        N = int(rng.integers(1, 201))
+        K = blocksize * int(rng.integers(1, 3072 // blocksize + 1))
+        nested = bool(rng.integers(0, 2))
+        w = make_weight(5000 + case, N, K, blocksize, nested)
+        am = oracle_absmax(oracle, w)
+        assert np.array_equal(R.expand_absmax(w), am), (case, N, K, blocksize, nested)
+        assert np.array_equal(R.dequantize_kn(w), oracle.dequantize_kn(w.packed, w.quant_map, am, N, K, blocksize)), \
+            (case, N, K, blocksize, nested)
+        x = _x(6000 + case, 1, K)
+        assert np.array_equal(R.forward(w, x, 1).reshape(-1), oracle.gemv(w.packed, w.quant_map, am, x, N, K, blocksize)), \
+            (case, N, K, blocksize, nested)
