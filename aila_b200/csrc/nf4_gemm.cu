@@ -102,13 +102,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     return d;
 }
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
+// tcgen05.mma with the two shared-memory descriptors given as their low words (start address field)
+// plus the high word both share (layout fields): the issuing thread keeps 32-bit arithmetic in its loop.
+__device__ __forceinline__ void umma_bf16_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -205,15 +209,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             const uint32_t b_bytes = (uint32_t)p.BN * BK * 2;
+            const uint32_t tx_bytes = FUSED ? (uint32_t)a_bytes : a_bytes + b_bytes;
+            const int half = p.BN / 2;
             int it = 0;
+            int s = 0;            // stage of step `it`
+            uint32_t ph = 0;      // parity its `empty` barrier shows when the stage is free again (from round 1 on)
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
                 const int m0 = mt * BM * p.mtile;
+                const int n0 = p.swiglu_ff == 0 ? nt * p.BN : nt * half;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (it >= kStages) {
-                        if (*abort_flag || !mbar_wait_bounded(&empty[s], ((it / kStages) - 1) & 1)) {
+                    if (it >= kStages && !mbar_try_wait(&empty[s], ph)) {
+                        if (*abort_flag || !mbar_wait_bounded(&empty[s], ph)) {
                             if (!*abort_flag) atomicExch(p.status, kStatusTimeoutEmpty);
                             *abort_flag = 1;
                             ok = false;
@@ -222,17 +230,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                     }
                     uint8_t* sa = base + s * kStageBytes;
                     uint8_t* sb = sa + a_bytes;
-                    mbar_expect_tx(&full[s], FUSED ? (uint32_t)a_bytes : a_bytes + b_bytes);
+                    mbar_expect_tx(&full[s], tx_bytes);
                     tma_load_2d(sa, &map_x, kb * BK, m0, &full[s]);
                     if (FUSED) {
                         // the dequantisation warps fill the w tile
                     } else if (p.swiglu_ff == 0) {
-                        tma_load_2d(sb, &map_w, kb * BK, nt * p.BN, &full[s]);
+                        tma_load_2d(sb, &map_w, kb * BK, n0, &full[s]);
                     } else {
-                        const int half = p.BN / 2;
-                        tma_load_2d(sb, &map_w, kb * BK, nt * half, &full[s]);
-                        tma_load_2d(sb + half * BK * 2, &map_w, kb * BK, p.swiglu_ff + nt * half,
-                                    &full[s]);
+                        tma_load_2d(sb, &map_w, kb * BK, n0, &full[s]);
+                        tma_load_2d(sb + half * BK * 2, &map_w, kb * BK, p.swiglu_ff + n0, &full[s]);
+                    }
+                    if (++s == kStages) {
+                        s = 0;
+                        if (it >= kStages) ph ^= 1u;
                     }
                 }
             }
@@ -243,13 +253,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
+            // One thread issues every MMA of the CTA, and its own instruction latencies are what a
+            // K step costs when the tiles are small: the loop keeps the stage index, the barrier
+            // parity and the descriptors' address fields as running 32-bit values (no division, no
+            // 64-bit arithmetic) and looks at the abort flag only when a wait is not satisfied at once.
             int it = 0, tcount = 0;
+            int s = 0;
+            uint32_t ph = 0;  // parity of full[s] for the current round
+            int as = 0;
+            uint32_t aph = 0;  // parity of acc_empty[as] once the accumulators are reused
+            const uint64_t d0 = make_smem_desc(smem_u32(base));
+            const uint32_t desc_hi = (uint32_t)(d0 >> 32);
+            const uint32_t a_lo0 = (uint32_t)d0;                     // stage 0, x tile rows 0..127
+            const uint32_t stage_inc = (uint32_t)kStageBytes >> 4;   // address field counts 16-byte units
+            const uint32_t a2_inc = (uint32_t)kABytes >> 4;          // rows 128..255 of x
+            const uint32_t b_inc = (uint32_t)a_bytes >> 4;           // the w tile
+            uint32_t a_cur = a_lo0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-                const int as = tcount % acc_stages;
-                if (tcount >= acc_stages) {
-                    if (*abort_flag ||
-                        !mbar_wait_bounded(&acc_empty[as], ((tcount / acc_stages) - 1) & 1)) {
+                if (tcount >= acc_stages && !mbar_try_wait(&acc_empty[as], aph)) {
+                    if (*abort_flag || !mbar_wait_bounded(&acc_empty[as], aph)) {
                         if (!*abort_flag) atomicExch(p.status, kStatusTimeoutTmem);
                         *abort_flag = 1;
                         break;
@@ -258,30 +281,44 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tacc = tmem_base + (uint32_t)(as * kMaxBN);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (*abort_flag || !mbar_wait_bounded(&full[s], (it / kStages) & 1)) {
-                        if (!*abort_flag) atomicExch(p.status, kStatusTimeoutFull);
-                        *abort_flag = 1;
-                        ok = false;
-                        break;
+                    if (!mbar_try_wait(&full[s], ph)) {
+                        if (*abort_flag || !mbar_wait_bounded(&full[s], ph)) {
+                            if (!*abort_flag) atomicExch(p.status, kStatusTimeoutFull);
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
                     }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sa = smem_u32(base + s * kStageBytes);
-                    const uint64_t adesc = make_smem_desc(sa);
-                    const uint64_t adesc2 = make_smem_desc(sa + kABytes);  // rows 128..255 of x
-                    const uint64_t bdesc = make_smem_desc(sa + a_bytes);
+                    // (the operands were made visible by the copies' / the producer warps' own
+                    // completion on `full`: no fence between the wait and the MMAs)
+                    const uint32_t b_cur = a_cur + b_inc;
+                    const uint32_t first = kb > 0 ? 1u : 0u;  // the tile's first MMA overwrites the accumulator
+                    if (p.mtile == 2) {
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        // advance 16 elements (32 bytes) along K inside the swizzled row
-                        umma_bf16(tacc, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
-                                  p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                        if (p.mtile == 2)
-                            umma_bf16(tacc + kMaxBN, adesc2 + (uint64_t)(2 * k),
-                                      bdesc + (uint64_t)(2 * k), p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < BK / 16; ++k) {
+                            // advance 16 elements (32 bytes = 2 address units) along K inside the swizzled row
+                            umma_bf16_lo(tacc, a_cur + 2 * k, b_cur + 2 * k, desc_hi, p.idesc, k > 0 ? 1u : first);
+                            umma_bf16_lo(tacc + kMaxBN, a_cur + a2_inc + 2 * k, b_cur + 2 * k, desc_hi, p.idesc,
+                                         k > 0 ? 1u : first);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_bf16_lo(tacc, a_cur + 2 * k, b_cur + 2 * k, desc_hi, p.idesc, k > 0 ? 1u : first);
                     }
                     umma_commit(&empty[s]);  // frees the stage when these MMAs have read it
+                    a_cur += stage_inc;
+                    if (++s == kStages) {
+                        s = 0;
+                        a_cur = a_lo0;
+                        ph ^= 1u;
+                    }
                 }
                 if (ok) umma_commit(&acc_full[as]);
+                if (++as == acc_stages) {
+                    as = 0;
+                    if (tcount >= acc_stages) aph ^= 1u;
+                }
             }
         }
     } else if (FUSED && warp >= kGemmThreads / 32) {
