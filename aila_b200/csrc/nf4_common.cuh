@@ -102,6 +102,14 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
 
+// Two floats to a bf16 pair (round to nearest even each, `lo` in the low half): one conversion
+// instruction instead of two conversions and a merge.
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2_bits(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) {
     return __uint_as_float(((uint32_t)h) << 16);
 }

@@ -50,7 +50,7 @@ dequant_kn_kernel(const uint8_t* __restrict__ units, const float* __restrict__ q
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+    return f32x2_to_bf16x2_bits(lo, hi);
 }
 
 // One thread per (unit, row): reads the row's 32 stored bytes (two 16-byte loads; a warp reads

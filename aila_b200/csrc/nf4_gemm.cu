@@ -133,7 +133,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+    return f32x2_to_bf16x2_bits(lo, hi);
 }
 
 extern __shared__ __align__(1024) uint8_t gemm_smem[];
