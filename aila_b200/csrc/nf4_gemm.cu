@@ -39,7 +39,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kMaxBN = 256;
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kABytes = BM * BK * 2;         // 16 KB per 128 rows of x
 constexpr int kBBytes = kMaxBN * BK * 2;     // 32 KB
 constexpr int kRingBytes = 4 * (kABytes + kBBytes);  // = 3 * (2 * kABytes + kBBytes) = 192 KB
@@ -52,7 +52,9 @@ constexpr int kNfSlotBytes = kUnitStrideF32; // one unit (528 or 576 bytes)
 constexpr int kFusedExtraBytes = kFusedTableBytes + kDequantWarps * kNfSlots * (kNfSlotBytes + 8);
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
-constexpr int kGemmSmem = kRingBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kRingBytesLarge = 216 * 1024;  // two-phase form: nothing else needs shared memory
+constexpr int kGemmSmem = kRingBytesLarge + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kGemmSmemFusedBase = kRingBytes + 1024 + 256;
 
 // The NF4 weight of the fused form (the w tiles are produced in shared memory from the unit stream
 // instead of being copied from a bf16 matrix).
@@ -77,7 +79,8 @@ struct GemmParams {
     int n_tiles;
     int swiglu_ff;  // 0 = plain
     int mtile;      // 1: CTA tile 128 x BN (double-buffered accumulator); 2: 256 x BN
-    int stages;     // 4 (mtile 1) or 3 (mtile 2)
+    int stages;     // ring depth: as many stages of (x tile + w tile) as fit, at most kMaxStages
+    int b_bytes;    // shared-memory bytes of one w tile (BN rows of 128 bytes, rounded up to 1024)
     uint32_t idesc;
 };
 
@@ -151,7 +154,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     // 1024-byte aligned ring (the swizzle pattern is a function of the absolute address)
     uint8_t* base = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + kRingBytes);
+    constexpr int kRing = FUSED ? kRingBytes : kRingBytesLarge;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + kRing);
     uint64_t* full = bars;                      // [kMaxStages]
     uint64_t* empty = bars + kMaxStages;        // [kMaxStages]
     uint64_t* acc_full = bars + 2 * kMaxStages; // [kAccStages]
@@ -169,7 +173,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int kStages = p.stages;
     const int a_bytes = kABytes * p.mtile;
-    const int kStageBytes = a_bytes + kBBytes;
+    const int kStageBytes = a_bytes + p.b_bytes;
     const int acc_stages = p.mtile == 1 ? kAccStages : 1;  // 256-row tiles keep both halves live
 
     if (threadIdx.x == 0) {
@@ -699,7 +703,9 @@ AilaNf4Status launch_gemm_common(const void* w_nk, const FusedWeight* fw, const 
         p.n_out = (int)N;
     }
     p.m_tiles = (M + BM * p.mtile - 1) / (BM * p.mtile);
-    p.stages = p.mtile == 2 ? 3 : 4;
+    p.b_bytes = (p.BN * BK * 2 + 1023) / 1024 * 1024;
+    p.stages = (fw ? kRingBytes : kRingBytesLarge) / (kABytes * p.mtile + p.b_bytes);
+    if (p.stages > kMaxStages) p.stages = kMaxStages;
     // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.BN >> 3) << 17) |
               ((uint32_t)(BM >> 4) << 24);
@@ -723,7 +729,7 @@ AilaNf4Status launch_gemm_common(const void* w_nk, const FusedWeight* fw, const 
         if (attr_err == cudaSuccess)
             attr_err = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<true>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            kGemmSmem + kFusedExtraBytes);
+                                            kGemmSmemFusedBase + kFusedExtraBytes);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(gemm)");
     const int total_tiles = p.m_tiles * p.n_tiles;
@@ -732,7 +738,7 @@ AilaNf4Status launch_gemm_common(const void* w_nk, const FusedWeight* fw, const 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(fw ? kFusedThreads : kGemmThreads);
-    cfg.dynamicSmemBytes = fw ? kGemmSmem + kFusedExtraBytes : kGemmSmem;
+    cfg.dynamicSmemBytes = fw ? kGemmSmemFusedBase + kFusedExtraBytes : kGemmSmem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
