@@ -5,14 +5,14 @@
 //
 // Blackwell-native structure (sm_100a):
 //   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, one copy per CTA) stages 128 x 64 tiles of x
-//     and BN x 64 tiles of w in a 4-deep shared-memory ring;
+//     and BN x 64 tiles of w in a shared-memory ring of as many stages as fit in 216 KB (at most 8);
 //   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN,
 //     K = 16) with both operands K-major in shared memory and the accumulator in TMEM;
 //   * two shapes of CTA tile, chosen per problem by a cost model (bytes per flop vs. waves):
 //     128 x BN with two TMEM accumulator buffers (2 x 256 columns), so the epilogue warps drain
 //     tile i with tcgen05.ld while the tensor core already works on tile i+1; or 256 x BN, two
-//     M = 128 MMAs per K step sharing one w tile (a third fewer operand bytes per flop, three
-//     64 KB stages in flight), with both accumulators live and eight epilogue warps;
+//     M = 128 MMAs per K step sharing one w tile (a third fewer operand bytes per flop, three or
+//     four stages in flight), with both accumulators live and eight epilogue warps;
 //   * persistent CTAs, one per SM; BN is a multiple of 16 (<= 256) picked so the tile count
 //     fills whole waves of 148 SMs.
 // Optional epilogues: + residual, or SwiGLU over a gate|up weight (tile = 128 gate columns'
