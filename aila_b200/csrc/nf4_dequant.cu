@@ -87,6 +87,15 @@ dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ q
         const float am = unit_absmax(unit, absmax_kind, sp, n, kb, r);
         const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
         uint32_t o[32];  // 64 bf16, natural k order
+        const uint32_t qa = (uint32_t)__cvta_generic_to_shared(q);
+        // code book value of nibble `n` (0 = lowest) of a word: the table offset (nibble * 4) comes
+        // out of the word with one shift and one mask
+        auto qv = [&](uint32_t word, int n) {
+            const uint32_t off = n == 0 ? (word << 2) & 0x3cu : (word >> (4 * n - 2)) & 0x3cu;
+            float v;
+            asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(qa + off));
+            return v;
+        };
 #pragma unroll
         for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -94,10 +103,11 @@ dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ q
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int p = 8 * t + 2 * j + e;  // stored byte
-                    const uint32_t b = (w[p >> 2] >> (8 * (p & 3))) & 0xffu;
+                    const uint32_t word = w[p >> 2];
+                    const int bi = p & 3;             // byte of the word: nibbles 2 bi (low), 2 bi + 1 (high)
                     // byte covers k = 16j + 4t + 2e (high nibble) and + 1 (low nibble)
                     o[(16 * j + 4 * t + 2 * e) >> 1] =
-                        pack_bf16x2(__fmul_rn(q[b >> 4], am), __fmul_rn(q[b & 15], am));
+                        pack_bf16x2(__fmul_rn(qv(word, 2 * bi + 1), am), __fmul_rn(qv(word, 2 * bi), am));
                 }
 #pragma unroll
         for (int i = 0; i < 8; ++i)
