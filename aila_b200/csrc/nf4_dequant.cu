@@ -76,8 +76,13 @@ dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ q
     const long long u = tid >> 4;  // this lane's unit (two units per warp)
     const int r = (int)(tid & 15);
     const bool live = u < total_units;
-    const int kb = live ? (int)(u % KU) : 0;
-    const int rt = live ? (int)(u / KU) : 0;
+    // (rt, kb) of the warp's two consecutive units: one 32-bit division per warp side instead of
+    // 64-bit divisions per lane and per store (the host guarantees total_units < 2^31)
+    const unsigned u_first = (unsigned)((tid - lane) >> 4);
+    const int rt_a = (int)(u_first / (unsigned)KU), kb_a = (int)(u_first - (unsigned)rt_a * (unsigned)KU);
+    const int kb_b = kb_a + 1 == KU ? 0 : kb_a + 1, rt_b = kb_a + 1 == KU ? rt_a + 1 : rt_a;
+    const int kb = (lane >> 4) ? kb_b : kb_a;
+    const int rt = (lane >> 4) ? rt_b : rt_a;
     const int n = rt * kTileRows + r;
     uint8_t* mine = tile[warp] + lane * kDqRowPitch;
     if (live && n < N) {
@@ -122,8 +127,8 @@ dequant_nk_kernel(const uint8_t* __restrict__ units, const float* __restrict__ q
         const int row = g * 4 + sub;          // 0..31: rows 0-15 unit u0, 16-31 unit u0 + 1
         const long long uu = u0 + (row >> 4);
         if (uu < total_units) {
-            const int kbb = (int)(uu % KU);
-            const int nn = (int)(uu / KU) * kTileRows + (row & 15);
+            const int kbb = (row >> 4) ? kb_b : kb_a;
+            const int nn = ((row >> 4) ? rt_b : rt_a) * kTileRows + (row & 15);
             if (nn < N) {
                 const uint4 v = *reinterpret_cast<const uint4*>(tile[warp] + row * kDqRowPitch + piece * 16);
                 *reinterpret_cast<uint4*>(out + (size_t)nn * K + (size_t)kbb * kUnitK + piece * 8) = v;
@@ -171,6 +176,7 @@ cudaError_t launch_dequant_kn(const AilaNf4Linear& w, void* out_kn, cudaStream_t
 cudaError_t launch_dequant_nk(const AilaNf4Linear& w, void* out_nk, cudaStream_t s) {
     const long long units = (long long)w.RT * w.KU;
     if (units == 0) return cudaSuccess;
+    if (units >= (1ll << 31)) return cudaErrorInvalidValue;  // (2^41 weights: beyond any linear the loader takes)
     const long long threads = units * 16;
     const long long blocks = (threads + 255) / 256;
     dequant_nk_kernel<<<(unsigned)blocks, 256, 0, s>>>(w.d_units, w.d_qmap, w.scale_params(),
