@@ -110,9 +110,17 @@ private:
 };
 
 // ops::argmax (reference src/ops/SamplingOps.cpp:321-365): greedy token over bf16 logits,
-// written to device memory.
+// written to device memory; equal logits resolve as in the reference's reduction.
 inline void argmax(Context& ctx, TensorView& logits, int vocab_size, int* d_result) {
     if (aila_argmax_bf16(logits.data(), vocab_size, d_result, ctx.device, ctx.stream) != AILA_NF4_OK)
+        throw std::runtime_error(aila_nf4_last_error());
+}
+
+// The same over one shard of a vocabulary (no reference counterpart): logits[0] has the global index
+// index_offset, ties are resolved on global indices, the result is the LOCAL index.
+inline void argmax_shard(Context& ctx, TensorView& logits, int shard_size, int64_t index_offset, int* d_result) {
+    if (aila_argmax_bf16_shard(logits.data(), shard_size, index_offset, d_result, ctx.device, ctx.stream) !=
+        AILA_NF4_OK)
         throw std::runtime_error(aila_nf4_last_error());
 }
 
