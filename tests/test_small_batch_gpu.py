@@ -30,9 +30,13 @@ def lin_of(w):
 # long enough that a CTA's range spans two slices, plain-absmax weights
 cases = [(16, 64, True, 2), (100, 448, False, 3), (2560, 9728, True, 8), (33, 128, True, 7), (6144, 2560, True, 5),
          (2560, 9728, True, 16), (6144, 2560, True, 32), (100, 448, False, 13), (5120, 5120, False, 27),
-         (33, 128, True, 32), (19456, 2560, True, 24), (272, 512, True, 9)]
-for N, K, nested, M in cases:
-    w = make_weight(8400 + N + M, N, K, 64, nested)
+         (33, 128, True, 32), (19456, 2560, True, 24), (272, 512, True, 9),
+         # absmax blocks of 128 and 256 weights (two and four units share one absmax entry)
+         (512, 1024, True, 20, 128), (272, 1024, True, 6, 256), (512, 2048, False, 31, 128)]
+for case in cases:
+    N, K, nested, M = case[:4]
+    bs = case[4] if len(case) > 4 else 64
+    w = make_weight(8400 + N + M, N, K, bs, nested)
     lin = lin_of(w)
     x = synth.gaussian_activation(8500 + N, M, K).cuda()
     res = synth.gaussian_activation(8600 + N, M, N).cuda()
@@ -47,7 +51,7 @@ for N, K, nested, M in cases:
     a, b = yb.float().cpu().numpy(), ys.float().cpu().numpy()
     assert np.abs(a - b).max() <= 1e-2 * np.abs(b).max() + 1e-6, (N, K, M, np.abs(a - b).max())
     am = oracle_absmax(O, w)
-    want = bits_to_f32(O.gemv(w.packed, w.quant_map, am, bf16_bits(x[M - 1:M]), N, K, 64)) + \
+    want = bits_to_f32(O.gemv(w.packed, w.quant_map, am, bf16_bits(x[M - 1:M]), N, K, bs)) + \
         bits_to_f32(bf16_bits(res[M - 1]))
     assert np.abs(a[M - 1] - want).max() <= 2e-2 * np.abs(want).max(), (N, K, M)
 # gate|up + SiLU
