@@ -16,6 +16,24 @@ from tests.helpers import make_weight, oracle_absmax
 pytestmark = pytest.mark.skipif(not R.available(), reason="oracle/_ref/libaila_ref.so was not built")
 
 
+def test_stand_in_runtime_selftest(tmp_path):
+    """The properties of the stand-in SYCL runtime that the pin relies on, checked directly
+    (tests/shim_selftest.cpp): barrier lock-step, the balanced-tree order of group and sub-group
+    reductions, index mapping of 2-D ranges, work-items that leave early."""
+    import os
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    exe = tmp_path / "shim_selftest"
+    subprocess.run([gxx, "-std=c++17", "-O1", "-Wno-attributes", "-I", os.path.join(root, "oracle", "ref_shim"),
+                    os.path.join(root, "tests", "shim_selftest.cpp"), "-o", str(exe)], check=True, capture_output=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "shim ok" in r.stdout, (r.returncode, r.stdout, r.stderr)
+
+
 def _x(seed, M, K):
     return synth.gaussian_activation(seed, M, K).view(torch.uint16).numpy()
 
