@@ -154,9 +154,14 @@ AILA_NF4_API AilaNf4Status aila_nf4_scratch_check(AilaNf4Scratch* scratch, void*
  * Replaces Bnb4BitLinear::forward (src/ops/Bnb4BitLinear.cpp:799-949):
  *   seq_len == 1  -> streaming decode GEMV (reference packed_nf4_gemv_bf16, :271-410),
  *                    fp32 accumulation, one rounding to bf16;
- *   seq_len  > 1  -> weights rounded to bf16 exactly as dequantize_weight (:723-757) does,
+ *   seq_len 2..64 -> small-batch decode launches of up to 32 rows each (one pass over the
+ *                    packed weights per launch, fp32 accumulation; no reference counterpart:
+ *                    the reference takes its seq_len > 1 route from two rows on);
+ *   above         -> weights rounded to bf16 exactly as dequantize_weight (:723-757) does,
  *                    then a tcgen05 tensor-core GEMM with fp32 accumulation (the reference
- *                    runs an oneDNN bf16 matmul, :689-721, :944).
+ *                    runs an oneDNN bf16 matmul, :689-721, :944). With blocksize 128 the
+ *                    reference instead takes a fused kernel (:18-136) whose result is not
+ *                    x W^T; this library returns x W^T for every blocksize.
  * `residual` (or NULL) is bf16 [seq_len][out] added before the final rounding - the
  * documented meaning of add_residual (:323); the reference's SG16 branch ignores it.
  * Errors: seq_len <= 0 and NULL pointers give AILA_NF4_ERR_INVALID_ARGUMENT where the
