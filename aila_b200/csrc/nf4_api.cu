@@ -353,15 +353,16 @@ AilaNf4Status ensure_io(void** buf, size_t* have, size_t need) {
     return AILA_NF4_OK;
 }
 
-// Small batches (2 .. AILA_NF4_DECODE_ROWS_MAX rows, default 64; 0 or 1 turns it off): batched decode
+// Small batches (2 .. AILA_NF4_DECODE_ROWS_MAX rows, default 48; 0 or 1 turns it off): batched decode
 // launches of up to 32 rows each (one pass over the weights per launch) instead of the dequantise +
 // GEMM route, when a small-batch kernel takes the shape and no bf16 weight cache exists (with a
-// cache the GEMM has nothing to dequantise). Two passes of 32 rows still beat the GEMM route
-// (measured on the cfg4 stack: 5.9 ms against 8.4 ms per step at 64 rows; three passes do not).
+// cache the GEMM has nothing to dequantise). A pass of 32 and one of 16 rows still beat the GEMM
+// route (measured on the cfg4 stack: 5.0 ms against 5.6 ms per step at 48 rows; two passes of 32
+// rows, 5.9 ms, do not).
 int decode_rows_max() {
     static const int v = [] {
         const char* e = std::getenv("AILA_NF4_DECODE_ROWS_MAX");
-        if (!e || !*e) return 64;
+        if (!e || !*e) return 48;
         const int n = std::atoi(e);
         return n < 0 ? 0 : (n > 128 ? 128 : n);
     }();

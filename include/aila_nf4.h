@@ -154,7 +154,7 @@ AILA_NF4_API AilaNf4Status aila_nf4_scratch_check(AilaNf4Scratch* scratch, void*
  * Replaces Bnb4BitLinear::forward (src/ops/Bnb4BitLinear.cpp:799-949):
  *   seq_len == 1  -> streaming decode GEMV (reference packed_nf4_gemv_bf16, :271-410),
  *                    fp32 accumulation, one rounding to bf16;
- *   seq_len 2..64 -> small-batch decode launches of up to 32 rows each (one pass over the
+ *   seq_len 2..48 -> small-batch decode launches of up to 32 rows each (one pass over the
  *                    packed weights per launch, fp32 accumulation; no reference counterpart:
  *                    the reference takes its seq_len > 1 route from two rows on);
  *   above         -> weights rounded to bf16 exactly as dequantize_weight (:723-757) does,
