@@ -61,3 +61,19 @@ def test_prepare_qkv_against_float64():
         assert np.abs(ref.to_f32(kc[h, pos]) - w).max() <= 2e-2 * np.abs(w).max()
         assert np.array_equal(vc[h, pos], _bits(v)[h * hd:(h + 1) * hd])
     assert not kc[:, :pos].any() and not kc[:, pos + 1:].any()
+
+
+def test_reference_tie_key_orders_like_the_reduction():
+    """sharded.reference_tie_key (the order the vocabulary-parallel head uses between ranks) picks,
+    among tied logits, the index the oracle's restatement of ops::argmax picks."""
+    import torch
+
+    from aila_b200 import sharded
+    rng = np.random.default_rng(11)
+    for _ in range(50):
+        n = int(rng.integers(300, 3000))
+        tied = rng.choice(n, size=int(rng.integers(2, 7)), replace=False)
+        logits = ref.to_bf16((rng.standard_normal(n) * 0.1).astype(np.float32))
+        logits[tied] = ref.to_bf16(np.float32([7.0]))[0]
+        keys = sharded.reference_tie_key(torch.from_numpy(tied.astype(np.int64)))
+        assert int(tied[int(torch.argmin(keys))]) == ref.argmax(logits)
